@@ -1,0 +1,354 @@
+"""Benchmark of the KV-cache decode hot path (KV append + decode attention) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (BASELINE.json configs[1]): B=32 rows, 12 q heads, 12 kv heads, head_dim 128, cache
+capacity 2048, cache_seqlens uniform in [1, 2047] (torch CPU generator, seed 2), caches and new
+q/k/v ~ N(0,1) bf16, one new token per row, full causal.  One "step" is one pass of the hot path
+over that batch: the fused RoPE + QK-norm + append launch followed by the split-KV decode
+attention launch.  At N > 1 every rank runs the same workload on its own rows (sequences are
+independent: no collective on the data path), so scaling is weak.
+
+Timing: CUDA events on the launching stream, W warm-up steps, K timed steps, barrier + device
+synchronisation on both sides, max over ranks.  Each step reads a different one of NSETS cache
+sets (NSETS x 403 MB, far larger than the 126 MB L2) so KV bytes come from HBM.
+  value     steps replayed from a CUDA graph, inputs resident in HBM
+  roofline  the decode-attention kernel alone, launched K times through the C ABI
+  e2e       the public Python call with HOST inputs: H2D of q/k/v, both launches, D2H of the output
+  cpu_baseline / --impl reference   the torch-eager port of the reference's CPU path (fp32, SDPA)
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+B, HQ, HKV, D, T_MAX = 32, 12, 12, 128, 2048
+NSETS = 4
+METRIC = "decode tokens/s (KV append + decode attention, B=32 x 12 heads x 128, ragged cache)"
+WORKLOAD = "configs[1]: op-level KV append + decode attention, B=32, 12q/12kv heads, D=128, T_max=2048, ragged seqlens seed 2"
+
+
+def seqlens_cpu():
+    return torch.randint(1, 2048, (B,), dtype=torch.int32, generator=torch.Generator().manual_seed(2))
+
+
+def algorithmic_bytes(seqlens):
+    """Bytes one append + decode-attention call must move (bf16): visible K and V rows, q in/out,
+    the new k/v read and written, cache_seqlens, one cos and one sin row per batch row."""
+    n_keys = int((seqlens.long() + 1).sum())
+    kv = 4 * HKV * D * n_keys
+    other = 2 * B * HQ * D * 2 + 2 * B * HKV * D * 2 * 2 + 4 * B + B * D * 2
+    return kv, other
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock/throttle samples taken while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.lines = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.gpu)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                pass
+        sm, mx, reasons = [], [], set()
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_setup(n_gpus):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local))
+    return rank, world, local
+
+
+def barrier(world):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(x, world, device):
+    if world == 1:
+        return x
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU baseline: the reference's CPU path (torch-eager port under oracle/), fp32, all host threads
+# ------------------------------------------------------------------------------------------------
+def cpu_reference_run(steps, warmup, budget_s=25.0):
+    from oracle import torch_ref as R
+    threads = torch.get_num_threads()
+    gen = torch.Generator().manual_seed(2)
+    seqlens = seqlens_cpu()
+    k_cache = torch.randn(B, T_MAX, HKV, D, generator=gen)
+    v_cache = torch.randn(B, T_MAX, HKV, D, generator=gen)
+    q = torch.randn(B, 1, HQ, D, generator=gen)
+    k = torch.randn(B, 1, HKV, D, generator=gen)
+    v = torch.randn(B, 1, HKV, D, generator=gen)
+    cos, sin = R.rotary_tables(T_MAX, D, "cpu", torch.float32)
+
+    def step():
+        q2 = R.rope_norm_scale_rows(q, cos, sin, seqlens)
+        k2 = R.rope_norm_scale_rows(k, cos, sin, seqlens)
+        return R.kvcache_attention(q2, k_cache, v_cache, k2, v, seqlens, -1)
+
+    with torch.inference_mode():
+        for _ in range(max(warmup, 1)):
+            step()
+        t0 = time.perf_counter()
+        done = 0
+        while done < steps and (time.perf_counter() - t0) < budget_s:
+            step()
+            done += 1
+        dt = time.perf_counter() - t0
+    return {"value": B * done / dt, "unit": "tokens/s", "cores": threads, "kind": "port",
+            "sample": f"{done} full configs[1] steps (fp32, torch SDPA row by row as the reference's CPU fallback does), "
+                      f"{dt:.1f} s", "ms_per_step": 1e3 * dt / done}, done, dt
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cb, done, dt = cpu_reference_run(args.steps, args.warmup)
+    line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "tokens/s", "n_gpus": args.gpus,
+            "steps": done, "warmup": args.warmup, "ms_per_step": cb["ms_per_step"], "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "device": "host CPU"},
+            "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------------
+def run_ours(args):
+    rank, world, local = dist_setup(args.gpus)
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (the hot path has no CPU implementation)")
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    from nanochat_b200 import _lib, ops
+    from nanochat_b200.gpt import precompute_rotary_embeddings
+
+    seqlens_h = seqlens_cpu()
+    kv_bytes, other_bytes = algorithmic_bytes(seqlens_h)
+    seqlens = seqlens_h.to(dev)
+    gen = torch.Generator(device=dev).manual_seed(2 + rank)
+    sets = []
+    for _ in range(NSETS):
+        kc = torch.randn(B, T_MAX, HKV, D, generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        vc = torch.randn(B, T_MAX, HKV, D, generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        sets.append((kc, vc))
+    q = torch.randn(B, 1, HQ, D, generator=gen, device=dev).to(torch.bfloat16)
+    k = torch.randn(B, 1, HKV, D, generator=gen, device=dev).to(torch.bfloat16)
+    v = torch.randn(B, 1, HKV, D, generator=gen, device=dev).to(torch.bfloat16)
+    cos, sin = precompute_rotary_embeddings(T_MAX, D, device=dev)
+    K, W = args.steps, args.warmup
+
+    def step(i):
+        kc, vc = sets[i % NSETS]
+        q2 = ops.append_rope_norm(q, k, v, kc, vc, seqlens, cos, sin)
+        return ops.decode_attention(q2[:, 0], kc, vc, seqlens, seqlen_offset=1, window_left=-1)
+
+    # ---- value: CUDA-graph replay of NSETS consecutive steps ------------------------------------
+    for i in range(max(W, 3)):
+        step(i)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream(dev)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        for i in range(NSETS):
+            step(i)  # allocate workspace for the side stream outside of capture
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(NSETS):
+                out_graph = step(i)
+    replays = (K + NSETS - 1) // NSETS
+    k_eff = replays * NSETS
+    for _ in range(max(1, (W + NSETS - 1) // NSETS)):
+        graph.replay()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    barrier(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(replays):
+        graph.replay()
+    e1.record()
+    barrier(world)
+    ms_total = max_over_ranks(e0.elapsed_time(e1), world, dev)
+    ms_step = ms_total / k_eff
+    value = world * B / (ms_step * 1e-3)
+
+    # ---- roofline: the decode-attention kernel alone, through the C ABI ----------------------------
+    q2 = ops.append_rope_norm(q, k, v, sets[0][0], sets[0][1], seqlens, cos, sin)[:, 0].contiguous()
+    out = torch.empty_like(q2)
+    ws = ops.workspace(dev, B, HQ, HKV)
+    stream = torch.cuda.current_stream(dev)
+
+    def attn_only(i):
+        kc, vc = sets[i % NSETS]
+        _lib.call("nckv_decode_attn", q2.data_ptr(), kc.data_ptr(), vc.data_ptr(), seqlens.data_ptr(), out.data_ptr(),
+                  None, None, B, HQ, HKV, D, T_MAX, kc.stride(0), kc.stride(1), 1, -1, 0, 0, ws.data_ptr(), ws.numel(),
+                  stream.cuda_stream)
+
+    for i in range(max(W, 3)):
+        attn_only(i)
+    torch.cuda.synchronize()
+    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n_attn = max(K, 20)
+    a0.record()
+    for i in range(n_attn):
+        attn_only(i)
+    a1.record()
+    torch.cuda.synchronize()
+    attn_ms = a0.elapsed_time(a1) / n_attn
+    status = ops.read_status(dev)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- e2e: public call, host buffers ------------------------------------------------------------
+    qh, kh, vh = (t.cpu().pin_memory() for t in (q, k, v))
+    out_h = torch.empty(B, HQ, D, dtype=torch.bfloat16).pin_memory()
+    h2d = qh.numel() * 2 + kh.numel() * 2 + vh.numel() * 2
+    d2h = out_h.numel() * 2
+
+    def e2e_step(i):
+        qd, kd, vd = qh.to(dev, non_blocking=True), kh.to(dev, non_blocking=True), vh.to(dev, non_blocking=True)
+        kc, vc = sets[i % NSETS]
+        q3 = ops.append_rope_norm(qd, kd, vd, kc, vc, seqlens, cos, sin)
+        o = ops.decode_attention(q3[:, 0], kc, vc, seqlens, seqlen_offset=1, window_left=-1)
+        out_h.copy_(o, non_blocking=True)
+        torch.cuda.current_stream(dev).synchronize()
+
+    for i in range(max(W, 3)):
+        e2e_step(i)
+    barrier(world)
+    t0 = time.perf_counter()
+    c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    c0.record()
+    for i in range(K):
+        e2e_step(i)
+    c1.record()
+    barrier(world)
+    e2e_ms = max_over_ranks(max(c0.elapsed_time(c1), 1e3 * 0), world, dev) / K
+    e2e_wall_ms = max_over_ranks(1e3 * (time.perf_counter() - t0), world, dev) / K
+    e2e_ms = max(e2e_ms, 0.0)
+    e2e_value = world * B / (e2e_ms * 1e-3)
+
+    if rank == 0:
+        peak, peak_kind = peaks()
+        achieved = (kv_bytes + other_bytes) / (attn_ms * 1e-3) / 1e9
+        cb = None
+        if world == 1 and not args.no_cpu_baseline:
+            cb_full, _, _ = cpu_reference_run(steps=100000, warmup=2, budget_s=12.0)
+            cb = {k_: cb_full[k_] for k_ in ("value", "unit", "cores", "kind", "sample")}
+        line = {
+            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": k_eff, "warmup": W,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "rows_per_gpu": B, "l2": f"{NSETS} cache sets rotated, {NSETS * 2 * B * T_MAX * HKV * D * 2 / 1e6:.0f} MB > L2",
+                       "launch": "CUDA graph replay of append + attention", "parallelism": f"{world} x independent sequences"},
+            "kv_read_gbs": world * kv_bytes / (ms_step * 1e-3) / 1e9,
+            "roofline": {"bound": "hbm", "kernel": "decode_attn_kernel", "achieved": achieved, "peak": peak,
+                         "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak,
+                         "frac_of_8000_nominal": achieved / 8000.0, "us_per_launch": attn_ms * 1e3,
+                         "algorithmic_bytes": kv_bytes + other_bytes, "traffic": args.traffic},
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms, "wall_ms_per_step": e2e_wall_ms},
+            "gpu_launches": 2 * k_eff, "device_status": status, "clocks": clocks,
+        }
+        if cb is not None:
+            line["cpu_baseline"] = cb
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=400)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--traffic", type=float, default=None,
+                    help="dram bytes per decode-attention launch from an ncu capture, recorded in the roofline object")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

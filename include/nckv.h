@@ -1,0 +1,154 @@
+/*
+ * nckv.h — C ABI of libnckv.so, the B200 (sm_100a) KV-cache decode path for nanochat.
+ *
+ * Every entry point takes raw device pointers, sizes, element strides and a CUDA
+ * stream (passed as void*, i.e. a cudaStream_t).  There are no torch types here;
+ * the Python package binds these symbols with ctypes.
+ *
+ * Conventions
+ *   - dtype: all tensors are bf16 unless a parameter says otherwise; head_dim D must be 128.
+ *   - return value: 0 = launched; < 0 = rejected on the host (NCKV_E_*), nothing ran.
+ *     Device-side guards (capacity overflow, a bounded wait that ran out) never trap:
+ *     they skip the access and OR a bit into the int32 status word at the start of the
+ *     workspace / at `status`; read it with nckv_read_status().
+ *   - nothing here allocates device memory except where stated.
+ *   - layouts follow the reference: new q/k/v are (B, T_new, H, D) contiguous; one
+ *     layer's cache is a (B, T_max, Hkv, D) view with element strides
+ *     (cache_batch_stride, cache_token_stride, D, 1); cache_seqlens is int32 (B,).
+ *
+ * Reference symbols are cited as file:line inside the nanochat source tree.
+ */
+#ifndef NCKV_H
+#define NCKV_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define NCKV_API __attribute__((visibility("default")))
+#else
+#define NCKV_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* host-side rejection codes */
+#define NCKV_OK 0
+#define NCKV_E_ARG (-1)         /* null pointer, non-positive size, misaligned pointer */
+#define NCKV_E_UNSUPPORTED (-2) /* head_dim != 128, group size > 16, batch too large ... */
+#define NCKV_E_CAPACITY (-3)    /* host-known capacity overflow (T_new > T_max, workspace too small) */
+#define NCKV_E_CUDA (-4)        /* a CUDA runtime/driver call failed; see nckv_last_error() */
+
+/* device status bits (OR-ed into the status word) */
+#define NCKV_ST_OVERFLOW 1u   /* cache_seqlens[b] + T_new > T_max, or position >= rope_len: row skipped */
+#define NCKV_ST_TIMEOUT 2u    /* a bounded wait on a shared-memory barrier ran out */
+#define NCKV_ST_BAD_SEQLEN 4u /* negative cache_seqlens[b] */
+
+/* Library version and the SM architecture the kernels were compiled for ("sm_100a"). */
+NCKV_API int nckv_version(void);
+NCKV_API const char *nckv_arch(void);
+/* Text of the last host-side error on this thread (empty string if none). */
+NCKV_API const char *nckv_last_error(void);
+
+/*
+ * Bytes of scratch nckv_decode_attn / nckv_prefill_attn need for a problem of this shape
+ * on the current device.  The first 256 bytes hold the status word; the rest holds split
+ * partials and arrival counters.  The buffer must be zero-filled once after allocation
+ * (the kernels leave the counters at zero when they finish) and must not be shared by
+ * launches that overlap in time.
+ */
+NCKV_API size_t nckv_workspace_bytes(int B, int Hq, int Hkv, int D);
+
+/* Synchronising read (stream-ordered copy + stream sync) of a status word; returns the
+ * word (>= 0) or NCKV_E_CUDA.  If `clear` is non-zero the word is reset to 0. */
+NCKV_API int nckv_read_status(void *status_word, int clear, void *stream);
+
+/*
+ * Fused RoPE + QK-norm + scale + KV append.
+ * Replaces apply_rotary_emb (gpt.py:57-63), norm (gpt.py:42-43), the 1.2 scale
+ * (gpt.py:101-102) and the cache slice-assign of flash_attn_with_kvcache
+ * (flash_attention.py:160-162), per row:  position p = cache_seqlens[b] + t,
+ *   q_out[b,t,h,:]        = bf16(1.2 * rmsnorm(rope(q_in[b,t,h,:], cos[p], sin[p])))
+ *   k_cache[b,p,h,:]      = same transform of k_in[b,t,h,:]
+ *   v_cache[b,p,h,:]      = v_in[b,t,h,:]
+ * with a bf16 rounding after every reference op so the bytes equal the eager bf16 path.
+ * cos/sin are the reference's own bf16 tables, (rope_len, D/2) contiguous.
+ * q_in may be NULL (then q_out is ignored) and q_out may alias q_in.
+ * cache_seqlens is not modified.
+ */
+NCKV_API int nckv_append_rope_norm(const void *q_in, const void *k_in, const void *v_in, void *q_out,
+                          void *k_cache, void *v_cache, const int32_t *cache_seqlens,
+                          const void *cos, const void *sin, int B, int T_new, int Hq, int Hkv,
+                          int D, int T_max, int64_t cache_batch_stride,
+                          int64_t cache_token_stride, int rope_len, float qk_scale, float eps,
+                          int32_t *status, void *stream);
+
+/*
+ * Plain append (k already rotated/normalised by the caller): the cache write of
+ * flash_attn_with_kvcache (flash_attention.py:160-162) with per-row positions.
+ */
+NCKV_API int nckv_append(const void *k_in, const void *v_in, void *k_cache, void *v_cache,
+                const int32_t *cache_seqlens, int B, int T_new, int Hkv, int D, int T_max,
+                int64_t cache_batch_stride, int64_t cache_token_stride, int32_t *status,
+                void *stream);
+
+/*
+ * Split-KV decode attention, one query token per row (T_new == 1).
+ * Replaces the Tq == 1 branch of _sdpa_attention (flash_attention.py:83-89) as reached
+ * from flash_attn_with_kvcache (flash_attention.py:165-177), with per-row lengths:
+ *   n_b   = cache_seqlens[b] + seqlen_offset          (keys present, incl. the new one)
+ *   keys  = [max(0, n_b - 1 - window_left), n_b)      (window_left < 0: from 0)
+ *           intersected with [kv_begin, kv_end) when kv_end > kv_begin (a cross-GPU shard)
+ *   out[b,h,:] = softmax(q[b,h,:] . K[keys, h / (Hq/Hkv), :] / sqrt(D)) V[keys, ...]
+ * q is (B, Hq, D) contiguous, out is (B, Hq, D) bf16.  When lse_out != NULL it receives
+ * the natural-log sum-exp per (b, h) as fp32 (-inf for an empty key range, out = 0), and
+ * when out_f32 != NULL the normalised output is also written there as fp32 (for the
+ * cross-GPU combine).  workspace: see nckv_workspace_bytes().
+ */
+NCKV_API int nckv_decode_attn(const void *q, const void *k_cache, const void *v_cache,
+                     const int32_t *cache_seqlens, void *out, float *out_f32, float *lse_out,
+                     int B, int Hq, int Hkv, int D, int T_max, int64_t cache_batch_stride,
+                     int64_t cache_token_stride, int seqlen_offset, int window_left,
+                     int kv_begin, int kv_end, void *workspace, size_t workspace_bytes,
+                     void *stream);
+
+/*
+ * Log-sum-exp combine of n_parts partial attention results (the exchange step of the
+ * sequence-split long-context path; no counterpart in the reference, which never splits
+ * the keys): parts_o is (n_parts, rows, D) fp32 normalised partial outputs, parts_lse is
+ * (n_parts, rows) fp32; out is (rows, D) bf16, lse_out (optional) is (rows,) fp32.
+ *   lse = log sum_i exp(lse_i),  out = sum_i exp(lse_i - lse) * o_i ; parts with -inf drop out.
+ */
+NCKV_API int nckv_lse_combine(const float *parts_o, const float *parts_lse, int n_parts, int rows, int D,
+                     void *out, float *lse_out, void *stream);
+
+/*
+ * Prefill broadcast: KVCache.prefill (engine.py:123-137).  Copies the first p tokens of a
+ * batch-1 cache (L, 1, T_src, Hkv, D) into every row of (L, B, T_dst, Hkv, D) for K and V
+ * and, when dst_seqlens != NULL, sets dst_seqlens[b] = p.  The source is read once.
+ */
+NCKV_API int nckv_prefill_broadcast(const void *src_k, const void *src_v, void *dst_k, void *dst_v,
+                           int32_t *dst_seqlens, int L, int B, int p, int Hkv, int D, int T_src,
+                           int T_dst, void *stream);
+
+/*
+ * Dense (T_new >= 1) causal attention over a cache or plain k/v, tcgen05/TMEM tiles.
+ * Replaces the full-causal and explicit-mask branches of _sdpa_attention
+ * (flash_attention.py:79-80, 92-102) as reached from flash_attn_with_kvcache
+ * (flash_attention.py:165-177) and flash_attn_func (flash_attention.py:107-128).
+ * Query t of row b sits at absolute position p = cache_seqlens[b] + t (cache_seqlens may
+ * be NULL = all zero) and sees keys j with j <= p and (window_left < 0 or p - j <= window_left).
+ * q and out are (B, T_new, Hq, D) contiguous; k/v are (B, T_k, Hkv, D) views with the
+ * given element strides, T_k being the capacity of the view.
+ */
+NCKV_API int nckv_prefill_attn(const void *q, const void *k, const void *v, const int32_t *cache_seqlens,
+                      void *out, int B, int T_new, int Hq, int Hkv, int D, int T_k,
+                      int64_t kv_batch_stride, int64_t kv_token_stride, int window_left,
+                      int32_t *status, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NCKV_H */

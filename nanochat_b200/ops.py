@@ -1,0 +1,326 @@
+"""PyTorch custom ops (namespace ``nckv``) over the C ABI of libnckv.so.
+
+Each op validates shapes/dtypes on the host, hands raw device pointers, element strides and the
+current CUDA stream of the tensors' device to the library, and returns torch tensors it
+allocated with ``torch.empty``.  Tensors must live on a CUDA device: there is no CPU
+implementation and no eager fallback, a non-CUDA tensor raises.
+"""
+import ctypes
+
+import torch
+
+from . import _lib
+
+HEAD_DIM = 128
+# F.rms_norm(x, (D,)) with eps=None on bf16 inputs (gpt.py:42-43) resolves to the fp32 machine epsilon.
+RMS_EPS = 1.1920928955078125e-07
+QK_SCALE = 1.2  # gpt.py:101-102
+
+_NS = torch.library.Library("nckv", "DEF")
+_workspaces = {}  # (device index, stream id) -> uint8 tensor
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
+
+
+def _stream(device):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _require_cuda(name, *tensors):
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError(
+                f"nckv::{name} needs CUDA tensors (got device {t.device}); the KV-cache decode path "
+                "has no CPU implementation")
+
+
+def _require_bf16(name, *tensors):
+    for t in tensors:
+        if t is not None and t.dtype != torch.bfloat16:
+            raise RuntimeError(f"nckv::{name} needs bfloat16 tensors, got {t.dtype}")
+
+
+def _cache_strides(name, cache):
+    """(batch_stride, token_stride) in elements of a (B, T, Hkv, D) cache view."""
+    if cache.dim() != 4 or cache.size(3) != HEAD_DIM:
+        raise RuntimeError(f"nckv::{name}: cache must be (B, T_max, Hkv, {HEAD_DIM}), got {tuple(cache.shape)}")
+    sb, st, sh, sd = cache.stride()
+    if sd != 1 or sh != HEAD_DIM:
+        raise RuntimeError(f"nckv::{name}: cache heads must be packed (strides {cache.stride()})")
+    return sb, st
+
+
+def workspace(device, B, Hq, Hkv):
+    """Zero-initialised scratch for the split-KV kernels, cached per (device, stream)."""
+    device = torch.device(device)
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    with torch.cuda.device(idx):
+        need = _lib.lib.nckv_workspace_bytes(B, Hq, Hkv, HEAD_DIM)
+    if need == 0:
+        raise RuntimeError(f"nckv: unsupported shape B={B} Hq={Hq} Hkv={Hkv}")
+    key = (idx, torch.cuda.current_stream(idx).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=torch.device("cuda", idx))
+        _workspaces[key] = ws
+    return ws
+
+
+def read_status(device, clear=True):
+    """Synchronously read (and by default clear) the device status word of the current stream's
+    workspace; 0 means no guard fired.  Bits: 1 overflow, 2 timeout, 4 bad cache_seqlens."""
+    device = torch.device(device)
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    key = (idx, torch.cuda.current_stream(idx).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None:
+        return 0
+    with torch.cuda.device(idx):
+        return _lib.call("nckv_read_status", _ptr(ws), int(bool(clear)), _stream(idx))
+
+
+def check_status(device):
+    st = read_status(device, clear=True)
+    if st:
+        names = [n for bit, n in ((1, "capacity overflow"), (2, "barrier timeout"), (4, "negative cache_seqlens")) if st & bit]
+        raise RuntimeError("nckv device status: " + ", ".join(names))
+
+
+# ------------------------------------------------------------------------------------------------
+# append (+ RoPE, QK-norm, scale)
+# ------------------------------------------------------------------------------------------------
+_NS.define("append_rope_norm(Tensor q, Tensor k, Tensor v, Tensor(a!) k_cache, Tensor(b!) v_cache, "
+           "Tensor cache_seqlens, Tensor cos, Tensor sin, float qk_scale, float eps) -> Tensor")
+
+
+def _append_rope_norm(q, k, v, k_cache, v_cache, cache_seqlens, cos, sin, qk_scale, eps):
+    name = "append_rope_norm"
+    _require_cuda(name, q, k, v, k_cache, v_cache, cache_seqlens, cos, sin)
+    _require_bf16(name, q, k, v, k_cache, v_cache, cos, sin)
+    if cache_seqlens.dtype != torch.int32:
+        raise RuntimeError("nckv::append_rope_norm: cache_seqlens must be int32")
+    B, T_new, Hq, D = q.shape
+    Hkv = k.size(2)
+    if k.shape != (B, T_new, Hkv, D) or v.shape != k.shape:
+        raise RuntimeError(f"nckv::{name}: k/v shapes {tuple(k.shape)}/{tuple(v.shape)} do not match q {tuple(q.shape)}")
+    if k_cache.shape != v_cache.shape or k_cache.stride() != v_cache.stride():
+        raise RuntimeError(f"nckv::{name}: k_cache and v_cache must share shape and strides")
+    if k_cache.size(0) != B or k_cache.size(2) != Hkv:
+        raise RuntimeError(f"nckv::{name}: cache {tuple(k_cache.shape)} does not match B={B}, Hkv={Hkv}")
+    sb, st = _cache_strides(name, k_cache)
+    cos2 = cos.reshape(-1, D // 2)
+    sin2 = sin.reshape(-1, D // 2)
+    if not (cos2.is_contiguous() and sin2.is_contiguous()):
+        cos2, sin2 = cos2.contiguous(), sin2.contiguous()
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    q_out = torch.empty_like(q)
+    ws = workspace(q.device, B, Hq, Hkv)
+    with torch.cuda.device(q.device):
+        _lib.call("nckv_append_rope_norm", _ptr(q), _ptr(k), _ptr(v), _ptr(q_out), _ptr(k_cache), _ptr(v_cache),
+                  _ptr(cache_seqlens), _ptr(cos2), _ptr(sin2), B, T_new, Hq, Hkv, D, k_cache.size(1), sb, st,
+                  cos2.size(0), float(qk_scale), float(eps), _ptr(ws), _stream(q.device))
+    return q_out
+
+
+_NS.impl("append_rope_norm", _append_rope_norm, "CUDA")
+_NS.impl("append_rope_norm", _append_rope_norm, "CPU")  # raises: no CPU implementation
+
+_NS.define("append_kv(Tensor k, Tensor v, Tensor(a!) k_cache, Tensor(b!) v_cache, Tensor cache_seqlens) -> ()")
+
+
+def _append_kv(k, v, k_cache, v_cache, cache_seqlens):
+    name = "append_kv"
+    _require_cuda(name, k, v, k_cache, v_cache, cache_seqlens)
+    _require_bf16(name, k, v, k_cache, v_cache)
+    if cache_seqlens.dtype != torch.int32:
+        raise RuntimeError("nckv::append_kv: cache_seqlens must be int32")
+    B, T_new, Hkv, D = k.shape
+    if v.shape != k.shape:
+        raise RuntimeError(f"nckv::{name}: k/v shapes differ")
+    if k_cache.shape != v_cache.shape or k_cache.stride() != v_cache.stride():
+        raise RuntimeError(f"nckv::{name}: k_cache and v_cache must share shape and strides")
+    if k_cache.size(0) != B or k_cache.size(2) != Hkv:
+        raise RuntimeError(f"nckv::{name}: cache {tuple(k_cache.shape)} does not match B={B}, Hkv={Hkv}")
+    sb, st = _cache_strides(name, k_cache)
+    k, v = k.contiguous(), v.contiguous()
+    ws = workspace(k.device, B, Hkv, Hkv)
+    with torch.cuda.device(k.device):
+        _lib.call("nckv_append", _ptr(k), _ptr(v), _ptr(k_cache), _ptr(v_cache), _ptr(cache_seqlens), B, T_new, Hkv,
+                  D, k_cache.size(1), sb, st, _ptr(ws), _stream(k.device))
+
+
+_NS.impl("append_kv", _append_kv, "CUDA")
+_NS.impl("append_kv", _append_kv, "CPU")
+
+# ------------------------------------------------------------------------------------------------
+# decode attention (T_new == 1)
+# ------------------------------------------------------------------------------------------------
+_NS.define("decode_attn(Tensor q, Tensor k_cache, Tensor v_cache, Tensor cache_seqlens, int seqlen_offset, "
+           "int window_left, int kv_begin, int kv_end, bool partial) -> (Tensor, Tensor, Tensor)")
+
+
+def _decode_attn(q, k_cache, v_cache, cache_seqlens, seqlen_offset, window_left, kv_begin, kv_end, partial):
+    name = "decode_attn"
+    _require_cuda(name, q, k_cache, v_cache, cache_seqlens)
+    _require_bf16(name, q, k_cache, v_cache)
+    if cache_seqlens.dtype != torch.int32:
+        raise RuntimeError("nckv::decode_attn: cache_seqlens must be int32")
+    if q.dim() != 3 or q.size(2) != HEAD_DIM:
+        raise RuntimeError(f"nckv::{name}: q must be (B, Hq, {HEAD_DIM}), got {tuple(q.shape)}")
+    B, Hq, D = q.shape
+    if k_cache.shape != v_cache.shape or k_cache.stride() != v_cache.stride():
+        raise RuntimeError(f"nckv::{name}: k_cache and v_cache must share shape and strides")
+    Hkv = k_cache.size(2)
+    if k_cache.size(0) != B or Hq % Hkv:
+        raise RuntimeError(f"nckv::{name}: cache {tuple(k_cache.shape)} does not match q {tuple(q.shape)}")
+    sb, st = _cache_strides(name, k_cache)
+    q = q.contiguous()
+    out = torch.empty_like(q)
+    if partial:
+        out_f32 = torch.empty(B, Hq, D, dtype=torch.float32, device=q.device)
+        lse = torch.empty(B, Hq, dtype=torch.float32, device=q.device)
+    else:
+        out_f32 = lse = None
+    ws = workspace(q.device, B, Hq, Hkv)
+    with torch.cuda.device(q.device):
+        _lib.call("nckv_decode_attn", _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(cache_seqlens), _ptr(out),
+                  _ptr(out_f32), _ptr(lse), B, Hq, Hkv, D, k_cache.size(1), sb, st, int(seqlen_offset),
+                  int(window_left), int(kv_begin), int(kv_end), _ptr(ws), ws.numel(), _stream(q.device))
+    if not partial:
+        out_f32, lse = out.new_empty(0, dtype=torch.float32), out.new_empty(0, dtype=torch.float32)
+    return out, out_f32, lse
+
+
+_NS.impl("decode_attn", _decode_attn, "CUDA")
+_NS.impl("decode_attn", _decode_attn, "CPU")
+
+# ------------------------------------------------------------------------------------------------
+# dense prefill attention (T_new >= 1)
+# ------------------------------------------------------------------------------------------------
+_NS.define("prefill_attn(Tensor q, Tensor k, Tensor v, Tensor? cache_seqlens, int window_left) -> Tensor")
+
+
+def _prefill_attn(q, k, v, cache_seqlens, window_left):
+    name = "prefill_attn"
+    _require_cuda(name, q, k, v, cache_seqlens)
+    _require_bf16(name, q, k, v)
+    if cache_seqlens is not None and cache_seqlens.dtype != torch.int32:
+        raise RuntimeError("nckv::prefill_attn: cache_seqlens must be int32")
+    if q.dim() != 4 or q.size(3) != HEAD_DIM:
+        raise RuntimeError(f"nckv::{name}: q must be (B, T, Hq, {HEAD_DIM}), got {tuple(q.shape)}")
+    B, T_new, Hq, D = q.shape
+    if k.shape != v.shape or k.stride() != v.stride():
+        raise RuntimeError(f"nckv::{name}: k and v must share shape and strides")
+    Hkv = k.size(2)
+    if k.size(0) != B or Hq % Hkv:
+        raise RuntimeError(f"nckv::{name}: k {tuple(k.shape)} does not match q {tuple(q.shape)}")
+    sb, st = _cache_strides(name, k)
+    q = q.contiguous()
+    out = torch.empty_like(q)
+    ws = workspace(q.device, B, Hq, Hkv)
+    with torch.cuda.device(q.device):
+        _lib.call("nckv_prefill_attn", _ptr(q), _ptr(k), _ptr(v), _ptr(cache_seqlens), _ptr(out), B, T_new, Hq, Hkv,
+                  D, k.size(1), sb, st, int(window_left), _ptr(ws), _stream(q.device))
+    return out
+
+
+_NS.impl("prefill_attn", _prefill_attn, "CUDA")
+_NS.impl("prefill_attn", _prefill_attn, "CPU")
+
+# ------------------------------------------------------------------------------------------------
+# prefill broadcast and LSE combine
+# ------------------------------------------------------------------------------------------------
+_NS.define("prefill_broadcast(Tensor src_k, Tensor src_v, Tensor(a!) dst_k, Tensor(b!) dst_v, "
+           "Tensor(c!)? dst_seqlens, int p) -> ()")
+
+
+def _prefill_broadcast(src_k, src_v, dst_k, dst_v, dst_seqlens, p):
+    name = "prefill_broadcast"
+    _require_cuda(name, src_k, src_v, dst_k, dst_v, dst_seqlens)
+    for t in (src_k, src_v, dst_k, dst_v):
+        if t.dim() != 5 or not t.is_contiguous():
+            raise RuntimeError(f"nckv::{name}: caches must be contiguous (L, B, T, Hkv, D) tensors")
+        if t.dtype != dst_k.dtype or t.element_size() != 2:
+            raise RuntimeError(f"nckv::{name}: caches must share a 16-bit dtype")
+    L, B, T_dst, Hkv, D = dst_k.shape
+    if src_k.shape != src_v.shape or dst_k.shape != dst_v.shape:
+        raise RuntimeError(f"nckv::{name}: K and V shapes differ")
+    if src_k.size(0) != L or src_k.size(1) != 1 or src_k.size(3) != Hkv or src_k.size(4) != D:
+        raise RuntimeError(f"nckv::{name}: source {tuple(src_k.shape)} does not match destination {tuple(dst_k.shape)}")
+    if dst_seqlens is not None and (dst_seqlens.dtype != torch.int32 or dst_seqlens.numel() != B):
+        raise RuntimeError(f"nckv::{name}: dst_seqlens must be int32 of {B} rows")
+    with torch.cuda.device(dst_k.device):
+        _lib.call("nckv_prefill_broadcast", _ptr(src_k), _ptr(src_v), _ptr(dst_k), _ptr(dst_v), _ptr(dst_seqlens), L, B,
+                  int(p), Hkv, D, src_k.size(2), T_dst, _stream(dst_k.device))
+
+
+_NS.impl("prefill_broadcast", _prefill_broadcast, "CUDA")
+_NS.impl("prefill_broadcast", _prefill_broadcast, "CPU")
+
+_NS.define("lse_combine(Tensor parts_o, Tensor parts_lse) -> (Tensor, Tensor)")
+
+
+def _lse_combine(parts_o, parts_lse):
+    name = "lse_combine"
+    _require_cuda(name, parts_o, parts_lse)
+    if parts_o.dtype != torch.float32 or parts_lse.dtype != torch.float32:
+        raise RuntimeError("nckv::lse_combine: partials must be float32")
+    n_parts = parts_o.size(0)
+    D = parts_o.size(-1)
+    rows = parts_lse[0].numel()
+    if parts_o[0].numel() != rows * D or parts_lse.size(0) != n_parts:
+        raise RuntimeError(f"nckv::{name}: shapes {tuple(parts_o.shape)} / {tuple(parts_lse.shape)} do not match")
+    parts_o, parts_lse = parts_o.contiguous(), parts_lse.contiguous()
+    out = torch.empty(parts_o.shape[1:], dtype=torch.bfloat16, device=parts_o.device)
+    lse = torch.empty(parts_lse.shape[1:], dtype=torch.float32, device=parts_o.device)
+    with torch.cuda.device(parts_o.device):
+        _lib.call("nckv_lse_combine", _ptr(parts_o), _ptr(parts_lse), n_parts, rows, D, _ptr(out), _ptr(lse),
+                  _stream(parts_o.device))
+    return out, lse
+
+
+_NS.impl("lse_combine", _lse_combine, "CUDA")
+_NS.impl("lse_combine", _lse_combine, "CPU")
+
+# ------------------------------------------------------------------------------------------------
+# thin Python entry points
+# ------------------------------------------------------------------------------------------------
+_ops = torch.ops.nckv
+
+
+def append_rope_norm(q, k, v, k_cache, v_cache, cache_seqlens, cos, sin, qk_scale=QK_SCALE, eps=RMS_EPS):
+    """RoPE + QK-norm + scale on q and k, append k/v at ``cache_seqlens`` (per row); returns q'."""
+    return _ops.append_rope_norm(q, k, v, k_cache, v_cache, cache_seqlens, cos, sin, qk_scale, eps)
+
+
+def append_kv(k, v, k_cache, v_cache, cache_seqlens):
+    """Write already-transformed k/v at ``cache_seqlens`` (per row)."""
+    _ops.append_kv(k, v, k_cache, v_cache, cache_seqlens)
+
+
+def decode_attention(q, k_cache, v_cache, cache_seqlens, seqlen_offset=1, window_left=-1, kv_begin=0, kv_end=0,
+                     partial=False):
+    """One-token attention over the cache. q: (B, Hq, D). With ``partial`` also returns the fp32
+    normalised output and the natural-log sum-exp (for a cross-GPU combine)."""
+    out, out_f32, lse = _ops.decode_attn(q, k_cache, v_cache, cache_seqlens, seqlen_offset, window_left, kv_begin,
+                                         kv_end, partial)
+    return (out, out_f32, lse) if partial else out
+
+
+def prefill_attention(q, k, v, cache_seqlens=None, window_left=-1):
+    """Dense causal attention of T_new query tokens per row against a cache view or plain k/v."""
+    return _ops.prefill_attn(q, k, v, cache_seqlens, window_left)
+
+
+def prefill_broadcast(src_k, src_v, dst_k, dst_v, dst_seqlens, p):
+    """Copy the first p tokens of a batch-1 (L,1,T,H,D) cache into all rows of (L,B,T',H,D)."""
+    _ops.prefill_broadcast(src_k, src_v, dst_k, dst_v, dst_seqlens, p)
+
+
+def lse_combine(parts_o, parts_lse):
+    """Merge partial attention results over disjoint key ranges; returns (bf16 out, fp32 lse)."""
+    return _ops.lse_combine(parts_o, parts_lse)

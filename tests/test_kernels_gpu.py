@@ -1,0 +1,307 @@
+"""Parity of the CUDA kernels (through the nckv custom ops / the C ABI) against the numpy oracle
+and against the torch-eager restatement of the reference's bf16 GPU path."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import kv_oracle as O
+from oracle import torch_ref as E
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+BF = torch.bfloat16
+# Tolerance of the reference's own differential tests (tests/test_attention_fallback.py:39-45).
+ATOL = RTOL = 1e-2
+
+
+def ops():
+    from nanochat_b200 import ops as _ops
+    return _ops
+
+
+def bits(t):
+    return t.contiguous().view(torch.int16)
+
+
+def rel_err(got, ref):
+    got, ref = got.double(), ref.double()
+    return ((got - ref).abs().max() / ref.abs().max().clamp_min(1e-30)).item()
+
+
+def make_cache(B, T_max, Hkv, seqlens, gen, layers=None):
+    shape = (B, T_max, Hkv, 128) if layers is None else (layers, B, T_max, Hkv, 128)
+    k = torch.randn(shape, generator=gen, device=DEV, dtype=torch.float32).to(BF)
+    v = torch.randn(shape, generator=gen, device=DEV, dtype=torch.float32).to(BF)
+    return k, v
+
+
+# ------------------------------------------------------------------------------------------------
+# (a) fused RoPE + QK-norm + scale + append
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("B,T_new,Hq,Hkv,T_max", [(32, 1, 12, 12, 2048), (5, 1, 16, 4, 300), (3, 7, 4, 2, 64),
+                                                  (1, 33, 2, 2, 40), (64, 1, 1, 1, 16)])
+def test_append_rope_norm_bit_exact(B, T_new, Hq, Hkv, T_max):
+    gen = torch.Generator(device=DEV).manual_seed(100 + B)
+    cos, sin = E.rotary_tables(T_max + 8, 128, DEV, BF)
+    seqlens = torch.randint(0, T_max - T_new + 1, (B,), generator=gen, device=DEV, dtype=torch.int32)
+    seqlens[0] = T_max - T_new  # last slot of the cache
+    if B > 1:
+        seqlens[1] = 0
+    q = torch.randn(B, T_new, Hq, 128, generator=gen, device=DEV).to(BF)
+    k = torch.randn(B, T_new, Hkv, 128, generator=gen, device=DEV).to(BF) * 3.0
+    v = torch.randn(B, T_new, Hkv, 128, generator=gen, device=DEV).to(BF)
+    k_cache, v_cache = make_cache(B, T_max, Hkv, seqlens, gen)
+    k_ref, v_ref = k_cache.clone(), v_cache.clone()
+
+    q_out = ops().append_rope_norm(q, k, v, k_cache, v_cache, seqlens, cos, sin)
+    assert ops().read_status(DEV) == 0
+
+    # reference bf16 GPU path: eager ops, then the slice-assign, row by row
+    q_ref = E.rope_norm_scale_rows(q, cos, sin, seqlens)
+    k_new = E.rope_norm_scale_rows(k, cos, sin, seqlens)
+    for b, L in enumerate(seqlens.tolist()):
+        k_ref[b, L:L + T_new] = k_new[b]
+        v_ref[b, L:L + T_new] = v[b]
+    assert torch.equal(bits(v_cache), bits(v_ref)), "V bytes differ"
+    n_bad_k = (bits(k_cache) != bits(k_ref)).sum().item()
+    n_bad_q = (bits(q_out) != bits(q_ref)).sum().item()
+    assert n_bad_k == 0, f"{n_bad_k} K cache elements differ from the eager bf16 path"
+    assert n_bad_q == 0, f"{n_bad_q} q elements differ from the eager bf16 path"
+
+    # numpy oracle (CPU restatement): identical up to isolated last-bit flips from rsqrt flavour
+    cos_np, sin_np = cos[0, :, 0].float().cpu().numpy(), sin[0, :, 0].float().cpu().numpy()
+    q_or = O.rope_norm_scale_rows(q.float().cpu().numpy(), cos_np, sin_np, seqlens.cpu().numpy(), bf16=True)
+    bad = (O.f32_to_bf16_bits(q_or) != bits(q_out).cpu().numpy().view(np.uint16))
+    assert bad.mean() < 1e-3
+    assert np.abs(q_or - q_out.float().cpu().numpy()).max() <= 2.0 ** -6
+
+
+def test_append_statistics_ten_million_elements():
+    """Mismatch count against the eager bf16 path over > 10^7 elements (target 0)."""
+    gen = torch.Generator(device=DEV).manual_seed(7)
+    B, T_new, H = 64, 128, 12
+    T_max = 128
+    cos, sin = E.rotary_tables(T_max, 128, DEV, BF)
+    seqlens = torch.zeros(B, device=DEV, dtype=torch.int32)
+    total_bad = 0
+    for scale in (1.0, 0.05, 30.0):
+        q = (torch.randn(B, T_new, H, 128, generator=gen, device=DEV) * scale).to(BF)
+        k = (torch.randn(B, T_new, H, 128, generator=gen, device=DEV) * scale).to(BF)
+        v = torch.randn(B, T_new, H, 128, generator=gen, device=DEV).to(BF)
+        k_cache = torch.zeros(B, T_max, H, 128, device=DEV, dtype=BF)
+        v_cache = torch.zeros_like(k_cache)
+        q_out = ops().append_rope_norm(q, k, v, k_cache, v_cache, seqlens, cos, sin)
+        q_ref = E.rope_norm_scale(q, cos, sin)
+        k_ref = E.rope_norm_scale(k, cos, sin)
+        total_bad += (bits(q_out) != bits(q_ref)).sum().item() + (bits(k_cache) != bits(k_ref)).sum().item()
+    print(f"append mismatches over {3 * 2 * B * T_new * H * 128} elements: {total_bad}")
+    assert total_bad == 0
+
+
+def test_append_overflow_sets_status_and_skips_row():
+    gen = torch.Generator(device=DEV).manual_seed(3)
+    B, Hkv, T_max = 3, 2, 8
+    seqlens = torch.tensor([2, 8, 7], device=DEV, dtype=torch.int32)  # row 1 is full
+    k = torch.randn(B, 1, Hkv, 128, generator=gen, device=DEV).to(BF)
+    v = torch.randn(B, 1, Hkv, 128, generator=gen, device=DEV).to(BF)
+    k_cache = torch.zeros(B, T_max + 1, Hkv, 128, device=DEV, dtype=BF)[:, :T_max]  # canary row behind each row
+    v_cache = torch.zeros(B, T_max + 1, Hkv, 128, device=DEV, dtype=BF)[:, :T_max]
+    ops().append_kv(k, v, k_cache, v_cache, seqlens)
+    st = ops().read_status(DEV)
+    assert st & 1, "overflow bit not set"
+    assert ops().read_status(DEV) == 0, "status was not cleared"
+    assert torch.equal(k_cache[0, 2], k[0, 0]) and torch.equal(k_cache[2, 7], k[2, 0])
+    assert k_cache[1].abs().sum().item() == 0, "full row must be left untouched"
+    base = k_cache._base if k_cache._base is not None else k_cache
+    assert base[:, T_max].abs().sum().item() == 0, "canary row written"
+
+
+# ------------------------------------------------------------------------------------------------
+# (b) decode attention
+# ------------------------------------------------------------------------------------------------
+def run_decode_case(B, Hq, Hkv, T_max, seqlens, window, seed, kv_range=(0, 0), check_eager=True):
+    gen = torch.Generator(device=DEV).manual_seed(seed)
+    seqlens_t = torch.tensor(seqlens, device=DEV, dtype=torch.int32)
+    q = torch.randn(B, Hq, 128, generator=gen, device=DEV).to(BF)
+    k_cache, v_cache = make_cache(B, T_max, Hkv, seqlens_t, gen)
+    partial = kv_range != (0, 0)
+    res = ops().decode_attention(q, k_cache, v_cache, seqlens_t, seqlen_offset=1, window_left=window,
+                                 kv_begin=kv_range[0], kv_end=kv_range[1], partial=partial)
+    torch.cuda.synchronize()
+    assert ops().read_status(DEV) == 0
+    out = res[0] if partial else res
+    ref, ref_lse = O.attention_kvcache(q.float().cpu().numpy()[:, None], k_cache.float().cpu().numpy(),
+                                       v_cache.float().cpu().numpy(), np.array(seqlens), window_left=window,
+                                       kv_begin=kv_range[0], kv_end=kv_range[1])
+    ref = torch.from_numpy(ref[:, 0])
+    got = out.float().cpu()
+    assert not torch.isnan(got).any()
+    assert torch.allclose(got, ref, atol=ATOL, rtol=RTOL), f"max diff {(got - ref).abs().max().item()}"
+    assert rel_err(got, ref) <= 1e-2
+    if partial:
+        lse = res[2].float().cpu().numpy()
+        ref_lse = ref_lse[:, 0]
+        finite = np.isfinite(ref_lse)
+        assert np.array_equal(np.isneginf(lse), ~finite)
+        np.testing.assert_allclose(lse[finite], ref_lse[finite], rtol=1e-3, atol=2e-3)
+        f32 = res[1].float().cpu()
+        assert torch.allclose(f32, ref, atol=ATOL, rtol=RTOL)
+    if check_eager and not partial:
+        # the reference's own GPU path (SDPA on bf16), run row by row for ragged lengths
+        eager = E.kvcache_attention(q[:, None], k_cache, v_cache, None, None, seqlens_t, window)[:, 0]
+        assert torch.allclose(out.float(), eager.float(), atol=2e-2, rtol=2e-2)
+    return out
+
+
+@pytest.mark.parametrize("Hq,Hkv", [(2, 2), (12, 12), (16, 4), (8, 1), (16, 1), (24, 2)])
+def test_decode_attention_ragged_groups(Hq, Hkv):
+    rng = np.random.default_rng(Hq * 31 + Hkv)
+    B, T_max = 6, 300
+    seqlens = rng.integers(0, T_max - 1, size=B).tolist()
+    seqlens[0], seqlens[1] = 0, T_max - 1  # a single key; the full cache
+    run_decode_case(B, Hq, Hkv, T_max, seqlens, -1, seed=Hq)
+
+
+@pytest.mark.parametrize("window", [8, 31, 32, 33, 1024])
+def test_decode_attention_window_edges(window):
+    w = window
+    seqlens = [0, 1, max(w - 2, 0), w - 1, w, w + 1, 2 * w + 5, 70]
+    T_max = max(seqlens) + 2
+    run_decode_case(len(seqlens), 4, 2, T_max, seqlens, w, seed=window)
+
+
+def test_decode_attention_config1_shape_and_split_invariance():
+    """BASELINE configs[1]: B=32, 12/12 heads, capacity 2048, lengths uniform in [1, 2047] (seed 2)."""
+    seqlens = torch.randint(1, 2048, (32,), dtype=torch.int32, generator=torch.Generator().manual_seed(2)).tolist()
+    out = run_decode_case(32, 12, 12, 2048, seqlens, -1, seed=2)
+    # same rows evaluated alone (different slicing of the tile sequence) must agree closely
+    gen = torch.Generator(device=DEV).manual_seed(2)
+    q = torch.randn(32, 12, 128, generator=gen, device=DEV).to(BF)
+    k_cache, v_cache = make_cache(32, 2048, 12, None, gen)
+    st = torch.tensor(seqlens, device=DEV, dtype=torch.int32)
+    for b in (0, 7, 31):
+        alone = ops().decode_attention(q[b:b + 1], k_cache[b:b + 1], v_cache[b:b + 1], st[b:b + 1])
+        assert rel_err(alone.float(), out[b:b + 1].float()) <= 4e-3
+
+
+def test_decode_attention_long_rows_gqa():
+    """configs[4]-like (scaled down): few rows, long keys, 16 q heads on 4 kv heads."""
+    seqlens = [8191, 5000, 4097, 6143]
+    run_decode_case(4, 16, 4, 8192, seqlens, -1, seed=44, check_eager=False)
+
+
+def test_decode_attention_kv_shards_and_combine():
+    """Sequence-split: per-shard partials merged by lse_combine equal the unsplit result."""
+    B, Hq, Hkv, T_max = 5, 8, 2, 520
+    seqlens = [519, 100, 0, 259, 260]
+    full = run_decode_case(B, Hq, Hkv, T_max, seqlens, -1, seed=9)
+    parts_o, parts_lse = [], []
+    for lo, hi in [(0, 130), (130, 260), (260, 390), (390, 520)]:
+        gen = torch.Generator(device=DEV).manual_seed(9)
+        q = torch.randn(B, Hq, 128, generator=gen, device=DEV).to(BF)
+        k_cache, v_cache = make_cache(B, T_max, Hkv, None, gen)
+        st = torch.tensor(seqlens, device=DEV, dtype=torch.int32)
+        _, o32, lse = ops().decode_attention(q, k_cache, v_cache, st, kv_begin=lo, kv_end=hi, partial=True)
+        parts_o.append(o32)
+        parts_lse.append(lse)
+        run_decode_case(B, Hq, Hkv, T_max, seqlens, -1, seed=9, kv_range=(lo, hi))
+    out, lse = ops().lse_combine(torch.stack(parts_o), torch.stack(parts_lse))
+    assert rel_err(out.float(), full.float()) <= 4e-3
+    ref_o, ref_lse = O.lse_combine(torch.stack(parts_o).cpu().numpy(), torch.stack(parts_lse).cpu().numpy())
+    assert torch.allclose(out.float().cpu(), torch.from_numpy(ref_o), atol=1e-2, rtol=1e-2)
+    np.testing.assert_allclose(lse.cpu().numpy(), ref_lse, rtol=1e-5, atol=1e-5)
+
+
+def test_decode_attention_ignores_garbage_beyond_length():
+    """Bytes past cache_seqlens (NaN/Inf patterns included) must not reach the output."""
+    gen = torch.Generator(device=DEV).manual_seed(12)
+    B, H, T_max = 3, 2, 100
+    seqlens = [10, 40, 63]
+    st = torch.tensor(seqlens, device=DEV, dtype=torch.int32)
+    q = torch.randn(B, H, 128, generator=gen, device=DEV).to(BF)
+    k_cache, v_cache = make_cache(B, T_max, H, None, gen)
+    clean = ops().decode_attention(q, k_cache, v_cache, st)
+    for b, L in enumerate(seqlens):
+        k_cache[b, L + 1:] = float("nan")
+        v_cache[b, L + 1:] = float("inf")
+    dirty = ops().decode_attention(q, k_cache, v_cache, st)
+    assert torch.equal(bits(clean), bits(dirty))
+
+
+def test_workspace_counters_return_to_zero():
+    seqlens = [2000] * 4
+    run_decode_case(4, 2, 2, 2048, seqlens, -1, seed=1)  # long rows on few pairs: every pair is split
+    ws = ops().workspace(DEV, 4, 2, 2)
+    counters = ws[256:256 + 4 * 2 * 4].view(torch.int32)
+    assert counters.abs().sum().item() == 0
+
+
+# ------------------------------------------------------------------------------------------------
+# reference fixtures through the public wrapper
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("name", ["d128_single", "d128_single_window", "d128_gqa_single"])
+def test_flash_attn_with_kvcache_golden_decode(golden_dir, name):
+    from nanochat_b200.flash_attention import flash_attn
+    g = np.load(os.path.join(golden_dir, "attn_kvcache_fp32.npz"))
+    dev = lambda a: torch.from_numpy(a).to(DEV).to(BF)
+    q, k, v = dev(g[f"{name}.q"]), dev(g[f"{name}.k"]), dev(g[f"{name}.v"])
+    seqlens = torch.from_numpy(g[f"{name}.seqlens"]).to(DEV)
+    window = int(g[f"{name}.window"])
+    k_after, v_after = dev(g[f"{name}.k_cache_after"]), dev(g[f"{name}.v_cache_after"])
+    L = int(seqlens[0])
+    k_cache, v_cache = k_after.clone(), v_after.clone()
+    k_cache[:, L:L + 1] = 0
+    v_cache[:, L:L + 1] = 0
+    before = seqlens.clone()
+    out = flash_attn.flash_attn_with_kvcache(q, k_cache, v_cache, k=k, v=v, cache_seqlens=seqlens, causal=True,
+                                             window_size=(window, 0))
+    assert out.shape == q.shape
+    assert torch.equal(seqlens, before), "cache_seqlens must not be advanced by the attention call"
+    assert torch.equal(bits(k_cache), bits(k_after)) and torch.equal(bits(v_cache), bits(v_after))
+    ref = torch.from_numpy(g[f"{name}.out"])
+    # inputs were rounded to bf16 on the way in: compare loosely with the fp32 fixture and tightly
+    # with the oracle evaluated on the rounded inputs
+    assert torch.allclose(out.float().cpu(), ref, atol=3e-2, rtol=3e-2)
+    o2, _ = O.attention_kvcache(q.float().cpu().numpy(), k_cache.float().cpu().numpy(), v_cache.float().cpu().numpy(),
+                                before.cpu().numpy(), window_left=window)
+    assert torch.allclose(out.float().cpu(), torch.from_numpy(o2), atol=ATOL, rtol=RTOL)
+
+
+# ------------------------------------------------------------------------------------------------
+# (c) prefill broadcast
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("L,B,p,Hkv,T_src,T_dst", [(4, 4, 32, 2, 32, 96), (2, 7, 5, 3, 9, 11), (1, 64, 1024, 4, 1024, 1100),
+                                                   (3, 2, 0, 1, 4, 4)])
+def test_prefill_broadcast_bit_exact(L, B, p, Hkv, T_src, T_dst):
+    gen = torch.Generator(device=DEV).manual_seed(L * 100 + B)
+    src_k = torch.randn(L, 1, T_src, Hkv, 128, generator=gen, device=DEV).to(BF)
+    src_v = torch.randn(L, 1, T_src, Hkv, 128, generator=gen, device=DEV).to(BF)
+    dst_k = torch.full((L, B, T_dst, Hkv, 128), 7.0, device=DEV, dtype=BF)
+    dst_v = torch.full((L, B, T_dst, Hkv, 128), -7.0, device=DEV, dtype=BF)
+    seqlens = torch.zeros(B, device=DEV, dtype=torch.int32)
+    ref_k, ref_v = dst_k.cpu().float().numpy(), dst_v.cpu().float().numpy()
+    ref_s = np.zeros(B, dtype=np.int32)
+    O.prefill_broadcast(src_k.cpu().float().numpy(), src_v.cpu().float().numpy(), ref_k, ref_v, ref_s, p)
+    ops().prefill_broadcast(src_k, src_v, dst_k, dst_v, seqlens, p)
+    assert np.array_equal(dst_k.cpu().float().numpy(), ref_k)
+    assert np.array_equal(dst_v.cpu().float().numpy(), ref_v)
+    assert np.array_equal(seqlens.cpu().numpy(), ref_s)
+
+
+def test_lse_combine_matches_oracle():
+    gen = torch.Generator(device=DEV).manual_seed(77)
+    n, rows = 5, 37
+    po = torch.randn(n, rows, 128, generator=gen, device=DEV)
+    pl = torch.randn(n, rows, generator=gen, device=DEV) * 3
+    pl[2, 5] = float("-inf")
+    pl[:, 9] = float("-inf")  # a row nobody saw any key for
+    out, lse = ops().lse_combine(po, pl)
+    ro, rl = O.lse_combine(po.cpu().numpy(), pl.cpu().numpy())
+    assert torch.allclose(out.float().cpu(), torch.from_numpy(ro), atol=1e-2, rtol=1e-2)
+    assert np.array_equal(np.isneginf(lse.cpu().numpy()), np.isneginf(rl))
+    fin = np.isfinite(rl)
+    np.testing.assert_allclose(lse.cpu().numpy()[fin], rl[fin], rtol=1e-5, atol=1e-5)
+    assert out[9].abs().sum().item() == 0

@@ -1,0 +1,198 @@
+"""The numpy oracle against fixtures produced by the reference itself (tests/golden/make_golden.py)."""
+import os
+
+import numpy as np
+import pytest
+
+from oracle import kv_oracle as O
+
+
+def _load(golden_dir, name):
+    return np.load(os.path.join(golden_dir, name))
+
+
+def _bf(bits):
+    return O.bf16_bits_to_f32(bits.view(np.uint16))
+
+
+def test_bf16_rounding_is_round_to_nearest_even():
+    x = np.array([1.0, 1.00390625, 1.01171875, -3.1415927, 65504.0, 1e-40, 0.0], dtype=np.float32)
+    # 1.00390625 = 1 + 2^-8 is a tie between 1.0 and 1.0078125 -> even mantissa (1.0)
+    assert O.bf16_round(x)[1] == np.float32(1.0)
+    # 1.01171875 = 1 + 3*2^-8 is a tie between 1.0078125 and 1.015625 -> even (1.015625)
+    assert O.bf16_round(x)[2] == np.float32(1.015625)
+    import torch
+    t = torch.from_numpy(x).bfloat16().float().numpy()
+    assert np.array_equal(O.bf16_round(x), t)
+    r = np.random.default_rng(0).standard_normal(100000).astype(np.float32)
+    assert np.array_equal(O.bf16_round(r), torch.from_numpy(r).bfloat16().float().numpy())
+
+
+def test_rope_norm_scale_bf16_matches_reference(golden_dir):
+    g = _load(golden_dir, "rope_norm_bf16.npz")
+    x = _bf(g["x"])
+    T0 = int(g["T0"])
+    cos, sin = _bf(g["cos"]), _bf(g["sin"])
+    T = x.shape[1]
+    c = cos[T0:T0 + T][None, :, None, :]
+    s = sin[T0:T0 + T][None, :, None, :]
+    y = O.rope(x, c, s, bf16=True)
+    assert np.array_equal(O.f32_to_bf16_bits(y), g["rope"].view(np.uint16)), "RoPE bytes differ"
+    # rms_norm: fp32 eps, statistics in fp32.  The summation order inside torch's CPU kernel is not
+    # the CUDA order the oracle follows, so allow isolated last-bit differences (none are expected
+    # at this size) and require everything else to be byte-identical.
+    z = O.rms_norm(y, bf16=True)
+    ref_z = g["norm"].view(np.uint16)
+    bad = O.f32_to_bf16_bits(z) != ref_z
+    assert bad.sum() <= 2, f"{bad.sum()} rms_norm elements differ"
+    out = O.rope_norm_scale(x, c, s, bf16=True)
+    bad = O.f32_to_bf16_bits(out) != g["out"].view(np.uint16)
+    assert bad.sum() <= 2
+    diff = np.abs(out - _bf(g["out"]))
+    assert diff.max() <= np.abs(_bf(g["out"])).max() * 2.0 ** -7
+    # the bf16 machine epsilon is NOT what eps=None resolves to
+    wrong = O.rms_norm(y, eps=0.0078125, bf16=True)
+    assert (O.f32_to_bf16_bits(wrong) != ref_z).mean() > 0.1
+
+
+def test_rope_norm_scale_rows_uses_per_row_positions(golden_dir):
+    g = _load(golden_dir, "rope_norm_bf16.npz")
+    x = _bf(g["x"])
+    T0 = int(g["T0"])
+    cos, sin = _bf(g["cos"]), _bf(g["sin"])
+    seqlens = np.full((x.shape[0],), T0, dtype=np.int32)
+    out = O.rope_norm_scale_rows(x, cos, sin, seqlens, bf16=True)
+    assert (O.f32_to_bf16_bits(out) != g["out"].view(np.uint16)).sum() <= 2
+
+
+def test_rope_norm_scale_fp32_and_tables(golden_dir):
+    g = _load(golden_dir, "rope_norm_fp32.npz")
+    cos, sin = O.rotary_tables(4096, 128)
+    rows = g["table_rows"]
+    # numpy's and torch's float32 pow differ in the last bit of inv_freq, which the position
+    # multiplies (up to 4095 here); parity tests therefore always feed tables made by torch ops
+    np.testing.assert_allclose(cos[rows], g["cos_rows"], rtol=0, atol=2e-4)
+    np.testing.assert_allclose(sin[rows], g["sin_rows"], rtol=0, atol=2e-4)
+    np.testing.assert_allclose(cos[rows[:5]], g["cos_rows"][:5], rtol=0, atol=5e-6)
+    T0 = int(g["T0"])
+    x = g["x"]
+    T = x.shape[1]
+    out = O.rope_norm_scale(x, cos[T0:T0 + T][None, :, None, :], sin[T0:T0 + T][None, :, None, :])
+    np.testing.assert_allclose(out, g["out"], rtol=1e-5, atol=1e-5)
+
+
+def test_window_sizes_match_reference(golden_dir):
+    g = _load(golden_dir, "window_sizes.npz")
+    assert len(g.files) >= 6
+    for key in g.files:
+        seq_len, n_layer, pattern = key.split("_")
+        got = np.array(O.window_sizes(int(seq_len), int(n_layer), pattern), dtype=np.int64)
+        assert np.array_equal(got, g[key]), key
+    # the case the survey notes: 2048 -> short window 512, long 2048
+    assert O.window_sizes(2048, 4)[0] == (512, 0) and O.window_sizes(2048, 4)[-1] == (2048, 0)
+    with pytest.raises(ValueError):
+        O.window_sizes(2048, 4, "SXL")
+
+
+KV_CASES = ["ref_prefill", "ref_single", "ref_single_window", "d128_prefill", "d128_single", "d128_single_window",
+            "d128_gqa_single", "d128_gqa_chunk_window", "d128_chunk_full"]
+
+
+@pytest.mark.parametrize("name", KV_CASES)
+def test_attention_kvcache_matches_reference(golden_dir, name):
+    g = _load(golden_dir, "attn_kvcache_fp32.npz")
+    q, k, v = g[f"{name}.q"], g[f"{name}.k"], g[f"{name}.v"]
+    seqlens = g[f"{name}.seqlens"]
+    window = int(g[f"{name}.window"])
+    k_after, v_after = g[f"{name}.k_cache_after"], g[f"{name}.v_cache_after"]
+    T_new = q.shape[1]
+    L = int(seqlens[0])
+    k_cache, v_cache = k_after.copy(), v_after.copy()
+    k_cache[:, L:L + T_new] = 0
+    v_cache[:, L:L + T_new] = 0
+    O.append(k_cache, v_cache, k, v, seqlens)
+    assert np.array_equal(k_cache, k_after) and np.array_equal(v_cache, v_after), "append bytes differ"
+    out, _ = O.attention_kvcache(q, k_cache, v_cache, seqlens, window_left=window)
+    np.testing.assert_allclose(out, g[f"{name}.out"], rtol=2e-5, atol=2e-6)
+
+
+@pytest.mark.parametrize("name", ["causal", "window", "window_ge_T"])
+def test_attention_nocache_matches_reference(golden_dir, name):
+    g = _load(golden_dir, "attn_func_fp32.npz")
+    out = O.attention_nocache(g[f"{name}.q"], g[f"{name}.k"], g[f"{name}.v"], window_left=int(g[f"{name}.window"]))
+    np.testing.assert_allclose(out, g[f"{name}.out"], rtol=2e-5, atol=2e-6)
+
+
+def test_prefill_broadcast_matches_reference(golden_dir):
+    g = _load(golden_dir, "kvcache_prefill.npz")
+    src_k, src_v = g["src_k"], g["src_v"]
+    dst_k, dst_v = np.zeros_like(g["dst_k"]), np.zeros_like(g["dst_v"])
+    seqlens = np.zeros(dst_k.shape[1], dtype=np.int32)
+    O.prefill_broadcast(src_k, src_v, dst_k, dst_v, seqlens, src_k.shape[2])
+    assert np.array_equal(dst_k, g["dst_k"]) and np.array_equal(dst_v, g["dst_v"])
+    assert np.array_equal(seqlens, g["dst_seqlens"])
+    with pytest.raises(ValueError):
+        O.prefill_broadcast(src_k, src_v, dst_k, dst_v, seqlens, src_k.shape[2] + 1)
+
+
+def test_append_overflow_and_visible_range_edges():
+    kc = np.zeros((1, 4, 1, 8), dtype=np.float32)
+    with pytest.raises(ValueError):
+        O.append(kc, kc.copy(), np.ones((1, 2, 1, 8), np.float32), np.ones((1, 2, 1, 8), np.float32), np.array([3]))
+    w = 8
+    # decode, T_new = 1: n_keys = min(L + 1, w + 1)
+    for L in [0, 1, w - 1, w, w + 1, 100]:
+        lo, hi = O.visible_range(L, 0, 1, w)
+        assert hi == L + 1 and hi - lo == min(L + 1, w + 1)
+    assert O.visible_range(50, 0, 1, -1) == (0, 51)
+    # chunk of 4 on a prefix of 10: token t sits at 10 + t
+    assert [O.visible_range(10, t, 4, 3) for t in range(4)] == [(7, 11), (8, 12), (9, 13), (10, 14)]
+
+
+def test_lse_combine_equals_single_softmax():
+    rng = np.random.default_rng(5)
+    B, Hq, Hkv, D, T = 2, 4, 2, 16, 37
+    q = rng.standard_normal((B, 1, Hq, D)).astype(np.float32)
+    kc = rng.standard_normal((B, T, Hkv, D)).astype(np.float32)
+    vc = rng.standard_normal((B, T, Hkv, D)).astype(np.float32)
+    seqlens = np.array([T - 1, 20], dtype=np.int32)
+    full, full_lse = O.attention_kvcache(q, kc, vc, seqlens)
+    parts = [O.attention_kvcache(q, kc, vc, seqlens, kv_begin=a, kv_end=b) for a, b in [(0, 9), (9, 25), (25, T)]]
+    out, lse = O.lse_combine(np.stack([p[0] for p in parts]), np.stack([p[1] for p in parts]))
+    np.testing.assert_allclose(out, full, rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(lse, full_lse, rtol=1e-5, atol=1e-6)
+    # row 1 has only 21 keys: the last shard is empty for it and must drop out
+    assert np.isneginf(parts[2][1][1]).all() and not np.isnan(out).any()
+
+
+# ---------------------------------------------------------------------------------------------
+# the torch-eager port (oracle/torch_ref.py) against the same fixtures
+# ---------------------------------------------------------------------------------------------
+def test_torch_port_matches_reference_fixtures(golden_dir):
+    import torch
+    from oracle import torch_ref as E
+    torch.set_num_threads(1)
+    g = _load(golden_dir, "rope_norm_bf16.npz")
+    x = torch.from_numpy(g["x"]).view(torch.bfloat16)
+    cos = torch.from_numpy(g["cos"]).view(torch.bfloat16)[None, :, None, :]
+    sin = torch.from_numpy(g["sin"]).view(torch.bfloat16)[None, :, None, :]
+    T0 = int(g["T0"])
+    seqlens = torch.full((x.size(0),), T0, dtype=torch.int32)
+    out = E.rope_norm_scale_rows(x, cos, sin, seqlens)
+    assert torch.equal(out.view(torch.int16), torch.from_numpy(g["out"]))
+    tc, ts = E.rotary_tables(4096, 128, "cpu", torch.bfloat16)
+    g32 = _load(golden_dir, "rope_norm_fp32.npz")
+    rows = g32["table_rows"]
+    assert np.array_equal(tc[0, rows, 0].view(torch.int16).numpy(), g32["cos_rows_bf16"])
+    assert np.array_equal(ts[0, rows, 0].view(torch.int16).numpy(), g32["sin_rows_bf16"])
+    g = _load(golden_dir, "attn_kvcache_fp32.npz")
+    for name in KV_CASES:
+        q, k, v = (torch.from_numpy(g[f"{name}.{n}"]) for n in "qkv")
+        seqlens = torch.from_numpy(g[f"{name}.seqlens"])
+        L, T_new = int(seqlens[0]), q.size(1)
+        kc, vc = torch.from_numpy(g[f"{name}.k_cache_after"]).clone(), torch.from_numpy(g[f"{name}.v_cache_after"]).clone()
+        kc[:, L:L + T_new] = 0
+        vc[:, L:L + T_new] = 0
+        out = E.kvcache_attention(q, kc, vc, k, v, seqlens, int(g[f"{name}.window"]))
+        np.testing.assert_allclose(out.numpy(), g[f"{name}.out"], rtol=1e-5, atol=1e-6)
+        assert np.array_equal(kc.numpy(), g[f"{name}.k_cache_after"])
