@@ -410,9 +410,12 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
                 __threadfence();
                 __syncwarp();
                 const int pair = cons.b * Hkv + cons.h;
-                const long long w_first = ((P0 + 1) * W - 1) / total;
-                const long long w_last = (P1 * W - 1) / total;
-                const int nparts = (int)(w_last - w_first + 1);
+                // parts of this pair = the warps whose (non-empty) slices intersect [P0, P1);
+                // warp_of(x) is the warp whose slice holds tile x, and the next part starts at
+                // the first tile past that warp's slice
+                auto warp_of = [&](long long x) { return ((x + 1) * W - 1) / total; };
+                int nparts = 0;
+                for (long long x = P0; x < P1; x = (warp_of(x) + 1) * total / W) ++nparts;
                 int old = 0;
                 if (lane == 0) old = atomicAdd(&p.counters[pair], 1);
                 old = __shfl_sync(0xffffffffu, old, 0);
@@ -421,19 +424,23 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
                     // last arriver: merge.  lane owns channels 4*lane .. 4*lane+3 of every head row
                     for (int hg = 0; hg < G; ++hg) {
                         float M = -INFINITY;
-                        for (long long w = w_first; w <= w_last; ++w) {
+                        for (long long x = P0; x < P1;) {
+                            const long long w = warp_of(x);
                             const long long s2 = 2 * w + ((w * total / W) <= P0 ? 1 : 0);
                             M = fmaxf(M, __ldcg(p.partials + s2 * p.rec_floats + G * NCKV_D + hg));
+                            x = (w + 1) * total / W;
                         }
                         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
                         float L = 0.f;
-                        for (long long w = w_first; w <= w_last; ++w) {
+                        for (long long x = P0; x < P1;) {
+                            const long long w = warp_of(x);
                             const long long s2 = 2 * w + ((w * total / W) <= P0 ? 1 : 0);
                             const float *r2 = p.partials + s2 * p.rec_floats;
                             const float sc = exp2f(__ldcg(r2 + G * NCKV_D + hg) - M);
                             L += sc * __ldcg(r2 + G * NCKV_D + G + hg);
                             const float4 v = __ldcg(reinterpret_cast<const float4 *>(r2 + hg * NCKV_D) + lane);
                             acc.x += sc * v.x; acc.y += sc * v.y; acc.z += sc * v.z; acc.w += sc * v.w;
+                            x = (w + 1) * total / W;
                         }
                         const float inv = 1.f / L;
                         acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
