@@ -48,6 +48,9 @@ struct DecodeParams {
     int seqlen_offset, window_left, kv_begin, kv_end;
     int rec_floats;
     float scale_log2;
+#ifdef NCKV_TIMELINE
+    unsigned long long *timeline;  // 8 stamps per warp of the grid (debug builds only)
+#endif
 };
 
 struct TileCursor {
@@ -66,11 +69,11 @@ __device__ __forceinline__ void cursor_advance(TileCursor &c, const int *s_pref,
 }
 
 // Largest b with Hkv * pref[b] <= x; the row it names always owns tile x.
-__device__ __forceinline__ int find_row(const int *s_pref, int B, int Hkv, long long x) {
+__device__ __forceinline__ int find_row(const int *s_pref, int B, int Hkv, int x) {
     int lo = 0, hi = B;  // invariant: Hkv*pref[lo] <= x < Hkv*pref[hi]
     while (hi - lo > 1) {
         int mid = (lo + hi) >> 1;
-        if ((long long)Hkv * s_pref[mid] <= x) lo = mid; else hi = mid;
+        if (Hkv * s_pref[mid] <= x) lo = mid; else hi = mid;
     }
     return lo;
 }
@@ -93,6 +96,15 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
     const int warp = tid >> 5;
     const int lane = tid & 31;
     const int B = p.B, Hkv = p.Hkv, G = p.G;
+#ifdef NCKV_TIMELINE
+    unsigned long long *tl = p.timeline + ((long long)blockIdx.x * DEC_WARPS + warp) * 8;
+    unsigned long long tl_fin = 0;
+#define TL_STAMP(i) do { if (lane == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); tl[i] = t_; } } while (0)
+#define TL_NOW(v) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(v))
+    TL_STAMP(0);
+#else
+#define TL_STAMP(i)
+#endif
 
     // ---- set-up: per-row visible key range and tile counts --------------------------------
     for (int b = tid; b < B; b += blockDim.x) {
@@ -159,14 +171,22 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
         if (p.lse) for (int i = tid; i < p.Hq; i += blockDim.x) p.lse[(long long)b * p.Hq + i] = -INFINITY;
     }
 
-    const long long total = (long long)Hkv * s_pref[B];
+    TL_STAMP(1);
+    // Slices: with q = total / W and r = total % W, warp w owns q + (w < r) consecutive tiles
+    // starting at w*q + min(w, r).  Everything is 32-bit (the host bounds total below 2^31).
+    const int total = Hkv * s_pref[B];
     if (total == 0) return;
-    const long long W = (long long)gridDim.x * DEC_WARPS;
-    const long long gw = (long long)blockIdx.x * DEC_WARPS + warp;
-    const long long lo_tile = gw * total / W;
-    const long long hi_tile = (gw + 1) * total / W;
-    const int n_my = (int)(hi_tile - lo_tile);
+    const int W = gridDim.x * DEC_WARPS;
+    const int gw = blockIdx.x * DEC_WARPS + warp;
+    const int sl_q = total / W, sl_r = total % W;
+    const int lo_tile = gw * sl_q + min(gw, sl_r);
+    const int n_my = sl_q + (gw < sl_r ? 1 : 0);
     if (n_my == 0) return;
+    auto slice_lo = [&](int w) { return w * sl_q + min(w, sl_r); };
+    auto warp_of = [&](int x) {  // the warp whose slice holds tile x
+        const int big = sl_r * (sl_q + 1);
+        return x < big ? x / (sl_q + 1) : sl_r + (x - big) / sl_q;
+    };
 
     uint8_t *my_stages = stages + warp * DEC_STAGES * DEC_STAGE_BYTES;
     uint64_t *my_bar = full_bar + warp * DEC_STAGES;
@@ -175,9 +195,9 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
     cons.b = find_row(s_pref, B, Hkv, lo_tile);
     cons.nt = s_pref[cons.b + 1] - s_pref[cons.b];
     {
-        const long long rel = lo_tile - (long long)Hkv * s_pref[cons.b];
-        cons.h = (int)(rel / cons.nt);
-        cons.j = (int)(rel % cons.nt);
+        const int rel = lo_tile - Hkv * s_pref[cons.b];
+        cons.h = rel / cons.nt;
+        cons.j = rel - cons.h * cons.nt;
     }
     TileCursor prod = cons;
 
@@ -200,6 +220,7 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
         cursor_advance(prod, s_pref, B, Hkv);
     }
 
+    TL_STAMP(2);
     const int g = lane >> 2;  // MMA row within 8 (query head within the group)
     const int t4 = lane & 3;
     uint32_t qa[8][GHI ? 4 : 2];  // A fragments of Q for the 8 k-steps over D
@@ -208,6 +229,10 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
     float l_run[2] = {0.f, 0.f};
     int seg_j0 = 0;
     bool timed_out = false;
+    int pend0 = 0, pend1 = 0, n_pend = 0;  // pairs whose partial record awaits its arrival (at most 2 per slice)
+#ifdef NCKV_TIMELINE
+    unsigned long long tf0s = 0;
+#endif
 
     for (int it = 0; it < n_my; ++it) {
         const int stage = it % DEC_STAGES;
@@ -239,6 +264,9 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
             break;
         }
 
+#ifdef NCKV_TIMELINE
+        if (it == 0) TL_STAMP(3);
+#endif
         const uint32_t kbase = smem_u32(my_stages + stage * DEC_STAGE_BYTES);
         const uint32_t vbase = kbase + 2 * DEC_HALF_BYTES;
         const int key0 = s_start[cons.b] + cons.j * DEC_TILE;
@@ -358,6 +386,10 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
         // ---- end of this pair's run inside my slice? ----
         const bool seg_end = (it == n_my - 1) || (cons.j == cons.nt - 1);
         if (seg_end) {
+#ifdef NCKV_TIMELINE
+            TL_NOW(tf0s);
+            if (it == n_my - 1) TL_STAMP(4);
+#endif
             float l0 = l_run[0], l1 = l_run[1];
             l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
             l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
@@ -391,11 +423,11 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
                     if (GHI && g + 8 < G) p.lse[row_base + g + 8] = (m_run[1] + log2f(l1)) * 0.69314718055994531f;
                 }
             } else {
-                // partial record: [G][128] un-normalised O, then m[G], l[G]
-                const long long P0 = (long long)Hkv * s_pref[cons.b] + (long long)cons.h * cons.nt;
-                const long long P1 = P0 + cons.nt;
-                const long long slot = 2 * gw + (seg_j0 == 0 ? 1 : 0);
-                float *rec = p.partials + slot * p.rec_floats;
+                // partial record: [G][128] un-normalised O, then m[G], l[G].  The arrival on the
+                // pair's counter is deferred to the end of this warp's slice, so that no fence sits
+                // in the middle of the tile stream.
+                const int slot = 2 * gw + (seg_j0 == 0 ? 1 : 0);
+                float *rec = p.partials + (long long)slot * p.rec_floats;
 #pragma unroll
                 for (int nd = 0; nd < 16; ++nd) {
                     const int d = nd * 8 + 2 * t4;
@@ -407,57 +439,90 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
                     if (g < G) { __stcg(rec + G * NCKV_D + g, m_run[0]); __stcg(rec + G * NCKV_D + G + g, l0); }
                     if (GHI && g + 8 < G) { __stcg(rec + G * NCKV_D + g + 8, m_run[1]); __stcg(rec + G * NCKV_D + G + g + 8, l1); }
                 }
-                __threadfence();
-                __syncwarp();
-                const int pair = cons.b * Hkv + cons.h;
-                // parts of this pair = the warps whose (non-empty) slices intersect [P0, P1);
-                // warp_of(x) is the warp whose slice holds tile x, and the next part starts at
-                // the first tile past that warp's slice
-                auto warp_of = [&](long long x) { return ((x + 1) * W - 1) / total; };
-                int nparts = 0;
-                for (long long x = P0; x < P1; x = (warp_of(x) + 1) * total / W) ++nparts;
-                int old = 0;
-                if (lane == 0) old = atomicAdd(&p.counters[pair], 1);
-                old = __shfl_sync(0xffffffffu, old, 0);
-                if (old == nparts - 1) {
-                    __threadfence();
-                    // last arriver: merge.  lane owns channels 4*lane .. 4*lane+3 of every head row
-                    for (int hg = 0; hg < G; ++hg) {
-                        float M = -INFINITY;
-                        for (long long x = P0; x < P1;) {
-                            const long long w = warp_of(x);
-                            const long long s2 = 2 * w + ((w * total / W) <= P0 ? 1 : 0);
-                            M = fmaxf(M, __ldcg(p.partials + s2 * p.rec_floats + G * NCKV_D + hg));
-                            x = (w + 1) * total / W;
-                        }
-                        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                        float L = 0.f;
-                        for (long long x = P0; x < P1;) {
-                            const long long w = warp_of(x);
-                            const long long s2 = 2 * w + ((w * total / W) <= P0 ? 1 : 0);
-                            const float *r2 = p.partials + s2 * p.rec_floats;
-                            const float sc = exp2f(__ldcg(r2 + G * NCKV_D + hg) - M);
-                            L += sc * __ldcg(r2 + G * NCKV_D + G + hg);
-                            const float4 v = __ldcg(reinterpret_cast<const float4 *>(r2 + hg * NCKV_D) + lane);
-                            acc.x += sc * v.x; acc.y += sc * v.y; acc.z += sc * v.z; acc.w += sc * v.w;
-                            x = (w + 1) * total / W;
-                        }
-                        const float inv = 1.f / L;
-                        acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
-                        const long long o = (row_base + hg) * NCKV_D + lane * 4;
-                        uint2 packed;
-                        packed.x = pack_bf16x2(acc.x, acc.y);
-                        packed.y = pack_bf16x2(acc.z, acc.w);
-                        *reinterpret_cast<uint2 *>(p.out + o) = packed;
-                        if (p.out_f32) *reinterpret_cast<float4 *>(p.out_f32 + o) = acc;
-                        if (p.lse && lane == 0) p.lse[row_base + hg] = (M + log2f(L)) * 0.69314718055994531f;
-                    }
-                    if (lane == 0) p.counters[pair] = 0;
-                }
+                if (n_pend == 0) pend0 = cons.b * Hkv + cons.h; else pend1 = cons.b * Hkv + cons.h;
+                ++n_pend;
             }
+#ifdef NCKV_TIMELINE
+            { unsigned long long tf1; TL_NOW(tf1); tl_fin += tf1 - tf0s; }
+#endif
         }
         cursor_advance(cons, s_pref, B, Hkv);
     }
+#ifdef NCKV_TIMELINE
+    unsigned long long tf2; TL_NOW(tf2);
+#endif
+    // ---- deferred arrivals: publish my partial records, merge the pairs I complete ---------------
+    if (n_pend > 0 && !timed_out) {
+        __syncwarp();
+        if (lane == 0) __threadfence();  // cumulative: orders the whole warp's record stores (after the barrier)
+        __syncwarp();
+        for (int e = 0; e < n_pend; ++e) {
+            const int pair = e == 0 ? pend0 : pend1;
+            const int pb = pair / Hkv, ph = pair - pb * Hkv;
+            const int nt = s_pref[pb + 1] - s_pref[pb];
+            const int P0 = Hkv * s_pref[pb] + ph * nt;
+            const int w_first = warp_of(P0), w_last = warp_of(P0 + nt - 1);
+            const int nparts = w_last - w_first + 1;  // non-empty slices are contiguous in w
+            int old = 0;
+            if (lane == 0) old = atomicAdd(&p.counters[pair], 1);
+            old = __shfl_sync(0xffffffffu, old, 0);
+            if (old != nparts - 1) continue;
+            // last arriver: log-sum-exp merge.  Lane i looks after parts i, i+32, ...; for the
+            // O rows every lane owns channels 4*lane .. 4*lane+3.
+            __threadfence();
+            const long long row_base = (long long)pb * p.Hq + (long long)ph * G;
+            for (int hg = 0; hg < G; ++hg) {
+                float mloc = -INFINITY;
+                for (int i = lane; i < nparts; i += 32) {
+                    const int w = w_first + i;
+                    const float *r2 = p.partials + (long long)(2 * w + (slice_lo(w) <= P0 ? 1 : 0)) * p.rec_floats;
+                    mloc = fmaxf(mloc, __ldcg(r2 + G * NCKV_D + hg));
+                }
+#pragma unroll
+                for (int off = 16; off >= 1; off >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, off));
+                const float M = mloc;
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                float Lloc = 0.f;
+                for (int base = 0; base < nparts; base += 32) {
+                    const int i = base + lane;
+                    float sc = 0.f;
+                    int my_slot = 0;
+                    if (i < nparts) {
+                        const int w = w_first + i;
+                        my_slot = 2 * w + (slice_lo(w) <= P0 ? 1 : 0);
+                        const float *r2 = p.partials + (long long)my_slot * p.rec_floats;
+                        sc = exp2f(__ldcg(r2 + G * NCKV_D + hg) - M);
+                        Lloc += sc * __ldcg(r2 + G * NCKV_D + G + hg);
+                    }
+                    const int cnt = min(32, nparts - base);
+#pragma unroll 4
+                    for (int jn = 0; jn < cnt; ++jn) {
+                        const float s_j = __shfl_sync(0xffffffffu, sc, jn);
+                        const int slot_j = __shfl_sync(0xffffffffu, my_slot, jn);
+                        const float4 v = __ldcg(reinterpret_cast<const float4 *>(p.partials + (long long)slot_j * p.rec_floats + hg * NCKV_D) + lane);
+                        acc.x = fmaf(s_j, v.x, acc.x); acc.y = fmaf(s_j, v.y, acc.y);
+                        acc.z = fmaf(s_j, v.z, acc.z); acc.w = fmaf(s_j, v.w, acc.w);
+                    }
+                }
+#pragma unroll
+                for (int off = 16; off >= 1; off >>= 1) Lloc += __shfl_xor_sync(0xffffffffu, Lloc, off);
+                const float inv = 1.f / Lloc;
+                acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+                const long long o = (row_base + hg) * NCKV_D + lane * 4;
+                uint2 packed;
+                packed.x = pack_bf16x2(acc.x, acc.y);
+                packed.y = pack_bf16x2(acc.z, acc.w);
+                *reinterpret_cast<uint2 *>(p.out + o) = packed;
+                if (p.out_f32) *reinterpret_cast<float4 *>(p.out_f32 + o) = acc;
+                if (p.lse && lane == 0) p.lse[row_base + hg] = (M + log2f(Lloc)) * 0.69314718055994531f;
+            }
+            if (lane == 0) p.counters[pair] = 0;
+        }
+    }
+    TL_STAMP(5);
+#ifdef NCKV_TIMELINE
+    if (lane == 0) { unsigned long long tf3; TL_NOW(tf3); tl[6] = tl_fin + (tf3 - tf2); tl[7] = (unsigned long long)n_my; }
+#endif
 
     if (timed_out) {
         if (lane == 0) atomicOr(p.status, (int)NCKV_ST_TIMEOUT);
@@ -479,9 +544,17 @@ static size_t ws_partial_bytes(int G) {
     return (size_t)2 * sm_count() * DEC_WARPS * (size_t)rec_floats_for(G) * sizeof(float);
 }
 
+#ifdef NCKV_TIMELINE
+static unsigned long long *g_timeline = nullptr;
+#endif
+
 }  // namespace nckv
 
 extern "C" {
+
+#ifdef NCKV_TIMELINE
+NCKV_API void nckv_debug_set_timeline(void *ptr) { nckv::g_timeline = static_cast<unsigned long long *>(ptr); }
+#endif
 
 size_t nckv_workspace_bytes(int B, int Hq, int Hkv, int D) {
     using namespace nckv;
@@ -520,6 +593,10 @@ int nckv_decode_attn(const void *q, const void *k_cache, const void *v_cache,
         set_error("decode_attn: q/out/workspace must be 16-byte aligned");
         return NCKV_E_ARG;
     }
+    if ((long long)B * Hkv * ((T_max + DEC_TILE - 1) / DEC_TILE) >= (1LL << 31) / (sm_count() * DEC_WARPS)) {
+        set_error("decode_attn: B*Hkv*T_max too large for 32-bit tile arithmetic");
+        return NCKV_E_UNSUPPORTED;
+    }
     const size_t need = nckv_workspace_bytes(B, Hq, Hkv, D);
     if (workspace_bytes < need) {
         set_error("decode_attn: workspace of %zu bytes given, %zu needed", workspace_bytes, need);
@@ -549,6 +626,9 @@ int nckv_decode_attn(const void *q, const void *k_cache, const void *v_cache,
     p.kv_end = kv_end;
     p.rec_floats = rec_floats_for(G);
     p.scale_log2 = (float)(1.4426950408889634 / sqrt((double)D));
+#ifdef NCKV_TIMELINE
+    p.timeline = g_timeline;
+#endif
 
     const size_t smem = decode_smem_bytes();
     static bool attr_set[64][2] = {{false}};
