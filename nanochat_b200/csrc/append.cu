@@ -108,6 +108,11 @@ __device__ __forceinline__ uint4 rope_norm_scale(const uint4 &xin, const uint4 &
 }
 
 __global__ void __launch_bounds__(256) append_rope_norm_kernel(const AppendParams p) {
+    // Programmatic dependent launch: this grid may have been scheduled while its predecessor was
+    // still running; its inputs come from that predecessor, so wait first.  The attention kernel
+    // that follows may be scheduled right away (it waits for this grid before reading the cache).
+    pdl_wait_prior_grids();
+    pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
     const int j = lane & 15;
     const int heads_per_tok = (p.q_in ? p.Hq : 0) + 2 * p.Hkv;
@@ -204,8 +209,17 @@ static int launch_append(const AppendParams &p, cudaStream_t stream) {
     long long blocks = (rows + 15) / 16;
     const long long cap = (long long)sm_count() * 8 * 4;       // grid-stride beyond this
     if (blocks > cap) blocks = cap;
-    append_rope_norm_kernel<<<(unsigned)blocks, threads, 0, stream>>>(p);
-    NCKV_CUDA_CHECK(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)blocks);
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    NCKV_CUDA_CHECK(cudaLaunchKernelEx(&cfg, append_rope_norm_kernel, p));
     return NCKV_OK;
 }
 

@@ -2,22 +2,31 @@
 //
 // Work decomposition.  Keys of row b are cut into tiles of DEC_TILE tokens starting at the first
 // visible key; the tiles of all (row, kv-head) pairs form one flat sequence (row outer, head
-// middle, tile inner).  Every WARP of the persistent grid (one CTA per SM) takes an equal,
-// contiguous slice of that sequence, so ragged cache_seqlens balance to within one tile.  A warp
-// is a self-contained stream processor: lane 0 issues TMA tile loads (K and V, 128-byte swizzle)
-// into the warp's private ring of DEC_STAGES shared-memory stages, completion is signalled on
-// the warp's own mbarriers, and the loads run ahead across pair boundaries.  There is no CTA-wide
-// synchronisation after set-up.
+// middle, tile inner) of `total` tiles.  The sequence is handed out as RUNS of consecutive tiles:
+//   * the sequence is cut into one equal slice per warp of the persistent grid (one CTA per SM,
+//     DEC_WARPS warps each); the first 70% of a slice is that warp's static run, so a warp starts
+//     without any global traffic;
+//   * the last 30% of every slice is cut into small runs that warps claim from an atomic ticket counter (drawn one
+//     run ahead, so the round trip is hidden) when they finish what they have.  SMs do not all
+//     see the same HBM bandwidth (two dies, distance to the stacks); the dynamic part lets the
+//     fast ones absorb the difference.
+// A warp is a self-contained stream processor: lane 0 issues TMA tile loads (K and V, 128-byte
+// swizzle, L2 evict-first) into the warp's private ring of DEC_STAGES shared-memory stages,
+// completion is signalled on the warp's own mbarriers, and the loads run ahead across pair and
+// run boundaries.  There is no CTA-wide synchronisation after set-up and no fence or wait on
+// another warp anywhere in the stream.
 //
 // Math per tile.  All G = Hq/Hkv query heads that share a kv head are the rows of one
 // m16n8k16 tile (rows >= G are zero), so K/V bytes are read once per group.  S = Q K^T and
 // O += P V use the warp-level bf16 MMA with fp32 accumulation; running max / sum use quad
 // shuffles; P is rounded to bf16 for the second product, as the flash-style library kernels do.
 //
-// Combine.  A pair whose tiles all fall inside one warp's slice is normalised and written
-// directly.  Otherwise each warp writes an un-normalised partial (O, m, l) to the workspace and
-// bumps the pair's arrival counter; the last warp to arrive merges the partials with a
-// log-sum-exp and resets the counter.  Nothing ever waits on another warp.
+// Combine.  A pair whose tiles all fall inside one run is normalised and written directly.
+// Otherwise every run that touches the pair leaves an un-normalised partial (O, m, l) in the
+// workspace; which runs exist is a pure function of cache_seqlens, so a second, tiny kernel
+// (decode_merge_kernel, one warp per (row, q head)) recomputes the cut and merges the partials
+// with a log-sum-exp.  It is launched with programmatic dependent launch: its set-up overlaps the
+// tail of the streaming kernel.
 //
 // Replaces: flash_attention.py:83-89 (Tq == 1 branch of _sdpa_attention) reached through
 // flash_attention.py:165-177, with the per-row cache_seqlens contract of flash_attention.py:142.
@@ -33,7 +42,12 @@ constexpr int DEC_WARPS = 4;    // warps (independent streams) per CTA
 constexpr int DEC_MAX_B = 1024; // rows per launch (bounds the shared-memory row tables)
 constexpr int DEC_HALF_BYTES = DEC_TILE * 128;        // one 64-channel half of a K or V tile
 constexpr int DEC_STAGE_BYTES = 4 * DEC_HALF_BYTES;   // K lo, K hi, V lo, V hi
-constexpr int DEC_STATUS_BYTES = 256;
+constexpr int DEC_STATUS_BYTES = 256;                 // status word, then the ticket counter at +16
+constexpr int DEC_RING = 4;                           // runs a warp may have claimed but not finished
+constexpr int DEC_DYN_PER_WARP = 4;                   // at most this many dynamic runs per warp of the grid
+constexpr int DEC_STATIC_NUM = 7, DEC_STATIC_DEN = 10; // statically assigned fraction of the tiles
+constexpr int MERGE_WARPS = 8;
+constexpr int MERGE_PLAN = 4;  // chunks of 32 parts whose record slots a merge warp works out ahead of time
 
 struct DecodeParams {
     const __nv_bfloat16 *q;
@@ -42,19 +56,25 @@ struct DecodeParams {
     float *out_f32;
     float *lse;
     int32_t *status;
-    int32_t *counters;  // one per (row, kv head); zero on entry, zero on exit
-    float *partials;    // 2 records per warp of the grid, rec_floats each
+    int32_t *run_counter;  // dynamic run tickets; zero on entry, zero on exit
+    float *partials;       // 2 records per run, rec_floats each
     int B, Hq, Hkv, G, T_max;
     int seqlen_offset, window_left, kv_begin, kv_end;
     int rec_floats;
+    int W;                 // warps of the streaming grid (the run geometry depends on it)
     float scale_log2;
 #ifdef NCKV_TIMELINE
-    unsigned long long *timeline;  // 8 stamps per warp of the grid (debug builds only)
+    unsigned long long *timeline;  // 16 stamps per warp of the grid (debug builds only)
 #endif
 };
 
 struct TileCursor {
     int b, h, j, nt;
+};
+
+struct RunEntry {  // one claimed run, handed from the issuing side of a warp to its consuming side
+    int k, n;      // run id, tiles
+    TileCursor start;
 };
 
 __device__ __forceinline__ void cursor_advance(TileCursor &c, const int *s_pref, int B, int Hkv) {
@@ -68,53 +88,103 @@ __device__ __forceinline__ void cursor_advance(TileCursor &c, const int *s_pref,
     c.nt = b < B ? s_pref[b + 1] - s_pref[b] : 0;
 }
 
-// Largest b with Hkv * pref[b] <= x; the row it names always owns tile x.
-__device__ __forceinline__ int find_row(const int *s_pref, int B, int Hkv, int x) {
+// Cursor of flat tile index x: the row is the largest b with Hkv * pref[b] <= x.
+__device__ __forceinline__ TileCursor locate_tile(const int *s_pref, int B, int Hkv, int x) {
     int lo = 0, hi = B;  // invariant: Hkv*pref[lo] <= x < Hkv*pref[hi]
     while (hi - lo > 1) {
         int mid = (lo + hi) >> 1;
         if (Hkv * s_pref[mid] <= x) lo = mid; else hi = mid;
     }
-    return lo;
+    TileCursor c;
+    c.b = lo;
+    c.nt = s_pref[lo + 1] - s_pref[lo];
+    const int rel = x - Hkv * s_pref[lo];
+    c.h = rel / c.nt;
+    c.j = rel - c.h * c.nt;
+    return c;
 }
 
-template <bool GHI>  // GHI: group size 9..16 (rows 8..15 of the MMA tile carry heads too)
-__global__ void __launch_bounds__(DEC_WARPS * 32, 1)
-decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
-                   const __grid_constant__ CUtensorMap tmap_v, const DecodeParams p) {
-    extern __shared__ uint8_t smem_raw[];
-    // 1024-byte alignment: the 128-byte swizzle pattern is a function of address bits 4..9
-    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                                ~static_cast<uintptr_t>(1023));
-    uint8_t *stages = smem;  // [DEC_WARPS][DEC_STAGES][DEC_STAGE_BYTES]
-    uint64_t *full_bar = reinterpret_cast<uint64_t *>(stages + DEC_WARPS * DEC_STAGES * DEC_STAGE_BYTES);
-    int *s_start = reinterpret_cast<int *>(full_bar + DEC_WARPS * DEC_STAGES);
-    int *s_end = s_start + DEC_MAX_B;
-    int *s_pref = s_end + DEC_MAX_B;  // B + 1 entries
+// How the flat tile sequence [0, total) is cut into runs.  A pure function of (total, W), so the
+// streaming kernel and the merge kernel agree on it.
+//   slice w (w < W) = q + (w < r) consecutive tiles, q = total / W, r = total % W
+//   static run w    = the first 70% of slice w (all of it when the slice is shorter than 4 tiles)
+//   dynamic runs    = the rest of each slice in chunks of CH tiles, numbered in tile order
+// Interleaving static and dynamic stretches keeps the number of runs that touch any one
+// (row, head) pair small, which bounds the work of the merge.
+struct RunGeometry {
+    int total, W;
+    int q, r;            // slice lengths
+    int s_big, s_small;  // static tiles of a slice of q+1 / q tiles
+    int d_big, d_small;  // dynamic runs of a slice of q+1 / q tiles
+    int CH, n_dyn;
 
-    const int tid = threadIdx.x;
-    const int warp = tid >> 5;
-    const int lane = tid & 31;
-    const int B = p.B, Hkv = p.Hkv, G = p.G;
-#ifdef NCKV_TIMELINE
-    unsigned long long *tl = p.timeline + ((long long)blockIdx.x * DEC_WARPS + warp) * 8;
-    unsigned long long tl_fin = 0;
-#define TL_STAMP(i) do { if (lane == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); tl[i] = t_; } } while (0)
-#define TL_NOW(v) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(v))
-    TL_STAMP(0);
-#else
-#define TL_STAMP(i)
-#endif
+    __device__ __forceinline__ static int static_part(int n) { return n < 4 ? n : (n * DEC_STATIC_NUM) / DEC_STATIC_DEN; }
+    __device__ __forceinline__ void init(int total_, int W_) {
+        total = total_;
+        W = W_;
+        q = total / W;
+        r = total - q * W;
+        s_big = static_part(q + 1);
+        s_small = static_part(q);
+        const int tail = (q + 1) - s_big;  // the longest dynamic stretch
+        CH = max(2, (tail + DEC_DYN_PER_WARP - 1) / DEC_DYN_PER_WARP);
+        d_big = (q + 1 - s_big + CH - 1) / CH;
+        d_small = (q - s_small + CH - 1) / CH;
+        n_dyn = r * d_big + (W - r) * d_small;
+    }
+    __device__ __forceinline__ int slice_lo(int w) const { return w * q + min(w, r); }
+    __device__ __forceinline__ int slice_len(int w) const { return q + (w < r ? 1 : 0); }
+    __device__ __forceinline__ int slice_of(int x) const {
+        const int big = r * (q + 1);
+        return x < big ? x / (q + 1) : r + (x - big) / q;
+    }
+    // dynamic run id k >= W  ->  (slice, chunk within the slice's dynamic stretch)
+    __device__ __forceinline__ void dyn_split(int k, int &w, int &c) const {
+        const int idx = k - W;
+        const int big = r * d_big;
+        if (idx < big) {
+            w = idx / d_big;
+            c = idx - w * d_big;
+        } else {
+            w = r + (idx - big) / d_small;
+            c = (idx - big) - (w - r) * d_small;
+        }
+    }
+    __device__ __forceinline__ void run_range(int k, int &lo, int &len) const {
+        if (k < W) {
+            lo = slice_lo(k);
+            len = k < r ? s_big : s_small;
+            return;
+        }
+        int w, c;
+        dyn_split(k, w, c);
+        const int st = w < r ? s_big : s_small;
+        lo = slice_lo(w) + st + c * CH;
+        len = min(CH, slice_len(w) - st - c * CH);
+    }
+    __device__ __forceinline__ int run_of(int x) const {  // the run that holds tile x
+        const int w = slice_of(x);
+        const int off = x - slice_lo(w);
+        const int st = w < r ? s_big : s_small;
+        if (off < st) return w;
+        const int c = (off - st) / CH;
+        return W + (w < r ? w * d_big : r * d_big + (w - r) * d_small) + c;
+    }
+};
 
-    // ---- set-up: per-row visible key range and tile counts --------------------------------
+// Per-row visible key range [s_start, s_end) and the exclusive prefix sum of tiles per row
+// (s_pref, B + 1 entries), computed by a whole CTA.  Ends with a __syncthreads().
+__device__ __forceinline__ void build_row_tables(const DecodeParams &p, int *s_start, int *s_end, int *s_pref,
+                                                 bool report) {
+    const int tid = threadIdx.x, lane = tid & 31, B = p.B;
     for (int b = tid; b < B; b += blockDim.x) {
         int n = p.seqlens[b] + p.seqlen_offset;
         if (n < 0) {
-            if (blockIdx.x == 0) atomicOr(p.status, (int)NCKV_ST_BAD_SEQLEN);
+            if (report) atomicOr(p.status, (int)NCKV_ST_BAD_SEQLEN);
             n = 0;
         }
         if (n > p.T_max) {
-            if (blockIdx.x == 0) atomicOr(p.status, (int)NCKV_ST_OVERFLOW);
+            if (report) atomicOr(p.status, (int)NCKV_ST_OVERFLOW);
             n = p.T_max;
         }
         int lo = 0, hi = n;
@@ -127,14 +197,8 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
         s_start[b] = lo;
         s_end[b] = hi;
     }
-    if (tid == 0) {
-        for (int i = 0; i < DEC_WARPS * DEC_STAGES; ++i) mbar_init(&full_bar[i], 1);
-        fence_mbar_init();
-        prefetch_tensormap(&tmap_k);
-        prefetch_tensormap(&tmap_v);
-    }
     __syncthreads();
-    if (warp == 0) {  // exclusive prefix sum of tiles per row
+    if (tid < 32) {  // exclusive prefix sum of tiles per row
         const int per = (B + 31) / 32;
         const int b0 = lane * per;
         int local = 0;
@@ -159,6 +223,58 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
         if (lane == 31) s_pref[B] = incl;
     }
     __syncthreads();
+}
+
+#ifdef NCKV_TIMELINE
+#define TL_STAMP(i) do { if (lane == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); tl[i] = t_; } } while (0)
+#else
+#define TL_STAMP(i)
+#endif
+
+template <bool GHI>  // GHI: group size 9..16 (rows 8..15 of the MMA tile carry heads too)
+__global__ void __launch_bounds__(DEC_WARPS * 32, 1)
+decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
+                   const __grid_constant__ CUtensorMap tmap_v, const DecodeParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    // 1024-byte alignment: the 128-byte swizzle pattern is a function of address bits 4..9
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                                ~static_cast<uintptr_t>(1023));
+    uint8_t *stages = smem;  // [DEC_WARPS][DEC_STAGES][DEC_STAGE_BYTES]
+    uint64_t *full_bar = reinterpret_cast<uint64_t *>(stages + DEC_WARPS * DEC_STAGES * DEC_STAGE_BYTES);
+    RunEntry *rings = reinterpret_cast<RunEntry *>(full_bar + DEC_WARPS * DEC_STAGES);  // [DEC_WARPS][DEC_RING]
+    int *s_start = reinterpret_cast<int *>(rings + DEC_WARPS * DEC_RING);
+    int *s_end = s_start + DEC_MAX_B;
+    int *s_pref = s_end + DEC_MAX_B;  // B + 1 entries
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+    const int B = p.B, Hkv = p.Hkv, G = p.G;
+#ifdef NCKV_TIMELINE
+    unsigned long long *tl = p.timeline + ((long long)blockIdx.x * DEC_WARPS + warp) * 16;
+    long long tl_segend = 0;
+    int tl_tiles = 0, tl_runs = 0;
+    TL_STAMP(0);
+#endif
+
+    // ---- set-up ---------------------------------------------------------------------------------
+    if (tid == 0) {
+        prefetch_tensormap(&tmap_k);
+        prefetch_tensormap(&tmap_v);
+        for (int i = 0; i < DEC_WARPS * DEC_STAGES; ++i) mbar_init(&full_bar[i], 1);
+        fence_mbar_init();
+    }
+    // Everything from here on may depend on the kernel right before this one in the stream
+    // (cache_seqlens, q, the appended K/V rows): wait for it.  Only the launch itself and the
+    // lines above overlap its tail.
+    pdl_wait_prior_grids();
+    build_row_tables(p, s_start, s_end, s_pref, blockIdx.x == 0);
+    pdl_launch_dependents();  // the merge kernel may be scheduled and run its own set-up now
+    TL_STAMP(1);
+
+    RunGeometry geo;
+    geo.init(Hkv * s_pref[B], p.W);
+    const int gw = blockIdx.x * DEC_WARPS + warp;
 
     // rows without any visible key: zero output, lse = -inf (only sharded calls can produce them)
     for (int b = blockIdx.x; b < B; b += gridDim.x) {
@@ -170,74 +286,115 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
         }
         if (p.lse) for (int i = tid; i < p.Hq; i += blockDim.x) p.lse[(long long)b * p.Hq + i] = -INFINITY;
     }
-
-    TL_STAMP(1);
-    // Slices: with q = total / W and r = total % W, warp w owns q + (w < r) consecutive tiles
-    // starting at w*q + min(w, r).  Everything is 32-bit (the host bounds total below 2^31).
-    const int total = Hkv * s_pref[B];
-    if (total == 0) return;
-    const int W = gridDim.x * DEC_WARPS;
-    const int gw = blockIdx.x * DEC_WARPS + warp;
-    const int sl_q = total / W, sl_r = total % W;
-    const int lo_tile = gw * sl_q + min(gw, sl_r);
-    const int n_my = sl_q + (gw < sl_r ? 1 : 0);
-    if (n_my == 0) return;
-    auto slice_lo = [&](int w) { return w * sl_q + min(w, sl_r); };
-    auto warp_of = [&](int x) {  // the warp whose slice holds tile x
-        const int big = sl_r * (sl_q + 1);
-        return x < big ? x / (sl_q + 1) : sl_r + (x - big) / sl_q;
-    };
+    if (geo.total == 0) return;  // every warp of the grid takes this exit together
 
     uint8_t *my_stages = stages + warp * DEC_STAGES * DEC_STAGE_BYTES;
     uint64_t *my_bar = full_bar + warp * DEC_STAGES;
+    RunEntry *my_ring = rings + warp * DEC_RING;
+    const uint64_t kv_policy = l2_policy_evict_first();
 
-    TileCursor cons;
-    cons.b = find_row(s_pref, B, Hkv, lo_tile);
-    cons.nt = s_pref[cons.b + 1] - s_pref[cons.b];
-    {
-        const int rel = lo_tile - Hkv * s_pref[cons.b];
-        cons.h = rel / cons.nt;
-        cons.j = rel - cons.h * cons.nt;
-    }
-    TileCursor prod = cons;
+    // ---- issuing side: claims runs, keeps DEC_STAGES tile loads in flight --------------------
+    TileCursor prod = {0, 0, 0, 0};
+    int prod_left = 0;       // tiles of the current run not yet issued
+    int ring_push = 0, ring_pop = 0;
+    int issue_idx = 0;       // tiles issued so far (stage = idx % DEC_STAGES)
+    bool first_claim = true, sched_done = false;
+    int next_ticket = 0;     // lane 0 only: a dynamic ticket drawn ahead of need, so its latency is hidden
 
-    auto issue_tile = [&](const TileCursor &c, int stage) {
-        // lane 0 only
-        uint8_t *dst = my_stages + stage * DEC_STAGE_BYTES;
-        uint64_t *bar = &my_bar[stage];
-        const int key0 = s_start[c.b] + c.j * DEC_TILE;
-        fence_proxy_async_smem();
-        mbar_arrive_expect_tx(bar, DEC_STAGE_BYTES);
-        tma_load_4d(dst, &tmap_k, bar, 0, c.h, key0, c.b);
-        tma_load_4d(dst + DEC_HALF_BYTES, &tmap_k, bar, 64, c.h, key0, c.b);
-        tma_load_4d(dst + 2 * DEC_HALF_BYTES, &tmap_v, bar, 0, c.h, key0, c.b);
-        tma_load_4d(dst + 3 * DEC_HALF_BYTES, &tmap_v, bar, 64, c.h, key0, c.b);
+    auto claim_run = [&]() -> int {  // next run id for this warp; >= W + n_dyn means "no more"
+        if (first_claim) {
+            first_claim = false;
+            if (lane == 0) next_ticket = atomicAdd(p.run_counter, 1);
+            return gw;
+        }
+        const int t = __shfl_sync(0xffffffffu, next_ticket, 0);
+        // Tickets n_dyn .. n_dyn + W - 1 are the W terminating ones, one per warp (a warp stops
+        // drawing at its first); whoever holds the last knows nobody will draw again and re-arms
+        // the counter for the next launch.
+        if (t < geo.n_dyn) {
+            if (lane == 0) next_ticket = atomicAdd(p.run_counter, 1);
+        } else if (t == geo.n_dyn + geo.W - 1 && lane == 0) {
+            *p.run_counter = 0;
+        }
+        return geo.W + t;
     };
 
-    int issued = 0;
-    for (; issued < DEC_STAGES && issued < n_my; ++issued) {
-        if (lane == 0) issue_tile(prod, issued);
+    auto issue_one = [&]() -> bool {  // issue the next tile load if there is one
+        if (prod_left == 0) {
+            if (sched_done) return false;
+            int k, n, run_lo;
+            for (;;) {
+                k = claim_run();
+                if (k >= geo.W + geo.n_dyn) {
+                    sched_done = true;
+                    return false;
+                }
+                geo.run_range(k, run_lo, n);
+                if (n > 0) break;  // only a static run can be empty (fewer tiles than warps)
+            }
+            prod = locate_tile(s_pref, B, Hkv, run_lo);
+            prod_left = n;
+            if (lane == 0) {
+                RunEntry e;
+                e.k = k; e.n = n; e.start = prod;
+                my_ring[ring_push % DEC_RING] = e;
+            }
+            ++ring_push;
+            __syncwarp();
+        }
+        if (lane == 0) {
+            const int stage = issue_idx % DEC_STAGES;
+            uint8_t *dst = my_stages + stage * DEC_STAGE_BYTES;
+            uint64_t *bar = &my_bar[stage];
+            const int key0 = s_start[prod.b] + prod.j * DEC_TILE;
+            fence_proxy_async_smem();
+            mbar_arrive_expect_tx(bar, DEC_STAGE_BYTES);
+            // K/V bytes are used once: evict-first keeps them from flushing q and the partial
+            // records out of L2
+            tma_load_4d_hint(dst, &tmap_k, bar, 0, prod.h, key0, prod.b, kv_policy);
+            tma_load_4d_hint(dst + DEC_HALF_BYTES, &tmap_k, bar, 64, prod.h, key0, prod.b, kv_policy);
+            tma_load_4d_hint(dst + 2 * DEC_HALF_BYTES, &tmap_v, bar, 0, prod.h, key0, prod.b, kv_policy);
+            tma_load_4d_hint(dst + 3 * DEC_HALF_BYTES, &tmap_v, bar, 64, prod.h, key0, prod.b, kv_policy);
+        }
+        ++issue_idx;
+        --prod_left;
         cursor_advance(prod, s_pref, B, Hkv);
-    }
+        return true;
+    };
 
+    while (issue_idx < DEC_STAGES && issue_one()) {
+    }
     TL_STAMP(2);
+
+    // ---- consuming side -----------------------------------------------------------------------
     const int g = lane >> 2;  // MMA row within 8 (query head within the group)
     const int t4 = lane & 3;
     uint32_t qa[8][GHI ? 4 : 2];  // A fragments of Q for the 8 k-steps over D
     float o_acc[16][4];
     float m_run[2] = {-INFINITY, -INFINITY};
     float l_run[2] = {0.f, 0.f};
+    TileCursor cons = {0, 0, 0, 0};
+    int cons_left = 0, cons_k = 0;
+    int cons_idx = 0;
     int seg_j0 = 0;
-    bool timed_out = false;
-    int pend0 = 0, pend1 = 0, n_pend = 0;  // pairs whose partial record awaits its arrival (at most 2 per slice)
-#ifdef NCKV_TIMELINE
-    unsigned long long tf0s = 0;
-#endif
+    bool run_begin = false, timed_out = false;
 
-    for (int it = 0; it < n_my; ++it) {
-        const int stage = it % DEC_STAGES;
-        const uint32_t parity = (uint32_t)((it / DEC_STAGES) & 1);
-        const bool seg_begin = (it == 0) || (cons.j == 0);
+    while (cons_idx < issue_idx) {
+        if (cons_left == 0) {
+            const RunEntry e = my_ring[ring_pop % DEC_RING];
+            ++ring_pop;
+            cons = e.start;
+            cons_k = e.k;
+            cons_left = e.n;
+            run_begin = true;
+#ifdef NCKV_TIMELINE
+            ++tl_runs;
+#endif
+        }
+        const int stage = cons_idx % DEC_STAGES;
+        const uint32_t parity = (uint32_t)((cons_idx / DEC_STAGES) & 1);
+        const bool seg_begin = run_begin || (cons.j == 0);
+        run_begin = false;
         if (seg_begin) {
             seg_j0 = cons.j;
             m_run[0] = m_run[1] = -INFINITY;
@@ -253,8 +410,8 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
                 qa[kk][1] = g < G ? __ldg(r0 + 4) : 0u;
                 if (GHI) {
                     const uint32_t *r1 = reinterpret_cast<const uint32_t *>(qrow + (long long)(g + 8) * NCKV_D + kk * 16 + 2 * t4);
-                    qa[kk][2] = (g + 8) < G ? __ldg(r1) : 0u;
-                    qa[kk][3] = (g + 8) < G ? __ldg(r1 + 4) : 0u;
+                    qa[kk][GHI ? 2 : 0] = (g + 8) < G ? __ldg(r1) : 0u;
+                    qa[kk][GHI ? 3 : 1] = (g + 8) < G ? __ldg(r1 + 4) : 0u;
                 }
             }
         }
@@ -263,10 +420,11 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
             timed_out = true;
             break;
         }
-
 #ifdef NCKV_TIMELINE
-        if (it == 0) TL_STAMP(3);
+        if (cons_idx == 0) TL_STAMP(3);
+        ++tl_tiles;
 #endif
+
         const uint32_t kbase = smem_u32(my_stages + stage * DEC_STAGE_BYTES);
         const uint32_t vbase = kbase + 2 * DEC_HALF_BYTES;
         const int key0 = s_start[cons.b] + cons.j * DEC_TILE;
@@ -375,20 +533,17 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
             }
         }
 
-        // ---- this stage is free again: fetch the tile DEC_STAGES ahead ----
+        // ---- this stage is free again: keep the ring of loads full ----
+        ++cons_idx;
+        --cons_left;
         __syncwarp();
-        if (issued < n_my) {
-            if (lane == 0) issue_tile(prod, stage);
-            cursor_advance(prod, s_pref, B, Hkv);
-            ++issued;
-        }
+        issue_one();
 
-        // ---- end of this pair's run inside my slice? ----
-        const bool seg_end = (it == n_my - 1) || (cons.j == cons.nt - 1);
+        // ---- end of this pair's stretch inside the run? ----
+        const bool seg_end = (cons_left == 0) || (cons.j == cons.nt - 1);
         if (seg_end) {
 #ifdef NCKV_TIMELINE
-            TL_NOW(tf0s);
-            if (it == n_my - 1) TL_STAMP(4);
+            const long long tc0 = clock64();
 #endif
             float l0 = l_run[0], l1 = l_run[1];
             l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
@@ -423,130 +578,208 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
                     if (GHI && g + 8 < G) p.lse[row_base + g + 8] = (m_run[1] + log2f(l1)) * 0.69314718055994531f;
                 }
             } else {
-                // partial record: [G][128] un-normalised O, then m[G], l[G].  The arrival on the
-                // pair's counter is deferred to the end of this warp's slice, so that no fence sits
-                // in the middle of the tile stream.
-                const int slot = 2 * gw + (seg_j0 == 0 ? 1 : 0);
+                // partial record: [G][128] un-normalised O, then m[G], l[G]; a run leaves at most
+                // two (one where it starts inside a pair, one where it ends inside a pair).  Plain
+                // stores: the merge kernel only runs after this grid has completed.
+                const int slot = 2 * cons_k + (seg_j0 == 0 ? 1 : 0);
                 float *rec = p.partials + (long long)slot * p.rec_floats;
 #pragma unroll
                 for (int nd = 0; nd < 16; ++nd) {
                     const int d = nd * 8 + 2 * t4;
-                    if (g < G) __stcg(reinterpret_cast<float2 *>(rec + g * NCKV_D + d), make_float2(o_acc[nd][0], o_acc[nd][1]));
+                    if (g < G) *reinterpret_cast<float2 *>(rec + g * NCKV_D + d) = make_float2(o_acc[nd][0], o_acc[nd][1]);
                     if (GHI && g + 8 < G)
-                        __stcg(reinterpret_cast<float2 *>(rec + (g + 8) * NCKV_D + d), make_float2(o_acc[nd][2], o_acc[nd][3]));
+                        *reinterpret_cast<float2 *>(rec + (g + 8) * NCKV_D + d) = make_float2(o_acc[nd][2], o_acc[nd][3]);
                 }
                 if (t4 == 0) {
-                    if (g < G) { __stcg(rec + G * NCKV_D + g, m_run[0]); __stcg(rec + G * NCKV_D + G + g, l0); }
-                    if (GHI && g + 8 < G) { __stcg(rec + G * NCKV_D + g + 8, m_run[1]); __stcg(rec + G * NCKV_D + G + g + 8, l1); }
+                    if (g < G) { rec[G * NCKV_D + g] = m_run[0]; rec[G * NCKV_D + G + g] = l0; }
+                    if (GHI && g + 8 < G) { rec[G * NCKV_D + g + 8] = m_run[1]; rec[G * NCKV_D + G + g + 8] = l1; }
                 }
-                if (n_pend == 0) pend0 = cons.b * Hkv + cons.h; else pend1 = cons.b * Hkv + cons.h;
-                ++n_pend;
             }
 #ifdef NCKV_TIMELINE
-            { unsigned long long tf1; TL_NOW(tf1); tl_fin += tf1 - tf0s; }
+            tl_segend += clock64() - tc0;
 #endif
         }
         cursor_advance(cons, s_pref, B, Hkv);
     }
-#ifdef NCKV_TIMELINE
-    unsigned long long tf2; TL_NOW(tf2);
-#endif
-    // ---- deferred arrivals: publish my partial records, merge the pairs I complete ---------------
-    if (n_pend > 0 && !timed_out) {
-        __syncwarp();
-        if (lane == 0) __threadfence();  // cumulative: orders the whole warp's record stores (after the barrier)
-        __syncwarp();
-        for (int e = 0; e < n_pend; ++e) {
-            const int pair = e == 0 ? pend0 : pend1;
-            const int pb = pair / Hkv, ph = pair - pb * Hkv;
-            const int nt = s_pref[pb + 1] - s_pref[pb];
-            const int P0 = Hkv * s_pref[pb] + ph * nt;
-            const int w_first = warp_of(P0), w_last = warp_of(P0 + nt - 1);
-            const int nparts = w_last - w_first + 1;  // non-empty slices are contiguous in w
-            int old = 0;
-            if (lane == 0) old = atomicAdd(&p.counters[pair], 1);
-            old = __shfl_sync(0xffffffffu, old, 0);
-            if (old != nparts - 1) continue;
-            // last arriver: log-sum-exp merge.  Lane i looks after parts i, i+32, ...; for the
-            // O rows every lane owns channels 4*lane .. 4*lane+3.
-            __threadfence();
-            const long long row_base = (long long)pb * p.Hq + (long long)ph * G;
-            for (int hg = 0; hg < G; ++hg) {
-                float mloc = -INFINITY;
-                for (int i = lane; i < nparts; i += 32) {
-                    const int w = w_first + i;
-                    const float *r2 = p.partials + (long long)(2 * w + (slice_lo(w) <= P0 ? 1 : 0)) * p.rec_floats;
-                    mloc = fmaxf(mloc, __ldcg(r2 + G * NCKV_D + hg));
-                }
-#pragma unroll
-                for (int off = 16; off >= 1; off >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, off));
-                const float M = mloc;
-                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                float Lloc = 0.f;
-                for (int base = 0; base < nparts; base += 32) {
-                    const int i = base + lane;
-                    float sc = 0.f;
-                    int my_slot = 0;
-                    if (i < nparts) {
-                        const int w = w_first + i;
-                        my_slot = 2 * w + (slice_lo(w) <= P0 ? 1 : 0);
-                        const float *r2 = p.partials + (long long)my_slot * p.rec_floats;
-                        sc = exp2f(__ldcg(r2 + G * NCKV_D + hg) - M);
-                        Lloc += sc * __ldcg(r2 + G * NCKV_D + G + hg);
-                    }
-                    const int cnt = min(32, nparts - base);
-#pragma unroll 4
-                    for (int jn = 0; jn < cnt; ++jn) {
-                        const float s_j = __shfl_sync(0xffffffffu, sc, jn);
-                        const int slot_j = __shfl_sync(0xffffffffu, my_slot, jn);
-                        const float4 v = __ldcg(reinterpret_cast<const float4 *>(p.partials + (long long)slot_j * p.rec_floats + hg * NCKV_D) + lane);
-                        acc.x = fmaf(s_j, v.x, acc.x); acc.y = fmaf(s_j, v.y, acc.y);
-                        acc.z = fmaf(s_j, v.z, acc.z); acc.w = fmaf(s_j, v.w, acc.w);
-                    }
-                }
-#pragma unroll
-                for (int off = 16; off >= 1; off >>= 1) Lloc += __shfl_xor_sync(0xffffffffu, Lloc, off);
-                const float inv = 1.f / Lloc;
-                acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
-                const long long o = (row_base + hg) * NCKV_D + lane * 4;
-                uint2 packed;
-                packed.x = pack_bf16x2(acc.x, acc.y);
-                packed.y = pack_bf16x2(acc.z, acc.w);
-                *reinterpret_cast<uint2 *>(p.out + o) = packed;
-                if (p.out_f32) *reinterpret_cast<float4 *>(p.out_f32 + o) = acc;
-                if (p.lse && lane == 0) p.lse[row_base + hg] = (M + log2f(Lloc)) * 0.69314718055994531f;
-            }
-            if (lane == 0) p.counters[pair] = 0;
-        }
-    }
     TL_STAMP(5);
 #ifdef NCKV_TIMELINE
-    if (lane == 0) { unsigned long long tf3; TL_NOW(tf3); tl[6] = tl_fin + (tf3 - tf2); tl[7] = (unsigned long long)n_my; }
+    if (lane == 0) { tl[6] = (unsigned long long)tl_segend; tl[7] = (unsigned long long)tl_tiles; tl[8] = (unsigned long long)tl_runs; }
 #endif
 
     if (timed_out) {
         if (lane == 0) atomicOr(p.status, (int)NCKV_ST_TIMEOUT);
         // give copies already issued a bounded chance to land before the CTA's memory is released
         for (int s = 0; s < DEC_STAGES; ++s) mbar_wait_bounded(&my_bar[s], 0, 1u << 12);
+        // leave the ticket counter consistent: draw (without working on them) until this warp
+        // has taken its terminating ticket
+        for (int guard = 0; !sched_done && guard < geo.n_dyn + geo.W + 1; ++guard) {
+            if (claim_run() >= geo.W + geo.n_dyn) sched_done = true;
+        }
     }
+}
+
+// Merge of the partial records: one warp per (row, q head).  Lane i looks after part base+i of a
+// chunk of 32 parts for the softmax statistics; for the O row every lane owns channels
+// 4*lane .. 4*lane+3.  Which records belong to a pair follows from cache_seqlens alone, so the
+// record slots of a warp's first item are worked out BEFORE the grid-dependency wait, while the
+// streaming kernel is still running; after the wait only loads, a few shuffles and the store remain.
+__global__ void __launch_bounds__(MERGE_WARPS * 32) decode_merge_kernel(const DecodeParams p) {
+    __shared__ int s_start[DEC_MAX_B], s_end[DEC_MAX_B], s_pref[DEC_MAX_B + 1];
+    const int lane = threadIdx.x & 31;
+    const int B = p.B, Hkv = p.Hkv, G = p.G;
+#ifdef NCKV_TIMELINE
+    unsigned long long *tl = p.timeline + (long long)p.W * 16 + blockIdx.x * 4;
+    if (threadIdx.x == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); tl[0] = t_; }
+#endif
+    pdl_launch_dependents();  // whatever follows in the stream may be scheduled behind this grid
+    // cache_seqlens is stable by now: the streaming kernel only lets this grid start after it has
+    // itself waited for its predecessor
+    build_row_tables(p, s_start, s_end, s_pref, false);
+    RunGeometry geo;
+    geo.init(Hkv * s_pref[B], p.W);
+    const int n_items = B * p.Hq;
+    const int first_item = blockIdx.x * MERGE_WARPS + (threadIdx.x >> 5);
+    const int item_stride = gridDim.x * MERGE_WARPS;
+
+    // Walks the runs that intersect the pair of `item`; lane i keeps the record slots of parts
+    // base + i, base + 32 + i, ... (MERGE_PLAN chunks of 32).  Returns the number of parts
+    // (0: nothing to merge).
+    auto plan = [&](int item, int base, int (&slots)[MERGE_PLAN], int &hg) -> int {
+        const int b = item / p.Hq, hq = item - b * p.Hq;
+        const int h = hq / G;
+        hg = hq - h * G;
+#pragma unroll
+        for (int c = 0; c < MERGE_PLAN; ++c) slots[c] = 0;
+        const int nt = s_pref[b + 1] - s_pref[b];
+        if (nt == 0) return 0;  // no visible key: the streaming kernel wrote zeros
+        const int P0 = Hkv * s_pref[b] + h * nt, P1 = P0 + nt;
+        int n = 0;
+        for (int x = P0; x < P1; ++n) {
+            const int k = geo.run_of(x);
+            int lo, len;
+            geo.run_range(k, lo, len);
+            const int rel = n - base - lane;
+#pragma unroll
+            for (int c = 0; c < MERGE_PLAN; ++c)
+                if (rel == 32 * c) slots[c] = 2 * k + (lo <= P0 ? 1 : 0);
+            x = lo + len;
+        }
+        return n == 1 ? 0 : n;  // a single run held the whole pair and wrote the output itself
+    };
+
+    int plan_slots[MERGE_PLAN], plan_hg = 0, plan_n = 0;
+    if (geo.total > 0 && first_item < n_items) plan_n = plan(first_item, 0, plan_slots, plan_hg);
+
+    pdl_wait_prior_grids();  // the streaming kernel has completed and its records are visible
+#ifdef NCKV_TIMELINE
+    if (threadIdx.x == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); tl[1] = t_; }
+#endif
+    if (geo.total == 0) return;
+
+    for (int item = first_item; item < n_items; item += item_stride) {
+        int hg = plan_hg, nparts = plan_n;
+        if (item != first_item) nparts = plan(item, 0, plan_slots, hg);
+        if (nparts == 0) continue;
+        float M = -INFINITY, L = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int base = 0; base < nparts; base += 32) {
+            if (base > 0 && (base / 32) % MERGE_PLAN == 0) plan(item, base, plan_slots, hg);  // beyond the planned window
+            int my_slot = plan_slots[0];
+#pragma unroll
+            for (int c = 1; c < MERGE_PLAN; ++c)
+                if ((base / 32) % MERGE_PLAN == c) my_slot = plan_slots[c];
+            const int i = base + lane;
+            const int cnt = min(32, nparts - base);
+            float m_i = -INFINITY, l_i = 0.f;
+            if (i < nparts) {
+                const float *r2 = p.partials + (long long)my_slot * p.rec_floats;
+                m_i = __ldcg(r2 + G * NCKV_D + hg);
+                l_i = __ldcg(r2 + G * NCKV_D + G + hg);
+            }
+            // O rows in batches of 8 predicated loads issued back to back (one round trip per
+            // batch instead of one per part); the first batch is in flight during the reductions
+            float4 v[8];
+            auto fetch8 = [&](int jb) {
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int slot_j = __shfl_sync(0xffffffffu, my_slot, (jb + u) & 31);
+                    v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (jb + u < cnt)
+                        v[u] = __ldcg(reinterpret_cast<const float4 *>(p.partials + (long long)slot_j * p.rec_floats + hg * NCKV_D) + lane);
+                }
+            };
+            fetch8(0);
+            float cm = m_i;
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) cm = fmaxf(cm, __shfl_xor_sync(0xffffffffu, cm, off));
+            const float newM = fmaxf(M, cm);
+            const float rescale = exp2f(M - newM);  // first chunk: exp2(-inf) = 0
+            const float sc = i < nparts ? exp2f(m_i - newM) : 0.f;
+            float cl = sc * l_i;
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) cl += __shfl_xor_sync(0xffffffffu, cl, off);
+            L = L * rescale + cl;
+            acc.x *= rescale; acc.y *= rescale; acc.z *= rescale; acc.w *= rescale;
+            M = newM;
+            for (int jb = 0; jb < cnt; jb += 8) {
+                if (jb > 0) fetch8(jb);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const float s_j = __shfl_sync(0xffffffffu, sc, (jb + u) & 31);  // 0 for lanes past the chunk
+                    acc.x = fmaf(s_j, v[u].x, acc.x); acc.y = fmaf(s_j, v[u].y, acc.y);
+                    acc.z = fmaf(s_j, v[u].z, acc.z); acc.w = fmaf(s_j, v[u].w, acc.w);
+                }
+            }
+        }
+        const float inv = 1.f / L;
+        acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+        const long long o = (long long)item * NCKV_D + lane * 4;
+        uint2 packed;
+        packed.x = pack_bf16x2(acc.x, acc.y);
+        packed.y = pack_bf16x2(acc.z, acc.w);
+        *reinterpret_cast<uint2 *>(p.out + o) = packed;
+        if (p.out_f32) *reinterpret_cast<float4 *>(p.out_f32 + o) = acc;
+        if (p.lse && lane == 0) p.lse[item] = (M + log2f(L)) * 0.69314718055994531f;
+    }
+#ifdef NCKV_TIMELINE
+    __syncthreads();
+    if (threadIdx.x == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); tl[2] = t_; }
+#endif
 }
 
 static size_t decode_smem_bytes() {
     return 1024 + (size_t)DEC_WARPS * DEC_STAGES * DEC_STAGE_BYTES + DEC_WARPS * DEC_STAGES * sizeof(uint64_t) +
-           (3 * DEC_MAX_B + 4) * sizeof(int);
+           DEC_WARPS * DEC_RING * sizeof(RunEntry) + (3 * DEC_MAX_B + 4) * sizeof(int);
 }
 
-// Workspace layout: [0,256) status; counters (B*Hkv int32, rounded to 256 B); partial records.
-static size_t ws_counter_bytes(int B, int Hkv) { return (((size_t)B * Hkv * 4) + 255) & ~(size_t)255; }
+// Workspace layout: [0,256) status word and ticket counter; then the partial records, two per run,
+// (1 + DEC_DYN_PER_WARP) * W runs at most.
 // One partial record: [G][128] fp32 O, then m[G] and l[G], padded so records stay 16-byte aligned.
 static int rec_floats_for(int G) { return G * NCKV_D + ((2 * G + 3) & ~3); }
 static size_t ws_partial_bytes(int G) {
-    return (size_t)2 * sm_count() * DEC_WARPS * (size_t)rec_floats_for(G) * sizeof(float);
+    const size_t runs = (size_t)(1 + DEC_DYN_PER_WARP) * sm_count() * DEC_WARPS + 2;
+    return 2 * runs * (size_t)rec_floats_for(G) * sizeof(float);
 }
 
 #ifdef NCKV_TIMELINE
 static unsigned long long *g_timeline = nullptr;
 #endif
+
+template <typename Kernel, typename... Args>
+static cudaError_t launch_pdl(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool pdl,
+                              Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
 
 }  // namespace nckv
 
@@ -559,7 +792,7 @@ NCKV_API void nckv_debug_set_timeline(void *ptr) { nckv::g_timeline = static_cas
 size_t nckv_workspace_bytes(int B, int Hq, int Hkv, int D) {
     using namespace nckv;
     if (B <= 0 || Hq <= 0 || Hkv <= 0 || D != NCKV_D || Hq % Hkv) return 0;
-    return DEC_STATUS_BYTES + ws_counter_bytes(B, Hkv) + ws_partial_bytes(Hq / Hkv);
+    return DEC_STATUS_BYTES + ws_partial_bytes(Hq / Hkv);
 }
 
 int nckv_decode_attn(const void *q, const void *k_cache, const void *v_cache,
@@ -593,7 +826,7 @@ int nckv_decode_attn(const void *q, const void *k_cache, const void *v_cache,
         set_error("decode_attn: q/out/workspace must be 16-byte aligned");
         return NCKV_E_ARG;
     }
-    if ((long long)B * Hkv * ((T_max + DEC_TILE - 1) / DEC_TILE) >= (1LL << 31) / (sm_count() * DEC_WARPS)) {
+    if ((long long)B * Hkv * ((T_max + DEC_TILE - 1) / DEC_TILE) >= (1LL << 30)) {
         set_error("decode_attn: B*Hkv*T_max too large for 32-bit tile arithmetic");
         return NCKV_E_UNSUPPORTED;
     }
@@ -609,6 +842,7 @@ int nckv_decode_attn(const void *q, const void *k_cache, const void *v_cache,
     rc = make_kv_tensor_map(&mv, v_cache, B, T_max, Hkv, cache_batch_stride, cache_token_stride, DEC_TILE);
     if (rc != NCKV_OK) return rc;
 
+    const int grid = sm_count();
     uint8_t *ws = static_cast<uint8_t *>(workspace);
     DecodeParams p;
     p.q = static_cast<const __nv_bfloat16 *>(q);
@@ -617,14 +851,15 @@ int nckv_decode_attn(const void *q, const void *k_cache, const void *v_cache,
     p.out_f32 = out_f32;
     p.lse = lse_out;
     p.status = reinterpret_cast<int32_t *>(ws);
-    p.counters = reinterpret_cast<int32_t *>(ws + DEC_STATUS_BYTES);
-    p.partials = reinterpret_cast<float *>(ws + DEC_STATUS_BYTES + ws_counter_bytes(B, Hkv));
+    p.run_counter = reinterpret_cast<int32_t *>(ws + 16);
+    p.partials = reinterpret_cast<float *>(ws + DEC_STATUS_BYTES);
     p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.G = G; p.T_max = T_max;
     p.seqlen_offset = seqlen_offset;
     p.window_left = window_left;
     p.kv_begin = kv_begin;
     p.kv_end = kv_end;
     p.rec_floats = rec_floats_for(G);
+    p.W = grid * DEC_WARPS;
     p.scale_log2 = (float)(1.4426950408889634 / sqrt((double)D));
 #ifdef NCKV_TIMELINE
     p.timeline = g_timeline;
@@ -642,13 +877,17 @@ int nckv_decode_attn(const void *q, const void *k_cache, const void *v_cache,
             NCKV_CUDA_CHECK(cudaFuncSetAttribute(decode_attn_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attr_set[dev][ghi] = true;
     }
-    const int grid = sm_count();
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // Both launches allow programmatic overlap with their predecessor in the stream: each kernel
+    // runs its set-up early and waits (griddepcontrol.wait) before it touches dependent data.
     if (ghi)
-        decode_attn_kernel<true><<<grid, DEC_WARPS * 32, smem, s>>>(mk, mv, p);
+        NCKV_CUDA_CHECK(launch_pdl(decode_attn_kernel<true>, dim3(grid), dim3(DEC_WARPS * 32), smem, s, true, mk, mv, p));
     else
-        decode_attn_kernel<false><<<grid, DEC_WARPS * 32, smem, s>>>(mk, mv, p);
-    NCKV_CUDA_CHECK(cudaGetLastError());
+        NCKV_CUDA_CHECK(launch_pdl(decode_attn_kernel<false>, dim3(grid), dim3(DEC_WARPS * 32), smem, s, true, mk, mv, p));
+    const int items = B * Hq;
+    int merge_grid = (items + MERGE_WARPS - 1) / MERGE_WARPS;
+    if (merge_grid > 4 * grid) merge_grid = 4 * grid;
+    NCKV_CUDA_CHECK(launch_pdl(decode_merge_kernel, dim3(merge_grid), dim3(MERGE_WARPS * 32), 0, s, true, p));
     return NCKV_OK;
 }
 

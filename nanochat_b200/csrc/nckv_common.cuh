@@ -109,6 +109,29 @@ __device__ __forceinline__ void tma_load_4d(void *smem_dst, const CUtensorMap *m
         "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(smem_u32(bar))
         : "memory");
 }
+// Same, with an L2 cache policy (e.g. evict-first for data that is streamed once).
+__device__ __forceinline__ void tma_load_4d_hint(void *smem_dst, const CUtensorMap *map, uint64_t *bar,
+                                                 int c0, int c1, int c2, int c3, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%2, %3, %4, %5}], [%6], %7;" ::"r"(smem_u32(smem_dst)),
+        "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(smem_u32(bar)), "l"(policy)
+        : "memory");
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+// Programmatic dependent launch: let the next kernel of the stream start its prologue early /
+// wait until everything the previous kernel wrote is visible.  Both are no-ops for a kernel that
+// was launched without the programmatic-serialization attribute.
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait_prior_grids() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
 __device__ __forceinline__ void tma_load_5d(void *smem_dst, const CUtensorMap *map, uint64_t *bar,
                                             int c0, int c1, int c2, int c3, int c4) {
     asm volatile(
