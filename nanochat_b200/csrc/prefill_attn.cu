@@ -1,10 +1,444 @@
-// Kernel (d) placeholder while the tcgen05 tile kernel is being brought up.
+// Kernel (d): dense causal attention for T_new >= 1 query tokens per row (prefill, chunked
+// prefill, flash_attn_func), on the 5th-generation tensor cores: tcgen05.mma with both operands
+// in shared memory (TMA, 128-byte swizzle) and the accumulators in tensor memory (TMEM).
+//
+// One CTA (128 threads) owns a tile of PF_M = 128 query tokens of one (row, q head) and walks the
+// visible keys in tiles of PF_N = 64:
+//   1. S = Q K^T      one elected thread issues 8 x tcgen05.mma (M128 N64 K16) into TMEM columns
+//                     [0, 64); completion arrives on an mbarrier through tcgen05.commit
+//   2. softmax        thread r owns query row r = TMEM lane r: tcgen05.ld brings its 64 scores
+//                     into registers, causal / window masking is done by index, running max and
+//                     sum are per-thread scalars, P is rounded to bf16 and written to shared
+//                     memory in the K-major swizzled layout the next product reads
+//   3. O_t = P V      4 x tcgen05.mma (M128 N128 K16), V used in place as an MN-major operand,
+//                     into TMEM columns [128, 256)
+//   4. O = a*O + O_t  tcgen05.ld, accumulation in registers with the softmax rescale a
+// K/V tiles are double buffered.  Two CTAs fit on an SM (about 112 KB of shared memory and 256 of
+// the 512 TMEM columns each), so one CTA's softmax overlaps the other's tensor work.
+// Every barrier wait is bounded; a wait that runs out sets NCKV_ST_TIMEOUT, the CTA stops issuing
+// work, frees its TMEM and returns.
+//
+// Replaces: the full-causal and explicit-mask branches of _sdpa_attention
+// (flash_attention.py:79-80, 92-102) reached from flash_attn_with_kvcache
+// (flash_attention.py:165-177) and flash_attn_func (flash_attention.py:107-128).
+#include <math.h>
+
 #include "nckv_common.cuh"
+
+namespace nckv {
+
+constexpr int PF_M = 128;  // query tokens per CTA
+constexpr int PF_N = 64;   // keys per tile
+constexpr int PF_STAGES = 2;
+constexpr int PF_Q_BYTES = PF_M * NCKV_D * 2;        // 32 KB: two 64-channel halves of [128][128 B]
+constexpr int PF_KV_BYTES = PF_N * NCKV_D * 2;       // 16 KB: two halves of [64][128 B]
+constexpr int PF_P_BYTES = PF_M * PF_N * 2;          // 16 KB: [128][128 B]
+constexpr int PF_TMEM_COLS = 256;                    // S: [0,64)  O tile: [128,256)
+constexpr uint32_t PF_WAIT_LIMIT = 1u << 22;
+
+struct PrefillParams {
+    const int32_t *seqlens;  // may be null (all zero)
+    __nv_bfloat16 *out;
+    int32_t *status;
+    int B, T_new, Hq, Hkv, T_k;
+    int window_left;
+    float scale_log2;
+};
+
+// ---- tcgen05 wrappers ------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t *smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem] * B[smem], bf16 inputs, fp32 accumulate; issued by one thread.
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// mbarrier arrive once every tcgen05 operation issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+// 32 lanes x 32 consecutive fp32 columns: thread l of the warp receives row (lane base + l).
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    tmem_wait_ld();
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor (128-byte swizzle).  Fields: start address >> 4 in bits 0..13,
+// leading-dimension byte offset >> 4 in bits 16..29, stride-dimension byte offset >> 4 in bits
+// 32..45, descriptor version 1 in bits 46..47, layout type (2 = 128-byte swizzle) in bits 61..63.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3fff);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3fff) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3fff) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// Instruction descriptor for kind::f16 with bf16 inputs and fp32 accumulation: accumulator format
+// in bits 4..5 (1 = f32), A/B formats in bits 7..9 / 10..12 (1 = bf16), A/B majorness in bits 15 /
+// 16 (0 = K-major, 1 = MN-major), N >> 3 in bits 17..22, M >> 4 in bits 24..28.
+__host__ __device__ constexpr uint32_t umma_idesc(int M, int N, int a_mn_major, int b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) |
+           ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+__global__ void __launch_bounds__(128, 2)
+prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                    const __grid_constant__ CUtensorMap tmap_v, const PrefillParams p) {
+    // The swizzled tiles need 1024-byte aligned bases; the dynamic segment is declared with that
+    // alignment (no slack bytes: two CTAs must fit in one SM's shared memory).
+    extern __shared__ __align__(1024) uint8_t smem[];
+    if ((smem_u32(smem) & 1023u) != 0) {  // uniform; checked rather than assumed
+        if (threadIdx.x == 0) atomicOr(p.status, (int)NCKV_ST_TIMEOUT);
+        return;
+    }
+    uint8_t *sQ = smem;                                   // 32 KB
+    uint8_t *sK = sQ + PF_Q_BYTES;                        // 2 x 16 KB
+    uint8_t *sV = sK + PF_STAGES * PF_KV_BYTES;           // 2 x 16 KB
+    uint8_t *sP = sV + PF_STAGES * PF_KV_BYTES;           // 16 KB
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sP + PF_P_BYTES);
+    uint64_t *bar_q = bars;          // Q landed
+    uint64_t *bar_k = bars + 1;      // [PF_STAGES] K tile landed
+    uint64_t *bar_v = bars + 3;      // [PF_STAGES] V tile landed
+    uint64_t *bar_s = bars + 5;      // S = QK^T complete
+    uint64_t *bar_o = bars + 6;      // O_t = PV complete
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 7);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int n_qtiles = (p.T_new + PF_M - 1) / PF_M;
+    const int qt = n_qtiles - 1 - (int)blockIdx.x;  // long tiles first
+    const int hq = blockIdx.y, b = blockIdx.z;
+    const int hkv = hq / (p.Hq / p.Hkv);
+    const int t0 = qt * PF_M;
+
+    pdl_wait_prior_grids();
+    int L = p.seqlens ? p.seqlens[b] : 0;
+    if (L < 0) {
+        if (tid == 0) atomicOr(p.status, (int)NCKV_ST_BAD_SEQLEN);
+        L = 0;
+    }
+    int Tk = L + p.T_new;  // keys present after the append
+    if (Tk > p.T_k) {
+        if (tid == 0) atomicOr(p.status, (int)NCKV_ST_OVERFLOW);
+        Tk = p.T_k;
+    }
+    // keys any row of this tile may see: [kv_lo, kv_hi)
+    const int last_t = min(t0 + PF_M, p.T_new) - 1;
+    const int kv_hi = min(Tk, L + last_t + 1);
+    const int kv_lo = p.window_left >= 0 ? max(0, L + t0 - p.window_left) : 0;
+    const int n_tiles = kv_hi > kv_lo ? (kv_hi - kv_lo + PF_N - 1) / PF_N : 0;
+
+    if (tid == 0) {
+        prefetch_tensormap(&tmap_q);
+        prefetch_tensormap(&tmap_k);
+        prefetch_tensormap(&tmap_v);
+        mbar_init(bar_q, 1);
+        for (int s = 0; s < PF_STAGES; ++s) {
+            mbar_init(&bar_k[s], 1);
+            mbar_init(&bar_v[s], 1);
+        }
+        mbar_init(bar_s, 1);
+        mbar_init(bar_o, 1);
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 0) {
+        tmem_alloc(tmem_slot, PF_TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_s = tmem_base;          // columns [0, 64)
+    const uint32_t tmem_o = tmem_base + 128;    // columns [128, 256)
+    const uint32_t lane_sel = (uint32_t)(warp * 32) << 16;
+
+    auto load_kv = [&](int tile, int stage) {  // thread 0 only
+        const int key0 = kv_lo + tile * PF_N;
+        uint8_t *kd = sK + stage * PF_KV_BYTES, *vd = sV + stage * PF_KV_BYTES;
+        fence_proxy_async_smem();
+        mbar_arrive_expect_tx(&bar_k[stage], PF_KV_BYTES);
+        tma_load_4d(kd, &tmap_k, &bar_k[stage], 0, hkv, key0, b);
+        tma_load_4d(kd + PF_KV_BYTES / 2, &tmap_k, &bar_k[stage], 64, hkv, key0, b);
+        mbar_arrive_expect_tx(&bar_v[stage], PF_KV_BYTES);
+        tma_load_4d(vd, &tmap_v, &bar_v[stage], 0, hkv, key0, b);
+        tma_load_4d(vd + PF_KV_BYTES / 2, &tmap_v, &bar_v[stage], 64, hkv, key0, b);
+    };
+
+    if (tid == 0 && n_tiles > 0) {
+        mbar_arrive_expect_tx(bar_q, PF_Q_BYTES);
+        tma_load_4d(sQ, &tmap_q, bar_q, 0, hq, t0, b);
+        tma_load_4d(sQ + PF_Q_BYTES / 2, &tmap_q, bar_q, 64, hq, t0, b);
+        for (int i = 0; i < PF_STAGES && i < n_tiles; ++i) load_kv(i, i);
+    }
+
+    constexpr uint32_t IDESC_S = umma_idesc(PF_M, PF_N, 0, 0);
+    constexpr uint32_t IDESC_O = umma_idesc(PF_M, NCKV_D, 0, 1);
+
+    float o_reg[NCKV_D];
+#pragma unroll
+    for (int i = 0; i < NCKV_D; ++i) o_reg[i] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+    const int row = tid;               // query row inside the tile == TMEM lane
+    const int pos = L + t0 + row;      // absolute position of this row's token
+    bool aborted = false;
+
+    auto wait_or_abort = [&](uint64_t *bar, uint32_t parity) -> bool {
+        if (mbar_wait_bounded(bar, parity, PF_WAIT_LIMIT)) return true;
+        *abort_flag = 1;
+        atomicOr(p.status, (int)NCKV_ST_TIMEOUT);
+        return false;
+    };
+
+    for (int it = 0; it < n_tiles; ++it) {
+        const int stage = it % PF_STAGES;
+        const uint32_t kv_parity = (uint32_t)((it / PF_STAGES) & 1);
+        const uint32_t it_parity = (uint32_t)(it & 1);
+        const int key0 = kv_lo + it * PF_N;
+
+        // ---- 1. S = Q K^T ------------------------------------------------------------------
+        if (tid == 0) {
+            bool ok = it > 0 || wait_or_abort(bar_q, 0);
+            ok = ok && wait_or_abort(&bar_k[stage], kv_parity);
+            if (ok) {
+                tc_fence_after();
+                const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + stage * PF_KV_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < NCKV_D / 16; ++kk) {
+                    const uint32_t off = (uint32_t)(kk & 3) * 32;
+                    const uint64_t da = smem_desc_sw128(qa + (kk >> 2) * (PF_Q_BYTES / 2) + off, 16, 1024);
+                    const uint64_t db = smem_desc_sw128(ka + (kk >> 2) * (PF_KV_BYTES / 2) + off, 16, 1024);
+                    umma_bf16(tmem_s, da, db, IDESC_S, kk > 0 ? 1u : 0u);
+                }
+            }
+            umma_commit(bar_s);  // also on the abort path: nobody may be left waiting without a bound
+        }
+        if (!mbar_wait_bounded(bar_s, it_parity, PF_WAIT_LIMIT)) {
+            *abort_flag = 1;
+            atomicOr(p.status, (int)NCKV_ST_TIMEOUT);
+        }
+        tc_fence_after();
+
+        // ---- 2. softmax on row `row` ---------------------------------------------------------
+        float s_val[PF_N];
+        {
+            float c0[32], c1[32];
+            tmem_ld32(tmem_s + lane_sel, c0);
+            tmem_ld32(tmem_s + lane_sel + 32, c1);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) { s_val[i] = c0[i]; s_val[32 + i] = c1[i]; }
+        }
+        float mx = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < PF_N; ++c) {
+            const int j = key0 + c;
+            const bool visible = (j <= pos) && (j < kv_hi) && (p.window_left < 0 || pos - j <= p.window_left);
+            s_val[c] = visible ? s_val[c] * p.scale_log2 : -INFINITY;
+            mx = fmaxf(mx, s_val[c]);
+        }
+        const float m_new = fmaxf(m_run, mx);
+        const float m_use = m_new == -INFINITY ? 0.f : m_new;  // a row that has seen no key yet
+        const float alpha = exp2f(m_run - m_use);               // exp2(-inf) = 0 on the first tile
+        m_run = m_new;
+        float rsum = 0.f;
+        uint32_t pk[PF_N / 2];
+#pragma unroll
+        for (int c = 0; c < PF_N; c += 2) {
+            const float p0 = exp2f(s_val[c] - m_use), p1 = exp2f(s_val[c + 1] - m_use);
+            rsum += p0 + p1;
+            pk[c / 2] = pack_bf16x2(p0, p1);
+        }
+        l_run = l_run * alpha + rsum;
+        // P row -> shared memory, K-major with the 128-byte swizzle (16-byte chunk c ^ (row % 8))
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            uint4 v = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+            *reinterpret_cast<uint4 *>(sP + row * 128 + ((c ^ (row & 7)) << 4)) = v;
+        }
+        // rows of the V tile past the last key may hold stale bytes: zero them so that a zero
+        // probability never multiplies a NaN/Inf bit pattern
+        if (key0 + PF_N > kv_hi) {
+            uint8_t *vd = sV + stage * PF_KV_BYTES;
+            if (mbar_wait_bounded(&bar_v[stage], kv_parity, PF_WAIT_LIMIT)) {
+                for (int idx = tid; idx < (key0 + PF_N - kv_hi) * 16; idx += 128) {
+                    const int r = (kv_hi - key0) + idx / 16, ch = idx % 16;
+                    *reinterpret_cast<uint4 *>(vd + (ch >> 3) * (PF_KV_BYTES / 2) + r * 128 + ((ch & 7) << 4)) =
+                        make_uint4(0, 0, 0, 0);
+                }
+            }
+        }
+        fence_proxy_async_smem();  // P (and the zeroed V rows) must be visible to the tensor core
+        tc_fence_before();
+        __syncthreads();
+        aborted = *abort_flag != 0;
+        if (aborted) break;
+
+        // ---- 3. O_t = P V ------------------------------------------------------------------
+        if (tid == 0) {
+            const bool ok = wait_or_abort(&bar_v[stage], kv_parity);
+            if (ok) {
+                tc_fence_after();
+                const uint32_t pa = smem_u32(sP), va = smem_u32(sV + stage * PF_KV_BYTES);
+#pragma unroll
+                for (int ks = 0; ks < PF_N / 16; ++ks) {
+                    const uint64_t da = smem_desc_sw128(pa + ks * 32, 16, 1024);
+                    // V in place: N (channels) contiguous, the two 64-channel halves PF_KV_BYTES/2
+                    // apart (leading offset), 8-key groups 1024 B apart (stride offset)
+                    const uint64_t db = smem_desc_sw128(va + ks * 16 * 128, PF_KV_BYTES / 2, 1024);
+                    umma_bf16(tmem_o, da, db, IDESC_O, ks > 0 ? 1u : 0u);
+                }
+            }
+            umma_commit(bar_o);
+        }
+        if (!mbar_wait_bounded(bar_o, it_parity, PF_WAIT_LIMIT)) {
+            *abort_flag = 1;
+            atomicOr(p.status, (int)NCKV_ST_TIMEOUT);
+        }
+        tc_fence_after();
+
+        // ---- 4. O = alpha * O + O_t ----------------------------------------------------------
+#pragma unroll
+        for (int ch = 0; ch < NCKV_D / 32; ++ch) {
+            float c[32];
+            tmem_ld32(tmem_o + lane_sel + ch * 32, c);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o_reg[ch * 32 + i] = fmaf(o_reg[ch * 32 + i], alpha, c[i]);
+        }
+        tc_fence_before();
+        __syncthreads();  // S, O_t, P and this K/V stage are free again
+        aborted = *abort_flag != 0;
+        if (aborted) break;
+        if (tid == 0 && it + PF_STAGES < n_tiles) load_kv(it + PF_STAGES, stage);
+    }
+
+    // ---- epilogue -----------------------------------------------------------------------------
+    const int t = t0 + row;
+    if (!aborted && t < p.T_new) {
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        uint4 *dst = reinterpret_cast<uint4 *>(p.out + (((long long)b * p.T_new + t) * p.Hq + hq) * NCKV_D);
+#pragma unroll
+        for (int c = 0; c < NCKV_D / 8; ++c) {
+            uint4 v;
+            v.x = pack_bf16x2(o_reg[8 * c + 0] * inv, o_reg[8 * c + 1] * inv);
+            v.y = pack_bf16x2(o_reg[8 * c + 2] * inv, o_reg[8 * c + 3] * inv);
+            v.z = pack_bf16x2(o_reg[8 * c + 4] * inv, o_reg[8 * c + 5] * inv);
+            v.w = pack_bf16x2(o_reg[8 * c + 6] * inv, o_reg[8 * c + 7] * inv);
+            dst[c] = v;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_base, PF_TMEM_COLS);
+}
+
+static size_t prefill_smem_bytes() {
+    return PF_Q_BYTES + 2 * PF_STAGES * PF_KV_BYTES + PF_P_BYTES + 16 * sizeof(uint64_t);
+}
+
+}  // namespace nckv
 
 extern "C" int nckv_prefill_attn(const void *q, const void *k, const void *v, const int32_t *cache_seqlens,
                                  void *out, int B, int T_new, int Hq, int Hkv, int D, int T_k,
                                  int64_t kv_batch_stride, int64_t kv_token_stride, int window_left,
                                  int32_t *status, void *stream) {
-    nckv::set_error("prefill_attn: not built yet");
-    return NCKV_E_UNSUPPORTED;
+    using namespace nckv;
+    if (!q || !k || !v || !out || !status) {
+        set_error("prefill_attn: null pointer argument");
+        return NCKV_E_ARG;
+    }
+    if (B <= 0 || T_new <= 0 || Hq <= 0 || Hkv <= 0 || T_k <= 0) {
+        set_error("prefill_attn: non-positive size (B=%d T_new=%d Hq=%d Hkv=%d T_k=%d)", B, T_new, Hq, Hkv, T_k);
+        return NCKV_E_ARG;
+    }
+    if (D != NCKV_D) {
+        set_error("prefill_attn: head_dim %d unsupported (kernels are built for 128)", D);
+        return NCKV_E_UNSUPPORTED;
+    }
+    if (Hq % Hkv != 0) {
+        set_error("prefill_attn: Hq=%d must be a multiple of Hkv=%d", Hq, Hkv);
+        return NCKV_E_UNSUPPORTED;
+    }
+    if (T_new > T_k) {
+        set_error("prefill_attn: T_new=%d exceeds the key capacity T_k=%d", T_new, T_k);
+        return NCKV_E_CAPACITY;
+    }
+    if (B > 65535 || Hq > 65535) {
+        set_error("prefill_attn: B=%d / Hq=%d exceed the grid limits", B, Hq);
+        return NCKV_E_UNSUPPORTED;
+    }
+    if (((uintptr_t)q | (uintptr_t)out) & 15) {
+        set_error("prefill_attn: q/out must be 16-byte aligned");
+        return NCKV_E_ARG;
+    }
+    CUtensorMap mq, mk, mv;
+    int rc = make_kv_tensor_map(&mq, q, B, T_new, Hq, (int64_t)T_new * Hq * D, (int64_t)Hq * D, PF_M);
+    if (rc != NCKV_OK) return rc;
+    rc = make_kv_tensor_map(&mk, k, B, T_k, Hkv, kv_batch_stride, kv_token_stride, PF_N);
+    if (rc != NCKV_OK) return rc;
+    rc = make_kv_tensor_map(&mv, v, B, T_k, Hkv, kv_batch_stride, kv_token_stride, PF_N);
+    if (rc != NCKV_OK) return rc;
+
+    PrefillParams p;
+    p.seqlens = cache_seqlens;
+    p.out = static_cast<__nv_bfloat16 *>(out);
+    p.status = status;
+    p.B = B; p.T_new = T_new; p.Hq = Hq; p.Hkv = Hkv; p.T_k = T_k;
+    p.window_left = window_left;
+    p.scale_log2 = (float)(1.4426950408889634 / sqrt((double)D));
+
+    const size_t smem = prefill_smem_bytes();
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    NCKV_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 64 && !attr_set[dev]) {
+        NCKV_CUDA_CHECK(cudaFuncSetAttribute(prefill_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_set[dev] = true;
+    }
+    const int n_qtiles = (T_new + PF_M - 1) / PF_M;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_qtiles, Hq, B);
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    NCKV_CUDA_CHECK(cudaLaunchKernelEx(&cfg, prefill_attn_kernel, mq, mk, mv, p));
+    return NCKV_OK;
 }

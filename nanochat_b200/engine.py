@@ -6,7 +6,12 @@
 arithmetic and works on any device; ``prefill`` — the batch-1 -> num_samples broadcast — is the
 CUDA copy kernel of libnckv and raises for non-CUDA caches (there is no CPU path).
 """
+import signal
+import warnings
+from collections import deque
+
 import torch
+import torch.nn.functional as F
 
 from . import ops
 
@@ -61,3 +66,156 @@ class KVCache:
         ops.prefill_broadcast(other.k_cache, other.v_cache, self.k_cache, self.v_cache, self.cache_seqlens, other_pos)
         if other.prev_embedding is not None:
             self.prev_embedding = other.prev_embedding.expand(self.batch_size, -1, -1).clone()
+
+
+# ------------------------------------------------------------------------------------------------
+# The caller of the hot path: token-level generation (nanochat/engine.py:141-304)
+# ------------------------------------------------------------------------------------------------
+def _eval_with_deadline(expr, seconds=3):
+    """Evaluate a vetted arithmetic/string expression with an alarm-based deadline; None on failure."""
+    def on_alarm(signum, frame):
+        raise TimeoutError(expr)
+
+    try:
+        signal.signal(signal.SIGALRM, on_alarm)
+        signal.alarm(seconds)
+        try:
+            with warnings.catch_warnings():
+                warnings.simplefilter("ignore", SyntaxWarning)
+                return eval(expr, {"__builtins__": {}}, {})
+        finally:
+            signal.alarm(0)
+    except Exception:
+        return None
+
+
+_MATH_CHARS = set("0123456789*+-/.() ")
+_TEXT_CHARS = set("abcdefghijklmnopqrstuvwxyzABCDEFGHIJKLMNOPQRSTUVWXYZ0123456789'\"()._ ")
+_BANNED = ("__", "import", "exec", "eval", "compile", "open", "file", "input", "raw_input", "globals", "locals",
+           "vars", "dir", "getattr", "setattr", "delattr", "hasattr")
+
+
+def use_calculator(expr):
+    """The calculator tool of the reference (engine.py:47-79): plain arithmetic without ``**``, or a
+    ``.count()`` call on a string literal; anything else yields None."""
+    expr = expr.replace(",", "")
+    if all(ch in _MATH_CHARS for ch in expr):
+        return None if "**" in expr else _eval_with_deadline(expr)
+    if not all(ch in _TEXT_CHARS for ch in expr):
+        return None
+    lowered = expr.lower()
+    if any(word in lowered for word in _BANNED) or ".count(" not in expr:
+        return None
+    return _eval_with_deadline(expr)
+
+
+@torch.inference_mode()
+def sample_next_token(logits, rng, temperature=1.0, top_k=None):
+    """One token per row from (B, vocab) logits -> (B, 1); argmax at temperature 0, otherwise
+    (top-k) softmax sampling with ``rng`` (engine.py:141-156)."""
+    assert temperature >= 0.0, "temperature must be non-negative"
+    if temperature == 0.0:
+        return torch.argmax(logits, dim=-1, keepdim=True)
+    if top_k is not None and top_k > 0:
+        vals, idx = torch.topk(logits, min(top_k, logits.size(-1)), dim=-1)
+        choice = torch.multinomial(F.softmax(vals / temperature, dim=-1), num_samples=1, generator=rng)
+        return idx.gather(1, choice)
+    return torch.multinomial(F.softmax(logits / temperature, dim=-1), num_samples=1, generator=rng)
+
+
+class RowState:
+    """Per-row bookkeeping of the generation loop (engine.py:160-167)."""
+
+    def __init__(self, current_tokens=None):
+        self.current_tokens = current_tokens or []
+        self.forced_tokens = deque()    # tool output waiting to be injected
+        self.in_python_block = False
+        self.python_expr_tokens = []
+        self.completed = False
+
+
+class Engine:
+    """Batch-1 prefill, broadcast of the prompt cache to ``num_samples`` rows, then one forward per
+    generated token (engine.py:169-304).  The model only has to offer ``config``, ``get_device()``
+    and ``forward(ids, kv_cache=...)``; the tokenizer only the special-token lookups, ``encode``
+    and ``decode``."""
+
+    def __init__(self, model, tokenizer):
+        self.model = model
+        self.tokenizer = tokenizer
+
+    @torch.inference_mode()
+    def generate(self, tokens, num_samples=1, max_tokens=None, temperature=1.0, top_k=None, seed=42):
+        assert isinstance(tokens, list) and isinstance(tokens[0], int), "expecting list of ints"
+        device = self.model.get_device()
+        dtype = torch.bfloat16 if device.type == "cuda" else torch.float32
+        rng = torch.Generator(device=device)
+        rng.manual_seed(seed)
+        special = self.tokenizer.encode_special
+        python_start, python_end = special("<|python_start|>"), special("<|python_end|>")
+        output_start, output_end = special("<|output_start|>"), special("<|output_end|>")
+        assistant_end = special("<|assistant_end|>")
+        bos = self.tokenizer.get_bos_token_id()
+
+        cfg = self.model.config
+        geometry = dict(num_heads=cfg.n_kv_head, head_dim=cfg.n_embd // cfg.n_head, num_layers=cfg.n_layer)
+        prompt_cache = KVCache(batch_size=1, seq_len=len(tokens), device=device, dtype=dtype, **geometry)
+        ids = torch.tensor([tokens], dtype=torch.long, device=device)
+        logits = self.model.forward(ids, kv_cache=prompt_cache)[:, -1, :].expand(num_samples, -1)
+
+        capacity = (len(tokens) + max_tokens) if max_tokens is not None else cfg.sequence_len
+        cache = KVCache(batch_size=num_samples, seq_len=capacity, device=device, dtype=dtype, **geometry)
+        cache.prefill(prompt_cache)
+        del prompt_cache
+
+        rows = [RowState(tokens.copy()) for _ in range(num_samples)]
+        produced = 0
+        while (max_tokens is None or produced < max_tokens) and not all(r.completed for r in rows):
+            sampled = sample_next_token(logits, rng, temperature, top_k)[:, 0].tolist()
+            column, masks = [], []
+            for row, drawn in zip(rows, sampled):
+                forced = len(row.forced_tokens) > 0
+                tok = row.forced_tokens.popleft() if forced else drawn
+                masks.append(0 if forced else 1)
+                column.append(tok)
+                row.current_tokens.append(tok)
+                if tok == assistant_end or tok == bos:
+                    row.completed = True
+                if tok == python_start:
+                    row.in_python_block, row.python_expr_tokens = True, []
+                elif tok == python_end and row.in_python_block:
+                    row.in_python_block = False
+                    if row.python_expr_tokens:
+                        result = use_calculator(self.tokenizer.decode(row.python_expr_tokens))
+                        if result is not None:
+                            row.forced_tokens.append(output_start)
+                            row.forced_tokens.extend(self.tokenizer.encode(str(result)))
+                            row.forced_tokens.append(output_end)
+                    row.python_expr_tokens = []
+                elif row.in_python_block:
+                    row.python_expr_tokens.append(tok)
+            yield column, masks
+            produced += 1
+            ids = torch.tensor(column, dtype=torch.long, device=device).unsqueeze(1)
+            logits = self.model.forward(ids, kv_cache=cache)[:, -1, :]
+
+    def generate_batch(self, tokens, num_samples=1, **kwargs):
+        """Run ``generate`` to the end; returns (token lists, sampled/forced masks) without the
+        terminal tokens (engine.py:282-304)."""
+        assistant_end = self.tokenizer.encode_special("<|assistant_end|>")
+        bos = self.tokenizer.get_bos_token_id()
+        results = [tokens.copy() for _ in range(num_samples)]
+        masks = [[0] * len(tokens) for _ in range(num_samples)]
+        done = [False] * num_samples
+        for column, column_masks in self.generate(tokens, num_samples, **kwargs):
+            for i, (tok, m) in enumerate(zip(column, column_masks)):
+                if done[i]:
+                    continue
+                if tok == assistant_end or tok == bos:
+                    done[i] = True
+                else:
+                    results[i].append(tok)
+                    masks[i].append(m)
+            if all(done):
+                break
+        return results, masks

@@ -1,10 +1,28 @@
-"""The attention KV branch of nanochat's GPT (gpt.py:97-121) on the fused kernels, plus the two
-pure-host helpers it depends on (rotary tables, per-layer windows)."""
+"""Inference-side mirror of nanochat's GPT (nanochat/gpt.py) with the attention KV branch on the
+fused sm_100a kernels.
+
+Scope.  The reference's hot path runs through ``CausalSelfAttention.forward`` (gpt.py:82-126); what
+this module replaces is its KV branch (gpt.py:97-121): RoPE, QK-norm, the 1.2 scale, the cache
+append and the attention call become two kernel launches (``kv_attention``).  Everything around it
+(embeddings, smear, residual lambdas, value embeddings, MLP, backout, logit softcap) is the same
+sequence of torch ops as the reference, kept so that the path can be driven end to end by
+``Engine`` on random-init or checkpointed weights; parameter names match the reference's
+``state_dict`` so its checkpoints load unchanged.  Training (loss, optimizers, autograd through
+attention) is out of scope and absent.
+"""
+from dataclasses import dataclass
+
 import torch
+import torch.nn as nn
+import torch.nn.functional as F
 
 from . import ops
+from .flash_attention import flash_attn
 
 
+# ------------------------------------------------------------------------------------------------
+# pure-host helpers
+# ------------------------------------------------------------------------------------------------
 def precompute_rotary_embeddings(seq_len, head_dim, base=100000, device=None, dtype=torch.bfloat16):
     """cos/sin tables of shape (1, seq_len, 1, head_dim/2): the op sequence of
     GPT._precompute_rotary_embeddings (gpt.py:268-283), so the tables are bit-identical to the
@@ -55,3 +73,242 @@ def kv_attention(q, k, v, cos_sin_tables, window_size, kv_cache, layer_idx):
     if layer_idx == kv_cache.n_layers - 1:
         kv_cache.advance(T)
     return y
+
+
+# ------------------------------------------------------------------------------------------------
+# model
+# ------------------------------------------------------------------------------------------------
+@dataclass
+class GPTConfig:
+    """Same fields and defaults as the reference's GPTConfig (gpt.py:28-39)."""
+    sequence_len: int = 2048
+    vocab_size: int = 32768
+    n_layer: int = 12
+    n_head: int = 6
+    n_kv_head: int = 6
+    n_embd: int = 768
+    window_pattern: str = "SSSL"
+
+
+def rms(x):
+    """Parameter-free rms-norm over the last dim (gpt.py:42-43)."""
+    return F.rms_norm(x, (x.size(-1),))
+
+
+def layer_has_value_embedding(layer_idx, n_layer):
+    """Alternating layers carry a value embedding, the last layer always does (gpt.py:53-55)."""
+    return layer_idx % 2 == (n_layer - 1) % 2
+
+
+class CastLinear(nn.Linear):
+    """Bias-free linear whose weight is used in the activation's dtype (gpt.py:45-50).  The cast is
+    skipped when the dtypes already agree, e.g. after ``model.to(torch.bfloat16)``."""
+
+    def forward(self, x):
+        w = self.weight if self.weight.dtype == x.dtype else self.weight.to(dtype=x.dtype)
+        return F.linear(x, w)
+
+
+class Attention(nn.Module):
+    def __init__(self, config, layer_idx):
+        super().__init__()
+        self.layer_idx = layer_idx
+        self.n_head, self.n_kv_head = config.n_head, config.n_kv_head
+        assert config.n_embd % config.n_head == 0 and config.n_head % config.n_kv_head == 0
+        self.head_dim = config.n_embd // config.n_head
+        self.c_q = CastLinear(config.n_embd, self.n_head * self.head_dim, bias=False)
+        self.c_k = CastLinear(config.n_embd, self.n_kv_head * self.head_dim, bias=False)
+        self.c_v = CastLinear(config.n_embd, self.n_kv_head * self.head_dim, bias=False)
+        self.c_proj = CastLinear(config.n_embd, config.n_embd, bias=False)
+        self.ve_gate_channels = 12
+        self.ve_gate = (CastLinear(self.ve_gate_channels, self.n_kv_head, bias=False)
+                        if layer_has_value_embedding(layer_idx, config.n_layer) else None)
+
+    def forward(self, x, ve, rope_tables, window_size, kv_cache):
+        B, T, _ = x.shape
+        q = self.c_q(x).view(B, T, self.n_head, self.head_dim)
+        k = self.c_k(x).view(B, T, self.n_kv_head, self.head_dim)
+        v = self.c_v(x).view(B, T, self.n_kv_head, self.head_dim)
+        if ve is not None:  # value residual with an input-dependent per-head gate (gpt.py:92-95)
+            gate = 3 * torch.sigmoid(self.ve_gate(x[..., :self.ve_gate_channels]))
+            v = v + gate.unsqueeze(-1) * ve.view(B, T, self.n_kv_head, self.head_dim)
+        if kv_cache is not None:
+            y = kv_attention(q, k, v, rope_tables, window_size, kv_cache, self.layer_idx)
+        else:
+            # no cache (naive generation): positions start at 0 for every row; RoPE / QK-norm are
+            # plain torch ops here, the attention itself is the dense kernel
+            cos, sin = rope_tables[0][:, :T], rope_tables[1][:, :T]
+            q, k = _rope_norm_scale(q, cos, sin), _rope_norm_scale(k, cos, sin)
+            y = flash_attn.flash_attn_func(q, k, v, causal=True, window_size=window_size)
+        return self.c_proj(y.contiguous().view(B, T, -1))
+
+
+def _rope_norm_scale(x, cos, sin):
+    d = x.shape[3] // 2
+    x1, x2 = x[..., :d], x[..., d:]
+    y = torch.cat([x1 * cos + x2 * sin, x1 * (-sin) + x2 * cos], 3)
+    return rms(y) * 1.2
+
+
+class MLP(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        self.c_fc = CastLinear(config.n_embd, 4 * config.n_embd, bias=False)
+        self.c_proj = CastLinear(4 * config.n_embd, config.n_embd, bias=False)
+
+    def forward(self, x):
+        return self.c_proj(F.relu(self.c_fc(x)).square())
+
+
+class Block(nn.Module):
+    def __init__(self, config, layer_idx):
+        super().__init__()
+        self.attn = Attention(config, layer_idx)
+        self.mlp = MLP(config)
+
+    def forward(self, x, ve, rope_tables, window_size, kv_cache):
+        x = x + self.attn(rms(x), ve, rope_tables, window_size, kv_cache)
+        return x + self.mlp(rms(x))
+
+
+class GPT(nn.Module):
+    """Inference-only GPT with the reference's module tree and forward arithmetic (gpt.py:154-481)."""
+
+    def __init__(self, config, pad_vocab_size_to=64, compute_dtype=None):
+        super().__init__()
+        self.config = config
+        self.compute_dtype = compute_dtype  # resolved in init_weights / on first forward
+        self.window_sizes = compute_window_sizes(config.sequence_len, config.n_layer, config.window_pattern)
+        padded = -(-config.vocab_size // pad_vocab_size_to) * pad_vocab_size_to
+        self.transformer = nn.ModuleDict({
+            "wte": nn.Embedding(padded, config.n_embd),
+            "h": nn.ModuleList([Block(config, i) for i in range(config.n_layer)]),
+        })
+        self.lm_head = CastLinear(config.n_embd, padded, bias=False)
+        self.resid_lambdas = nn.Parameter(torch.ones(config.n_layer))
+        self.x0_lambdas = nn.Parameter(torch.zeros(config.n_layer))
+        self.smear_gate = CastLinear(24, 1, bias=False)
+        self.smear_lambda = nn.Parameter(torch.zeros(1))
+        self.backout_lambda = nn.Parameter(0.2 * torch.ones(1))
+        head_dim = config.n_embd // config.n_head
+        kv_dim = config.n_kv_head * head_dim
+        self.value_embeds = nn.ModuleDict({str(i): nn.Embedding(padded, kv_dim) for i in range(config.n_layer)
+                                           if layer_has_value_embedding(i, config.n_layer)})
+        self.rotary_seq_len = config.sequence_len * 10  # same over-allocation as gpt.py:195
+        self.register_buffer("cos", torch.empty(0), persistent=False)
+        self.register_buffer("sin", torch.empty(0), persistent=False)
+
+    def get_device(self):
+        return self.transformer.wte.weight.device
+
+    def _resolve_dtype(self):
+        if self.compute_dtype is None:
+            self.compute_dtype = torch.bfloat16 if self.get_device().type == "cuda" else torch.float32
+        return self.compute_dtype
+
+    def build_rotary(self, seq_len=None):
+        """(Re)build the cos/sin tables on the model's device in the compute dtype."""
+        if seq_len is not None:
+            self.rotary_seq_len = seq_len
+        head_dim = self.config.n_embd // self.config.n_head
+        self.cos, self.sin = precompute_rotary_embeddings(self.rotary_seq_len, head_dim, device=self.get_device(),
+                                                          dtype=self._resolve_dtype())
+
+    @torch.no_grad()
+    def init_weights(self):
+        """Random init that consumes the torch RNG in the reference's order (gpt.py:202-265), so the
+        same seed gives the same weights."""
+        cfg = self.config
+        s = 3 ** 0.5 * cfg.n_embd ** -0.5
+        nn.init.normal_(self.transformer.wte.weight, mean=0.0, std=0.8)
+        nn.init.normal_(self.lm_head.weight, mean=0.0, std=0.001)
+        for blk in self.transformer.h:
+            for lin in (blk.attn.c_q, blk.attn.c_k, blk.attn.c_v):
+                nn.init.uniform_(lin.weight, -s, s)
+            nn.init.zeros_(blk.attn.c_proj.weight)
+            nn.init.uniform_(blk.mlp.c_fc.weight, -s * 0.4, s * 0.4)
+            nn.init.zeros_(blk.mlp.c_proj.weight)
+        denom = max(cfg.n_layer - 1, 1)
+        for i in range(cfg.n_layer):
+            self.resid_lambdas.data[i] = 1.15 - (0.10 * i / denom)
+        for i in range(cfg.n_layer):
+            self.x0_lambdas.data[i] = 0.20 - (0.15 * i / denom)
+        nn.init.zeros_(self.smear_lambda)
+        nn.init.constant_(self.backout_lambda, 0.2)
+        nn.init.uniform_(self.smear_gate.weight, 0.0, 0.02)
+        for ve in self.value_embeds.values():
+            nn.init.uniform_(ve.weight, -s, s)
+        for blk in self.transformer.h:
+            if blk.attn.ve_gate is not None:
+                nn.init.uniform_(blk.attn.ve_gate.weight, 0.0, 0.02)
+        self.build_rotary()
+        dtype = self._resolve_dtype()
+        if dtype != torch.float16:  # embeddings live in the compute dtype (gpt.py:259-265)
+            self.transformer.wte.to(dtype=dtype)
+            for ve in self.value_embeds.values():
+                ve.to(dtype=dtype)
+
+    @torch.inference_mode()
+    def forward(self, idx, targets=None, kv_cache=None, loss_reduction="mean"):
+        """Logits (B, T, vocab) in fp32.  Same arithmetic as gpt.py:416-472; ``targets`` is rejected
+        (no training here)."""
+        if targets is not None:
+            raise NotImplementedError("this GPT is inference-only")
+        B, T = idx.shape
+        dtype = self._resolve_dtype()
+        if self.cos.numel() == 0:
+            self.build_rotary()
+        assert T <= self.cos.size(1), f"Sequence length grew beyond the rotary embeddings cache: {T} > {self.cos.size(1)}"
+        x = rms(self.transformer.wte(idx).to(dtype))
+        if kv_cache is None:
+            assert T > 1, "a forward pass without a KV cache needs T > 1"
+            gate = self.smear_lambda.to(x.dtype) * torch.sigmoid(self.smear_gate(x[:, 1:, :24]))
+            x = torch.cat([x[:, :1], x[:, 1:] + gate * x[:, :-1]], dim=1)
+        else:
+            prev = kv_cache.prev_embedding
+            kv_cache.prev_embedding = x[:, -1:, :]
+            if T > 1:
+                gate = self.smear_lambda.to(x.dtype) * torch.sigmoid(self.smear_gate(x[:, 1:, :24]))
+                x = torch.cat([x[:, :1], x[:, 1:] + gate * x[:, :-1]], dim=1)
+            elif prev is not None:
+                gate = self.smear_lambda.to(x.dtype) * torch.sigmoid(self.smear_gate(x[:, :, :24]))
+                x = x + gate * prev
+        x0 = x
+        backout_at = self.config.n_layer // 2
+        x_backout = None
+        rope_tables = (self.cos, self.sin)
+        for i, block in enumerate(self.transformer.h):
+            x = self.resid_lambdas[i] * x + self.x0_lambdas[i] * x0
+            ve = self.value_embeds[str(i)](idx).to(x.dtype) if str(i) in self.value_embeds else None
+            x = block(x, ve, rope_tables, self.window_sizes[i], kv_cache)
+            if i == backout_at:
+                x_backout = x
+        if x_backout is not None:
+            x = x - self.backout_lambda.to(x.dtype) * x_backout
+        x = rms(x)
+        logits = self.lm_head(x)[..., :self.config.vocab_size].float()
+        return 15 * torch.tanh(logits / 15)
+
+    @torch.inference_mode()
+    def generate(self, tokens, max_tokens, temperature=1.0, top_k=None, seed=42):
+        """Naive generation without a cache, one full forward per token (gpt.py:483-512); kept as
+        the independent check of the cached path (engine.py:307-357)."""
+        assert isinstance(tokens, list)
+        device = self.get_device()
+        rng = None
+        if temperature > 0:
+            rng = torch.Generator(device=device)
+            rng.manual_seed(seed)
+        ids = torch.tensor([tokens], dtype=torch.long, device=device)
+        for _ in range(max_tokens):
+            logits = self.forward(ids)[:, -1, :]
+            if top_k is not None and top_k > 0:
+                vals, _ = torch.topk(logits, min(top_k, logits.size(-1)))
+                logits[logits < vals[:, [-1]]] = -float("inf")
+            if temperature > 0:
+                probs = F.softmax(logits / temperature, dim=-1)
+                nxt = torch.multinomial(probs, num_samples=1, generator=rng)
+            else:
+                nxt = torch.argmax(logits, dim=-1, keepdim=True)
+            ids = torch.cat((ids, nxt), dim=1)
+            yield nxt.item()

@@ -306,3 +306,110 @@ def test_lse_combine_matches_oracle():
     fin = np.isfinite(rl)
     np.testing.assert_allclose(lse.cpu().numpy()[fin], rl[fin], rtol=1e-5, atol=1e-5)
     assert out[9].abs().sum().item() == 0
+
+
+# ------------------------------------------------------------------------------------------------
+# (d) dense prefill attention (tcgen05 / TMEM)
+# ------------------------------------------------------------------------------------------------
+def run_prefill_case(B, T_new, Hq, Hkv, T_k, prefix, window, seed, tol=ATOL):
+    gen = torch.Generator(device=DEV).manual_seed(seed)
+    seqlens = torch.tensor(prefix, device=DEV, dtype=torch.int32)
+    q = torch.randn(B, T_new, Hq, 128, generator=gen, device=DEV).to(BF)
+    k_cache, v_cache = make_cache(B, T_k, Hkv, None, gen)
+    out = ops().prefill_attention(q, k_cache, v_cache, seqlens, window)
+    torch.cuda.synchronize()
+    assert ops().read_status(DEV) == 0
+    ref, _ = O.attention_kvcache(q.float().cpu().numpy(), k_cache.float().cpu().numpy(), v_cache.float().cpu().numpy(),
+                                 np.array(prefix), window_left=window)
+    ref = torch.from_numpy(ref)
+    got = out.float().cpu()
+    assert not torch.isnan(got).any()
+    assert torch.allclose(got, ref, atol=tol, rtol=tol), f"max diff {(got - ref).abs().max().item()}"
+    assert rel_err(got, ref) <= 1e-2
+    return out
+
+
+@pytest.mark.parametrize("B,T_new,Hq,Hkv,T_k,prefix,window", [
+    (2, 16, 2, 2, 48, [0, 0], -1),          # prefill into an empty cache (test_kvcache_prefill shape at D=128)
+    (1, 128, 2, 2, 128, [0], -1),           # exactly one query tile, one and two key tiles
+    (2, 200, 4, 2, 300, [0, 37], -1),       # ragged prefixes, partial tiles, GQA
+    (1, 5, 4, 2, 40, [12], 6),              # chunk with a window (d128_gqa_chunk_window shape)
+    (1, 300, 2, 1, 400, [90], 64),          # window shorter than a key tile's reach
+    (2, 130, 2, 2, 260, [129, 1], 128),
+    (1, 64, 16, 4, 1100, [1000], -1),       # long prefix, short chunk
+])
+def test_prefill_attention_matches_oracle(B, T_new, Hq, Hkv, T_k, prefix, window):
+    run_prefill_case(B, T_new, Hq, Hkv, T_k, prefix, window, seed=T_new + Hq)
+
+
+def test_prefill_attention_ignores_garbage_beyond_length():
+    gen = torch.Generator(device=DEV).manual_seed(5)
+    B, T_new, H, T_k = 1, 70, 2, 256
+    q = torch.randn(B, T_new, H, 128, generator=gen, device=DEV).to(BF)
+    k_cache, v_cache = make_cache(B, T_k, H, None, gen)
+    st = torch.tensor([20], device=DEV, dtype=torch.int32)
+    clean = ops().prefill_attention(q, k_cache, v_cache, st, -1)
+    k_cache[:, 90:] = float("nan")
+    v_cache[:, 90:] = float("inf")
+    dirty = ops().prefill_attention(q, k_cache, v_cache, st, -1)
+    assert torch.equal(bits(clean), bits(dirty))
+
+
+@pytest.mark.parametrize("name", ["causal", "window", "window_ge_T"])
+def test_flash_attn_func_golden(golden_dir, name):
+    from nanochat_b200.flash_attention import flash_attn
+    g = np.load(os.path.join(golden_dir, "attn_func_fp32.npz"))
+    dev = lambda a: torch.from_numpy(a).to(DEV).to(BF)
+    q, k, v = dev(g[f"{name}.q"]), dev(g[f"{name}.k"]), dev(g[f"{name}.v"])
+    window = int(g[f"{name}.window"])
+    out = flash_attn.flash_attn_func(q, k, v, causal=True, window_size=(window, 0))
+    assert out.shape == q.shape
+    assert torch.allclose(out.float().cpu(), torch.from_numpy(g[f"{name}.out"]), atol=3e-2, rtol=3e-2)
+    ref = O.attention_nocache(q.float().cpu().numpy(), k.float().cpu().numpy(), v.float().cpu().numpy(), window_left=window)
+    assert torch.allclose(out.float().cpu(), torch.from_numpy(ref), atol=ATOL, rtol=RTOL)
+
+
+@pytest.mark.parametrize("name", ["d128_prefill", "d128_gqa_chunk_window", "d128_chunk_full"])
+def test_flash_attn_with_kvcache_golden_prefill(golden_dir, name):
+    from nanochat_b200.flash_attention import flash_attn
+    g = np.load(os.path.join(golden_dir, "attn_kvcache_fp32.npz"))
+    dev = lambda a: torch.from_numpy(a).to(DEV).to(BF)
+    q, k, v = dev(g[f"{name}.q"]), dev(g[f"{name}.k"]), dev(g[f"{name}.v"])
+    seqlens = torch.from_numpy(g[f"{name}.seqlens"]).to(DEV)
+    window = int(g[f"{name}.window"])
+    k_after, v_after = dev(g[f"{name}.k_cache_after"]), dev(g[f"{name}.v_cache_after"])
+    L, T_new = int(seqlens[0]), q.size(1)
+    k_cache, v_cache = k_after.clone(), v_after.clone()
+    k_cache[:, L:L + T_new] = 0
+    v_cache[:, L:L + T_new] = 0
+    out = flash_attn.flash_attn_with_kvcache(q, k_cache, v_cache, k=k, v=v, cache_seqlens=seqlens, causal=True,
+                                             window_size=(window, 0))
+    assert torch.equal(bits(k_cache), bits(k_after)) and torch.equal(bits(v_cache), bits(v_after))
+    assert torch.allclose(out.float().cpu(), torch.from_numpy(g[f"{name}.out"]), atol=3e-2, rtol=3e-2)
+
+
+def test_prefill_then_decode_matches_eager_reference_path():
+    """KVCache + two calls + advance, as tests/test_attention_fallback.py:292-334, against the eager bf16 path."""
+    from nanochat_b200.engine import KVCache
+    from nanochat_b200.flash_attention import flash_attn
+    gen = torch.Generator(device=DEV).manual_seed(21)
+    B, T_max, H = 2, 64, 4
+    cache = KVCache(batch_size=B, num_heads=H, seq_len=T_max, head_dim=128, num_layers=1, device=DEV, dtype=BF)
+    k_cache, v_cache = cache.get_layer_cache(0)
+    ref_k, ref_v = k_cache.clone(), v_cache.clone()
+    mk = lambda T: [torch.randn(B, T, H, 128, generator=gen, device=DEV).to(BF) for _ in range(3)]
+    q, k, v = mk(16)
+    y = flash_attn.flash_attn_with_kvcache(q, k_cache, v_cache, k=k, v=v, cache_seqlens=cache.cache_seqlens,
+                                           causal=True, window_size=(T_max, 0))
+    y_ref = E.kvcache_attention(q, ref_k, ref_v, k, v, cache.cache_seqlens, T_max)
+    cache.advance(16)
+    assert y.shape == (B, 16, H, 128) and cache.get_pos() == 16
+    assert torch.allclose(y.float(), y_ref.float(), atol=2e-2, rtol=2e-2)
+    q1, k1, v1 = mk(1)
+    y1 = flash_attn.flash_attn_with_kvcache(q1, k_cache, v_cache, k=k1, v=v1, cache_seqlens=cache.cache_seqlens,
+                                            causal=True, window_size=(T_max, 0))
+    y1_ref = E.kvcache_attention(q1, ref_k, ref_v, k1, v1, cache.cache_seqlens, T_max)
+    cache.advance(1)
+    assert y1.shape == (B, 1, H, 128) and cache.get_pos() == 17
+    assert torch.allclose(y1.float(), y1_ref.float(), atol=2e-2, rtol=2e-2)
+    assert torch.equal(bits(k_cache), bits(ref_k)) and torch.equal(bits(v_cache), bits(ref_v))
