@@ -115,6 +115,31 @@ NCKV_API int nckv_decode_attn(const void *q, const void *k_cache, const void *v_
                      void *stream);
 
 /*
+ * Decode attention without any allocation (no counterpart in the reference; same computation and
+ * arguments as nckv_decode_attn, minus the workspace).
+ *
+ * For callers that cannot obtain device memory at the point of the call: a serving loop that has
+ * handed all of its memory to the KV cache up front, a host thread that may not enter the torch
+ * allocator, a plugin boundary that forbids cudaMalloc.  The split partials and the ticket
+ * counter live in a 14 MiB device array built into the library (held on every GPU that loads it,
+ * until the process exits), so the call performs no cudaMalloc / cudaFree and calls no allocating
+ * routine.  Limits and rules:
+ *   - shapes whose nckv_workspace_bytes() exceeds 14 MiB are rejected with NCKV_E_CAPACITY
+ *     (group sizes Hq/Hkv up to 4 fit, any B up to the per-launch row limit);
+ *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress); make
+ *     that first call outside any stream capture;
+ *   - all calls on a device share the one array: two calls whose kernels can overlap on the GPU
+ *     (different streams, no ordering between them) race on it.  Serialise them;
+ *   - if status_word != NULL it receives the device address of the status word, to be read with
+ *     nckv_read_status().
+ */
+NCKV_API int nckv_decode_attn_static(const void *q, const void *k_cache, const void *v_cache,
+                            const int32_t *cache_seqlens, void *out, float *out_f32, float *lse_out,
+                            int B, int Hq, int Hkv, int D, int T_max, int64_t cache_batch_stride,
+                            int64_t cache_token_stride, int seqlen_offset, int window_left,
+                            int kv_begin, int kv_end, void **status_word, void *stream);
+
+/*
  * Log-sum-exp combine of n_parts partial attention results (the exchange step of the
  * sequence-split long-context path; no counterpart in the reference, which never splits
  * the keys): parts_o is (n_parts, rows, D) fp32 normalised partial outputs, parts_lse is

@@ -891,4 +891,48 @@ int nckv_decode_attn(const void *q, const void *k_cache, const void *v_cache,
     return NCKV_OK;
 }
 
+// ---- decode attention for callers that must not allocate ----------------------------------------
+// Scratch lives in this file-scope device array instead of a caller-provided workspace.  Every GPU
+// that loads the library carries it until the process exits.
+#define NCKV_STATIC_SCRATCH_BYTES (14u << 20)
+static __device__ __align__(256) unsigned char g_static_scratch[NCKV_STATIC_SCRATCH_BYTES];
+
+int nckv_decode_attn_static(const void *q, const void *k_cache, const void *v_cache,
+                            const int32_t *cache_seqlens, void *out, float *out_f32, float *lse_out,
+                            int B, int Hq, int Hkv, int D, int T_max, int64_t cache_batch_stride,
+                            int64_t cache_token_stride, int seqlen_offset, int window_left,
+                            int kv_begin, int kv_end, void **status_word, void *stream) {
+    using namespace nckv;
+    // In host code `g_static_scratch` is only a handle; the address kernels can use has to be
+    // asked for, once per device, with that device current.
+    static void *dev_ptr[64] = {nullptr};
+    int dev = 0;
+    NCKV_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) {
+        set_error("decode_attn_static: device index %d out of range", dev);
+        return NCKV_E_UNSUPPORTED;
+    }
+    if (dev_ptr[dev] == nullptr) {
+        void *ptr = nullptr;
+        NCKV_CUDA_CHECK(cudaGetSymbolAddress(&ptr, g_static_scratch));
+        dev_ptr[dev] = ptr;
+    }
+    const size_t need = nckv_workspace_bytes(B, Hq, Hkv, D);
+    if (need == 0 || need > (size_t)NCKV_STATIC_SCRATCH_BYTES) {
+        set_error("decode_attn_static: this shape needs %zu bytes of scratch, the built-in array holds %u "
+                  "(group size Hq/Hkv up to 4 fits); use nckv_decode_attn with a workspace instead",
+                  need, (unsigned)NCKV_STATIC_SCRATCH_BYTES);
+        return need == 0 ? NCKV_E_UNSUPPORTED : NCKV_E_CAPACITY;
+    }
+    unsigned char *base = static_cast<unsigned char *>(dev_ptr[dev]);
+    if (status_word) *status_word = base;
+    // The array keeps whatever the previous call left.  The ticket counter must start at zero (it
+    // returns to zero by itself unless a call was cut short); the partial records need no clearing,
+    // every record that is read was written by the same call.
+    NCKV_CUDA_CHECK(cudaMemsetAsync(base + 16, 0, sizeof(int32_t), static_cast<cudaStream_t>(stream)));
+    return nckv_decode_attn(q, k_cache, v_cache, cache_seqlens, out, out_f32, lse_out, B, Hq, Hkv, D, T_max,
+                            cache_batch_stride, cache_token_stride, seqlen_offset, window_left, kv_begin, kv_end,
+                            base, NCKV_STATIC_SCRATCH_BYTES, stream);
+}
+
 }  // extern "C"
