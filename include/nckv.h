@@ -142,12 +142,14 @@ NCKV_API int nckv_decode_attn_static(const void *q, const void *k_cache, const v
 /*
  * Log-sum-exp combine of n_parts partial attention results (the exchange step of the
  * sequence-split long-context path; no counterpart in the reference, which never splits
- * the keys): parts_o is (n_parts, rows, D) fp32 normalised partial outputs, parts_lse is
- * (n_parts, rows) fp32; out is (rows, D) bf16, lse_out (optional) is (rows,) fp32.
+ * the keys): parts_o holds n_parts blocks of (rows, D) fp32 normalised partial outputs,
+ * part_stride_o elements apart (>= rows*D, multiple of 4); parts_lse holds n_parts blocks of
+ * (rows,) fp32, part_stride_lse elements apart (>= rows), so the two may be views of one
+ * gathered buffer; out is (rows, D) bf16, lse_out (optional) is (rows,) fp32.
  *   lse = log sum_i exp(lse_i),  out = sum_i exp(lse_i - lse) * o_i ; parts with -inf drop out.
  */
 NCKV_API int nckv_lse_combine(const float *parts_o, const float *parts_lse, int n_parts, int rows, int D,
-                     void *out, float *lse_out, void *stream);
+                     int64_t part_stride_o, int64_t part_stride_lse, void *out, float *lse_out, void *stream);
 
 /*
  * Prefill broadcast: KVCache.prefill (engine.py:123-137).  Copies the first p tokens of a

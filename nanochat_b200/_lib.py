@@ -29,7 +29,7 @@ SIGNATURES = {
                          [c_void_p, c_size_t, c_void_p]),
     "nckv_decode_attn_static": (c_int, [c_void_p] * 7 + [c_int] * 5 + [c_i64, c_i64] + [c_int] * 4 +
                                 [ctypes.POINTER(c_void_p), c_void_p]),
-    "nckv_lse_combine": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "nckv_lse_combine": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_i64, c_i64, c_void_p, c_void_p, c_void_p]),
     "nckv_prefill_broadcast": (c_int, [c_void_p] * 5 + [c_int] * 7 + [c_void_p]),
     "nckv_prefill_attn": (c_int, [c_void_p] * 5 + [c_int] * 6 + [c_i64, c_i64, c_int, c_void_p, c_void_p]),
 }

@@ -10,21 +10,22 @@ namespace nckv {
 
 __global__ void __launch_bounds__(256) lse_combine_kernel(const float *__restrict__ parts_o,
                                                          const float *__restrict__ parts_lse,
-                                                         int n_parts, int rows,
+                                                         int n_parts, int rows, long long stride_o,
+                                                         long long stride_lse,
                                                          __nv_bfloat16 *__restrict__ out,
                                                          float *__restrict__ lse_out) {
     const int lane = threadIdx.x & 31;
     const long long row = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (row >= rows) return;
     float M = -INFINITY;
-    for (int i = 0; i < n_parts; ++i) M = fmaxf(M, parts_lse[(long long)i * rows + row]);
+    for (int i = 0; i < n_parts; ++i) M = fmaxf(M, parts_lse[(long long)i * stride_lse + row]);
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     float L = 0.f;
     if (M > -INFINITY) {
         for (int i = 0; i < n_parts; ++i) {
-            const float w = expf(parts_lse[(long long)i * rows + row] - M);  // exp(-inf) = 0 drops empty parts
+            const float w = expf(parts_lse[(long long)i * stride_lse + row] - M);  // exp(-inf) = 0 drops empty parts
             if (w == 0.f) continue;
-            const float4 v = reinterpret_cast<const float4 *>(parts_o + ((long long)i * rows + row) * NCKV_D)[lane];
+            const float4 v = reinterpret_cast<const float4 *>(parts_o + (long long)i * stride_o + row * NCKV_D)[lane];
             L += w;
             acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
         }
@@ -41,7 +42,8 @@ __global__ void __launch_bounds__(256) lse_combine_kernel(const float *__restric
 }  // namespace nckv
 
 extern "C" int nckv_lse_combine(const float *parts_o, const float *parts_lse, int n_parts, int rows,
-                                int D, void *out, float *lse_out, void *stream) {
+                                int D, int64_t part_stride_o, int64_t part_stride_lse, void *out, float *lse_out,
+                                void *stream) {
     using namespace nckv;
     if (!parts_o || !parts_lse || !out) {
         set_error("lse_combine: null pointer argument");
@@ -55,6 +57,11 @@ extern "C" int nckv_lse_combine(const float *parts_o, const float *parts_lse, in
         set_error("lse_combine: head_dim %d unsupported (kernels are built for 128)", D);
         return NCKV_E_UNSUPPORTED;
     }
+    if (part_stride_o < (int64_t)rows * D || part_stride_lse < rows || (part_stride_o % 4) != 0) {
+        set_error("lse_combine: part strides (%lld, %lld) too small or misaligned for %d rows", (long long)part_stride_o,
+                  (long long)part_stride_lse, rows);
+        return NCKV_E_ARG;
+    }
     if (((uintptr_t)parts_o | (uintptr_t)out) & 15) {
         set_error("lse_combine: tensors must be 16-byte aligned");
         return NCKV_E_ARG;
@@ -62,7 +69,8 @@ extern "C" int nckv_lse_combine(const float *parts_o, const float *parts_lse, in
     const int threads = 256;
     const long long blocks = ((long long)rows * 32 + threads - 1) / threads;
     lse_combine_kernel<<<(unsigned)blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(
-        parts_o, parts_lse, n_parts, rows, static_cast<__nv_bfloat16 *>(out), lse_out);
+        parts_o, parts_lse, n_parts, rows, (long long)part_stride_o, (long long)part_stride_lse,
+        static_cast<__nv_bfloat16 *>(out), lse_out);
     NCKV_CUDA_CHECK(cudaGetLastError());
     return NCKV_OK;
 }

@@ -274,12 +274,17 @@ def _lse_combine(parts_o, parts_lse):
     rows = parts_lse[0].numel()
     if parts_o[0].numel() != rows * D or parts_lse.size(0) != n_parts:
         raise RuntimeError(f"nckv::{name}: shapes {tuple(parts_o.shape)} / {tuple(parts_lse.shape)} do not match")
-    parts_o, parts_lse = parts_o.contiguous(), parts_lse.contiguous()
+    # each part must be dense; the parts themselves may be strided (views of one gathered buffer)
+    if not parts_o[0].is_contiguous() or parts_o.stride(0) % 4 or parts_o.data_ptr() % 16:
+        parts_o = parts_o.contiguous()
+    if not parts_lse[0].is_contiguous():
+        parts_lse = parts_lse.contiguous()
     out = torch.empty(parts_o.shape[1:], dtype=torch.bfloat16, device=parts_o.device)
     lse = torch.empty(parts_lse.shape[1:], dtype=torch.float32, device=parts_o.device)
     with torch.cuda.device(parts_o.device):
-        _lib.call("nckv_lse_combine", _ptr(parts_o), _ptr(parts_lse), n_parts, rows, D, _ptr(out), _ptr(lse),
-                  _stream(parts_o.device))
+        _lib.call("nckv_lse_combine", _ptr(parts_o), _ptr(parts_lse), n_parts, rows, D,
+                  parts_o.stride(0) if n_parts > 1 else rows * D, parts_lse.stride(0) if n_parts > 1 else rows,
+                  _ptr(out), _ptr(lse), _stream(parts_o.device))
     return out, lse
 
 

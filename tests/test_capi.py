@@ -41,11 +41,11 @@ def test_host_side_rejections():
     assert rc == -3 and b"capacity" in _lib.lib.nckv_last_error()
     rc = _lib.lib.nckv_prefill_broadcast(one, one, one, one, null, 1, 2, 9, 1, 128, 8, 16, null)
     assert rc == -3
-    rc = _lib.lib.nckv_lse_combine(one, one, 0, 4, 128, one, null, null)
+    rc = _lib.lib.nckv_lse_combine(one, one, 0, 4, 128, 512, 4, one, null, null)
     assert rc == -1
     assert _lib.lib.nckv_workspace_bytes(1, 3, 2, 128) == 0
     try:
-        _lib.call("nckv_lse_combine", one, one, 2, 4, 64, one, null, null)
+        _lib.call("nckv_lse_combine", one, one, 2, 4, 64, 256, 4, one, null, null)
     except _lib.NckvError as e:
         assert e.code == -2 and "head_dim" in str(e)
     else:

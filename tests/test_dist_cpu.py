@@ -1,0 +1,90 @@
+"""N > 1 host logic on CPU: world_size-2 (and 3) gloo groups exercise the row sharding and the
+key-split exchange (all-gather + log-sum-exp combine) with the oracle standing in for the kernels."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from nanochat_b200.dist import KVSplitAttention, kv_shard_range, shard_rows
+from oracle import kv_oracle as O
+
+
+def test_shard_rows_and_kv_ranges():
+    assert [shard_rows(64, r, 8) for r in range(8)] == [(8 * r, 8 * r + 8) for r in range(8)]
+    assert [shard_rows(10, r, 4) for r in range(4)] == [(0, 3), (3, 6), (6, 8), (8, 10)]
+    with pytest.raises(ValueError):
+        shard_rows(3, 0, 4)  # fewer rows than ranks
+    with pytest.raises(ValueError):
+        shard_rows(8, 4, 4)
+    rng = [kv_shard_range(65536, r, 8) for r in range(8)]
+    assert rng[0] == (0, 8192) and rng[-1] == (57344, 65536)
+    assert all(a[1] == b[0] for a, b in zip(rng, rng[1:]))
+    odd = [kv_shard_range(100, r, 3) for r in range(3)]
+    assert odd == [(0, 64), (64, 100), (100, 100)]  # tile-aligned cuts; the last rank is empty
+    assert all(b % 32 == 0 for b, _ in odd[:2])
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, B, Hq, Hkv, D, T, seqlens, window, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g = torch.Generator().manual_seed(7)  # identical data on every rank
+        q = torch.randn(B, Hq, D, generator=g)
+        kc = torch.randn(B, T, Hkv, D, generator=g)
+        vc = torch.randn(B, T, Hkv, D, generator=g)
+        lens = torch.tensor(seqlens, dtype=torch.int32)
+
+        def partial_fn(q_, kc_, vc_, lens_):
+            o, l = O.attention_kvcache(q_.numpy()[:, None], kc_.numpy(), vc_.numpy(), lens_.numpy(), window_left=window,
+                                       kv_begin=att.kv_begin, kv_end=att.kv_end)
+            if att.kv_end <= att.kv_begin:
+                o[:], l[:] = 0.0, -np.inf
+            return torch.from_numpy(o[:, 0]), torch.from_numpy(l[:, 0])
+
+        def combine_fn(po, pl):
+            o, l = O.lse_combine(po.numpy(), pl.numpy())
+            return torch.from_numpy(o), torch.from_numpy(l)
+
+        att = KVSplitAttention(T, window_left=window, partial_fn=partial_fn, combine_fn=combine_fn)
+        # poison the keys this rank does not own: the result must not depend on them
+        kc_local, vc_local = kc.clone(), vc.clone()
+        kc_local[:, :att.kv_begin] = 1e4
+        kc_local[:, att.kv_end:] = -1e4
+        out = att.attend(q, kc_local, vc_local, lens)
+        full, _ = O.attention_kvcache(q.numpy()[:, None], kc.numpy(), vc.numpy(), lens.numpy(), window_left=window)
+        err = float(np.abs(out.numpy() - full[:, 0]).max())
+        gathered = [None] * world
+        dist.all_gather_object(gathered, err)
+        if rank == 0:
+            ret.put(gathered)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,window", [(2, -1), (2, 40), (3, -1)])
+def test_kv_split_exchange_matches_unsplit_attention(world, window):
+    ctx = mp.get_context("spawn")
+    ret = ctx.Queue()
+    port = _free_port()
+    B, Hq, Hkv, D, T = 3, 4, 2, 16, 100
+    seqlens = [99, 10, 63]  # row 1 leaves the later ranks without keys
+    procs = [ctx.Process(target=_worker, args=(r, world, port, B, Hq, Hkv, D, T,
+                                               seqlens, window, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    errs = ret.get(timeout=10)
+    assert len(errs) == world and max(errs) < 1e-5, errs
+
