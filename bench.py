@@ -35,6 +35,9 @@ if ROOT not in sys.path:
 
 B, HQ, HKV, D, T_MAX = 32, 12, 12, 128, 2048
 NSETS = 4
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode_attn_kernel launch on this workload, from the ncu
+# capture summarised in profiles/decode_attn_config1.md
+TRAFFIC_BYTES_PER_LAUNCH = 201.70e6
 METRIC = "decode tokens/s (KV append + decode attention, B=32 x 12 heads x 128, ragged cache)"
 WORKLOAD = "configs[1]: op-level KV append + decode attention, B=32, 12q/12kv heads, D=128, T_max=2048, ragged seqlens seed 2"
 
@@ -239,7 +242,7 @@ def run_ours(args):
     if rank == 0:
         sampler.start()
         time.sleep(0.5)
-        for _ in range(200):  # keep the GPU under load while the first samples are taken
+        for _ in range(200 if K >= 200 else 0):  # keep the GPU under load while the first samples are taken
             graph.replay()
     barrier(world)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -268,7 +271,7 @@ def run_ours(args):
         attn_only(i)
     torch.cuda.synchronize()
     a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    n_attn = max(K, 200)
+    n_attn = max(K, 200) if K >= 200 else max(K, 10)
     a0.record()
     for i in range(n_attn):
         attn_only(i)
@@ -324,7 +327,7 @@ def run_ours(args):
             "roofline": {"bound": "hbm", "kernel": "decode_attn_kernel + decode_merge_kernel (one nckv_decode_attn call)", "achieved": achieved, "peak": peak,
                          "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak,
                          "frac_of_8000_nominal": achieved / 8000.0, "us_per_launch": attn_ms * 1e3,
-                         "algorithmic_bytes": kv_bytes + other_bytes, "traffic": args.traffic},
+                         "algorithmic_bytes": kv_bytes + other_bytes, "traffic": TRAFFIC_BYTES_PER_LAUNCH},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms, "wall_ms_per_step": e2e_wall_ms},
             "gpu_launches": 3 * k_eff, "device_status": status, "clocks": clocks,
@@ -337,6 +340,94 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------------------------
+# secondary cases (one JSON line each): the other kernels and the other BASELINE configs, op level
+# ------------------------------------------------------------------------------------------------
+def _time_cuda(fn, iters, warmup=3):
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters * 1e-3  # seconds per call
+
+
+def run_case(args):
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    from nanochat_b200 import ops
+    from nanochat_b200.gpt import precompute_rotary_embeddings
+    peak, peak_kind = peaks()
+    gen = torch.Generator(device=dev).manual_seed(4)
+    bf = torch.bfloat16
+    rnd = lambda *shape: torch.randn(*shape, generator=gen, device=dev, dtype=torch.float32).to(bf)
+    iters = max(args.steps, 3)
+    out = {"case": args.case, "n_gpus": 1, "steps": iters, "data": "synthetic", "dtype": "bf16"}
+    if args.case in ("decode_long", "decode_gqa", "decode_gqa_window", "decode_d24"):
+        if args.case == "decode_long":      # configs[4]: long-context op-level decode
+            Bc, Hq, Hkv, T, w, nsets = 8, 16, 4, 65536, -1, 2
+            lens = torch.randint(32768, 65536, (Bc,), dtype=torch.int32, generator=torch.Generator().manual_seed(4))
+        elif args.case == "decode_d24":     # one layer of configs[2] at mid generation
+            Bc, Hq, Hkv, T, w, nsets = 64, 12, 12, 1024, -1, 2
+            lens = torch.full((Bc,), 767, dtype=torch.int32)
+        else:                               # one layer of configs[3]: GQA 16/4, ragged, capacity 4096
+            Bc, Hq, Hkv, T, nsets = 256, 16, 4, 4096, 1
+            w = 2048 if args.case.endswith("window") else -1
+            lens = torch.randint(128, 4095, (Bc,), dtype=torch.int32, generator=torch.Generator().manual_seed(5))
+        sets = [(rnd(Bc, T, Hkv, D), rnd(Bc, T, Hkv, D)) for _ in range(nsets)]
+        q = rnd(Bc, Hq, D)
+        lens_d = lens.to(dev)
+        sec = _time_cuda(lambda i: ops.decode_attention(q, sets[i % nsets][0], sets[i % nsets][1], lens_d, 1, w), iters)
+        n = lens.long() + 1
+        if w >= 0:
+            n = n.clamp(max=w + 1)
+        nbytes = 4 * Hkv * D * int(n.sum()) + 4 * Bc * Hq * D + 4 * Bc
+        out.update(metric="decode attention KV-read GB/s", value=nbytes / sec / 1e9, unit="GB/s", us_per_call=sec * 1e6,
+                   algorithmic_bytes=nbytes, frac=nbytes / sec / 1e9 / peak, peak=peak, peak_kind=f"of {peak_kind}",
+                   config={"B": Bc, "Hq": Hq, "Hkv": Hkv, "T_max": T, "window_left": w})
+    elif args.case == "prefill":            # dense causal attention, d24 shape: 12 heads, T=2048
+        Bc, T, Hq, Hkv = 8, 2048, 12, 12
+        q, k, v = rnd(Bc, T, Hq, D), rnd(Bc, T, Hkv, D), rnd(Bc, T, Hkv, D)
+        sec = _time_cuda(lambda i: ops.prefill_attention(q, k, v, None, -1), iters)
+        flops = 4.0 * D * Bc * Hq * (T * (T + 1) / 2)
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                tpeak = float(json.load(f)["bf16_tflops"])
+        except Exception:
+            tpeak = 1590.0
+        out.update(metric="prefill attention TFLOP/s (causal, useful FLOPs)", value=flops / sec / 1e12, unit="TFLOP/s",
+                   us_per_call=sec * 1e6, frac=flops / sec / 1e12 / tpeak, peak=tpeak,
+                   config={"B": Bc, "T": T, "Hq": Hq, "Hkv": Hkv})
+    elif args.case == "broadcast":          # configs[4]: 8192-token block -> 64 sample rows, one layer
+        L, Bc, p, Hkv = 1, 64, 8192, 4
+        src_k, src_v = rnd(L, 1, p, Hkv, D), rnd(L, 1, p, Hkv, D)
+        dst_k = torch.empty(L, Bc, p, Hkv, D, device=dev, dtype=bf)
+        dst_v = torch.empty_like(dst_k)
+        lens = torch.zeros(Bc, device=dev, dtype=torch.int32)
+        sec = _time_cuda(lambda i: ops.prefill_broadcast(src_k, src_v, dst_k, dst_v, lens, p), iters)
+        nbytes = 2 * L * (Bc + 1) * p * Hkv * D * 2
+        out.update(metric="prefill broadcast GB/s (written + read)", value=nbytes / sec / 1e9, unit="GB/s",
+                   us_per_call=sec * 1e6, algorithmic_bytes=nbytes, frac=nbytes / sec / 1e9 / peak, peak=peak,
+                   peak_kind=f"of {peak_kind}", config={"L": L, "B": Bc, "p": p, "Hkv": Hkv})
+    elif args.case == "append":             # configs[1] append alone
+        kc, vc = rnd(B, T_MAX, HKV, D), rnd(B, T_MAX, HKV, D)
+        q, k, v = rnd(B, 1, HQ, D), rnd(B, 1, HKV, D), rnd(B, 1, HKV, D)
+        cos, sin = precompute_rotary_embeddings(T_MAX, D, device=dev)
+        lens = seqlens_cpu().to(dev)
+        sec = _time_cuda(lambda i: ops.append_rope_norm(q, k, v, kc, vc, lens, cos, sin), iters)
+        nbytes = 2 * B * (HQ + 2 * HKV) * D * 2 + B * D * 2
+        out.update(metric="append us per call", value=sec * 1e6, unit="us", algorithmic_bytes=nbytes,
+                   config={"B": B, "Hq": HQ, "Hkv": HKV})
+    else:
+        raise SystemExit(f"unknown case {args.case}")
+    out["device_status"] = ops.read_status(dev)
+    print(json.dumps(out), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -344,10 +435,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--traffic", type=float, default=None,
-                    help="dram bytes per decode-attention launch from an ncu capture, recorded in the roofline object")
+    ap.add_argument("--case", default=None,
+                    help="secondary op-level measurement instead of the headline workload: decode_long, decode_gqa, "
+                         "decode_gqa_window, decode_d24, prefill, broadcast, append")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.case:
+        run_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
