@@ -17,6 +17,10 @@ RMS_EPS = 1.1920928955078125e-07
 QK_SCALE = 1.2  # gpt.py:101-102
 
 _NS = torch.library.Library("nckv", "DEF")
+_F_APPEND_ROPE = _lib.lib.nckv_append_rope_norm
+_F_APPEND = _lib.lib.nckv_append
+_F_DECODE = _lib.lib.nckv_decode_attn
+_F_PREFILL = _lib.lib.nckv_prefill_attn
 _workspaces = {}  # (device index, stream id) -> uint8 tensor
 
 
@@ -52,6 +56,41 @@ def _cache_strides(name, cache):
     if sd != 1 or sh != HEAD_DIM:
         raise RuntimeError(f"nckv::{name}: cache heads must be packed (strides {cache.stride()})")
     return sb, st
+
+
+class _device_guard:
+    """Make `idx` the current CUDA device for the duration of a call; free when it already is."""
+    __slots__ = ("idx", "prev")
+
+    def __init__(self, idx):
+        self.idx = idx
+        self.prev = -1
+
+    def __enter__(self):
+        cur = torch.cuda.current_device()
+        if cur != self.idx:
+            self.prev = cur
+            torch.cuda.set_device(self.idx)
+
+    def __exit__(self, *exc):
+        if self.prev >= 0:
+            torch.cuda.set_device(self.prev)
+        return False
+
+
+_ws_need = {}  # (B, Hq, Hkv) -> bytes
+
+
+def _launch_ctx(t, B, Hq, Hkv):
+    """(device index, raw stream handle, workspace tensor) for a launch on t's device."""
+    idx = t.device.index
+    stream = torch.cuda.current_stream(idx).cuda_stream
+    ws = _workspaces.get((idx, stream))
+    need = _ws_need.get((B, Hq, Hkv))
+    if ws is None or need is None or ws.numel() < need:
+        ws = workspace(t.device, B, Hq, Hkv)
+        _ws_need[(B, Hq, Hkv)] = _lib.lib.nckv_workspace_bytes(B, Hq, Hkv, HEAD_DIM)
+    return idx, stream, ws
 
 
 def workspace(device, B, Hq, Hkv):
@@ -118,11 +157,13 @@ def _append_rope_norm(q, k, v, k_cache, v_cache, cache_seqlens, cos, sin, qk_sca
         cos2, sin2 = cos2.contiguous(), sin2.contiguous()
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     q_out = torch.empty_like(q)
-    ws = workspace(q.device, B, Hq, Hkv)
-    with torch.cuda.device(q.device):
-        _lib.call("nckv_append_rope_norm", _ptr(q), _ptr(k), _ptr(v), _ptr(q_out), _ptr(k_cache), _ptr(v_cache),
-                  _ptr(cache_seqlens), _ptr(cos2), _ptr(sin2), B, T_new, Hq, Hkv, D, k_cache.size(1), sb, st,
-                  cos2.size(0), float(qk_scale), float(eps), _ptr(ws), _stream(q.device))
+    idx, stream, ws = _launch_ctx(q, B, Hq, Hkv)
+    with _device_guard(idx):
+        rc = _F_APPEND_ROPE(q.data_ptr(), k.data_ptr(), v.data_ptr(), q_out.data_ptr(), k_cache.data_ptr(),
+                            v_cache.data_ptr(), cache_seqlens.data_ptr(), cos2.data_ptr(), sin2.data_ptr(), B, T_new, Hq,
+                            Hkv, D, k_cache.size(1), sb, st, cos2.size(0), qk_scale, eps, ws.data_ptr(), stream)
+    if rc < 0:
+        _lib.check("nckv_append_rope_norm", rc)
     return q_out
 
 
@@ -147,10 +188,12 @@ def _append_kv(k, v, k_cache, v_cache, cache_seqlens):
         raise RuntimeError(f"nckv::{name}: cache {tuple(k_cache.shape)} does not match B={B}, Hkv={Hkv}")
     sb, st = _cache_strides(name, k_cache)
     k, v = k.contiguous(), v.contiguous()
-    ws = workspace(k.device, B, Hkv, Hkv)
-    with torch.cuda.device(k.device):
-        _lib.call("nckv_append", _ptr(k), _ptr(v), _ptr(k_cache), _ptr(v_cache), _ptr(cache_seqlens), B, T_new, Hkv,
-                  D, k_cache.size(1), sb, st, _ptr(ws), _stream(k.device))
+    idx, stream, ws = _launch_ctx(k, B, Hkv, Hkv)
+    with _device_guard(idx):
+        rc = _F_APPEND(k.data_ptr(), v.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), cache_seqlens.data_ptr(), B,
+                       T_new, Hkv, D, k_cache.size(1), sb, st, ws.data_ptr(), stream)
+    if rc < 0:
+        _lib.check("nckv_append", rc)
 
 
 _NS.impl("append_kv", _append_kv, "CUDA")
@@ -163,7 +206,7 @@ _NS.define("decode_attn(Tensor q, Tensor k_cache, Tensor v_cache, Tensor cache_s
            "int window_left, int kv_begin, int kv_end, bool partial) -> (Tensor, Tensor, Tensor)")
 
 
-def _decode_attn(q, k_cache, v_cache, cache_seqlens, seqlen_offset, window_left, kv_begin, kv_end, partial):
+def _decode_attn_core(q, k_cache, v_cache, cache_seqlens, seqlen_offset, window_left, kv_begin, kv_end, partial):
     name = "decode_attn"
     _require_cuda(name, q, k_cache, v_cache, cache_seqlens)
     _require_bf16(name, q, k_cache, v_cache)
@@ -185,18 +228,27 @@ def _decode_attn(q, k_cache, v_cache, cache_seqlens, seqlen_offset, window_left,
         lse = torch.empty(B, Hq, dtype=torch.float32, device=q.device)
     else:
         out_f32 = lse = None
-    ws = workspace(q.device, B, Hq, Hkv)
-    with torch.cuda.device(q.device):
-        _lib.call("nckv_decode_attn", _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(cache_seqlens), _ptr(out),
-                  _ptr(out_f32), _ptr(lse), B, Hq, Hkv, D, k_cache.size(1), sb, st, int(seqlen_offset),
-                  int(window_left), int(kv_begin), int(kv_end), _ptr(ws), ws.numel(), _stream(q.device))
-    if not partial:
+    idx, stream, ws = _launch_ctx(q, B, Hq, Hkv)
+    with _device_guard(idx):
+        rc = _F_DECODE(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), cache_seqlens.data_ptr(), out.data_ptr(),
+                       out_f32.data_ptr() if partial else None, lse.data_ptr() if partial else None, B, Hq, Hkv, D,
+                       k_cache.size(1), sb, st, seqlen_offset, window_left, kv_begin, kv_end, ws.data_ptr(), ws.numel(),
+                       stream)
+    if rc < 0:
+        _lib.check("nckv_decode_attn", rc)
+    return out, out_f32, lse
+
+
+def _decode_attn_op(q, k_cache, v_cache, cache_seqlens, seqlen_offset, window_left, kv_begin, kv_end, partial):
+    out, out_f32, lse = _decode_attn_core(q, k_cache, v_cache, cache_seqlens, seqlen_offset, window_left, kv_begin,
+                                          kv_end, partial)
+    if not partial:  # the op schema returns three tensors
         out_f32, lse = out.new_empty(0, dtype=torch.float32), out.new_empty(0, dtype=torch.float32)
     return out, out_f32, lse
 
 
-_NS.impl("decode_attn", _decode_attn, "CUDA")
-_NS.impl("decode_attn", _decode_attn, "CPU")
+_NS.impl("decode_attn", _decode_attn_op, "CUDA")
+_NS.impl("decode_attn", _decode_attn_op, "CPU")
 
 # ------------------------------------------------------------------------------------------------
 # dense prefill attention (T_new >= 1)
@@ -221,10 +273,12 @@ def _prefill_attn(q, k, v, cache_seqlens, window_left):
     sb, st = _cache_strides(name, k)
     q = q.contiguous()
     out = torch.empty_like(q)
-    ws = workspace(q.device, B, Hq, Hkv)
-    with torch.cuda.device(q.device):
-        _lib.call("nckv_prefill_attn", _ptr(q), _ptr(k), _ptr(v), _ptr(cache_seqlens), _ptr(out), B, T_new, Hq, Hkv,
-                  D, k.size(1), sb, st, int(window_left), _ptr(ws), _stream(q.device))
+    idx, stream, ws = _launch_ctx(q, B, Hq, Hkv)
+    with _device_guard(idx):
+        rc = _F_PREFILL(q.data_ptr(), k.data_ptr(), v.data_ptr(), cache_seqlens.data_ptr() if cache_seqlens is not None else None,
+                        out.data_ptr(), B, T_new, Hq, Hkv, D, k.size(1), sb, st, window_left, ws.data_ptr(), stream)
+    if rc < 0:
+        _lib.check("nckv_prefill_attn", rc)
     return out
 
 
@@ -292,40 +346,41 @@ _NS.impl("lse_combine", _lse_combine, "CUDA")
 _NS.impl("lse_combine", _lse_combine, "CPU")
 
 # ------------------------------------------------------------------------------------------------
-# thin Python entry points
+# thin Python entry points.  They call the op implementations directly (the dispatcher round trip of
+# a Python-defined op costs more than the kernels at decode sizes); the same functions are what
+# ``torch.ops.nckv.*`` dispatches to.
 # ------------------------------------------------------------------------------------------------
-_ops = torch.ops.nckv
 
 
 def append_rope_norm(q, k, v, k_cache, v_cache, cache_seqlens, cos, sin, qk_scale=QK_SCALE, eps=RMS_EPS):
     """RoPE + QK-norm + scale on q and k, append k/v at ``cache_seqlens`` (per row); returns q'."""
-    return _ops.append_rope_norm(q, k, v, k_cache, v_cache, cache_seqlens, cos, sin, qk_scale, eps)
+    return _append_rope_norm(q, k, v, k_cache, v_cache, cache_seqlens, cos, sin, qk_scale, eps)
 
 
 def append_kv(k, v, k_cache, v_cache, cache_seqlens):
     """Write already-transformed k/v at ``cache_seqlens`` (per row)."""
-    _ops.append_kv(k, v, k_cache, v_cache, cache_seqlens)
+    _append_kv(k, v, k_cache, v_cache, cache_seqlens)
 
 
 def decode_attention(q, k_cache, v_cache, cache_seqlens, seqlen_offset=1, window_left=-1, kv_begin=0, kv_end=0,
                      partial=False):
     """One-token attention over the cache. q: (B, Hq, D). With ``partial`` also returns the fp32
     normalised output and the natural-log sum-exp (for a cross-GPU combine)."""
-    out, out_f32, lse = _ops.decode_attn(q, k_cache, v_cache, cache_seqlens, seqlen_offset, window_left, kv_begin,
-                                         kv_end, partial)
+    out, out_f32, lse = _decode_attn_core(q, k_cache, v_cache, cache_seqlens, seqlen_offset, window_left, kv_begin,
+                                          kv_end, partial)
     return (out, out_f32, lse) if partial else out
 
 
 def prefill_attention(q, k, v, cache_seqlens=None, window_left=-1):
     """Dense causal attention of T_new query tokens per row against a cache view or plain k/v."""
-    return _ops.prefill_attn(q, k, v, cache_seqlens, window_left)
+    return _prefill_attn(q, k, v, cache_seqlens, window_left)
 
 
 def prefill_broadcast(src_k, src_v, dst_k, dst_v, dst_seqlens, p):
     """Copy the first p tokens of a batch-1 (L,1,T,H,D) cache into all rows of (L,B,T',H,D)."""
-    _ops.prefill_broadcast(src_k, src_v, dst_k, dst_v, dst_seqlens, p)
+    _prefill_broadcast(src_k, src_v, dst_k, dst_v, dst_seqlens, p)
 
 
 def lse_combine(parts_o, parts_lse):
     """Merge partial attention results over disjoint key ranges; returns (bf16 out, fp32 lse)."""
-    return _ops.lse_combine(parts_o, parts_lse)
+    return _lse_combine(parts_o, parts_lse)

@@ -413,3 +413,22 @@ def test_prefill_then_decode_matches_eager_reference_path():
     assert y1.shape == (B, 1, H, 128) and cache.get_pos() == 17
     assert torch.allclose(y1.float(), y1_ref.float(), atol=2e-2, rtol=2e-2)
     assert torch.equal(bits(k_cache), bits(ref_k)) and torch.equal(bits(v_cache), bits(ref_v))
+
+
+def test_registered_custom_ops_dispatch():
+    """torch.ops.nckv.* (the dispatcher route) gives the same results as the direct entry points."""
+    gen = torch.Generator(device=DEV).manual_seed(31)
+    B, H, T_max = 3, 4, 96
+    st = torch.tensor([5, 50, 94], device=DEV, dtype=torch.int32)
+    q = torch.randn(B, H, 128, generator=gen, device=DEV).to(BF)
+    k_cache, v_cache = make_cache(B, T_max, H, None, gen)
+    a = ops().decode_attention(q, k_cache, v_cache, st)
+    b, e1, e2 = torch.ops.nckv.decode_attn(q, k_cache, v_cache, st, 1, -1, 0, 0, False)
+    assert torch.equal(bits(a), bits(b)) and e1.numel() == 0 and e2.numel() == 0
+    k = torch.randn(B, 1, H, 128, generator=gen, device=DEV).to(BF)
+    kc2, vc2 = k_cache.clone(), v_cache.clone()
+    torch.ops.nckv.append_kv(k, k, kc2, vc2, st)
+    ops().append_kv(k, k, k_cache, v_cache, st)
+    assert torch.equal(bits(kc2), bits(k_cache)) and torch.equal(bits(vc2), bits(v_cache))
+    with pytest.raises(RuntimeError, match="CUDA"):
+        torch.ops.nckv.decode_attn(q.cpu(), k_cache.cpu(), v_cache.cpu(), st.cpu(), 1, -1, 0, 0, False)
