@@ -47,6 +47,7 @@ constexpr int DEC_RING = 4;                           // runs a warp may have cl
 constexpr int DEC_DYN_PER_WARP = 4;                   // at most this many dynamic runs per warp of the grid
 constexpr int DEC_STATIC_NUM = 7, DEC_STATIC_DEN = 10; // statically assigned fraction of the tiles
 constexpr int MERGE_WARPS = 8;
+constexpr int MERGE_BATCH = 16; // O rows fetched per round trip
 constexpr int MERGE_PLAN = 4;  // chunks of 32 parts whose record slots a merge warp works out ahead of time
 
 struct DecodeParams {
@@ -88,17 +89,23 @@ __device__ __forceinline__ void cursor_advance(TileCursor &c, const int *s_pref,
     c.nt = b < B ? s_pref[b + 1] - s_pref[b] : 0;
 }
 
-// Cursor of flat tile index x: the row is the largest b with Hkv * pref[b] <= x.
+// Cursor of flat tile index x: the row is the largest b with Hkv * pref[b] <= x.  Called by a whole
+// warp: lanes test 32 candidate rows at a time and vote.
 __device__ __forceinline__ TileCursor locate_tile(const int *s_pref, int B, int Hkv, int x) {
-    int lo = 0, hi = B;  // invariant: Hkv*pref[lo] <= x < Hkv*pref[hi]
-    while (hi - lo > 1) {
-        int mid = (lo + hi) >> 1;
-        if (Hkv * s_pref[mid] <= x) lo = mid; else hi = mid;
+    const int lane = threadIdx.x & 31;
+    int row = 0;
+    for (int base = 0; base < B; base += 32) {
+        const int b = base + lane;
+        const bool le = b < B && Hkv * s_pref[b] <= x;
+        const unsigned m = __ballot_sync(0xffffffffu, le);
+        if (m == 0) break;            // prefix sums are non-decreasing: nothing further can qualify
+        row = base + 31 - __clz(m);   // highest qualifying row of this block
+        if (m != 0xffffffffu) break;
     }
     TileCursor c;
-    c.b = lo;
-    c.nt = s_pref[lo + 1] - s_pref[lo];
-    const int rel = x - Hkv * s_pref[lo];
+    c.b = row;
+    c.nt = s_pref[row + 1] - s_pref[row];
+    const int rel = x - Hkv * s_pref[row];
     c.h = rel / c.nt;
     c.j = rel - c.h * c.nt;
     return c;
@@ -231,7 +238,9 @@ __device__ __forceinline__ void build_row_tables(const DecodeParams &p, int *s_s
 #define TL_STAMP(i)
 #endif
 
-template <bool GHI>  // GHI: group size 9..16 (rows 8..15 of the MMA tile carry heads too)
+// GHI: group size 9..16 (rows 8..15 of the MMA tile carry heads too).  MAP5: the tensor maps are the
+// 5-D form (one copy per K or V tile) instead of the 4-D form (one copy per 64-channel half).
+template <bool GHI, bool MAP5>
 __global__ void __launch_bounds__(DEC_WARPS * 32, 1)
 decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
                    const __grid_constant__ CUtensorMap tmap_v, const DecodeParams p) {
@@ -275,6 +284,7 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
     RunGeometry geo;
     geo.init(Hkv * s_pref[B], p.W);
     const int gw = blockIdx.x * DEC_WARPS + warp;
+    TL_STAMP(9);
 
     // rows without any visible key: zero output, lse = -inf (only sharded calls can produce them)
     for (int b = blockIdx.x; b < B; b += gridDim.x) {
@@ -287,6 +297,7 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
         if (p.lse) for (int i = tid; i < p.Hq; i += blockDim.x) p.lse[(long long)b * p.Hq + i] = -INFINITY;
     }
     if (geo.total == 0) return;  // every warp of the grid takes this exit together
+    TL_STAMP(10);
 
     uint8_t *my_stages = stages + warp * DEC_STAGES * DEC_STAGE_BYTES;
     uint64_t *my_bar = full_bar + warp * DEC_STAGES;
@@ -298,14 +309,18 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
     int prod_left = 0;       // tiles of the current run not yet issued
     int ring_push = 0, ring_pop = 0;
     int issue_idx = 0;       // tiles issued so far (stage = idx % DEC_STAGES)
-    bool first_claim = true, sched_done = false;
+    bool first_claim = true, sched_done = false, have_ticket = false;
+    unsigned stage_dirty = 0;  // lane 0: stages whose V rows were zeroed by ordinary stores
     int next_ticket = 0;     // lane 0 only: a dynamic ticket drawn ahead of need, so its latency is hidden
 
     auto claim_run = [&]() -> int {  // next run id for this warp; >= W + n_dyn means "no more"
-        if (first_claim) {
+        if (first_claim) {  // the static run; the first ticket is drawn once its loads are in flight
             first_claim = false;
-            if (lane == 0) next_ticket = atomicAdd(p.run_counter, 1);
             return gw;
+        }
+        if (!have_ticket) {  // only when the static run was empty
+            if (lane == 0) next_ticket = atomicAdd(p.run_counter, 1);
+            have_ticket = true;
         }
         const int t = __shfl_sync(0xffffffffu, next_ticket, 0);
         // Tickets n_dyn .. n_dyn + W - 1 are the W terminating ones, one per warp (a warp stops
@@ -334,6 +349,9 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
             }
             prod = locate_tile(s_pref, B, Hkv, run_lo);
             prod_left = n;
+#ifdef NCKV_TIMELINE
+            if (issue_idx == 0) TL_STAMP(11);
+#endif
             if (lane == 0) {
                 RunEntry e;
                 e.k = k; e.n = n; e.start = prod;
@@ -347,21 +365,39 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
             uint8_t *dst = my_stages + stage * DEC_STAGE_BYTES;
             uint64_t *bar = &my_bar[stage];
             const int key0 = s_start[prod.b] + prod.j * DEC_TILE;
-            fence_proxy_async_smem();
+            // the only generic-proxy writes to a stage are the zeroed V rows of a tail tile; order
+            // them before the bulk copy that reuses the stage
+            if (stage_dirty & (1u << stage)) {
+                fence_proxy_async_smem();
+                stage_dirty &= ~(1u << stage);
+            }
             mbar_arrive_expect_tx(bar, DEC_STAGE_BYTES);
             // K/V bytes are used once: evict-first keeps them from flushing q and the partial
             // records out of L2
-            tma_load_4d_hint(dst, &tmap_k, bar, 0, prod.h, key0, prod.b, kv_policy);
-            tma_load_4d_hint(dst + DEC_HALF_BYTES, &tmap_k, bar, 64, prod.h, key0, prod.b, kv_policy);
-            tma_load_4d_hint(dst + 2 * DEC_HALF_BYTES, &tmap_v, bar, 0, prod.h, key0, prod.b, kv_policy);
-            tma_load_4d_hint(dst + 3 * DEC_HALF_BYTES, &tmap_v, bar, 64, prod.h, key0, prod.b, kv_policy);
+            if (MAP5) {
+                tma_load_5d_hint(dst, &tmap_k, bar, 0, key0, 0, prod.h, prod.b, kv_policy);
+                tma_load_5d_hint(dst + 2 * DEC_HALF_BYTES, &tmap_v, bar, 0, key0, 0, prod.h, prod.b, kv_policy);
+            } else {
+                tma_load_4d_hint(dst, &tmap_k, bar, 0, prod.h, key0, prod.b, kv_policy);
+                tma_load_4d_hint(dst + DEC_HALF_BYTES, &tmap_k, bar, 64, prod.h, key0, prod.b, kv_policy);
+                tma_load_4d_hint(dst + 2 * DEC_HALF_BYTES, &tmap_v, bar, 0, prod.h, key0, prod.b, kv_policy);
+                tma_load_4d_hint(dst + 3 * DEC_HALF_BYTES, &tmap_v, bar, 64, prod.h, key0, prod.b, kv_policy);
+            }
         }
+#ifdef NCKV_TIMELINE
+        if (issue_idx == 0) TL_STAMP(12);
+#endif
         ++issue_idx;
         --prod_left;
         cursor_advance(prod, s_pref, B, Hkv);
         return true;
     };
 
+    issue_one();
+    if (!have_ticket) {  // needed once the static run has been issued; by then it has long arrived
+        if (lane == 0) next_ticket = atomicAdd(p.run_counter, 1);
+        have_ticket = true;
+    }
     while (issue_idx < DEC_STAGES && issue_one()) {
     }
     TL_STAMP(2);
@@ -439,6 +475,7 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
                     *reinterpret_cast<uint4 *>(vb + (lane >> 3) * DEC_HALF_BYTES + r * 128 + (lane & 7) * 16) =
                         make_uint4(0, 0, 0, 0);
             }
+            stage_dirty |= 1u << stage;
             __syncwarp();
         }
 
@@ -696,12 +733,12 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) decode_merge_kernel(const De
                 m_i = __ldcg(r2 + G * NCKV_D + hg);
                 l_i = __ldcg(r2 + G * NCKV_D + G + hg);
             }
-            // O rows in batches of 8 predicated loads issued back to back (one round trip per
+            // O rows in batches of MERGE_BATCH predicated loads issued back to back (one round trip per
             // batch instead of one per part); the first batch is in flight during the reductions
-            float4 v[8];
+            float4 v[MERGE_BATCH];
             auto fetch8 = [&](int jb) {
 #pragma unroll
-                for (int u = 0; u < 8; ++u) {
+                for (int u = 0; u < MERGE_BATCH; ++u) {
                     const int slot_j = __shfl_sync(0xffffffffu, my_slot, (jb + u) & 31);
                     v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
                     if (jb + u < cnt)
@@ -721,10 +758,10 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) decode_merge_kernel(const De
             L = L * rescale + cl;
             acc.x *= rescale; acc.y *= rescale; acc.z *= rescale; acc.w *= rescale;
             M = newM;
-            for (int jb = 0; jb < cnt; jb += 8) {
+            for (int jb = 0; jb < cnt; jb += MERGE_BATCH) {
                 if (jb > 0) fetch8(jb);
 #pragma unroll
-                for (int u = 0; u < 8; ++u) {
+                for (int u = 0; u < MERGE_BATCH; ++u) {
                     const float s_j = __shfl_sync(0xffffffffu, sc, (jb + u) & 31);  // 0 for lanes past the chunk
                     acc.x = fmaf(s_j, v[u].x, acc.x); acc.y = fmaf(s_j, v[u].y, acc.y);
                     acc.z = fmaf(s_j, v[u].z, acc.z); acc.w = fmaf(s_j, v[u].w, acc.w);
@@ -836,11 +873,25 @@ int nckv_decode_attn(const void *q, const void *k_cache, const void *v_cache,
         return NCKV_E_CAPACITY;
     }
     const int G = Hq / Hkv;
+    // Prefer the 5-D maps (one copy instruction per tile and tensor); if this driver does not accept
+    // their stride order, use the 4-D maps (two per tile and tensor).  Decided once per process.
+    static int map5_state = 0;  // 0 unknown, 1 usable, -1 refused
     CUtensorMap mk, mv;
-    int rc = make_kv_tensor_map(&mk, k_cache, B, T_max, Hkv, cache_batch_stride, cache_token_stride, DEC_TILE);
-    if (rc != NCKV_OK) return rc;
-    rc = make_kv_tensor_map(&mv, v_cache, B, T_max, Hkv, cache_batch_stride, cache_token_stride, DEC_TILE);
-    if (rc != NCKV_OK) return rc;
+    int rc = NCKV_E_CUDA;
+    if (map5_state >= 0) {
+        rc = make_kv_tensor_map_5d(&mk, k_cache, B, T_max, Hkv, cache_batch_stride, cache_token_stride, DEC_TILE);
+        if (rc == NCKV_OK)
+            rc = make_kv_tensor_map_5d(&mv, v_cache, B, T_max, Hkv, cache_batch_stride, cache_token_stride, DEC_TILE);
+        if (rc == NCKV_E_ARG) return rc;
+        if (map5_state == 0) map5_state = rc == NCKV_OK ? 1 : -1;
+    }
+    const bool map5 = rc == NCKV_OK;
+    if (!map5) {
+        rc = make_kv_tensor_map(&mk, k_cache, B, T_max, Hkv, cache_batch_stride, cache_token_stride, DEC_TILE);
+        if (rc != NCKV_OK) return rc;
+        rc = make_kv_tensor_map(&mv, v_cache, B, T_max, Hkv, cache_batch_stride, cache_token_stride, DEC_TILE);
+        if (rc != NCKV_OK) return rc;
+    }
 
     const int grid = sm_count();
     uint8_t *ws = static_cast<uint8_t *>(workspace);
@@ -866,24 +917,25 @@ int nckv_decode_attn(const void *q, const void *k_cache, const void *v_cache,
 #endif
 
     const size_t smem = decode_smem_bytes();
-    static bool attr_set[64][2] = {{false}};
+    static bool attr_set[64] = {false};
     int dev = 0;
     NCKV_CUDA_CHECK(cudaGetDevice(&dev));
     const bool ghi = G > 8;
-    if (dev < 64 && !attr_set[dev][ghi]) {
-        if (ghi)
-            NCKV_CUDA_CHECK(cudaFuncSetAttribute(decode_attn_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        else
-            NCKV_CUDA_CHECK(cudaFuncSetAttribute(decode_attn_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_set[dev][ghi] = true;
+    if (dev < 64 && !attr_set[dev]) {
+        NCKV_CUDA_CHECK(cudaFuncSetAttribute(decode_attn_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        NCKV_CUDA_CHECK(cudaFuncSetAttribute(decode_attn_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        NCKV_CUDA_CHECK(cudaFuncSetAttribute(decode_attn_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        NCKV_CUDA_CHECK(cudaFuncSetAttribute(decode_attn_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_set[dev] = true;
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // Both launches allow programmatic overlap with their predecessor in the stream: each kernel
     // runs its set-up early and waits (griddepcontrol.wait) before it touches dependent data.
-    if (ghi)
-        NCKV_CUDA_CHECK(launch_pdl(decode_attn_kernel<true>, dim3(grid), dim3(DEC_WARPS * 32), smem, s, true, mk, mv, p));
-    else
-        NCKV_CUDA_CHECK(launch_pdl(decode_attn_kernel<false>, dim3(grid), dim3(DEC_WARPS * 32), smem, s, true, mk, mv, p));
+    const dim3 g3(grid), b3(DEC_WARPS * 32);
+    if (ghi && map5) NCKV_CUDA_CHECK(launch_pdl(decode_attn_kernel<true, true>, g3, b3, smem, s, true, mk, mv, p));
+    else if (ghi) NCKV_CUDA_CHECK(launch_pdl(decode_attn_kernel<true, false>, g3, b3, smem, s, true, mk, mv, p));
+    else if (map5) NCKV_CUDA_CHECK(launch_pdl(decode_attn_kernel<false, true>, g3, b3, smem, s, true, mk, mv, p));
+    else NCKV_CUDA_CHECK(launch_pdl(decode_attn_kernel<false, false>, g3, b3, smem, s, true, mk, mv, p));
     const int items = B * Hq;
     int merge_grid = (items + MERGE_WARPS - 1) / MERGE_WARPS;
     if (merge_grid > 4 * grid) merge_grid = 4 * grid;

@@ -84,6 +84,34 @@ int make_kv_tensor_map(CUtensorMap *map, const void *base, int B, int T, int Hkv
     return NCKV_OK;
 }
 
+// The same view as a 5-D tensor (d_lo[64], t, d_hi[2], h, b): one box of 64 x box_tokens x 2 brings both
+// 64-channel halves of a tile with a single copy instruction and lays them out exactly like two
+// 4-D boxes would ([half][token][128 B], 128-byte swizzle).  Returns NCKV_E_CUDA if the driver
+// refuses the (non-monotonic) stride order; callers then fall back to make_kv_tensor_map.
+int make_kv_tensor_map_5d(CUtensorMap *map, const void *base, int B, int T, int Hkv,
+                          int64_t batch_stride, int64_t token_stride, int box_tokens) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return NCKV_E_CUDA;
+    if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || token_stride < (int64_t)Hkv * NCKV_D ||
+        (token_stride % 8) != 0 || (batch_stride % 8) != 0) {
+        set_error("cache pointer/strides unsuitable for a tensor map");
+        return NCKV_E_ARG;
+    }
+    cuuint64_t dims[5] = {64, (cuuint64_t)T, 2, (cuuint64_t)Hkv, (cuuint64_t)B};
+    cuuint64_t strides[4] = {(cuuint64_t)token_stride * 2, 128, (cuuint64_t)NCKV_D * 2,
+                             B == 1 ? (cuuint64_t)T * token_stride * 2 : (cuuint64_t)batch_stride * 2};
+    cuuint32_t box[5] = {64u, (cuuint32_t)box_tokens, 2u, 1u, 1u};
+    cuuint32_t estr[5] = {1u, 1u, 1u, 1u, 1u};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled (5-D) failed with CUresult %d", (int)r);
+        return NCKV_E_CUDA;
+    }
+    return NCKV_OK;
+}
+
 }  // namespace nckv
 
 extern "C" {

@@ -31,6 +31,9 @@ int sm_count();
 int make_kv_tensor_map(CUtensorMap *map, const void *base, int B, int T, int Hkv,
                        int64_t batch_stride, int64_t token_stride, int box_tokens);
 
+int make_kv_tensor_map_5d(CUtensorMap *map, const void *base, int B, int T, int Hkv,
+                          int64_t batch_stride, int64_t token_stride, int box_tokens);
+
 // ---- device helpers ----------------------------------------------------------------------
 #ifdef __CUDACC__
 
@@ -138,6 +141,14 @@ __device__ __forceinline__ void tma_load_5d(void *smem_dst, const CUtensorMap *m
         "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes"
         " [%0], [%1, {%2, %3, %4, %5, %6}], [%7];" ::"r"(smem_u32(smem_dst)),
         "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_5d_hint(void *smem_dst, const CUtensorMap *map, uint64_t *bar,
+                                                 int c0, int c1, int c2, int c3, int c4, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%2, %3, %4, %5, %6}], [%7], %8;" ::"r"(smem_u32(smem_dst)),
+        "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(smem_u32(bar)), "l"(policy)
         : "memory");
 }
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *map) {
