@@ -646,7 +646,7 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
     if (timed_out) {
         if (lane == 0) atomicOr(p.status, (int)NCKV_ST_TIMEOUT);
         // give copies already issued a bounded chance to land before the CTA's memory is released
-        for (int s = 0; s < DEC_STAGES; ++s) mbar_wait_bounded(&my_bar[s], 0, 1u << 12);
+        for (int s = 0; s < DEC_STAGES; ++s) mbar_wait_bounded(&my_bar[s], 0, 1000000ull);
         // leave the ticket counter consistent: draw (without working on them) until this warp
         // has taken its terminating ticket
         for (int guard = 0; !sched_done && guard < geo.n_dyn + geo.W + 1; ++guard) {

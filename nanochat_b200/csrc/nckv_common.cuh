@@ -86,14 +86,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after `limit` polls (each poll may itself suspend for a
-// hardware-defined time slice) and reports failure instead of spinning for ever.
+// Bounded wait: polls until the phase completes or about `limit_ns` of wall time have passed
+// (each poll may suspend for a short, hardware-defined slice) and reports failure instead of
+// spinning for ever.
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+constexpr unsigned long long NCKV_WAIT_LIMIT_NS = 2000000000ull;  // 2 s: far beyond any legitimate wait
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity,
-                                                  uint32_t limit = (1u << 22)) {
-    for (uint32_t i = 0; i < limit; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
+                                                  unsigned long long limit_ns = NCKV_WAIT_LIMIT_NS) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_timer_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; ++i) {
+            if (mbar_try_wait(bar, parity)) return true;
+        }
+        if (global_timer_ns() - t0 > limit_ns) return false;
     }
-    return false;
 }
 
 __device__ __forceinline__ void fence_proxy_async_smem() {

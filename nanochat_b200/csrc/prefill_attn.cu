@@ -10,9 +10,12 @@
 //                     into registers, causal / window masking is done by index, running max and
 //                     sum are per-thread scalars, P is rounded to bf16 and written to shared
 //                     memory in the K-major swizzled layout the next product reads
-//   3. O_t = P V      4 x tcgen05.mma (M128 N128 K16), V used in place as an MN-major operand,
-//                     into TMEM columns [128, 256)
-//   4. O = a*O + O_t  tcgen05.ld, accumulation in registers with the softmax rescale a
+//   3. O += P V       4 x tcgen05.mma (M128 N128 K16), V used in place as an MN-major operand,
+//                     accumulating in TMEM columns [128, 256) over all tiles; S of the next tile is
+//                     issued straight behind it.  P is scaled by a running max that is only raised
+//                     when the true max has grown by more than 2^8; only then is the O row
+//                     rescaled in TMEM (tcgen05.ld / multiply / tcgen05.st), so most tiles touch
+//                     the accumulator not at all.  O is read once, at the end.
 // K/V tiles are double buffered.  Two CTAs fit on an SM (about 112 KB of shared memory and 256 of
 // the 512 TMEM columns each), so one CTA's softmax overlaps the other's tensor work.
 // Every barrier wait is bounded; a wait that runs out sets NCKV_ST_TIMEOUT, the CTA stops issuing
@@ -34,7 +37,7 @@ constexpr int PF_Q_BYTES = PF_M * NCKV_D * 2;        // 32 KB: two 64-channel ha
 constexpr int PF_KV_BYTES = PF_N * NCKV_D * 2;       // 16 KB: two halves of [64][128 B]
 constexpr int PF_P_BYTES = PF_M * PF_N * 2;          // 16 KB: [128][128 B]
 constexpr int PF_TMEM_COLS = 256;                    // S: [0,64)  O tile: [128,256)
-constexpr uint32_t PF_WAIT_LIMIT = 1u << 22;
+constexpr unsigned long long PF_WAIT_LIMIT = NCKV_WAIT_LIMIT_NS;
 
 struct PrefillParams {
     const int32_t *seqlens;  // may be null (all zero)
@@ -92,6 +95,23 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
     tmem_wait_ld();
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+          "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+          "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+          "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+          "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])),
+          "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])),
+          "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])),
+          "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])),
+          "r"(__float_as_uint(v[31]))
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
 // Shared-memory matrix descriptor (128-byte swizzle).  Fields: start address >> 4 in bits 0..13,
@@ -209,10 +229,10 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     constexpr uint32_t IDESC_S = umma_idesc(PF_M, PF_N, 0, 0);
     constexpr uint32_t IDESC_O = umma_idesc(PF_M, NCKV_D, 0, 1);
 
-    float o_reg[NCKV_D];
-#pragma unroll
-    for (int i = 0; i < NCKV_D; ++i) o_reg[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
+    // Softmax state of this thread's row.  P is scaled by m_used, which follows the true running
+    // max lazily: it is only raised (and the O row in TMEM rescaled) when the max has grown by more
+    // than 2^8, so exp2(s - m_used) stays <= 256 and most tiles need no rescale at all.
+    float m_used = -INFINITY, l_run = 0.f;
     const int row = tid;               // query row inside the tile == TMEM lane
     const int pos = L + t0 + row;      // absolute position of this row's token
     bool aborted = false;
@@ -223,57 +243,101 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         atomicOr(p.status, (int)NCKV_ST_TIMEOUT);
         return false;
     };
+    // thread 0: S(tile) = Q K(tile)^T into TMEM columns [0, 64), then arrive on bar_s
+    auto issue_s = [&](int tile) {
+        const int stage = tile % PF_STAGES;
+        bool ok = tile > 0 || wait_or_abort(bar_q, 0);
+        ok = ok && wait_or_abort(&bar_k[stage], (uint32_t)((tile / PF_STAGES) & 1));
+        if (ok) {
+            tc_fence_after();
+            const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + stage * PF_KV_BYTES);
+#pragma unroll
+            for (int kk = 0; kk < NCKV_D / 16; ++kk) {
+                const uint32_t off = (uint32_t)(kk & 3) * 32;
+                const uint64_t da = smem_desc_sw128(qa + (kk >> 2) * (PF_Q_BYTES / 2) + off, 16, 1024);
+                const uint64_t db = smem_desc_sw128(ka + (kk >> 2) * (PF_KV_BYTES / 2) + off, 16, 1024);
+                umma_bf16(tmem_s, da, db, IDESC_S, kk > 0 ? 1u : 0u);
+            }
+        }
+        umma_commit(bar_s);  // also on the abort path: nobody may be left waiting without a bound
+    };
+    // thread 0: O (+)= P V(tile) into TMEM columns [128, 256), then arrive on bar_o
+    auto issue_pv = [&](int tile) {
+        const int stage = tile % PF_STAGES;
+        if (wait_or_abort(&bar_v[stage], (uint32_t)((tile / PF_STAGES) & 1))) {
+            tc_fence_after();
+            const uint32_t pa = smem_u32(sP), va = smem_u32(sV + stage * PF_KV_BYTES);
+#pragma unroll
+            for (int ks = 0; ks < PF_N / 16; ++ks) {
+                const uint64_t da = smem_desc_sw128(pa + ks * 32, 16, 1024);
+                // V in place: N (channels) contiguous, the two 64-channel halves PF_KV_BYTES/2 apart
+                // (leading offset), 8-key groups 1024 B apart (stride offset)
+                const uint64_t db = smem_desc_sw128(va + ks * 16 * 128, PF_KV_BYTES / 2, 1024);
+                umma_bf16(tmem_o, da, db, IDESC_O, (tile > 0 || ks > 0) ? 1u : 0u);
+            }
+        }
+        umma_commit(bar_o);
+    };
+
+    if (tid == 0 && n_tiles > 0) issue_s(0);
 
     for (int it = 0; it < n_tiles; ++it) {
         const int stage = it % PF_STAGES;
         const uint32_t kv_parity = (uint32_t)((it / PF_STAGES) & 1);
-        const uint32_t it_parity = (uint32_t)(it & 1);
         const int key0 = kv_lo + it * PF_N;
 
-        // ---- 1. S = Q K^T ------------------------------------------------------------------
-        if (tid == 0) {
-            bool ok = it > 0 || wait_or_abort(bar_q, 0);
-            ok = ok && wait_or_abort(&bar_k[stage], kv_parity);
-            if (ok) {
-                tc_fence_after();
-                const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + stage * PF_KV_BYTES);
-#pragma unroll
-                for (int kk = 0; kk < NCKV_D / 16; ++kk) {
-                    const uint32_t off = (uint32_t)(kk & 3) * 32;
-                    const uint64_t da = smem_desc_sw128(qa + (kk >> 2) * (PF_Q_BYTES / 2) + off, 16, 1024);
-                    const uint64_t db = smem_desc_sw128(ka + (kk >> 2) * (PF_KV_BYTES / 2) + off, 16, 1024);
-                    umma_bf16(tmem_s, da, db, IDESC_S, kk > 0 ? 1u : 0u);
-                }
-            }
-            umma_commit(bar_s);  // also on the abort path: nobody may be left waiting without a bound
-        }
-        if (!mbar_wait_bounded(bar_s, it_parity, PF_WAIT_LIMIT)) {
+        // ---- S(it) is complete; the tensor pipe works in issue order, so O (+)= P V of tile it-1 is
+        //      complete too: its P buffer, its K/V stage and the O accumulator are ours again -----
+        if (!mbar_wait_bounded(bar_s, (uint32_t)(it & 1), PF_WAIT_LIMIT)) {
             *abort_flag = 1;
             atomicOr(p.status, (int)NCKV_ST_TIMEOUT);
         }
         tc_fence_after();
+        if (tid == 0 && it >= 1 && it + 1 < n_tiles) load_kv(it + 1, (it + 1) % PF_STAGES);
 
-        // ---- 2. softmax on row `row` ---------------------------------------------------------
+        // ---- softmax on row `row` ------------------------------------------------------------
         float s_val[PF_N];
         {
             float c0[32], c1[32];
             tmem_ld32(tmem_s + lane_sel, c0);
             tmem_ld32(tmem_s + lane_sel + 32, c1);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) { s_val[i] = c0[i]; s_val[32 + i] = c1[i]; }
+            for (int i = 0; i < 32; ++i) { s_val[i] = c0[i] * p.scale_log2; s_val[32 + i] = c1[i] * p.scale_log2; }
+        }
+        // only tiles that touch the causal diagonal, the window edge or the end of the keys need
+        // per-element masking (uniform over the CTA)
+        const bool edge = (key0 + PF_N - 1 > L + t0) || (key0 + PF_N > kv_hi) ||
+                          (p.window_left >= 0 && key0 < L + t0 + PF_M - 1 - p.window_left);
+        if (edge) {
+#pragma unroll
+            for (int c = 0; c < PF_N; ++c) {
+                const int j = key0 + c;
+                const bool visible = (j <= pos) && (j < kv_hi) && (p.window_left < 0 || pos - j <= p.window_left);
+                s_val[c] = visible ? s_val[c] : -INFINITY;
+            }
         }
         float mx = -INFINITY;
 #pragma unroll
-        for (int c = 0; c < PF_N; ++c) {
-            const int j = key0 + c;
-            const bool visible = (j <= pos) && (j < kv_hi) && (p.window_left < 0 || pos - j <= p.window_left);
-            s_val[c] = visible ? s_val[c] * p.scale_log2 : -INFINITY;
-            mx = fmaxf(mx, s_val[c]);
+        for (int c = 0; c < PF_N; ++c) mx = fmaxf(mx, s_val[c]);
+        // tcgen05.ld/st are warp-wide (.sync.aligned): the decision to touch the accumulator is
+        // taken per warp, every lane then applies its own factor (1 for rows that keep their scale)
+        const bool raise = mx > m_used + 8.f;  // also the first tile that shows this row a key (m_used = -inf)
+        const float alpha = raise ? exp2f(m_used - mx) : 1.f;  // exp2(-inf) = 0
+        if (it > 0 && __any_sync(0xffffffffu, raise)) {  // bring the O rows accumulated so far to the new scale
+#pragma unroll
+            for (int ch = 0; ch < NCKV_D / 32; ++ch) {
+                float c[32];
+                tmem_ld32(tmem_o + lane_sel + ch * 32, c);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) c[i] *= alpha;
+                tmem_st32(tmem_o + lane_sel + ch * 32, c);
+            }
         }
-        const float m_new = fmaxf(m_run, mx);
-        const float m_use = m_new == -INFINITY ? 0.f : m_new;  // a row that has seen no key yet
-        const float alpha = exp2f(m_run - m_use);               // exp2(-inf) = 0 on the first tile
-        m_run = m_new;
+        if (raise) {
+            l_run *= alpha;
+            m_used = mx;
+        }
+        const float m_use = m_used == -INFINITY ? 0.f : m_used;  // a row that has seen no key yet
         float rsum = 0.f;
         uint32_t pk[PF_N / 2];
 #pragma unroll
@@ -282,7 +346,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             rsum += p0 + p1;
             pk[c / 2] = pack_bf16x2(p0, p1);
         }
-        l_run = l_run * alpha + rsum;
+        l_run += rsum;
         // P row -> shared memory, K-major with the 128-byte swizzle (16-byte chunk c ^ (row % 8))
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
@@ -302,62 +366,53 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             }
         }
         fence_proxy_async_smem();  // P (and the zeroed V rows) must be visible to the tensor core
-        tc_fence_before();
+        tc_fence_before();         // orders this thread's TMEM loads/stores before the next MMAs
         __syncthreads();
         aborted = *abort_flag != 0;
         if (aborted) break;
 
-        // ---- 3. O_t = P V ------------------------------------------------------------------
+        // ---- O (+)= P V(it), and straight behind it S(it+1): the tensor pipe stays fed while
+        //      this CTA's threads wait, and the other CTA of the SM runs its softmax ------------
         if (tid == 0) {
-            const bool ok = wait_or_abort(&bar_v[stage], kv_parity);
-            if (ok) {
-                tc_fence_after();
-                const uint32_t pa = smem_u32(sP), va = smem_u32(sV + stage * PF_KV_BYTES);
-#pragma unroll
-                for (int ks = 0; ks < PF_N / 16; ++ks) {
-                    const uint64_t da = smem_desc_sw128(pa + ks * 32, 16, 1024);
-                    // V in place: N (channels) contiguous, the two 64-channel halves PF_KV_BYTES/2
-                    // apart (leading offset), 8-key groups 1024 B apart (stride offset)
-                    const uint64_t db = smem_desc_sw128(va + ks * 16 * 128, PF_KV_BYTES / 2, 1024);
-                    umma_bf16(tmem_o, da, db, IDESC_O, ks > 0 ? 1u : 0u);
-                }
-            }
-            umma_commit(bar_o);
+            issue_pv(it);
+            if (it + 1 < n_tiles) issue_s(it + 1);
         }
-        if (!mbar_wait_bounded(bar_o, it_parity, PF_WAIT_LIMIT)) {
-            *abort_flag = 1;
-            atomicOr(p.status, (int)NCKV_ST_TIMEOUT);
-        }
-        tc_fence_after();
-
-        // ---- 4. O = alpha * O + O_t ----------------------------------------------------------
-#pragma unroll
-        for (int ch = 0; ch < NCKV_D / 32; ++ch) {
-            float c[32];
-            tmem_ld32(tmem_o + lane_sel + ch * 32, c);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o_reg[ch * 32 + i] = fmaf(o_reg[ch * 32 + i], alpha, c[i]);
-        }
-        tc_fence_before();
-        __syncthreads();  // S, O_t, P and this K/V stage are free again
-        aborted = *abort_flag != 0;
-        if (aborted) break;
-        if (tid == 0 && it + PF_STAGES < n_tiles) load_kv(it + PF_STAGES, stage);
     }
 
     // ---- epilogue -----------------------------------------------------------------------------
     const int t = t0 + row;
-    if (!aborted && t < p.T_new) {
-        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+    if (!aborted && n_tiles > 0) {
+        if (!mbar_wait_bounded(bar_o, (uint32_t)((n_tiles - 1) & 1), PF_WAIT_LIMIT)) {
+            *abort_flag = 1;
+            atomicOr(p.status, (int)NCKV_ST_TIMEOUT);
+            aborted = true;
+        }
+        tc_fence_after();
+    }
+    aborted = __any_sync(0xffffffffu, aborted);  // keep the warp together for the TMEM loads below
+    if (!aborted) {  // uniform over the CTA: the TMEM loads below are warp-wide instructions
+        const float inv = (n_tiles > 0 && l_run > 0.f) ? 1.f / l_run : 0.f;
         uint4 *dst = reinterpret_cast<uint4 *>(p.out + (((long long)b * p.T_new + t) * p.Hq + hq) * NCKV_D);
 #pragma unroll
-        for (int c = 0; c < NCKV_D / 8; ++c) {
-            uint4 v;
-            v.x = pack_bf16x2(o_reg[8 * c + 0] * inv, o_reg[8 * c + 1] * inv);
-            v.y = pack_bf16x2(o_reg[8 * c + 2] * inv, o_reg[8 * c + 3] * inv);
-            v.z = pack_bf16x2(o_reg[8 * c + 4] * inv, o_reg[8 * c + 5] * inv);
-            v.w = pack_bf16x2(o_reg[8 * c + 6] * inv, o_reg[8 * c + 7] * inv);
-            dst[c] = v;
+        for (int ch = 0; ch < NCKV_D / 32; ++ch) {
+            float c[32];
+            if (n_tiles > 0) {
+                tmem_ld32(tmem_o + lane_sel + ch * 32, c);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) c[i] = 0.f;
+            }
+            if (t < p.T_new) {  // rows past the end of the sequence are padding
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    uint4 v;
+                    v.x = pack_bf16x2(c[8 * i + 0] * inv, c[8 * i + 1] * inv);
+                    v.y = pack_bf16x2(c[8 * i + 2] * inv, c[8 * i + 3] * inv);
+                    v.z = pack_bf16x2(c[8 * i + 4] * inv, c[8 * i + 5] * inv);
+                    v.w = pack_bf16x2(c[8 * i + 6] * inv, c[8 * i + 7] * inv);
+                    dst[ch * 4 + i] = v;
+                }
+            }
         }
     }
     tc_fence_before();
