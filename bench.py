@@ -282,26 +282,18 @@ def run_ours(args):
     clocks = sampler.stop() if rank == 0 else None
 
     # ---- e2e: public call, host buffers ------------------------------------------------------------
-    # host side of a step: q, k, v of the new token in ONE pinned buffer (one H2D copy), output pinned (D2H)
-    nq, nk = q.numel(), k.numel()
-    host_in = torch.empty(nq + 2 * nk, dtype=torch.bfloat16).pin_memory()
-    host_in[:nq].copy_(q.reshape(-1).cpu())
-    host_in[nq:nq + nk].copy_(k.reshape(-1).cpu())
-    host_in[nq + nk:].copy_(v.reshape(-1).cpu())
-    dev_in = torch.empty_like(host_in, device=dev)
-    qd, kd, vd = dev_in[:nq].view_as(q), dev_in[nq:nq + nk].view_as(k), dev_in[nq + nk:].view_as(v)
-    out_h = torch.empty(B, HQ, D, dtype=torch.bfloat16).pin_memory()
-    h2d = host_in.numel() * 2
-    d2h = out_h.numel() * 2
-    cur = torch.cuda.current_stream(dev)
+    # host side of a step: q, k, v of the new token in one pinned block (H2D), the output pinned (D2H);
+    # one public call per step (ops.HostDecodeStep.run -> nckv_decode_step_host), which synchronises
+    host_step = ops.HostDecodeStep(B, HQ, HKV, cos, sin, dev)
+    host_step.q.copy_(q[:, 0].cpu())
+    host_step.k.copy_(k[:, 0].cpu())
+    host_step.v.copy_(v[:, 0].cpu())
+    h2d = host_step.host_in.numel() * 2
+    d2h = host_step.out.numel() * 2
 
     def e2e_step(i):
-        dev_in.copy_(host_in, non_blocking=True)
         kc, vc = sets[i % NSETS]
-        q3 = ops.append_rope_norm(qd, kd, vd, kc, vc, seqlens, cos, sin)
-        o = ops.decode_attention(q3[:, 0], kc, vc, seqlens, seqlen_offset=1, window_left=-1)
-        out_h.copy_(o, non_blocking=True)
-        cur.synchronize()
+        return host_step.run(kc, vc, seqlens, -1)
 
     for i in range(max(W, 3)):
         e2e_step(i)

@@ -95,6 +95,21 @@ NCKV_API int nckv_append(const void *k_in, const void *v_in, void *k_cache, void
                 void *stream);
 
 /*
+ * One whole decode step of a layer for host-resident activations: the KV branch of
+ * CausalSelfAttention.forward (gpt.py:97-121) for T == 1, including the copies the reference's
+ * callers do around it (engine.py:279: ids to the device; the result read back on the host).
+ * qkv_host: pinned host block [q (B,Hq,D) | k (B,Hkv,D) | v (B,Hkv,D)] bf16; qkv_dev: device block of
+ * the same size; q_rot_dev, out_dev: device (B,Hq,D) bf16 scratch/result; out_host: pinned host
+ * (B,Hq,D) bf16.  Performs H2D, nckv_append_rope_norm, nckv_decode_attn, D2H and a stream
+ * synchronise; on return out_host holds the attention output.  cache_seqlens is not advanced.
+ */
+NCKV_API int nckv_decode_step_host(const void *qkv_host, void *qkv_dev, void *q_rot_dev, void *out_dev, void *out_host,
+                          void *k_cache, void *v_cache, const int32_t *cache_seqlens, const void *cos,
+                          const void *sin, int B, int Hq, int Hkv, int D, int T_max, int64_t cache_batch_stride,
+                          int64_t cache_token_stride, int rope_len, float qk_scale, float eps, int window_left,
+                          void *workspace, size_t workspace_bytes, void *stream);
+
+/*
  * Split-KV decode attention, one query token per row (T_new == 1).
  * Replaces the Tq == 1 branch of _sdpa_attention (flash_attention.py:83-89) as reached
  * from flash_attn_with_kvcache (flash_attention.py:165-177), with per-row lengths:

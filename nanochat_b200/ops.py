@@ -384,3 +384,53 @@ def prefill_broadcast(src_k, src_v, dst_k, dst_v, dst_seqlens, p):
 def lse_combine(parts_o, parts_lse):
     """Merge partial attention results over disjoint key ranges; returns (bf16 out, fp32 lse)."""
     return _lse_combine(parts_o, parts_lse)
+
+
+class HostDecodeStep:
+    """A decode step of one layer for activations that live in host memory.
+
+    Owns the pinned host blocks and the device staging buffers of a fixed (B, Hq, Hkv) shape;
+    ``run(k_cache, v_cache, cache_seqlens, window_left)`` copies ``self.q / self.k / self.v`` (views of
+    one pinned block, fill them in place) to the device, runs the fused append and the decode
+    attention, and returns ``self.out`` (pinned host, valid on return: the call synchronises).
+    One C-ABI call per step (nckv_decode_step_host)."""
+
+    def __init__(self, B, Hq, Hkv, cos, sin, device, qk_scale=QK_SCALE, eps=RMS_EPS):
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError("HostDecodeStep needs a CUDA device; the KV-cache decode path has no CPU implementation")
+        self.B, self.Hq, self.Hkv = B, Hq, Hkv
+        nq, nk = B * Hq * HEAD_DIM, B * Hkv * HEAD_DIM
+        self.host_in = torch.empty(nq + 2 * nk, dtype=torch.bfloat16).pin_memory()
+        self.q = self.host_in[:nq].view(B, Hq, HEAD_DIM)
+        self.k = self.host_in[nq:nq + nk].view(B, Hkv, HEAD_DIM)
+        self.v = self.host_in[nq + nk:].view(B, Hkv, HEAD_DIM)
+        self.out = torch.empty(B, Hq, HEAD_DIM, dtype=torch.bfloat16).pin_memory()
+        self._dev_in = torch.empty(nq + 2 * nk, dtype=torch.bfloat16, device=self.device)
+        self._q_rot = torch.empty(B, Hq, HEAD_DIM, dtype=torch.bfloat16, device=self.device)
+        self._out_dev = torch.empty_like(self._q_rot)
+        _require_bf16("decode_step_host", cos, sin)
+        self._cos = cos.reshape(-1, HEAD_DIM // 2).contiguous()
+        self._sin = sin.reshape(-1, HEAD_DIM // 2).contiguous()
+        self.qk_scale, self.eps = qk_scale, eps
+        self._fn = _lib.lib.nckv_decode_step_host
+
+    def run(self, k_cache, v_cache, cache_seqlens, window_left=-1):
+        name = "decode_step_host"
+        _require_cuda(name, k_cache, v_cache, cache_seqlens)
+        _require_bf16(name, k_cache, v_cache)
+        if k_cache.shape != v_cache.shape or k_cache.stride() != v_cache.stride():
+            raise RuntimeError(f"nckv::{name}: k_cache and v_cache must share shape and strides")
+        if k_cache.size(0) != self.B or k_cache.size(2) != self.Hkv or cache_seqlens.dtype != torch.int32:
+            raise RuntimeError(f"nckv::{name}: cache {tuple(k_cache.shape)} / seqlens do not match B={self.B}, Hkv={self.Hkv}")
+        sb, st = _cache_strides(name, k_cache)
+        idx, stream, ws = _launch_ctx(k_cache, self.B, self.Hq, self.Hkv)
+        with _device_guard(idx):
+            rc = self._fn(self.host_in.data_ptr(), self._dev_in.data_ptr(), self._q_rot.data_ptr(), self._out_dev.data_ptr(),
+                          self.out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), cache_seqlens.data_ptr(),
+                          self._cos.data_ptr(), self._sin.data_ptr(), self.B, self.Hq, self.Hkv, HEAD_DIM, k_cache.size(1),
+                          sb, st, self._cos.size(0), self.qk_scale, self.eps, int(window_left), ws.data_ptr(), ws.numel(),
+                          stream)
+        if rc < 0:
+            _lib.check("nckv_decode_step_host", rc)
+        return self.out

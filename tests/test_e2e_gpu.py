@@ -132,3 +132,65 @@ def test_config0_cache_bytes_and_seqlens_bit_exact():
         assert torch.allclose(ka.float(), kb.float(), atol=6e-2, rtol=6e-2)
     for x, y in zip(logits_a, logits_b):
         assert torch.allclose(x, y, atol=5e-2, rtol=5e-2)
+
+
+def test_ragged_batch_equals_rows_run_alone():
+    """Per-row positions end to end (the configs[3] situation: GQA, ragged prompt lengths, windows):
+    rows of different lengths decoded together must give what each row gives alone."""
+    from nanochat_b200.engine import KVCache
+    from nanochat_b200.gpt import GPT, GPTConfig
+    cfg = GPTConfig(sequence_len=256, vocab_size=1024, n_layer=3, n_head=4, n_kv_head=1, n_embd=512, window_pattern="SL")
+    torch.manual_seed(5)
+    model = GPT(cfg, compute_dtype=torch.bfloat16).to(DEV)
+    model.init_weights()
+    s = 3 ** 0.5 * cfg.n_embd ** -0.5
+    for blk in model.transformer.h:  # let attention reach the logits
+        torch.nn.init.uniform_(blk.attn.c_proj.weight, -s, s)
+        torch.nn.init.uniform_(blk.mlp.c_proj.weight, -s, s)
+    torch.nn.init.normal_(model.lm_head.weight, mean=0.0, std=0.02)
+    model.smear_lambda.data.fill_(0.5)
+    model.window_sizes = [(24, 0), (256, 0), (256, 0)]
+    geo = dict(num_heads=1, head_dim=128, num_layers=3)
+    gen = torch.Generator().manual_seed(9)
+    lengths = [5, 40, 17, 64]
+    prompts = [torch.randint(0, 1024, (n,), generator=gen).tolist() for n in lengths]
+    steps = 12
+
+    def run_alone(prompt):
+        cache = KVCache(batch_size=1, seq_len=len(prompt) + steps, device=DEV, dtype=torch.bfloat16, **geo)
+        logits = model.forward(torch.tensor([prompt], device=DEV), kv_cache=cache)[:, -1, :]
+        toks, outs = [], [logits]
+        for _ in range(steps):
+            nxt = logits.argmax(-1, keepdim=True)
+            toks.append(nxt.item())
+            logits = model.forward(nxt, kv_cache=cache)[:, -1, :]
+            outs.append(logits)
+        return cache, toks, torch.cat(outs, 0)
+
+    alone = [run_alone(p) for p in prompts]
+    # build the ragged batch cache from the rows' own prefill caches, then decode all rows together,
+    # feeding every row the tokens it produced alone (so near-ties cannot fork the comparison)
+    B, cap = len(prompts), max(lengths) + steps
+    batch = KVCache(batch_size=B, seq_len=cap, device=DEV, dtype=torch.bfloat16, **geo)
+    prev = []
+    for b, prompt in enumerate(prompts):
+        c = KVCache(batch_size=1, seq_len=len(prompt), device=DEV, dtype=torch.bfloat16, **geo)
+        model.forward(torch.tensor([prompt], device=DEV), kv_cache=c)
+        batch.k_cache[:, b, :len(prompt)] = c.k_cache[:, 0]
+        batch.v_cache[:, b, :len(prompt)] = c.v_cache[:, 0]
+        batch.cache_seqlens[b] = len(prompt)
+        prev.append(c.prev_embedding)
+    batch.prev_embedding = torch.cat(prev, 0)
+    for step in range(steps):
+        ids = torch.tensor([[alone[b][1][step]] for b in range(B)], device=DEV)
+        logits = model.forward(ids, kv_cache=batch)[:, -1, :]
+        for b in range(B):
+            ref = alone[b][2][step + 1]
+            assert torch.allclose(logits[b], ref, atol=3e-2, rtol=3e-2), f"row {b} step {step}"
+        assert batch.cache_seqlens.tolist() == [n + step + 1 for n in lengths]
+    from nanochat_b200 import ops
+    ops.check_status(DEV)
+    # layer 0's K bytes of every row equal the row-alone cache bit for bit
+    for b, (c, _, _) in enumerate(alone):
+        n = lengths[b] + steps
+        assert torch.equal(batch.k_cache[0, b, :n].view(torch.int16), c.k_cache[0, 0, :n].view(torch.int16))

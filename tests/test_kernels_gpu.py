@@ -432,3 +432,24 @@ def test_registered_custom_ops_dispatch():
     assert torch.equal(bits(kc2), bits(k_cache)) and torch.equal(bits(vc2), bits(v_cache))
     with pytest.raises(RuntimeError, match="CUDA"):
         torch.ops.nckv.decode_attn(q.cpu(), k_cache.cpu(), v_cache.cpu(), st.cpu(), 1, -1, 0, 0, False)
+
+
+def test_host_decode_step_matches_device_path():
+    """nckv_decode_step_host (H2D + append + attention + D2H in one call) == the two device ops."""
+    gen = torch.Generator(device=DEV).manual_seed(77)
+    B, Hq, Hkv, T_max = 5, 8, 2, 200
+    cos, sin = E.rotary_tables(T_max, 128, DEV, BF)
+    st = torch.tensor([0, 17, 100, 198, 64], device=DEV, dtype=torch.int32)
+    q = torch.randn(B, 1, Hq, 128, generator=gen, device=DEV).to(BF)
+    k = torch.randn(B, 1, Hkv, 128, generator=gen, device=DEV).to(BF)
+    v = torch.randn(B, 1, Hkv, 128, generator=gen, device=DEV).to(BF)
+    k_cache, v_cache = make_cache(B, T_max, Hkv, None, gen)
+    kc2, vc2 = k_cache.clone(), v_cache.clone()
+    q2 = ops().append_rope_norm(q, k, v, k_cache, v_cache, st, cos, sin)
+    ref = ops().decode_attention(q2[:, 0], k_cache, v_cache, st, window_left=50)
+    step = ops().HostDecodeStep(B, Hq, Hkv, cos, sin, DEV)
+    step.q.copy_(q[:, 0].cpu()); step.k.copy_(k[:, 0].cpu()); step.v.copy_(v[:, 0].cpu())
+    out = step.run(kc2, vc2, st, 50)
+    assert not out.is_cuda and torch.equal(bits(out), bits(ref.cpu()))
+    assert torch.equal(bits(kc2), bits(k_cache)) and torch.equal(bits(vc2), bits(v_cache))
+    assert ops().read_status(DEV) == 0
