@@ -389,6 +389,56 @@ def run_case(args):
         out.update(metric="decode attention KV-read GB/s", value=nbytes / sec / 1e9, unit="GB/s", us_per_call=sec * 1e6,
                    algorithmic_bytes=nbytes, frac=nbytes / sec / 1e9 / peak, peak=peak, peak_kind=f"of {peak_kind}",
                    config={"B": Bc, "Hq": Hq, "Hkv": Hkv, "T_max": T, "window_left": w})
+    elif args.case in ("engine_d24", "engine_d24_small"):
+        # configs[2]: nanochat d24 (24 x 1536, 12 heads), random-init bf16, batch 64, prompts of 512 ids,
+        # greedy decode; the whole forward (torch GEMMs + libnckv attention) replayed from a CUDA graph
+        from nanochat_b200.engine import GraphedDecodeStep, KVCache
+        from nanochat_b200.gpt import GPT, GPTConfig
+        small = args.case.endswith("small")
+        n_layer, Bc, T0 = (4, 8, 64) if small else (24, 64, 512)
+        cfg = GPTConfig(sequence_len=2048, vocab_size=32768, n_layer=n_layer, n_head=12, n_kv_head=12, n_embd=1536)
+        torch.manual_seed(3)
+        with torch.device("meta"):
+            model = GPT(cfg, compute_dtype=bf)
+        model.to_empty(device=dev)
+        model.init_weights()
+        model.to(bf)
+        model.window_sizes = [(1024, 0) if (i % 4) != 3 else (2048, 0) for i in range(n_layer)]
+        model.window_sizes[-1] = (2048, 0)
+        n_new = max(args.steps, 8)
+        cache = KVCache(batch_size=Bc, num_heads=12, seq_len=T0 + n_new + 8, head_dim=128, num_layers=n_layer,
+                        device=dev, dtype=bf)
+        prompts = torch.randint(0, 32768, (Bc, T0), generator=torch.Generator().manual_seed(3)).to(dev)
+        t0 = time.perf_counter()
+        logits = model.forward(prompts, kv_cache=cache)[:, -1, :]
+        torch.cuda.synchronize()
+        prefill_s = time.perf_counter() - t0
+        ids = logits.argmax(-1, keepdim=True)
+        # eager steps (one host round trip per token, as Engine.generate does)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(4):
+            ids = model.forward(ids, kv_cache=cache)[:, -1, :].argmax(-1, keepdim=True)
+        e1.record()
+        torch.cuda.synchronize()
+        eager_ms = e0.elapsed_time(e1) / 4
+        graphed = GraphedDecodeStep(model, cache, ids)
+        for _ in range(3):
+            ids = graphed.step(ids).argmax(-1, keepdim=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(n_new - 8):
+            ids = graphed.step(ids).argmax(-1, keepdim=True)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / (n_new - 8)
+        ctx = int(cache.cache_seqlens[0].item())
+        kv_step = sum(4 * 12 * D * Bc * (min(ctx, w[0] + 1)) for w in model.window_sizes)
+        w_bytes = 2 * sum(p_.numel() for n_, p_ in model.named_parameters() if "wte" not in n_ and "value_embeds" not in n_)
+        out.update(metric="decode tokens/s (whole model, CUDA-graphed step)", value=Bc / (ms * 1e-3), unit="tokens/s",
+                   ms_per_step=ms, eager_ms_per_step=eager_ms, prefill_s=prefill_s, context=ctx,
+                   roofline_ms=(kv_step + w_bytes) / (peak * 1e9) * 1e3, kv_bytes_per_step=kv_step, weight_bytes=w_bytes,
+                   config={"model": f"d{n_layer}", "B": Bc, "prompt": T0, "steps": n_new})
     elif args.case == "prefill":            # dense causal attention, d24 shape: 12 heads, T=2048
         Bc, T, Hq, Hkv = 8, 2048, 12, 12
         q, k, v = rnd(Bc, T, Hq, D), rnd(Bc, T, Hkv, D), rnd(Bc, T, Hkv, D)
@@ -437,7 +487,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--case", default=None,
                     help="secondary op-level measurement instead of the headline workload: decode_long, decode_gqa, "
-                         "decode_gqa_window, decode_d24, prefill, broadcast, append")
+                         "decode_gqa_window, decode_d24, prefill, broadcast, append, engine_d24, engine_d24_small")
     args = ap.parse_args()
     if args.case:
         run_case(args)

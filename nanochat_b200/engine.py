@@ -219,3 +219,55 @@ class Engine:
             if all(done):
                 break
         return results, masks
+
+
+class GraphedDecodeStep:
+    """One decode step (``model.forward(ids (B, 1), kv_cache)``) captured in a CUDA graph.
+
+    Possible because nothing on the cached path synchronises with the host: positions are read
+    from ``cache_seqlens`` on the device, the append and attention kernels take no host-known
+    lengths, and ``KVCache.advance`` is an in-place device add.  The reference's step cannot be
+    captured (``get_pos()`` / ``.item()`` per forward and per layer, gpt.py:424, flash_attention.py:157).
+
+    ``step(ids)`` copies the token ids into the graph's input buffer, replays, and returns the
+    logits buffer (B, vocab) — overwritten by the next call.  The smear state
+    (``kv_cache.prev_embedding``) is kept in a persistent buffer that the graph reads and updates.
+    """
+
+    def __init__(self, model, kv_cache, warmup_ids):
+        assert warmup_ids.dim() == 2 and warmup_ids.size(1) == 1
+        self.model, self.cache = model, kv_cache
+        dev = warmup_ids.device
+        self.ids = warmup_ids.clone()
+        if kv_cache.prev_embedding is None:
+            raise RuntimeError("capture after the prefill forward: the cache has no smear state yet")
+        self._prev = kv_cache.prev_embedding.clone()
+        kv_cache.prev_embedding = self._prev
+        # capture must not move the real cache forward: remember lengths, restore after warm-up/capture
+        saved_lens = kv_cache.cache_seqlens.clone()
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(2):  # warm-up on the capture stream (allocates workspaces, autotunes GEMMs)
+                self._body()
+            side.synchronize()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, stream=side):
+                self.logits = self._body()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        kv_cache.cache_seqlens.copy_(saved_lens)
+        self._prev.copy_(self._prev_saved)
+
+    def _body(self):
+        if not hasattr(self, "_prev_saved"):
+            self._prev_saved = self._prev.clone()
+        self.cache.prev_embedding = self._prev
+        logits = self.model.forward(self.ids, kv_cache=self.cache)[:, -1, :]
+        self._prev.copy_(self.cache.prev_embedding)
+        self.cache.prev_embedding = self._prev
+        return logits
+
+    def step(self, ids):
+        self.ids.copy_(ids, non_blocking=True)
+        self.graph.replay()
+        return self.logits

@@ -194,3 +194,34 @@ def test_ragged_batch_equals_rows_run_alone():
     for b, (c, _, _) in enumerate(alone):
         n = lengths[b] + steps
         assert torch.equal(batch.k_cache[0, b, :n].view(torch.int16), c.k_cache[0, 0, :n].view(torch.int16))
+
+
+def test_graphed_decode_step_equals_eager_steps():
+    """The CUDA-graphed decode step produces the tokens, cache lengths and cache bytes of eager steps."""
+    from nanochat_b200.engine import GraphedDecodeStep, KVCache
+    prompt = torch.randint(0, 32768, (20,), generator=torch.Generator().manual_seed(2)).tolist()
+    model = _to_gpu(_config0_model(True))
+    model.window_sizes = [(16, 0), (1024, 0), (16, 0), (2048, 0)]
+    geo = dict(num_heads=2, head_dim=128, num_layers=4)
+
+    def run(graphed):
+        cache = KVCache(batch_size=3, seq_len=64, device=DEV, dtype=torch.bfloat16, **geo)
+        ids = torch.tensor([prompt] * 3, dtype=torch.long, device=DEV)
+        ids[1, 3] += 1  # rows differ a little
+        logits = model.forward(ids, kv_cache=cache)[:, -1, :]
+        nxt = logits.argmax(-1, keepdim=True)
+        toks = [nxt[:, 0].tolist()]
+        stepper = GraphedDecodeStep(model, cache, nxt) if graphed else None
+        assert cache.cache_seqlens.tolist() == [20] * 3
+        for _ in range(10):
+            logits = stepper.step(nxt) if graphed else model.forward(nxt, kv_cache=cache)[:, -1, :]
+            nxt = logits.argmax(-1, keepdim=True)
+            toks.append(nxt[:, 0].tolist())
+        return toks, cache
+
+    toks_e, cache_e = run(False)
+    toks_g, cache_g = run(True)
+    assert toks_e == toks_g
+    assert cache_e.cache_seqlens.tolist() == cache_g.cache_seqlens.tolist() == [30] * 3
+    assert torch.equal(cache_e.k_cache.view(torch.int16), cache_g.k_cache.view(torch.int16))
+    assert torch.equal(cache_e.v_cache.view(torch.int16), cache_g.v_cache.view(torch.int16))
