@@ -356,7 +356,55 @@ def _time_cuda(fn, iters, warmup=3):
     return e0.elapsed_time(e1) / iters * 1e-3  # seconds per call
 
 
+def run_case_kv_split(args):
+    """configs[4] with the keys split across the ranks (torchrun): every rank attends over its key
+    range of every row, one all-gather of the partials, LSE combine.  Strong scaling: total work fixed."""
+    rank, world, local = dist_setup(args.gpus)
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    from nanochat_b200 import ops
+    from nanochat_b200.dist import KVSplitAttention
+    peak, peak_kind = peaks()
+    Bc, Hq, Hkv, T = 8, 16, 4, 65536
+    lens = torch.randint(32768, 65536, (Bc,), dtype=torch.int32, generator=torch.Generator().manual_seed(4))
+    att = KVSplitAttention(T, block=1024)  # block-cyclic ownership: ragged rows stay balanced
+    gen = torch.Generator(device=dev).manual_seed(4)
+    nsets = 2
+    cap = att.local_capacity
+    sets = [(torch.randn(Bc, cap, Hkv, D, generator=gen, device=dev).to(torch.bfloat16),
+             torch.randn(Bc, cap, Hkv, D, generator=gen, device=dev).to(torch.bfloat16)) for _ in range(nsets)]
+    q = torch.randn(Bc, Hq, D, generator=torch.Generator(device=dev).manual_seed(5), device=dev).to(torch.bfloat16)
+    lens_d = lens.to(dev)
+    iters = max(args.steps, 5)
+    for i in range(5):
+        att.attend(q, sets[i % nsets][0], sets[i % nsets][1], lens_d)
+    barrier(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        att.attend(q, sets[i % nsets][0], sets[i % nsets][1], lens_d)
+    e1.record()
+    barrier(world)
+    sec = max_over_ranks(e0.elapsed_time(e1), world, dev) / iters * 1e-3
+    status = ops.read_status(dev)
+    if rank == 0:
+        nbytes = 4 * Hkv * D * int((lens.long() + 1).sum()) + 4 * Bc * Hq * D + 4 * Bc
+        print(json.dumps({"case": "decode_long", "n_gpus": world, "steps": iters, "scaling": "strong", "data": "synthetic",
+                          "dtype": "bf16", "metric": "decode attention KV-read GB/s (keys split across GPUs, all-gather + LSE combine)",
+                          "value": nbytes / sec / 1e9, "unit": "GB/s", "us_per_call": sec * 1e6, "algorithmic_bytes": nbytes,
+                          "frac_of_n_x_peak": nbytes / sec / 1e9 / (peak * world), "peak": peak, "peak_kind": f"of {peak_kind}",
+                          "exchange_bytes_per_rank": Bc * Hq * (D + 1) * 4,
+                          "config": {"B": Bc, "Hq": Hq, "Hkv": Hkv, "T_max": T, "layout": "block-cyclic, 1024 keys", "keys_per_rank": cap,
+                                     "launch": f"eager, exchange={att.exchange}"},
+                          "device_status": status}), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
 def run_case(args):
+    if args.case == "decode_long" and int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        return run_case_kv_split(args)
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     from nanochat_b200 import ops

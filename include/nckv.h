@@ -86,6 +86,28 @@ NCKV_API int nckv_append_rope_norm(const void *q_in, const void *k_in, const voi
                           int32_t *status, void *stream);
 
 /*
+ * Same as nckv_append_rope_norm for a sequence-split cache (no counterpart in the reference):
+ * `positions[b]` is the sequence position of row b's first new token (drives RoPE, as
+ * cache_seqlens does above) while `write_slots[b]` is the index in THIS shard's cache where its
+ * k/v go, or -1 if another shard owns that position (q_out is still produced).
+ */
+NCKV_API int nckv_append_rope_norm_at(const void *q_in, const void *k_in, const void *v_in, void *q_out,
+                             void *k_cache, void *v_cache, const int32_t *positions, const int32_t *write_slots,
+                             const void *cos, const void *sin, int B, int T_new, int Hq, int Hkv,
+                             int D, int T_max, int64_t cache_batch_stride, int64_t cache_token_stride,
+                             int rope_len, float qk_scale, float eps, int32_t *status, void *stream);
+
+/*
+ * Bookkeeping of the sequence-split long-context path (no counterpart in the reference): key
+ * positions are owned block-cyclically, position p by shard (p / block) % world at local index
+ * (p / (block*world)) * block + p % block.  From the global cache_seqlens (lengths before the new
+ * tokens) computes, for shard `rank`: local_len_after[b] = keys of row b this shard holds once the
+ * T_new new tokens are in, and write_slot[b] = local index for the new token, or -1 if it is not ours.
+ */
+NCKV_API int nckv_kv_split_plan(const int32_t *cache_seqlens, int B, int T_new, int world, int rank, int block,
+                       int32_t *local_len_after, int32_t *write_slot, void *stream);
+
+/*
  * Plain append (k already rotated/normalised by the caller): the cache write of
  * flash_attn_with_kvcache (flash_attention.py:160-162) with per-row positions.
  */

@@ -24,6 +24,9 @@ SIGNATURES = {
     "nckv_read_status": (c_int, [c_void_p, c_int, c_void_p]),
     "nckv_append_rope_norm": (c_int, [c_void_p] * 9 + [c_int] * 6 + [c_i64, c_i64, c_int, c_float,
                                                              c_float, c_void_p, c_void_p]),
+    "nckv_append_rope_norm_at": (c_int, [c_void_p] * 10 + [c_int] * 6 + [c_i64, c_i64, c_int, c_float, c_float,
+                                                          c_void_p, c_void_p]),
+    "nckv_kv_split_plan": (c_int, [c_void_p] + [c_int] * 5 + [c_void_p, c_void_p, c_void_p]),
     "nckv_append": (c_int, [c_void_p] * 5 + [c_int] * 5 + [c_i64, c_i64, c_void_p, c_void_p]),
     "nckv_decode_step_host": (c_int, [c_void_p] * 10 + [c_int] * 5 + [c_i64, c_i64, c_int, c_float, c_float, c_int,
                                                        c_void_p, c_size_t, c_void_p]),

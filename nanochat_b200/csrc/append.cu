@@ -22,6 +22,7 @@ struct AppendParams {
     __nv_bfloat16 *k_cache;
     __nv_bfloat16 *v_cache;
     const int32_t *cache_seqlens;
+    const int32_t *write_slots;  // optional: cache index of token 0 per row (-1: do not write); null = cache_seqlens
     const uint4 *cos;  // (rope_len, 64) bf16 = 8 uint4 per position
     const uint4 *sin;
     int32_t *status;
@@ -129,16 +130,18 @@ __global__ void __launch_bounds__(256) append_rope_norm_kernel(const AppendParam
         const long long bt = r / heads_per_tok;
         const int t = (int)(bt % p.T_new);
         const int b = (int)(bt / p.T_new);
-        const int len = p.cache_seqlens[b];
+        const int len = p.cache_seqlens[b];          // sequence position of token 0 (drives RoPE)
+        const int wslot = p.write_slots ? p.write_slots[b] : len;  // cache index of token 0
         const int pos = len + t;
         bool ok = live;
-        if (len < 0) {
+        if (len < 0 || wslot < -1) {
             if (live && j == 0 && slot == 0 && t == 0) atomicOr(p.status, (int)NCKV_ST_BAD_SEQLEN);
             ok = false;
-        } else if (len + p.T_new > p.T_max || (p.rope_len > 0 && len + p.T_new > p.rope_len)) {
+        } else if ((wslot >= 0 && wslot + p.T_new > p.T_max) || (p.rope_len > 0 && len + p.T_new > p.rope_len)) {
             if (live && j == 0 && slot == 0 && t == 0) atomicOr(p.status, (int)NCKV_ST_OVERFLOW);
             ok = false;
         }
+        const bool write_kv = ok && wslot >= 0;  // -1: this row's token belongs to another shard
         const int safe_pos = ok ? pos : 0;
         // kind: 0 = q head, 1 = k head, 2 = v head.  The two half-warps of a warp may hold
         // different kinds, so the transform (which shuffles across the warp) runs unconditionally
@@ -160,10 +163,10 @@ __global__ void __launch_bounds__(256) append_rope_norm_kernel(const AppendParam
         if (ok) {
             if (kind == 0) {
                 p.q_out[src_idx] = o;
-            } else {
+            } else if (write_kv) {
                 __nv_bfloat16 *cache = kind == 1 ? p.k_cache : p.v_cache;
                 uint4 *dst = reinterpret_cast<uint4 *>(cache + (long long)b * p.cache_batch_stride +
-                                                       (long long)pos * p.cache_token_stride +
+                                                       (long long)(wslot + t) * p.cache_token_stride +
                                                        (long long)h * NCKV_D);
                 dst[j] = o;
             }
@@ -227,12 +230,12 @@ static int launch_append(const AppendParams &p, cudaStream_t stream) {
 
 extern "C" {
 
-int nckv_append_rope_norm(const void *q_in, const void *k_in, const void *v_in, void *q_out,
-                          void *k_cache, void *v_cache, const int32_t *cache_seqlens,
-                          const void *cos, const void *sin, int B, int T_new, int Hq, int Hkv,
-                          int D, int T_max, int64_t cache_batch_stride,
-                          int64_t cache_token_stride, int rope_len, float qk_scale, float eps,
-                          int32_t *status, void *stream) {
+static int append_rope_norm_impl(const void *q_in, const void *k_in, const void *v_in, void *q_out,
+                                 void *k_cache, void *v_cache, const int32_t *cache_seqlens,
+                                 const int32_t *write_slots, const void *cos, const void *sin, int B, int T_new,
+                                 int Hq, int Hkv, int D, int T_max, int64_t cache_batch_stride,
+                                 int64_t cache_token_stride, int rope_len, float qk_scale, float eps,
+                                 int32_t *status, void *stream) {
     using namespace nckv;
     int rc = check_common(k_in, v_in, k_cache, v_cache, cache_seqlens, B, T_new, Hkv, D, T_max,
                           cache_batch_stride, cache_token_stride, status);
@@ -257,6 +260,7 @@ int nckv_append_rope_norm(const void *q_in, const void *k_in, const void *v_in, 
     p.k_cache = static_cast<__nv_bfloat16 *>(k_cache);
     p.v_cache = static_cast<__nv_bfloat16 *>(v_cache);
     p.cache_seqlens = cache_seqlens;
+    p.write_slots = write_slots;
     p.cos = static_cast<const uint4 *>(cos);
     p.sin = static_cast<const uint4 *>(sin);
     p.status = status;
@@ -267,6 +271,31 @@ int nckv_append_rope_norm(const void *q_in, const void *k_in, const void *v_in, 
     p.eps = eps;
     p.transform_k = 1;
     return launch_append(p, static_cast<cudaStream_t>(stream));
+}
+
+int nckv_append_rope_norm(const void *q_in, const void *k_in, const void *v_in, void *q_out,
+                          void *k_cache, void *v_cache, const int32_t *cache_seqlens,
+                          const void *cos, const void *sin, int B, int T_new, int Hq, int Hkv,
+                          int D, int T_max, int64_t cache_batch_stride,
+                          int64_t cache_token_stride, int rope_len, float qk_scale, float eps,
+                          int32_t *status, void *stream) {
+    return append_rope_norm_impl(q_in, k_in, v_in, q_out, k_cache, v_cache, cache_seqlens, nullptr, cos, sin, B, T_new,
+                                 Hq, Hkv, D, T_max, cache_batch_stride, cache_token_stride, rope_len, qk_scale, eps,
+                                 status, stream);
+}
+
+int nckv_append_rope_norm_at(const void *q_in, const void *k_in, const void *v_in, void *q_out,
+                             void *k_cache, void *v_cache, const int32_t *positions, const int32_t *write_slots,
+                             const void *cos, const void *sin, int B, int T_new, int Hq, int Hkv,
+                             int D, int T_max, int64_t cache_batch_stride, int64_t cache_token_stride,
+                             int rope_len, float qk_scale, float eps, int32_t *status, void *stream) {
+    if (!write_slots) {
+        nckv::set_error("append_rope_norm_at: write_slots is required");
+        return NCKV_E_ARG;
+    }
+    return append_rope_norm_impl(q_in, k_in, v_in, q_out, k_cache, v_cache, positions, write_slots, cos, sin, B, T_new,
+                                 Hq, Hkv, D, T_max, cache_batch_stride, cache_token_stride, rope_len, qk_scale, eps,
+                                 status, stream);
 }
 
 int nckv_append(const void *k_in, const void *v_in, void *k_cache, void *v_cache,
@@ -285,6 +314,7 @@ int nckv_append(const void *k_in, const void *v_in, void *k_cache, void *v_cache
     p.k_cache = static_cast<__nv_bfloat16 *>(k_cache);
     p.v_cache = static_cast<__nv_bfloat16 *>(v_cache);
     p.cache_seqlens = cache_seqlens;
+    p.write_slots = nullptr;
     p.cos = nullptr;
     p.sin = nullptr;
     p.status = status;

@@ -39,7 +39,47 @@ __global__ void __launch_bounds__(256) lse_combine_kernel(const float *__restric
     if (lse_out && lane == 0) lse_out[row] = M > -INFINITY ? M + logf(L) : -INFINITY;
 }
 
+// Block-cyclic ownership of key positions for the sequence-split path: position p belongs to shard
+// (p / block) % world and sits at local index (p / (block*world)) * block + p % block there.
+__device__ __forceinline__ int owned_below(int n, int world, int rank, int block) {
+    const int cycle = block * world;
+    const int full = n / cycle, rem = n - full * cycle;
+    return full * block + min(max(rem - rank * block, 0), block);
+}
+
+__global__ void kv_split_plan_kernel(const int32_t *__restrict__ seqlens, int B, int T_new, int world, int rank,
+                                     int block, int32_t *__restrict__ local_len_after,
+                                     int32_t *__restrict__ write_slot) {
+    pdl_wait_prior_grids();
+    pdl_launch_dependents();
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= B) return;
+    const int L = max(seqlens[b], 0);
+    local_len_after[b] = owned_below(L + T_new, world, rank, block);
+    // the T_new new tokens are written by this shard only if it owns position L (callers keep
+    // T_new == 1 on this path, or chunks that do not straddle a block)
+    write_slot[b] = ((L / block) % world == rank) ? owned_below(L, world, rank, block) : -1;
+}
+
 }  // namespace nckv
+
+extern "C" int nckv_kv_split_plan(const int32_t *cache_seqlens, int B, int T_new, int world, int rank, int block,
+                                  int32_t *local_len_after, int32_t *write_slot, void *stream) {
+    using namespace nckv;
+    if (!cache_seqlens || !local_len_after || !write_slot) {
+        set_error("kv_split_plan: null pointer argument");
+        return NCKV_E_ARG;
+    }
+    if (B <= 0 || T_new <= 0 || world <= 0 || rank < 0 || rank >= world || block <= 0 || (block % 32) != 0) {
+        set_error("kv_split_plan: bad argument (B=%d T_new=%d world=%d rank=%d block=%d; block must be a multiple of 32)",
+                  B, T_new, world, rank, block);
+        return NCKV_E_ARG;
+    }
+    kv_split_plan_kernel<<<(B + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        cache_seqlens, B, T_new, world, rank, block, local_len_after, write_slot);
+    NCKV_CUDA_CHECK(cudaGetLastError());
+    return NCKV_OK;
+}
 
 extern "C" int nckv_lse_combine(const float *parts_o, const float *parts_lse, int n_parts, int rows,
                                 int D, int64_t part_stride_o, int64_t part_stride_lse, void *out, float *lse_out,

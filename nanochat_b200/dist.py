@@ -5,15 +5,20 @@ Two partitionings, both from BASELINE.json's north star:
 * by sequence (``shard_rows``): rows are independent, every rank owns a contiguous block of rows
   with its own KVCache and nothing crosses GPUs on the data path.  This is the replica-per-GPU
   form the reference itself serves with (scripts/chat_web.py:94-141).
-* by key range for long context (``KVSplitAttention``): rank r attends over keys
-  [r*T/N, (r+1)*T/N) of every row and the partial results (normalised fp32 output + log-sum-exp per
-  (row, q head), 66 KB per rank at B=8 x 16 heads) are exchanged with ONE all-gather and merged by
+* by key position for long context (``KVSplitAttention``): every rank holds a slice of the keys of
+  every row, attends over it, and the partial results (normalised fp32 output + log-sum-exp per
+  (row, q head); 66 KB per rank at B=8 x 16 heads) are exchanged with ONE all-gather and merged by
   the log-sum-exp combine kernel.  The reference has no counterpart (it never splits keys); the
   result equals a single softmax over all keys.
 
-Each rank keeps a cache of full capacity but only reads (and needs valid data in) its own key
-range; the append kernel writes the new token on every rank, which is harmless outside the owner's
-range and keeps positions and windows in global token indices.
+Two ownership layouts:
+  ``block > 0``  block-cyclic (the default for full-causal attention): position p belongs to rank
+                 (p / block) % N and is stored at local index (p / (block*N)) * block + p % block
+                 of that rank's compact cache (capacity about T/N).  Ragged and growing rows stay
+                 balanced across ranks; the new token is appended by its owner only.
+  ``block == 0`` contiguous ranges [r*T/N, (r+1)*T/N) in a cache of full capacity (global token
+                 indices, so sliding windows work); ranks are balanced only for rows of similar,
+                 full length.
 """
 import torch
 
@@ -33,8 +38,8 @@ def shard_rows(n_rows, rank, world_size):
 
 
 def kv_shard_range(capacity, rank, world_size, align=32):
-    """Key range [begin, end) of ``rank``: equal contiguous ranges, boundaries rounded up to a
-    multiple of ``align`` tokens (the decode kernel's tile) so no tile straddles two ranks."""
+    """Key range [begin, end) of ``rank`` in the contiguous layout: equal ranges, boundaries rounded
+    up to a multiple of ``align`` tokens (the decode kernel's tile) so no tile straddles two ranks."""
     if not 0 <= rank < world_size:
         raise ValueError(f"rank {rank} outside world of {world_size}")
     per = -(-capacity // world_size)
@@ -43,15 +48,23 @@ def kv_shard_range(capacity, rank, world_size, align=32):
     return begin, min(capacity, begin + per)
 
 
+def owned_below(n, world_size, rank, block):
+    """Positions p < n owned by ``rank`` in the block-cyclic layout (host-side twin of the kernel)."""
+    cycle = block * world_size
+    full, rem = divmod(n, cycle)
+    return full * block + min(max(rem - rank * block, 0), block)
+
+
 class KVSplitAttention:
     """Decode attention with the keys split across the ranks of ``group``.
 
-    ``attend(q, k_cache, v_cache, cache_seqlens)`` — q (B, Hq, D) replicated on every rank,
-    caches (B, T_max, Hkv, D) holding at least this rank's key range, cache_seqlens the global
-    lengths BEFORE the new token — returns the full attention output (B, Hq, D) bf16 on every rank.
+    ``attend(q, k_cache, v_cache, cache_seqlens)`` — q (B, Hq, D) replicated on every rank, caches
+    in this rank's layout (see module docstring), cache_seqlens the GLOBAL lengths before the new
+    token — returns the full attention output (B, Hq, D) bf16 on every rank.
+    ``append_and_attend`` first runs the fused RoPE/norm/append for the rows this rank owns.
     """
 
-    def __init__(self, capacity, group=None, window_left=-1, partial_fn=None, combine_fn=None):
+    def __init__(self, capacity, group=None, window_left=-1, block=1024, partial_fn=None, combine_fn=None):
         import torch.distributed as dist
         self.dist = dist
         self.group = group
@@ -59,38 +72,68 @@ class KVSplitAttention:
         self.world = dist.get_world_size(group)
         self.capacity = capacity
         self.window_left = window_left
-        self.kv_begin, self.kv_end = kv_shard_range(capacity, self.rank, self.world)
+        if block and window_left >= 0:
+            raise ValueError("the block-cyclic layout stores keys compactly and cannot express a sliding window; "
+                             "use block=0 (contiguous ranges) for windowed layers")
+        if block and block % 32:
+            raise ValueError("block must be a multiple of the 32-key tile")
+        self.block = block
+        if block:
+            self.kv_begin = self.kv_end = 0
+            self.local_capacity = owned_below(capacity, self.world, self.rank, block)
+        else:
+            self.kv_begin, self.kv_end = kv_shard_range(capacity, self.rank, self.world)
+            self.local_capacity = capacity
         # injectable for CPU tests of the exchange logic; the product path is the CUDA ops
         self._partial = partial_fn or self._partial_cuda
         self._combine = combine_fn or ops.lse_combine
-        self._gather = None
+        self._gather = self._send = None
 
-    def _partial_cuda(self, q, k_cache, v_cache, cache_seqlens):
-        if self.kv_end <= self.kv_begin:  # more ranks than tiles: this rank has nothing
-            B, Hq, D = q.shape
-            return (torch.zeros(B, Hq, D, dtype=torch.float32, device=q.device),
-                    torch.full((B, Hq), float("-inf"), dtype=torch.float32, device=q.device))
-        _, o32, lse = ops.decode_attention(q, k_cache, v_cache, cache_seqlens, seqlen_offset=1,
-                                           window_left=self.window_left, kv_begin=self.kv_begin, kv_end=self.kv_end,
-                                           partial=True)
-        return o32, lse
+    # ---- buffers: [rows*D output | rows lse] per rank, padded to a multiple of 4 floats ----------
+    def _buffers(self, rows, D, device):
+        per = rows * D + -(-rows // 4) * 4
+        if self._gather is None or self._gather.numel() != self.world * per or self._gather.device != device:
+            self._gather = torch.empty(self.world, per, dtype=torch.float32, device=device)
+            self._send = torch.empty(per, dtype=torch.float32, device=device)
+        return self._send[:rows * D], self._send[rows * D:rows * D + rows]
+
+    def _partial_cuda(self, q, k_cache, v_cache, cache_seqlens, out_f32, lse):
+        B, Hq, D = q.shape
+        if self.block:
+            local_len, _ = ops.kv_split_plan(cache_seqlens, self.world, self.rank, self.block)
+            ops.decode_attention(q, k_cache, v_cache, local_len, seqlen_offset=0, window_left=-1, partial=True,
+                                 out_f32=out_f32, lse=lse)
+        elif self.kv_end <= self.kv_begin:  # more ranks than tiles: this rank has nothing
+            out_f32.zero_()
+            lse.fill_(float("-inf"))
+        else:
+            ops.decode_attention(q, k_cache, v_cache, cache_seqlens, seqlen_offset=1, window_left=self.window_left,
+                                 kv_begin=self.kv_begin, kv_end=self.kv_end, partial=True, out_f32=out_f32, lse=lse)
+
+    def append_and_attend(self, q, k, v, k_cache, v_cache, cache_seqlens, cos, sin):
+        """q, k, v: (B, 1, H, D) raw projections.  RoPE/QK-norm/scale on q and k (positions are the
+        global lengths), the owner of position L_b stores k/v, then ``attend``."""
+        if self.block:
+            _, slots = ops.kv_split_plan(cache_seqlens, self.world, self.rank, self.block)
+            q2 = ops.append_rope_norm(q, k, v, k_cache, v_cache, cache_seqlens, cos, sin, write_slots=slots)
+        else:  # global indices: every rank may write, only the owner's range is ever read
+            q2 = ops.append_rope_norm(q, k, v, k_cache, v_cache, cache_seqlens, cos, sin)
+        return self.attend(q2[:, 0], k_cache, v_cache, cache_seqlens)
 
     def attend(self, q, k_cache, v_cache, cache_seqlens):
         B, Hq, D = q.shape
         rows = B * Hq
-        o32, lse = self._partial(q, k_cache, v_cache, cache_seqlens)
-        if o32.shape != (B, Hq, D) or lse.shape != (B, Hq):
-            raise RuntimeError(f"partial result has shape {tuple(o32.shape)} / {tuple(lse.shape)}, expected "
-                               f"{(B, Hq, D)} / {(B, Hq)}")
+        out_f32, lse = self._buffers(rows, D, q.device)
+        res = self._partial(q, k_cache, v_cache, cache_seqlens, out_f32.view(B, Hq, D), lse.view(B, Hq))
+        if res is not None:  # an injected partial_fn may return fresh tensors instead of filling the buffers
+            o32, l32 = res
+            if o32.shape != (B, Hq, D) or l32.shape != (B, Hq):
+                raise RuntimeError(f"partial result has shape {tuple(o32.shape)} / {tuple(l32.shape)}, expected "
+                                   f"{(B, Hq, D)} / {(B, Hq)}")
+            out_f32.copy_(o32.reshape(-1))
+            lse.copy_(l32.reshape(-1))
         if self.world == 1:
-            return self._combine(o32.view(1, rows, D), lse.view(1, rows))[0].view(B, Hq, D)
-        # one packed message per rank: [rows*D output | rows lse], padded to a multiple of 4 floats
-        per = rows * D + -(-rows // 4) * 4
-        if self._gather is None or self._gather.numel() != self.world * per or self._gather.device != q.device:
-            self._gather = torch.empty(self.world, per, dtype=torch.float32, device=q.device)
-            self._send = torch.empty(per, dtype=torch.float32, device=q.device)
-        self._send[:rows * D].copy_(o32.reshape(-1))
-        self._send[rows * D:rows * D + rows].copy_(lse.reshape(-1))
+            return self._combine(out_f32.view(1, rows, D), lse.view(1, rows))[0].view(B, Hq, D)
         self.dist.all_gather_into_tensor(self._gather.view(-1), self._send, group=self.group)
         parts_o = self._gather[:, :rows * D].unflatten(1, (rows, D))
         parts_lse = self._gather[:, rows * D:rows * D + rows]

@@ -136,7 +136,7 @@ _NS.define("append_rope_norm(Tensor q, Tensor k, Tensor v, Tensor(a!) k_cache, T
            "Tensor cache_seqlens, Tensor cos, Tensor sin, float qk_scale, float eps) -> Tensor")
 
 
-def _append_rope_norm(q, k, v, k_cache, v_cache, cache_seqlens, cos, sin, qk_scale, eps):
+def _append_rope_norm(q, k, v, k_cache, v_cache, cache_seqlens, cos, sin, qk_scale, eps, write_slots=None):
     name = "append_rope_norm"
     _require_cuda(name, q, k, v, k_cache, v_cache, cache_seqlens, cos, sin)
     _require_bf16(name, q, k, v, k_cache, v_cache, cos, sin)
@@ -159,9 +159,18 @@ def _append_rope_norm(q, k, v, k_cache, v_cache, cache_seqlens, cos, sin, qk_sca
     q_out = torch.empty_like(q)
     idx, stream, ws = _launch_ctx(q, B, Hq, Hkv)
     with _device_guard(idx):
-        rc = _F_APPEND_ROPE(q.data_ptr(), k.data_ptr(), v.data_ptr(), q_out.data_ptr(), k_cache.data_ptr(),
-                            v_cache.data_ptr(), cache_seqlens.data_ptr(), cos2.data_ptr(), sin2.data_ptr(), B, T_new, Hq,
-                            Hkv, D, k_cache.size(1), sb, st, cos2.size(0), qk_scale, eps, ws.data_ptr(), stream)
+        if write_slots is None:
+            rc = _F_APPEND_ROPE(q.data_ptr(), k.data_ptr(), v.data_ptr(), q_out.data_ptr(), k_cache.data_ptr(),
+                                v_cache.data_ptr(), cache_seqlens.data_ptr(), cos2.data_ptr(), sin2.data_ptr(), B, T_new,
+                                Hq, Hkv, D, k_cache.size(1), sb, st, cos2.size(0), qk_scale, eps, ws.data_ptr(), stream)
+        else:
+            if write_slots.dtype != torch.int32 or not write_slots.is_cuda or write_slots.numel() != B:
+                raise RuntimeError(f"nckv::{name}: write_slots must be a CUDA int32 tensor of {B} rows")
+            rc = _lib.lib.nckv_append_rope_norm_at(q.data_ptr(), k.data_ptr(), v.data_ptr(), q_out.data_ptr(),
+                                                   k_cache.data_ptr(), v_cache.data_ptr(), cache_seqlens.data_ptr(),
+                                                   write_slots.data_ptr(), cos2.data_ptr(), sin2.data_ptr(), B, T_new, Hq,
+                                                   Hkv, D, k_cache.size(1), sb, st, cos2.size(0), qk_scale, eps,
+                                                   ws.data_ptr(), stream)
     if rc < 0:
         _lib.check("nckv_append_rope_norm", rc)
     return q_out
@@ -206,7 +215,8 @@ _NS.define("decode_attn(Tensor q, Tensor k_cache, Tensor v_cache, Tensor cache_s
            "int window_left, int kv_begin, int kv_end, bool partial) -> (Tensor, Tensor, Tensor)")
 
 
-def _decode_attn_core(q, k_cache, v_cache, cache_seqlens, seqlen_offset, window_left, kv_begin, kv_end, partial):
+def _decode_attn_core(q, k_cache, v_cache, cache_seqlens, seqlen_offset, window_left, kv_begin, kv_end, partial,
+                      out_f32=None, lse=None):
     name = "decode_attn"
     _require_cuda(name, q, k_cache, v_cache, cache_seqlens)
     _require_bf16(name, q, k_cache, v_cache)
@@ -224,8 +234,12 @@ def _decode_attn_core(q, k_cache, v_cache, cache_seqlens, seqlen_offset, window_
     q = q.contiguous()
     out = torch.empty_like(q)
     if partial:
-        out_f32 = torch.empty(B, Hq, D, dtype=torch.float32, device=q.device)
-        lse = torch.empty(B, Hq, dtype=torch.float32, device=q.device)
+        if out_f32 is None:
+            out_f32 = torch.empty(B, Hq, D, dtype=torch.float32, device=q.device)
+            lse = torch.empty(B, Hq, dtype=torch.float32, device=q.device)
+        elif (out_f32.dtype != torch.float32 or lse.dtype != torch.float32 or out_f32.numel() != B * Hq * D or
+              lse.numel() != B * Hq or not out_f32.is_contiguous() or not lse.is_contiguous() or out_f32.data_ptr() % 16):
+            raise RuntimeError(f"nckv::{name}: out_f32 / lse buffers do not fit (B={B}, Hq={Hq})")
     else:
         out_f32 = lse = None
     idx, stream, ws = _launch_ctx(q, B, Hq, Hkv)
@@ -352,9 +366,12 @@ _NS.impl("lse_combine", _lse_combine, "CPU")
 # ------------------------------------------------------------------------------------------------
 
 
-def append_rope_norm(q, k, v, k_cache, v_cache, cache_seqlens, cos, sin, qk_scale=QK_SCALE, eps=RMS_EPS):
-    """RoPE + QK-norm + scale on q and k, append k/v at ``cache_seqlens`` (per row); returns q'."""
-    return _append_rope_norm(q, k, v, k_cache, v_cache, cache_seqlens, cos, sin, qk_scale, eps)
+def append_rope_norm(q, k, v, k_cache, v_cache, cache_seqlens, cos, sin, qk_scale=QK_SCALE, eps=RMS_EPS,
+                     write_slots=None):
+    """RoPE + QK-norm + scale on q and k, append k/v at ``cache_seqlens`` (per row); returns q'.
+    With ``write_slots`` (int32 per row; sequence-split caches) the position still comes from
+    ``cache_seqlens`` but k/v are written at ``write_slots[b]``, or not at all where it is -1."""
+    return _append_rope_norm(q, k, v, k_cache, v_cache, cache_seqlens, cos, sin, qk_scale, eps, write_slots)
 
 
 def append_kv(k, v, k_cache, v_cache, cache_seqlens):
@@ -363,12 +380,26 @@ def append_kv(k, v, k_cache, v_cache, cache_seqlens):
 
 
 def decode_attention(q, k_cache, v_cache, cache_seqlens, seqlen_offset=1, window_left=-1, kv_begin=0, kv_end=0,
-                     partial=False):
+                     partial=False, out_f32=None, lse=None):
     """One-token attention over the cache. q: (B, Hq, D). With ``partial`` also returns the fp32
     normalised output and the natural-log sum-exp (for a cross-GPU combine)."""
     out, out_f32, lse = _decode_attn_core(q, k_cache, v_cache, cache_seqlens, seqlen_offset, window_left, kv_begin,
-                                          kv_end, partial)
+                                          kv_end, partial, out_f32, lse)
     return (out, out_f32, lse) if partial else out
+
+
+def kv_split_plan(cache_seqlens, world, rank, block, T_new=1):
+    """Block-cyclic sequence split: (keys of each row this shard holds after the append, local
+    write index of the new token or -1) as two int32 tensors."""
+    _require_cuda("kv_split_plan", cache_seqlens)
+    B = cache_seqlens.numel()
+    local_len = torch.empty_like(cache_seqlens)
+    slot = torch.empty_like(cache_seqlens)
+    idx = cache_seqlens.device.index
+    with _device_guard(idx):
+        _lib.call("nckv_kv_split_plan", cache_seqlens.data_ptr(), B, T_new, world, rank, block, local_len.data_ptr(),
+                  slot.data_ptr(), torch.cuda.current_stream(idx).cuda_stream)
+    return local_len, slot
 
 
 def prefill_attention(q, k, v, cache_seqlens=None, window_left=-1):

@@ -9,7 +9,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from nanochat_b200.dist import KVSplitAttention, kv_shard_range, shard_rows
+from nanochat_b200.dist import KVSplitAttention, kv_shard_range, owned_below, shard_rows
 from oracle import kv_oracle as O
 
 
@@ -28,6 +28,15 @@ def test_shard_rows_and_kv_ranges():
     assert all(b % 32 == 0 for b, _ in odd[:2])
 
 
+def test_block_cyclic_ownership_counts():
+    world, block = 4, 64
+    for n in [0, 1, 63, 64, 65, 255, 256, 257, 1000, 4096]:
+        counts = [owned_below(n, world, r, block) for r in range(world)]
+        assert sum(counts) == n
+        brute = [sum(1 for p in range(n) if (p // block) % world == r) for r in range(world)]
+        assert counts == brute
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
@@ -44,7 +53,7 @@ def _worker(rank, world, port, B, Hq, Hkv, D, T, seqlens, window, ret):
         vc = torch.randn(B, T, Hkv, D, generator=g)
         lens = torch.tensor(seqlens, dtype=torch.int32)
 
-        def partial_fn(q_, kc_, vc_, lens_):
+        def partial_fn(q_, kc_, vc_, lens_, out_buf=None, lse_buf=None):
             o, l = O.attention_kvcache(q_.numpy()[:, None], kc_.numpy(), vc_.numpy(), lens_.numpy(), window_left=window,
                                        kv_begin=att.kv_begin, kv_end=att.kv_end)
             if att.kv_end <= att.kv_begin:
@@ -55,7 +64,7 @@ def _worker(rank, world, port, B, Hq, Hkv, D, T, seqlens, window, ret):
             o, l = O.lse_combine(po.numpy(), pl.numpy())
             return torch.from_numpy(o), torch.from_numpy(l)
 
-        att = KVSplitAttention(T, window_left=window, partial_fn=partial_fn, combine_fn=combine_fn)
+        att = KVSplitAttention(T, window_left=window, block=0, partial_fn=partial_fn, combine_fn=combine_fn)
         # poison the keys this rank does not own: the result must not depend on them
         kc_local, vc_local = kc.clone(), vc.clone()
         kc_local[:, :att.kv_begin] = 1e4

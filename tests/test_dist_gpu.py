@@ -33,15 +33,44 @@ def _worker(rank, world, port, ret):
         kc = torch.randn(B, T, Hkv, 128, generator=g).to(torch.bfloat16)
         vc = torch.randn(B, T, Hkv, 128, generator=g).to(torch.bfloat16)
         lens = torch.tensor([4095, 2047, 100, 3000], dtype=torch.int32)
-        att = KVSplitAttention(T)
+        # (1) contiguous ranges in a full-capacity cache
+        att = KVSplitAttention(T, block=0)
         kd, vd = kc.to(dev), vc.to(dev)
         kd[:, :att.kv_begin] = float("nan")  # keys of other ranks must never be read here
         kd[:, att.kv_end:] = float("nan")
         out = att.attend(q.to(dev), kd, vd, lens.to(dev))
         torch.cuda.synchronize()
-        status = ops.read_status(dev)
         full, _ = O.attention_kvcache(q.float().numpy()[:, None], kc.float().numpy(), vc.float().numpy(), lens.numpy())
         err = float(np.abs(out.float().cpu().numpy() - full[:, 0]).max() / np.abs(full).max())
+        # (2) block-cyclic ownership in compact caches, including the owner-only append of the new token
+        from oracle import torch_ref as R
+        block = 256
+        att2 = KVSplitAttention(T, block=block)
+        owner = (torch.arange(T) // block) % world
+        mine = (owner == rank).nonzero()[:, 0]
+        kl = torch.full((B, att2.local_capacity, Hkv, 128), float("nan"), dtype=torch.bfloat16)
+        vl = kl.clone()
+        for b_, L_ in enumerate(lens.tolist()):  # rows hold their first L keys; the rest stays NaN
+            keep = mine[mine < L_]
+            kl[b_, :keep.numel()] = kc[b_, keep]
+            vl[b_, :keep.numel()] = vc[b_, keep]
+        cos, sin = R.rotary_tables(T, 128, "cpu", torch.bfloat16)
+        q_raw = torch.randn(B, 1, Hq, 128, generator=g).to(torch.bfloat16)
+        k_raw = torch.randn(B, 1, Hkv, 128, generator=g).to(torch.bfloat16)
+        v_raw = torch.randn(B, 1, Hkv, 128, generator=g).to(torch.bfloat16)
+        out2 = att2.append_and_attend(q_raw.to(dev), k_raw.to(dev), v_raw.to(dev), kl.to(dev), vl.to(dev), lens.to(dev),
+                                      cos.to(dev), sin.to(dev))
+        torch.cuda.synchronize()
+        kc2, vc2 = kc.clone(), vc.clone()  # single-device reference: same append, full attention
+        q2 = R.rope_norm_scale_rows(q_raw, cos, sin, lens)
+        k2 = R.rope_norm_scale_rows(k_raw, cos, sin, lens)
+        for b_, L_ in enumerate(lens.tolist()):
+            kc2[b_, L_] = k2[b_, 0]
+            vc2[b_, L_] = v_raw[b_, 0]
+        full2, _ = O.attention_kvcache(q2.float().numpy(), kc2.float().numpy(), vc2.float().numpy(), lens.numpy())
+        err2 = float(np.abs(out2.float().cpu().numpy() - full2[:, 0]).max() / np.abs(full2).max())
+        err = max(err, err2)
+        status = ops.read_status(dev)
         res = [None] * world
         dist.all_gather_object(res, (err, status))
         if rank == 0:
