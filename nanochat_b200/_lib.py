@@ -35,6 +35,10 @@ SIGNATURES = {
     "nckv_decode_attn_static": (c_int, [c_void_p] * 7 + [c_int] * 5 + [c_i64, c_i64] + [c_int] * 4 +
                                 [ctypes.POINTER(c_void_p), c_void_p]),
     "nckv_lse_combine": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_i64, c_i64, c_void_p, c_void_p, c_void_p]),
+    "nckv_p2p_buffer_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "nckv_p2p_push": (c_int, [c_void_p, c_int, c_int, ctypes.POINTER(c_void_p), c_int, c_int, c_void_p, c_void_p]),
+    "nckv_p2p_wait_combine": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                      ctypes.c_uint64, c_void_p]),
     "nckv_prefill_broadcast": (c_int, [c_void_p] * 5 + [c_int] * 7 + [c_void_p]),
     "nckv_prefill_attn": (c_int, [c_void_p] * 5 + [c_int] * 6 + [c_i64, c_i64, c_int, c_void_p, c_void_p]),
 }

@@ -1,0 +1,175 @@
+// Exchange step of the sequence-split long-context path over NVLink peer memory, without NCCL.
+//
+// Every rank owns one symmetric buffer (same size on every GPU, peer-mapped into every process):
+//     data  [2][world][per] fp32   slot (parity, r) receives rank r's partial for a step of that parity
+//     flags [2][world]      u32    flag (parity, r) = number of the step whose data slot (parity, r) holds
+// per = rows*D normalised partial output + rows log-sum-exp values (padded to 4 floats).
+//
+//   p2p_push_kernel          one CTA of rank r advances the device-resident step counter, copies r's
+//                            partial into every peer's slot (step&1, r) with plain 16-byte stores
+//                            through the peer mappings, fences at system scope and then releases the
+//                            flags with the step number.
+//   p2p_wait_combine_kernel  waits (bounded, wall clock) until all `world` flags of its parity show the
+//                            step, then merges the partials with a log-sum-exp, reading the local
+//                            buffer with L1-bypassing loads.
+// Two parities suffice: a rank can only push step s+2 after it has combined step s+1, which needed every
+// peer's step-s+1 push, which each peer issues after its own combine of step s (stream order).
+// The reference has no counterpart: it never splits keys.
+#include <math.h>
+
+#include "nckv_common.cuh"
+
+#define NCKV_MAX_PEERS 16
+
+namespace nckv {
+
+struct PeerPtrs {
+    float *buf[NCKV_MAX_PEERS];
+};
+
+__host__ __device__ inline long long p2p_per_floats(int rows) { return (long long)rows * NCKV_D + ((rows + 3) & ~3); }
+
+__global__ void __launch_bounds__(1024) p2p_push_kernel(const float4 *__restrict__ send, long long per,
+                                                        const __grid_constant__ PeerPtrs peers, int world, int rank,
+                                                        unsigned *step_counter) {
+    __shared__ unsigned s_step;
+    pdl_wait_prior_grids();
+    pdl_launch_dependents();
+    // The step number lives on the device (so the whole exchange can sit in a CUDA graph): this
+    // single-CTA kernel advances it, the wait/combine kernel that follows reads the same value.
+    if (threadIdx.x == 0) s_step = *step_counter + 1u;
+    __syncthreads();
+    const unsigned step = s_step;
+    const unsigned parity = step & 1u;
+    const long long n_vec = per / 4;
+    for (int peer = 0; peer < world; ++peer) {
+        float4 *dst = reinterpret_cast<float4 *>(peers.buf[peer] + ((long long)parity * world + rank) * per);
+        for (long long i = threadIdx.x; i < n_vec; i += blockDim.x) dst[i] = send[i];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < world) {
+        unsigned *flags = reinterpret_cast<unsigned *>(peers.buf[threadIdx.x] + 2LL * world * per);
+        unsigned *f = flags + parity * world + rank;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(step) : "memory");
+    }
+    if (threadIdx.x == 0) *step_counter = step;
+}
+
+__global__ void __launch_bounds__(256) p2p_wait_combine_kernel(const float *__restrict__ local, long long per, int world,
+                                                               int rows, const unsigned *step_counter,
+                                                               __nv_bfloat16 *__restrict__ out,
+                                                               float *__restrict__ lse_out, int32_t *status,
+                                                               unsigned long long limit_ns) {
+    __shared__ int s_ok;
+    pdl_wait_prior_grids();
+    const unsigned step = *step_counter;  // written by the push kernel before this grid started
+    const unsigned parity = step & 1u;
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    if (threadIdx.x < world) {
+        const unsigned *f = reinterpret_cast<const unsigned *>(local + 2LL * world * per) + parity * world + threadIdx.x;
+        const unsigned long long t0 = global_timer_ns();
+        bool ok = false;
+        for (;;) {
+            unsigned v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+            if (v == step) { ok = true; break; }
+            if (global_timer_ns() - t0 > limit_ns) break;
+            __nanosleep(100);
+        }
+        if (!ok) s_ok = 0;
+    }
+    __syncthreads();
+    if (!s_ok) {  // a peer never delivered: report, write nothing, keep the context usable
+        if (threadIdx.x == 0) atomicOr(status, (int)NCKV_ST_TIMEOUT);
+        return;
+    }
+    const int lane = threadIdx.x & 31;
+    const long long row = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (row >= rows) return;
+    const float *data = local + (long long)parity * world * per;
+    float M = -INFINITY;
+    for (int i = 0; i < world; ++i) M = fmaxf(M, __ldcg(data + i * per + (long long)rows * NCKV_D + row));
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float L = 0.f;
+    if (M > -INFINITY) {
+        for (int i = 0; i < world; ++i) {
+            const float w = expf(__ldcg(data + i * per + (long long)rows * NCKV_D + row) - M);
+            if (w == 0.f) continue;
+            const float4 v = __ldcg(reinterpret_cast<const float4 *>(data + i * per + row * NCKV_D) + lane);
+            L += w;
+            acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
+        }
+        const float inv = 1.f / L;
+        acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+    }
+    uint2 packed;
+    packed.x = pack_bf16x2(acc.x, acc.y);
+    packed.y = pack_bf16x2(acc.z, acc.w);
+    reinterpret_cast<uint2 *>(out + row * NCKV_D)[lane] = packed;
+    if (lse_out && lane == 0) lse_out[row] = M > -INFINITY ? M + logf(L) : -INFINITY;
+}
+
+}  // namespace nckv
+
+extern "C" {
+
+size_t nckv_p2p_buffer_bytes(int world, int rows, int D) {
+    if (world <= 0 || world > NCKV_MAX_PEERS || rows <= 0 || D != NCKV_D) return 0;
+    return (size_t)(2LL * world * nckv::p2p_per_floats(rows)) * 4 + (size_t)2 * world * 4 + 256;
+}
+
+int nckv_p2p_push(const float *send, int rows, int D, void *const *peer_bufs, int world, int rank,
+                  uint32_t *step_counter, void *stream) {
+    using namespace nckv;
+    if (!send || !peer_bufs || !step_counter || rows <= 0 || world <= 0 || world > NCKV_MAX_PEERS || rank < 0 ||
+        rank >= world) {
+        set_error("p2p_push: bad argument (rows=%d world=%d rank=%d)", rows, world, rank);
+        return NCKV_E_ARG;
+    }
+    if (D != NCKV_D) {
+        set_error("p2p_push: head_dim %d unsupported (kernels are built for 128)", D);
+        return NCKV_E_UNSUPPORTED;
+    }
+    PeerPtrs pp;
+    for (int i = 0; i < NCKV_MAX_PEERS; ++i) pp.buf[i] = i < world ? static_cast<float *>(peer_bufs[i]) : nullptr;
+    for (int i = 0; i < world; ++i) {
+        if (!pp.buf[i] || ((uintptr_t)pp.buf[i] & 15)) {
+            set_error("p2p_push: peer buffer %d is null or misaligned", i);
+            return NCKV_E_ARG;
+        }
+    }
+    if ((uintptr_t)send & 15) {
+        set_error("p2p_push: send buffer must be 16-byte aligned");
+        return NCKV_E_ARG;
+    }
+    p2p_push_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const float4 *>(send),
+                                                                       p2p_per_floats(rows), pp, world, rank, step_counter);
+    NCKV_CUDA_CHECK(cudaGetLastError());
+    return NCKV_OK;
+}
+
+int nckv_p2p_wait_combine(const void *local_buf, int world, int rows, int D, const uint32_t *step_counter, void *out,
+                          float *lse_out, int32_t *status, uint64_t limit_ns, void *stream) {
+    using namespace nckv;
+    if (!local_buf || !out || !status || !step_counter || rows <= 0 || world <= 0 || world > NCKV_MAX_PEERS) {
+        set_error("p2p_wait_combine: bad argument (rows=%d world=%d)", rows, world);
+        return NCKV_E_ARG;
+    }
+    if (D != NCKV_D) {
+        set_error("p2p_wait_combine: head_dim %d unsupported (kernels are built for 128)", D);
+        return NCKV_E_UNSUPPORTED;
+    }
+    if (limit_ns == 0) limit_ns = NCKV_WAIT_LIMIT_NS;
+    const int threads = 256;
+    const long long blocks = ((long long)rows * 32 + threads - 1) / threads;
+    p2p_wait_combine_kernel<<<(unsigned)blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const float *>(local_buf), p2p_per_floats(rows), world, rows, step_counter,
+        static_cast<__nv_bfloat16 *>(out),
+        lse_out, status, (unsigned long long)limit_ns);
+    NCKV_CUDA_CHECK(cudaGetLastError());
+    return NCKV_OK;
+}
+
+}  // extern "C"

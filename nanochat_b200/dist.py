@@ -64,7 +64,8 @@ class KVSplitAttention:
     ``append_and_attend`` first runs the fused RoPE/norm/append for the rows this rank owns.
     """
 
-    def __init__(self, capacity, group=None, window_left=-1, block=1024, partial_fn=None, combine_fn=None):
+    def __init__(self, capacity, group=None, window_left=-1, block=1024, exchange="nccl", partial_fn=None,
+                 combine_fn=None):
         import torch.distributed as dist
         self.dist = dist
         self.group = group
@@ -88,6 +89,12 @@ class KVSplitAttention:
         self._partial = partial_fn or self._partial_cuda
         self._combine = combine_fn or ops.lse_combine
         self._gather = self._send = None
+        if exchange not in ("nccl", "p2p"):
+            raise ValueError("exchange must be 'nccl' (all-gather + combine kernel) or 'p2p' (peer-memory push + "
+                             "wait/combine kernel)")
+        self.exchange = exchange if self.world > 1 else "nccl"
+        self._symm = self._peer_ptrs = None
+        self.wait_limit_ns = 0  # 0 = the library default (2 s)
 
     # ---- buffers: [rows*D output | rows lse] per rank, padded to a multiple of 4 floats ----------
     def _buffers(self, rows, D, device):
@@ -134,8 +141,41 @@ class KVSplitAttention:
             lse.copy_(l32.reshape(-1))
         if self.world == 1:
             return self._combine(out_f32.view(1, rows, D), lse.view(1, rows))[0].view(B, Hq, D)
+        if self.exchange == "p2p":
+            return self._exchange_p2p(rows, D, q.device).view(B, Hq, D)
         self.dist.all_gather_into_tensor(self._gather.view(-1), self._send, group=self.group)
         parts_o = self._gather[:, :rows * D].unflatten(1, (rows, D))
         parts_lse = self._gather[:, rows * D:rows * D + rows]
         out, _ = self._combine(parts_o, parts_lse)
         return out.view(B, Hq, D)
+
+    # ---- exchange over NVLink peer memory (no collective library on the data path) ---------------
+    def _setup_p2p(self, rows, D, device):
+        import ctypes
+        import torch.distributed._symmetric_memory as symm_mem
+        from . import _lib
+        nbytes = _lib.lib.nckv_p2p_buffer_bytes(self.world, rows, D)
+        if nbytes == 0:
+            raise RuntimeError(f"p2p exchange: unsupported shape (world={self.world}, rows={rows}, D={D})")
+        buf = symm_mem.empty((nbytes + 3) // 4, dtype=torch.float32, device=device)
+        buf.zero_()
+        hdl = symm_mem.rendezvous(buf, self.group if self.group is not None else self.dist.group.WORLD)
+        ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in hdl.buffer_ptrs])
+        torch.cuda.synchronize(device)
+        self.dist.barrier(group=self.group)  # every buffer is zeroed before anyone pushes
+        self._symm, self._symm_hdl, self._peer_ptrs, self._p2p_rows = buf, hdl, ptrs, rows
+        self._p2p_out = torch.empty(rows, D, dtype=torch.bfloat16, device=device)
+        self._step_ctr = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def _exchange_p2p(self, rows, D, device):
+        from . import _lib
+        if self._symm is None or self._p2p_rows != rows:
+            self._setup_p2p(rows, D, device)
+        idx = device.index if device.index is not None else torch.cuda.current_device()
+        stream = torch.cuda.current_stream(idx).cuda_stream
+        ws = ops.workspace(device, 1, 1, 1)
+        _lib.call("nckv_p2p_push", self._send.data_ptr(), rows, D, self._peer_ptrs, self.world, self.rank,
+                  self._step_ctr.data_ptr(), stream)
+        _lib.call("nckv_p2p_wait_combine", self._symm.data_ptr(), self.world, rows, D, self._step_ctr.data_ptr(),
+                  self._p2p_out.data_ptr(), None, ws.data_ptr(), self.wait_limit_ns, stream)
+        return self._p2p_out

@@ -70,6 +70,20 @@ def _worker(rank, world, port, ret):
         full2, _ = O.attention_kvcache(q2.float().numpy(), kc2.float().numpy(), vc2.float().numpy(), lens.numpy())
         err2 = float(np.abs(out2.float().cpu().numpy() - full2[:, 0]).max() / np.abs(full2).max())
         err = max(err, err2)
+        # (3) the same with the exchange over peer memory instead of NCCL, several steps in a row
+        att3 = KVSplitAttention(T, block=block, exchange="p2p")
+        for step in range(3):
+            lens3 = (lens - step * 7).clamp(min=0)
+            kl3 = torch.full((B, att3.local_capacity, Hkv, 128), float("nan"), dtype=torch.bfloat16)
+            vl3 = kl3.clone()
+            for b_, L_ in enumerate((lens3 + 1).tolist()):
+                keep = mine[mine < L_]
+                kl3[b_, :keep.numel()] = kc[b_, keep]
+                vl3[b_, :keep.numel()] = vc[b_, keep]
+            out3 = att3.attend(q.to(dev), kl3.to(dev), vl3.to(dev), lens3.to(dev))
+            torch.cuda.synchronize()
+            full3, _ = O.attention_kvcache(q.float().numpy()[:, None], kc.float().numpy(), vc.float().numpy(), lens3.numpy())
+            err = max(err, float(np.abs(out3.float().cpu().numpy() - full3[:, 0]).max() / np.abs(full3).max()))
         status = ops.read_status(dev)
         res = [None] * world
         dist.all_gather_object(res, (err, status))

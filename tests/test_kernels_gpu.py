@@ -453,3 +453,41 @@ def test_host_decode_step_matches_device_path():
     assert not out.is_cuda and torch.equal(bits(out), bits(ref.cpu()))
     assert torch.equal(bits(kc2), bits(k_cache)) and torch.equal(bits(vc2), bits(v_cache))
     assert ops().read_status(DEV) == 0
+
+
+def test_p2p_wait_runs_out_and_reports_instead_of_hanging():
+    """A peer that never delivers: the wait/combine kernel gives up after its limit, sets the timeout
+    bit, leaves the output untouched and the context usable.  (The failure is a flag nothing sets.)"""
+    from nanochat_b200 import _lib
+    rows, world = 12, 2
+    nbytes = _lib.lib.nckv_p2p_buffer_bytes(world, rows, 128)
+    assert nbytes > 0
+    buf = torch.zeros((nbytes + 3) // 4, dtype=torch.float32, device=DEV)
+    send = torch.randn(rows * 128 + rows, device=DEV)
+    out = torch.full((rows, 128), 7.0, device=DEV, dtype=BF)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    stream = torch.cuda.current_stream().cuda_stream
+    import ctypes
+    ptrs = (ctypes.c_void_p * world)(buf.data_ptr(), buf.data_ptr())  # both "peers" map to the local buffer
+    # only rank 0's part arrives (we push as rank 0); rank 1's flag is never set
+    ctr = torch.zeros(1, dtype=torch.int32, device=DEV)
+    _lib.call("nckv_p2p_push", send.data_ptr(), rows, 128, ptrs, 1, 0, ctr.data_ptr(), stream)
+    t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    _lib.call("nckv_p2p_wait_combine", buf.data_ptr(), world, rows, 128, ctr.data_ptr(), out.data_ptr(), None,
+              status.data_ptr(), 2_000_000, stream)  # 2 ms limit
+    t1.record()
+    torch.cuda.synchronize()
+    assert status.item() & 2, "timeout bit not set"
+    assert t0.elapsed_time(t1) < 200.0
+    assert (out.float() == 7.0).all(), "output must be left untouched after a timeout"
+    # the context is fine: complete the exchange properly (world = 1 view of the same buffer, step 2)
+    status.zero_()
+    buf.zero_()
+    _lib.call("nckv_p2p_push", send.data_ptr(), rows, 128, ptrs, 1, 0, ctr.data_ptr(), stream)
+    _lib.call("nckv_p2p_wait_combine", buf.data_ptr(), 1, rows, 128, ctr.data_ptr(), out.data_ptr(), None,
+              status.data_ptr(), 0, stream)
+    assert ctr.item() == 2
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    assert torch.allclose(out.float(), send[:rows * 128].view(rows, 128).to(BF).float(), atol=1e-2, rtol=1e-2)
