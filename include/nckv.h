@@ -192,8 +192,9 @@ NCKV_API int nckv_lse_combine(const float *parts_o, const float *parts_lse, int 
  * The same exchange over NVLink peer memory instead of a collective library (no counterpart in
  * the reference).  Every rank owns a symmetric buffer of nckv_p2p_buffer_bytes() bytes, zeroed once
  * and mapped into every peer (peer_bufs[r] = rank r's buffer as seen from this process).  The step
- * number (1, 2, 3, ... in lock step on all ranks) lives in a device word `step_counter` (zeroed
- * once) that nckv_p2p_push advances, so the exchange can be replayed from a CUDA graph.  Per step:
+ * number (1, 2, 3, ... in lock step on all ranks) lives in two device words `step_counter[2]`
+ * (zeroed once; the wait/combine kernel advances it), so the exchange can be replayed from a CUDA
+ * graph.  Per step:
  * nckv_p2p_push copies this rank's packed partial
  * ([rows*D normalised output | rows lse, padded to 4 floats] fp32) into its slot of every peer's
  * buffer and releases a flag there; nckv_p2p_wait_combine waits until the local buffer has all
@@ -202,8 +203,8 @@ NCKV_API int nckv_lse_combine(const float *parts_o, const float *parts_lse, int 
  */
 NCKV_API size_t nckv_p2p_buffer_bytes(int world, int rows, int D);
 NCKV_API int nckv_p2p_push(const float *send, int rows, int D, void *const *peer_bufs, int world, int rank,
-                  uint32_t *step_counter, void *stream);
-NCKV_API int nckv_p2p_wait_combine(const void *local_buf, int world, int rows, int D, const uint32_t *step_counter,
+                  const uint32_t *step_counter, void *stream);
+NCKV_API int nckv_p2p_wait_combine(const void *local_buf, int world, int rows, int D, uint32_t *step_counter,
                           void *out, float *lse_out, int32_t *status, uint64_t limit_ns, void *stream);
 
 /*

@@ -5,10 +5,10 @@
 //     flags [2][world]      u32    flag (parity, r) = number of the step whose data slot (parity, r) holds
 // per = rows*D normalised partial output + rows log-sum-exp values (padded to 4 floats).
 //
-//   p2p_push_kernel          one CTA of rank r advances the device-resident step counter, copies r's
-//                            partial into every peer's slot (step&1, r) with plain 16-byte stores
-//                            through the peer mappings, fences at system scope and then releases the
-//                            flags with the step number.
+//   p2p_push_kernel          CTA p of rank r copies r's partial into peer p's slot (step&1, r) with
+//                            plain 16-byte stores through the peer mapping, fences at system scope
+//                            and then releases the flag with the step number (read from a device
+//                            word, so the exchange can be replayed from a CUDA graph).
 //   p2p_wait_combine_kernel  waits (bounded, wall clock) until all `world` flags of its parity show the
 //                            step, then merges the partials with a log-sum-exp, reading the local
 //                            buffer with L1-bypassing loads.
@@ -31,40 +31,36 @@ __host__ __device__ inline long long p2p_per_floats(int rows) { return (long lon
 
 __global__ void __launch_bounds__(1024) p2p_push_kernel(const float4 *__restrict__ send, long long per,
                                                         const __grid_constant__ PeerPtrs peers, int world, int rank,
-                                                        unsigned *step_counter) {
-    __shared__ unsigned s_step;
+                                                        const unsigned *step_counter) {
     pdl_wait_prior_grids();
     pdl_launch_dependents();
-    // The step number lives on the device (so the whole exchange can sit in a CUDA graph): this
-    // single-CTA kernel advances it, the wait/combine kernel that follows reads the same value.
-    if (threadIdx.x == 0) s_step = *step_counter + 1u;
-    __syncthreads();
-    const unsigned step = s_step;
+    // The step number lives on the device (so the whole exchange can sit in a CUDA graph).  This
+    // kernel only reads it; the wait/combine kernel that follows advances it when its last block ends.
+    const unsigned step = *step_counter + 1u;
     const unsigned parity = step & 1u;
+    const int peer = blockIdx.x;  // one CTA per destination
     const long long n_vec = per / 4;
-    for (int peer = 0; peer < world; ++peer) {
-        float4 *dst = reinterpret_cast<float4 *>(peers.buf[peer] + ((long long)parity * world + rank) * per);
-        for (long long i = threadIdx.x; i < n_vec; i += blockDim.x) dst[i] = send[i];
-    }
+    float4 *dst = reinterpret_cast<float4 *>(peers.buf[peer] + ((long long)parity * world + rank) * per);
+    for (long long i = threadIdx.x; i < n_vec; i += blockDim.x) dst[i] = send[i];
     __threadfence_system();
     __syncthreads();
-    if (threadIdx.x < world) {
-        unsigned *flags = reinterpret_cast<unsigned *>(peers.buf[threadIdx.x] + 2LL * world * per);
+    if (threadIdx.x == 0) {
+        unsigned *flags = reinterpret_cast<unsigned *>(peers.buf[peer] + 2LL * world * per);
         unsigned *f = flags + parity * world + rank;
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(step) : "memory");
     }
-    if (threadIdx.x == 0) *step_counter = step;
 }
 
 __global__ void __launch_bounds__(256) p2p_wait_combine_kernel(const float *__restrict__ local, long long per, int world,
-                                                               int rows, const unsigned *step_counter,
+                                                               int rows, unsigned *step_counter,
                                                                __nv_bfloat16 *__restrict__ out,
                                                                float *__restrict__ lse_out, int32_t *status,
                                                                unsigned long long limit_ns) {
     __shared__ int s_ok;
     pdl_wait_prior_grids();
-    const unsigned step = *step_counter;  // written by the push kernel before this grid started
+    const unsigned step = *step_counter + 1u;  // the step the push kernel before this grid delivered
     const unsigned parity = step & 1u;
+    unsigned *done = step_counter + 1;         // blocks of this grid that have finished
     if (threadIdx.x == 0) s_ok = 1;
     __syncthreads();
     if (threadIdx.x < world) {
@@ -81,34 +77,42 @@ __global__ void __launch_bounds__(256) p2p_wait_combine_kernel(const float *__re
         if (!ok) s_ok = 0;
     }
     __syncthreads();
-    if (!s_ok) {  // a peer never delivered: report, write nothing, keep the context usable
-        if (threadIdx.x == 0) atomicOr(status, (int)NCKV_ST_TIMEOUT);
-        return;
-    }
     const int lane = threadIdx.x & 31;
     const long long row = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    if (row >= rows) return;
-    const float *data = local + (long long)parity * world * per;
-    float M = -INFINITY;
-    for (int i = 0; i < world; ++i) M = fmaxf(M, __ldcg(data + i * per + (long long)rows * NCKV_D + row));
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    float L = 0.f;
-    if (M > -INFINITY) {
-        for (int i = 0; i < world; ++i) {
-            const float w = expf(__ldcg(data + i * per + (long long)rows * NCKV_D + row) - M);
-            if (w == 0.f) continue;
-            const float4 v = __ldcg(reinterpret_cast<const float4 *>(data + i * per + row * NCKV_D) + lane);
-            L += w;
-            acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
+    if (!s_ok) {  // a peer never delivered: report, write nothing, keep the context usable
+        if (threadIdx.x == 0) atomicOr(status, (int)NCKV_ST_TIMEOUT);
+    } else if (row < rows) {
+        const float *data = local + (long long)parity * world * per;
+        float M = -INFINITY;
+        for (int i = 0; i < world; ++i) M = fmaxf(M, __ldcg(data + i * per + (long long)rows * NCKV_D + row));
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        float L = 0.f;
+        if (M > -INFINITY) {
+            for (int i = 0; i < world; ++i) {
+                const float w = expf(__ldcg(data + i * per + (long long)rows * NCKV_D + row) - M);
+                if (w == 0.f) continue;
+                const float4 v = __ldcg(reinterpret_cast<const float4 *>(data + i * per + row * NCKV_D) + lane);
+                L += w;
+                acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
+            }
+            const float inv = 1.f / L;
+            acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
         }
-        const float inv = 1.f / L;
-        acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+        uint2 packed;
+        packed.x = pack_bf16x2(acc.x, acc.y);
+        packed.y = pack_bf16x2(acc.z, acc.w);
+        reinterpret_cast<uint2 *>(out + row * NCKV_D)[lane] = packed;
+        if (lse_out && lane == 0) lse_out[row] = M > -INFINITY ? M + logf(L) : -INFINITY;
     }
-    uint2 packed;
-    packed.x = pack_bf16x2(acc.x, acc.y);
-    packed.y = pack_bf16x2(acc.z, acc.w);
-    reinterpret_cast<uint2 *>(out + row * NCKV_D)[lane] = packed;
-    if (lse_out && lane == 0) lse_out[row] = M > -INFINITY ? M + logf(L) : -INFINITY;
+    // the last block to finish advances the step (every block has read the old value by then)
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned prev = atomicAdd(done, 1u);
+        if (prev == gridDim.x - 1) {
+            *done = 0;
+            *step_counter = step;
+        }
+    }
 }
 
 }  // namespace nckv
@@ -121,7 +125,7 @@ size_t nckv_p2p_buffer_bytes(int world, int rows, int D) {
 }
 
 int nckv_p2p_push(const float *send, int rows, int D, void *const *peer_bufs, int world, int rank,
-                  uint32_t *step_counter, void *stream) {
+                  const uint32_t *step_counter, void *stream) {
     using namespace nckv;
     if (!send || !peer_bufs || !step_counter || rows <= 0 || world <= 0 || world > NCKV_MAX_PEERS || rank < 0 ||
         rank >= world) {
@@ -144,13 +148,13 @@ int nckv_p2p_push(const float *send, int rows, int D, void *const *peer_bufs, in
         set_error("p2p_push: send buffer must be 16-byte aligned");
         return NCKV_E_ARG;
     }
-    p2p_push_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const float4 *>(send),
+    p2p_push_kernel<<<world, 1024, 0, static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const float4 *>(send),
                                                                        p2p_per_floats(rows), pp, world, rank, step_counter);
     NCKV_CUDA_CHECK(cudaGetLastError());
     return NCKV_OK;
 }
 
-int nckv_p2p_wait_combine(const void *local_buf, int world, int rows, int D, const uint32_t *step_counter, void *out,
+int nckv_p2p_wait_combine(const void *local_buf, int world, int rows, int D, uint32_t *step_counter, void *out,
                           float *lse_out, int32_t *status, uint64_t limit_ns, void *stream) {
     using namespace nckv;
     if (!local_buf || !out || !status || !step_counter || rows <= 0 || world <= 0 || world > NCKV_MAX_PEERS) {

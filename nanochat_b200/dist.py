@@ -165,7 +165,7 @@ class KVSplitAttention:
         self.dist.barrier(group=self.group)  # every buffer is zeroed before anyone pushes
         self._symm, self._symm_hdl, self._peer_ptrs, self._p2p_rows = buf, hdl, ptrs, rows
         self._p2p_out = torch.empty(rows, D, dtype=torch.bfloat16, device=device)
-        self._step_ctr = torch.zeros(1, dtype=torch.int32, device=device)
+        self._step_ctr = torch.zeros(2, dtype=torch.int32, device=device)  # [step, finished blocks]
 
     def _exchange_p2p(self, rows, D, device):
         from . import _lib

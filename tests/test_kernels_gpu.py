@@ -470,7 +470,7 @@ def test_p2p_wait_runs_out_and_reports_instead_of_hanging():
     import ctypes
     ptrs = (ctypes.c_void_p * world)(buf.data_ptr(), buf.data_ptr())  # both "peers" map to the local buffer
     # only rank 0's part arrives (we push as rank 0); rank 1's flag is never set
-    ctr = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ctr = torch.zeros(2, dtype=torch.int32, device=DEV)
     _lib.call("nckv_p2p_push", send.data_ptr(), rows, 128, ptrs, 1, 0, ctr.data_ptr(), stream)
     t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
     t0.record()
@@ -487,7 +487,7 @@ def test_p2p_wait_runs_out_and_reports_instead_of_hanging():
     _lib.call("nckv_p2p_push", send.data_ptr(), rows, 128, ptrs, 1, 0, ctr.data_ptr(), stream)
     _lib.call("nckv_p2p_wait_combine", buf.data_ptr(), 1, rows, 128, ctr.data_ptr(), out.data_ptr(), None,
               status.data_ptr(), 0, stream)
-    assert ctr.item() == 2
+    assert ctr.tolist() == [2, 0]
     torch.cuda.synchronize()
     assert status.item() == 0
     assert torch.allclose(out.float(), send[:rows * 128].view(rows, 128).to(BF).float(), atol=1e-2, rtol=1e-2)
