@@ -36,9 +36,18 @@
 
 namespace nckv {
 
-constexpr int DEC_TILE = 32;    // keys per tile
-constexpr int DEC_STAGES = 3;   // tiles in flight per warp
-constexpr int DEC_WARPS = 4;    // warps (independent streams) per CTA
+#ifndef NCKV_DEC_TILE
+#define NCKV_DEC_TILE 32
+#endif
+#ifndef NCKV_DEC_STAGES
+#define NCKV_DEC_STAGES 3
+#endif
+#ifndef NCKV_DEC_WARPS
+#define NCKV_DEC_WARPS 4
+#endif
+constexpr int DEC_TILE = NCKV_DEC_TILE;      // keys per tile (multiple of 16)
+constexpr int DEC_STAGES = NCKV_DEC_STAGES;  // tiles in flight per warp
+constexpr int DEC_WARPS = NCKV_DEC_WARPS;    // warps (independent streams) per CTA
 constexpr int DEC_MAX_B = 1024; // rows per launch (bounds the shared-memory row tables)
 constexpr int DEC_HALF_BYTES = DEC_TILE * 128;        // one 64-channel half of a K or V tile
 constexpr int DEC_STAGE_BYTES = 4 * DEC_HALF_BYTES;   // K lo, K hi, V lo, V hi
