@@ -11,7 +11,9 @@
 //     see the same HBM bandwidth (two dies, distance to the stacks); the dynamic part lets the
 //     fast ones absorb the difference.
 // A warp is a self-contained stream processor: lane 0 issues TMA tile loads (K and V, 128-byte
-// swizzle, L2 evict-first) into the warp's private ring of DEC_STAGES shared-memory stages,
+// swizzle, L2 evict-first) into the warp's private ring of DEC_STAGES shared-memory stages (48 keys x
+// 512 B = 24 KB each; 4 warps x 2 stages = 192 KB in flight per SM; measured best of the
+// tile/stage/warp splits of that budget on B200),
 // completion is signalled on the warp's own mbarriers, and the loads run ahead across pair and
 // run boundaries.  There is no CTA-wide synchronisation after set-up and no fence or wait on
 // another warp anywhere in the stream.
@@ -37,10 +39,10 @@
 namespace nckv {
 
 #ifndef NCKV_DEC_TILE
-#define NCKV_DEC_TILE 32
+#define NCKV_DEC_TILE 48
 #endif
 #ifndef NCKV_DEC_STAGES
-#define NCKV_DEC_STAGES 3
+#define NCKV_DEC_STAGES 2
 #endif
 #ifndef NCKV_DEC_WARPS
 #define NCKV_DEC_WARPS 4

@@ -182,9 +182,15 @@ def test_decode_attention_config1_shape_and_split_invariance():
     q = torch.randn(32, 12, 128, generator=gen, device=DEV).to(BF)
     k_cache, v_cache = make_cache(32, 2048, 12, None, gen)
     st = torch.tensor(seqlens, device=DEV, dtype=torch.int32)
+    _, batch32, _ = ops().decode_attention(q, k_cache, v_cache, st, kv_begin=0, kv_end=2048, partial=True)
     for b in (0, 7, 31):
-        alone = ops().decode_attention(q[b:b + 1], k_cache[b:b + 1], v_cache[b:b + 1], st[b:b + 1])
-        assert rel_err(alone.float(), out[b:b + 1].float()) <= 4e-3
+        alone, alone32, _ = ops().decode_attention(q[b:b + 1], k_cache[b:b + 1], v_cache[b:b + 1], st[b:b + 1],
+                                                   kv_begin=0, kv_end=2048, partial=True)
+        # fp32 outputs: only the bf16 rounding of P (taken against a different running max when the
+        # tiles are cut differently) separates the two evaluations
+        assert rel_err(alone32, batch32[b:b + 1]) <= 3e-3
+        # bf16 outputs may differ by one unit in the last place (2^-8 relative to the largest element)
+        assert rel_err(alone.float(), out[b:b + 1].float()) <= 1e-2
 
 
 def test_decode_attention_long_rows_gqa():
