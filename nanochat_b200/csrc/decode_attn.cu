@@ -56,7 +56,14 @@ constexpr int DEC_STAGE_BYTES = 4 * DEC_HALF_BYTES;   // K lo, K hi, V lo, V hi
 constexpr int DEC_STATUS_BYTES = 256;                 // status word, then the ticket counter at +16
 constexpr int DEC_RING = 4;                           // runs a warp may have claimed but not finished
 constexpr int DEC_DYN_PER_WARP = 4;                   // at most this many dynamic runs per warp of the grid
-constexpr int DEC_STATIC_NUM = 7, DEC_STATIC_DEN = 10; // statically assigned fraction of the tiles
+#ifndef NCKV_DEC_STATIC_NUM
+#define NCKV_DEC_STATIC_NUM 7
+#endif
+#ifndef NCKV_DEC_MIN_RUN
+#define NCKV_DEC_MIN_RUN 2
+#endif
+constexpr int DEC_STATIC_NUM = NCKV_DEC_STATIC_NUM, DEC_STATIC_DEN = 10; // statically assigned fraction of a slice
+constexpr int DEC_MIN_RUN = NCKV_DEC_MIN_RUN;  // tiles in the smallest dynamic run
 constexpr int MERGE_WARPS = 8;
 constexpr int MERGE_BATCH = 16; // O rows fetched per round trip
 constexpr int MERGE_PLAN = 4;  // chunks of 32 parts whose record slots a merge warp works out ahead of time
@@ -145,7 +152,7 @@ struct RunGeometry {
         s_big = static_part(q + 1);
         s_small = static_part(q);
         const int tail = (q + 1) - s_big;  // the longest dynamic stretch
-        CH = max(2, (tail + DEC_DYN_PER_WARP - 1) / DEC_DYN_PER_WARP);
+        CH = max(DEC_MIN_RUN, (tail + DEC_DYN_PER_WARP - 1) / DEC_DYN_PER_WARP);
         d_big = (q + 1 - s_big + CH - 1) / CH;
         d_small = (q - s_small + CH - 1) / CH;
         n_dyn = r * d_big + (W - r) * d_small;

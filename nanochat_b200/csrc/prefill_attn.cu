@@ -1,23 +1,30 @@
 // Kernel (d): dense causal attention for T_new >= 1 query tokens per row (prefill, chunked
-// prefill, flash_attn_func), on the 5th-generation tensor cores: tcgen05.mma with both operands
-// in shared memory (TMA, 128-byte swizzle) and the accumulators in tensor memory (TMEM).
+// prefill, flash_attn_func), on the 5th-generation tensor cores: tcgen05.mma with Q, K, V in
+// shared memory (TMA, 128-byte swizzle), the probabilities and the accumulators in tensor memory.
 //
-// One CTA (128 threads) owns a tile of PF_M = 128 query tokens of one (row, q head) and walks the
-// visible keys in tiles of PF_N = 64:
-//   1. S = Q K^T      one elected thread issues 8 x tcgen05.mma (M128 N64 K16) into TMEM columns
-//                     [0, 64); completion arrives on an mbarrier through tcgen05.commit
-//   2. softmax        thread r owns query row r = TMEM lane r: tcgen05.ld brings its 64 scores
-//                     into registers, causal / window masking is done by index, running max and
-//                     sum are per-thread scalars, P is rounded to bf16 and written to shared
-//                     memory in the K-major swizzled layout the next product reads
-//   3. O += P V       4 x tcgen05.mma (M128 N128 K16), V used in place as an MN-major operand,
-//                     accumulating in TMEM columns [128, 256) over all tiles; S of the next tile is
-//                     issued straight behind it.  P is scaled by a running max that is only raised
-//                     when the true max has grown by more than 2^8; only then is the O row
-//                     rescaled in TMEM (tcgen05.ld / multiply / tcgen05.st), so most tiles touch
-//                     the accumulator not at all.  O is read once, at the end.
-// K/V tiles are double buffered.  Two CTAs fit on an SM (about 112 KB of shared memory and 256 of
-// the 512 TMEM columns each), so one CTA's softmax overlaps the other's tensor work.
+// One CTA owns a tile of PF_M = 128 query tokens of one (row, q head) and walks the visible keys
+// in tiles of PF_N = 64.  Three roles, connected by mbarriers only (no CTA-wide barrier in the loop):
+//   producer warp     one lane issues the TMA copies: Q once, K and V through two stages each; a
+//                     stage is refilled as soon as the product that read it has completed
+//   MMA warp          one lane issues, per tile,
+//                       S = Q K^T   8 x tcgen05.mma (M128 N64 K16) into one of two S buffers in
+//                                   TMEM (columns [0, 64) and [64, 128)), two tiles ahead of the softmax
+//                       O += P V    4 x tcgen05.mma (M128 N128 K16): P is the A operand, read from
+//                                   TMEM; V is used in place as an MN-major shared-memory operand;
+//                                   the accumulator stays in TMEM columns [128, 256) over all tiles
+//                     and signals completion through tcgen05.commit
+//   softmax warps     thread r owns query row r = TMEM lane r: tcgen05.ld brings its 64 scores
+//                     into registers, causal / window masking is done by index (edge tiles only),
+//                     running max and sum are per-thread scalars, P is rounded to bf16 and stored
+//                     with tcgen05.st over the first 32 columns of the S buffer it came from.
+//                     P is scaled by a running max that is only raised when the true max has
+//                     grown by more than 2^8; only then is the O row rescaled in TMEM
+//                     (tcgen05.ld / multiply / tcgen05.st), so most tiles neither wait for nor
+//                     touch the accumulator.  O is read once, at the end.
+// Products issued by one thread execute in order: S of tile it+2 is issued behind O += P V(it)
+// and may therefore overwrite the buffer P(it) was read from.
+// Two CTAs fit on an SM (about 96 KB of shared memory and 256 of the 512 TMEM columns each), so
+// one CTA's softmax overlaps the other's tensor work.
 // Every barrier wait is bounded; a wait that runs out sets NCKV_ST_TIMEOUT, the CTA stops issuing
 // work, frees its TMEM and returns.
 //
@@ -33,10 +40,12 @@ namespace nckv {
 constexpr int PF_M = 128;  // query tokens per CTA
 constexpr int PF_N = 64;   // keys per tile
 constexpr int PF_STAGES = 2;
+constexpr int PF_SPLIT = 1;                           // softmax threads per query row (2 measured slower)
+constexpr int PF_SOFTMAX_THREADS = PF_M * PF_SPLIT;
+constexpr int PF_THREADS = PF_SOFTMAX_THREADS + 64;   // + one warp that issues the MMAs + one that issues the TMA copies
 constexpr int PF_Q_BYTES = PF_M * NCKV_D * 2;        // 32 KB: two 64-channel halves of [128][128 B]
 constexpr int PF_KV_BYTES = PF_N * NCKV_D * 2;       // 16 KB: two halves of [64][128 B]
-constexpr int PF_P_BYTES = PF_M * PF_N * 2;          // 16 KB: [128][128 B]
-constexpr int PF_TMEM_COLS = 256;                    // S: [0,64)  O tile: [128,256)
+constexpr int PF_TMEM_COLS = 256;                    // S/P buffers: [0,64), [64,128)   O: [128,256)
 constexpr unsigned long long PF_WAIT_LIMIT = NCKV_WAIT_LIMIT_NS;
 
 struct PrefillParams {
@@ -114,6 +123,51 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+// 32 lanes x 32 consecutive 32-bit columns, raw words (packed bf16 pairs of the P operand).
+__device__ __forceinline__ void tmem_st32_words(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+          "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]),
+          "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]),
+          "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// 32 lanes x 16 consecutive 32-bit columns, raw words.
+__device__ __forceinline__ void tmem_st16_words(uint32_t taddr, const uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+          "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_st_words(uint32_t taddr, const uint32_t (&v)[32]) { tmem_st32_words(taddr, v); }
+__device__ __forceinline__ void tmem_st_words(uint32_t taddr, const uint32_t (&v)[16]) { tmem_st16_words(taddr, v); }
+
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (row r of A in TMEM lane r, two bf16 per 32-bit column).
+__device__ __forceinline__ void umma_bf16_a_tmem(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ float ex2_approx(float x) {  // 2^x, one MUFU instruction; 2^-inf = 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // Shared-memory matrix descriptor (128-byte swizzle).  Fields: start address >> 4 in bits 0..13,
 // leading-dimension byte offset >> 4 in bits 16..29, stride-dimension byte offset >> 4 in bits
 // 32..45, descriptor version 1 in bits 46..47, layout type (2 = 128-byte swizzle) in bits 61..63.
@@ -134,7 +188,18 @@ __host__ __device__ constexpr uint32_t umma_idesc(int M, int N, int a_mn_major, 
            ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
-__global__ void __launch_bounds__(128, 2)
+// Debug builds with -DNCKV_PF_TIMELINE record clock64() stamps of two CTAs' loop phases.
+#ifdef NCKV_PF_TIMELINE
+__device__ long long *g_pf_tl = nullptr;
+#define PF_STAMP(k)                                                                                  \
+    do {                                                                                             \
+        if (tl_slot >= 0 && it < 40) tl_ptr[((tl_slot * 40) + it) * 8 + (k)] = clock64();            \
+    } while (0)
+#else
+#define PF_STAMP(k)
+#endif
+
+__global__ void __launch_bounds__(PF_THREADS, 2)
 prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const PrefillParams p) {
     // The swizzled tiles need 1024-byte aligned bases; the dynamic segment is declared with that
@@ -147,15 +212,20 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     uint8_t *sQ = smem;                                   // 32 KB
     uint8_t *sK = sQ + PF_Q_BYTES;                        // 2 x 16 KB
     uint8_t *sV = sK + PF_STAGES * PF_KV_BYTES;           // 2 x 16 KB
-    uint8_t *sP = sV + PF_STAGES * PF_KV_BYTES;           // 16 KB
-    uint64_t *bars = reinterpret_cast<uint64_t *>(sP + PF_P_BYTES);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sV + PF_STAGES * PF_KV_BYTES);
     uint64_t *bar_q = bars;          // Q landed
     uint64_t *bar_k = bars + 1;      // [PF_STAGES] K tile landed
     uint64_t *bar_v = bars + 3;      // [PF_STAGES] V tile landed
-    uint64_t *bar_s = bars + 5;      // S = QK^T complete
-    uint64_t *bar_o = bars + 6;      // O_t = PV complete
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 7);
+    uint64_t *bar_s = bars + 5;      // [2] S = QK^T complete (two S buffers in TMEM)
+    uint64_t *bar_o = bars + 7;      // [2] O (+)= P V(it) complete, on bar_o[it & 1]
+    // [2] P(it) in TMEM, S(it) read, O rescaled: one arrival per softmax warp on bar_p[it & 1].  Two
+    // barriers because the softmax may finish tile it+1 before the issuer has looked at tile it.
+    uint64_t *bar_p = bars + 9;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 11);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    // PF_SPLIT == 2 only: [2 buffers][2][PF_M] row maxima exchanged between the threads of a row
+    __nv_bfloat16 *s_xchg = reinterpret_cast<__nv_bfloat16 *>(bars + 12);
+    (void)s_xchg;
 
     const int tid = threadIdx.x, warp = tid >> 5;
     const int n_qtiles = (p.T_new + PF_M - 1) / PF_M;
@@ -190,8 +260,12 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             mbar_init(&bar_k[s], 1);
             mbar_init(&bar_v[s], 1);
         }
-        mbar_init(bar_s, 1);
-        mbar_init(bar_o, 1);
+        mbar_init(&bar_s[0], 1);
+        mbar_init(&bar_s[1], 1);
+        mbar_init(&bar_o[0], 1);
+        mbar_init(&bar_o[1], 1);
+        mbar_init(&bar_p[0], PF_SOFTMAX_THREADS / 32);
+        mbar_init(&bar_p[1], PF_SOFTMAX_THREADS / 32);
         *abort_flag = 0;
         fence_mbar_init();
     }
@@ -203,214 +277,319 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_s = tmem_base;          // columns [0, 64)
+    const uint32_t tmem_s = tmem_base;          // S buffer 0: columns [0, 64), S buffer 1: columns [64, 128)
     const uint32_t tmem_o = tmem_base + 128;    // columns [128, 256)
-    const uint32_t lane_sel = (uint32_t)(warp * 32) << 16;
-
-    auto load_kv = [&](int tile, int stage) {  // thread 0 only
-        const int key0 = kv_lo + tile * PF_N;
-        uint8_t *kd = sK + stage * PF_KV_BYTES, *vd = sV + stage * PF_KV_BYTES;
-        fence_proxy_async_smem();
-        mbar_arrive_expect_tx(&bar_k[stage], PF_KV_BYTES);
-        tma_load_4d(kd, &tmap_k, &bar_k[stage], 0, hkv, key0, b);
-        tma_load_4d(kd + PF_KV_BYTES / 2, &tmap_k, &bar_k[stage], 64, hkv, key0, b);
-        mbar_arrive_expect_tx(&bar_v[stage], PF_KV_BYTES);
-        tma_load_4d(vd, &tmap_v, &bar_v[stage], 0, hkv, key0, b);
-        tma_load_4d(vd + PF_KV_BYTES / 2, &tmap_v, &bar_v[stage], 64, hkv, key0, b);
-    };
-
-    if (tid == 0 && n_tiles > 0) {
-        mbar_arrive_expect_tx(bar_q, PF_Q_BYTES);
-        tma_load_4d(sQ, &tmap_q, bar_q, 0, hq, t0, b);
-        tma_load_4d(sQ + PF_Q_BYTES / 2, &tmap_q, bar_q, 64, hq, t0, b);
-        for (int i = 0; i < PF_STAGES && i < n_tiles; ++i) load_kv(i, i);
-    }
+    const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;  // a warp reaches TMEM lanes 32*(warp % 4) ..
 
     constexpr uint32_t IDESC_S = umma_idesc(PF_M, PF_N, 0, 0);
     constexpr uint32_t IDESC_O = umma_idesc(PF_M, NCKV_D, 0, 1);
-
-    // Softmax state of this thread's row.  P is scaled by m_used, which follows the true running
-    // max lazily: it is only raised (and the O row in TMEM rescaled) when the max has grown by more
-    // than 2^8, so exp2(s - m_used) stays <= 256 and most tiles need no rescale at all.
-    float m_used = -INFINITY, l_run = 0.f;
-    const int row = tid;               // query row inside the tile == TMEM lane
-    const int pos = L + t0 + row;      // absolute position of this row's token
+    const bool issuer_warp = warp == PF_SOFTMAX_THREADS / 32;
     bool aborted = false;
-
-    auto wait_or_abort = [&](uint64_t *bar, uint32_t parity) -> bool {
-        if (mbar_wait_bounded(bar, parity, PF_WAIT_LIMIT)) return true;
+#ifdef NCKV_PF_TIMELINE
+    int tl_slot = -1;
+    long long *const tl_ptr = g_pf_tl;
+    {
+        int cta = -1;
+        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) cta = 0;
+        if (blockIdx.x == 8 && blockIdx.y == 3 && blockIdx.z == 2) cta = 1;
+        int th = tid == 0 ? 0 : (tid == 64 ? 1 : (tid == PF_SOFTMAX_THREADS ? 2 : -1));
+        if (tl_ptr && cta >= 0 && th >= 0) tl_slot = cta * 3 + th;
+    }
+#endif
+    auto timed_out = [&]() {
         *abort_flag = 1;
         atomicOr(p.status, (int)NCKV_ST_TIMEOUT);
-        return false;
     };
-    // thread 0: S(tile) = Q K(tile)^T into TMEM columns [0, 64), then arrive on bar_s
-    auto issue_s = [&](int tile) {
-        const int stage = tile % PF_STAGES;
-        bool ok = tile > 0 || wait_or_abort(bar_q, 0);
-        ok = ok && wait_or_abort(&bar_k[stage], (uint32_t)((tile / PF_STAGES) & 1));
-        if (ok) {
-            tc_fence_after();
-            const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + stage * PF_KV_BYTES);
-#pragma unroll
-            for (int kk = 0; kk < NCKV_D / 16; ++kk) {
-                const uint32_t off = (uint32_t)(kk & 3) * 32;
-                const uint64_t da = smem_desc_sw128(qa + (kk >> 2) * (PF_Q_BYTES / 2) + off, 16, 1024);
-                const uint64_t db = smem_desc_sw128(ka + (kk >> 2) * (PF_KV_BYTES / 2) + off, 16, 1024);
-                umma_bf16(tmem_s, da, db, IDESC_S, kk > 0 ? 1u : 0u);
+
+    if (warp == PF_SOFTMAX_THREADS / 32 + 1) {
+        // =============== one lane moves the tiles: Q once, K and V through two stages each =======
+        if ((tid & 31) == 0 && n_tiles > 0) {
+            auto load_k = [&](int tile) {  // K(tile) -> stage tile % 2
+                const int stage = tile % PF_STAGES, key0 = kv_lo + tile * PF_N;
+                uint8_t *kd = sK + stage * PF_KV_BYTES;
+                mbar_arrive_expect_tx(&bar_k[stage], PF_KV_BYTES);
+                tma_load_4d(kd, &tmap_k, &bar_k[stage], 0, hkv, key0, b);
+                tma_load_4d(kd + PF_KV_BYTES / 2, &tmap_k, &bar_k[stage], 64, hkv, key0, b);
+            };
+            auto load_v = [&](int tile) {  // V(tile) -> stage tile % 2
+                const int stage = tile % PF_STAGES, key0 = kv_lo + tile * PF_N;
+                uint8_t *vd = sV + stage * PF_KV_BYTES;
+                mbar_arrive_expect_tx(&bar_v[stage], PF_KV_BYTES);
+                tma_load_4d(vd, &tmap_v, &bar_v[stage], 0, hkv, key0, b);
+                tma_load_4d(vd + PF_KV_BYTES / 2, &tmap_v, &bar_v[stage], 64, hkv, key0, b);
+            };
+            mbar_arrive_expect_tx(bar_q, PF_Q_BYTES);
+            tma_load_4d(sQ, &tmap_q, bar_q, 0, hq, t0, b);
+            tma_load_4d(sQ + PF_Q_BYTES / 2, &tmap_q, bar_q, 64, hq, t0, b);
+            for (int i = 0; i < PF_STAGES && i < n_tiles; ++i) {
+                load_k(i);
+                load_v(i);
             }
+            bool ok = true;
+            for (int it = 0; it + PF_STAGES < n_tiles && ok; ++it) {
+                // S(it) complete: its K stage is free for K(it+2)
+                ok = mbar_wait_bounded(&bar_s[it & 1], (uint32_t)((it >> 1) & 1), PF_WAIT_LIMIT);
+                if (!ok) break;
+                load_k(it + PF_STAGES);
+                // P V(it) complete: its V stage is free for V(it+2)
+                ok = mbar_wait_bounded(&bar_o[it & 1], (uint32_t)((it >> 1) & 1), PF_WAIT_LIMIT);
+                if (!ok) break;
+                load_v(it + PF_STAGES);
+            }
+            if (!ok) timed_out();
         }
-        umma_commit(bar_s);  // also on the abort path: nobody may be left waiting without a bound
-    };
-    // thread 0: O (+)= P V(tile) into TMEM columns [128, 256), then arrive on bar_o
-    auto issue_pv = [&](int tile) {
-        const int stage = tile % PF_STAGES;
-        if (wait_or_abort(&bar_v[stage], (uint32_t)((tile / PF_STAGES) & 1))) {
-            tc_fence_after();
-            const uint32_t pa = smem_u32(sP), va = smem_u32(sV + stage * PF_KV_BYTES);
+        __syncwarp();
+    } else if (issuer_warp) {
+        // =============== one warp feeds the tensor core ============================================
+        // The whole warp runs this loop so that control flow and every MMA operand (descriptors,
+        // TMEM addresses) stay warp-uniform; only the tcgen05.mma / tcgen05.commit instructions
+        // themselves are executed by a single lane.
+        if (n_tiles > 0) {
+            const bool leader = (tid & 31) == 0;
+            // Descriptors differ only in the start-address field (address >> 4 in the low 14 bits),
+            // so they are built once and advanced by adding the byte offset >> 4.
+            const uint64_t desc_q = smem_desc_sw128(smem_u32(sQ), 16, 1024);
+            const uint64_t desc_k = smem_desc_sw128(smem_u32(sK), 16, 1024);
+            const uint64_t desc_v = smem_desc_sw128(smem_u32(sV), PF_KV_BYTES / 2, 1024);
+            auto wait_all = [&](uint64_t *bar, uint32_t parity) -> bool {
+                return __all_sync(0xffffffffu, mbar_wait_bounded(bar, parity, PF_WAIT_LIMIT));
+            };
+            // S(tile) = Q K(tile)^T into S buffer tile & 1, then arrive on bar_s[tile & 1]
+            auto issue_s = [&](int tile) -> bool {
+                const int stage = tile % PF_STAGES;
+                if (tile == 0 && !wait_all(bar_q, 0)) return false;
+                if (!wait_all(&bar_k[stage], (uint32_t)((tile / PF_STAGES) & 1))) return false;
+                tc_fence_after();
+                const uint64_t dk = desc_k + (uint64_t)((stage * PF_KV_BYTES) >> 4);
+                const uint32_t ds = tmem_s + (uint32_t)(tile & 1) * PF_N;
 #pragma unroll
-            for (int ks = 0; ks < PF_N / 16; ++ks) {
-                const uint64_t da = smem_desc_sw128(pa + ks * 32, 16, 1024);
+                for (int kk = 0; kk < NCKV_D / 16; ++kk) {
+                    const uint32_t off = (uint32_t)(kk & 3) * 32;
+                    const uint64_t da = desc_q + (uint64_t)(((kk >> 2) * (PF_Q_BYTES / 2) + off) >> 4);
+                    const uint64_t db = dk + (uint64_t)(((kk >> 2) * (PF_KV_BYTES / 2) + off) >> 4);
+                    if (leader) umma_bf16(ds, da, db, IDESC_S, kk > 0 ? 1u : 0u);
+                }
+                if (leader) umma_commit(&bar_s[tile & 1]);
+                __syncwarp();
+                return true;
+            };
+            // O (+)= P V(tile) into TMEM columns [128, 256), then arrive on bar_o[tile & 1]
+            auto issue_pv = [&](int tile) -> bool {
+                const int stage = tile % PF_STAGES;
+                if (!wait_all(&bar_v[stage], (uint32_t)((tile / PF_STAGES) & 1))) return false;
+                tc_fence_after();
                 // V in place: N (channels) contiguous, the two 64-channel halves PF_KV_BYTES/2 apart
                 // (leading offset), 8-key groups 1024 B apart (stride offset)
-                const uint64_t db = smem_desc_sw128(va + ks * 16 * 128, PF_KV_BYTES / 2, 1024);
-                umma_bf16(tmem_o, da, db, IDESC_O, (tile > 0 || ks > 0) ? 1u : 0u);
+                const uint64_t dv = desc_v + (uint64_t)((stage * PF_KV_BYTES) >> 4);
+                const uint32_t pbase = tmem_s + (uint32_t)(tile & 1) * PF_N;
+#pragma unroll
+                for (int ks = 0; ks < PF_N / 16; ++ks) {
+                    // P(tile) sits in the first 32 columns of its S buffer; 16 keys = 8 columns
+                    const uint64_t db = dv + (uint64_t)((ks * 16 * 128) >> 4);
+                    if (leader) umma_bf16_a_tmem(tmem_o, pbase + (uint32_t)ks * 8, db, IDESC_O, (tile > 0 || ks > 0) ? 1u : 0u);
+                }
+                if (leader) umma_commit(&bar_o[tile & 1]);
+                __syncwarp();
+                return true;
+            };
+
+            // S runs two tiles ahead of the softmax
+            bool ok = issue_s(0);
+            if (ok && n_tiles > 1) ok = issue_s(1);
+            for (int it = 0; it < n_tiles && ok; ++it) {
+                PF_STAMP(0);
+                // P(it) is in TMEM, S(it) has been read, O carries the scale P was made with
+                ok = wait_all(&bar_p[it & 1], (uint32_t)((it >> 1) & 1));
+                if (!ok) break;
+                tc_fence_after();
+                PF_STAMP(3);
+                ok = issue_pv(it);
+                PF_STAMP(4);
+                if (ok && it + 2 < n_tiles) ok = issue_s(it + 2);
+                PF_STAMP(5);
             }
+            if (!ok && leader) timed_out();
         }
-        umma_commit(bar_o);
-    };
+        __syncwarp();
+    } else {
+        // =============== softmax threads: PF_SPLIT per query row =================================
+        // Softmax state of this thread's row.  P is scaled by m_used, which follows the true running
+        // max lazily: it is only raised (and the O row in TMEM rescaled) when the max has grown by
+        // more than 2^8, so exp2(s - m_used) stays <= 256 and most tiles need no rescale at all.
+        float m_used = -INFINITY, l_run = 0.f;
+        const int row = tid & (PF_M - 1);  // query row inside the tile == TMEM lane
+        const int half = tid / PF_M;       // which share of the tile's scores (and of the output channels) is mine
+        const int pos = L + t0 + row;      // absolute position of this row's token
+        constexpr int HN = PF_N / PF_SPLIT;    // scores per thread and tile
+        constexpr int OC = NCKV_D / PF_SPLIT;  // output channels per thread
 
-    if (tid == 0 && n_tiles > 0) issue_s(0);
-
-    for (int it = 0; it < n_tiles; ++it) {
-        const int stage = it % PF_STAGES;
-        const uint32_t kv_parity = (uint32_t)((it / PF_STAGES) & 1);
-        const int key0 = kv_lo + it * PF_N;
-
-        // ---- S(it) is complete; the tensor pipe works in issue order, so O (+)= P V of tile it-1 is
-        //      complete too: its P buffer, its K/V stage and the O accumulator are ours again -----
-        if (!mbar_wait_bounded(bar_s, (uint32_t)(it & 1), PF_WAIT_LIMIT)) {
-            *abort_flag = 1;
-            atomicOr(p.status, (int)NCKV_ST_TIMEOUT);
-        }
-        tc_fence_after();
-        if (tid == 0 && it >= 1 && it + 1 < n_tiles) load_kv(it + 1, (it + 1) % PF_STAGES);
-
-        // ---- softmax on row `row` ------------------------------------------------------------
-        float s_val[PF_N];
-        {
-            float c0[32], c1[32];
-            tmem_ld32(tmem_s + lane_sel, c0);
-            tmem_ld32(tmem_s + lane_sel + 32, c1);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) { s_val[i] = c0[i] * p.scale_log2; s_val[32 + i] = c1[i] * p.scale_log2; }
-        }
-        // only tiles that touch the causal diagonal, the window edge or the end of the keys need
-        // per-element masking (uniform over the CTA)
-        const bool edge = (key0 + PF_N - 1 > L + t0) || (key0 + PF_N > kv_hi) ||
-                          (p.window_left >= 0 && key0 < L + t0 + PF_M - 1 - p.window_left);
-        if (edge) {
-#pragma unroll
-            for (int c = 0; c < PF_N; ++c) {
-                const int j = key0 + c;
-                const bool visible = (j <= pos) && (j < kv_hi) && (p.window_left < 0 || pos - j <= p.window_left);
-                s_val[c] = visible ? s_val[c] : -INFINITY;
-            }
-        }
-        float mx = -INFINITY;
-#pragma unroll
-        for (int c = 0; c < PF_N; ++c) mx = fmaxf(mx, s_val[c]);
-        // tcgen05.ld/st are warp-wide (.sync.aligned): the decision to touch the accumulator is
-        // taken per warp, every lane then applies its own factor (1 for rows that keep their scale)
-        const bool raise = mx > m_used + 8.f;  // also the first tile that shows this row a key (m_used = -inf)
-        const float alpha = raise ? exp2f(m_used - mx) : 1.f;  // exp2(-inf) = 0
-        if (it > 0 && __any_sync(0xffffffffu, raise)) {  // bring the O rows accumulated so far to the new scale
-#pragma unroll
-            for (int ch = 0; ch < NCKV_D / 32; ++ch) {
-                float c[32];
-                tmem_ld32(tmem_o + lane_sel + ch * 32, c);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) c[i] *= alpha;
-                tmem_st32(tmem_o + lane_sel + ch * 32, c);
-            }
-        }
-        if (raise) {
-            l_run *= alpha;
-            m_used = mx;
-        }
-        const float m_use = m_used == -INFINITY ? 0.f : m_used;  // a row that has seen no key yet
-        float rsum = 0.f;
-        uint32_t pk[PF_N / 2];
-#pragma unroll
-        for (int c = 0; c < PF_N; c += 2) {
-            const float p0 = exp2f(s_val[c] - m_use), p1 = exp2f(s_val[c + 1] - m_use);
-            rsum += p0 + p1;
-            pk[c / 2] = pack_bf16x2(p0, p1);
-        }
-        l_run += rsum;
-        // P row -> shared memory, K-major with the 128-byte swizzle (16-byte chunk c ^ (row % 8))
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-            uint4 v = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-            *reinterpret_cast<uint4 *>(sP + row * 128 + ((c ^ (row & 7)) << 4)) = v;
-        }
-        // rows of the V tile past the last key may hold stale bytes: zero them so that a zero
-        // probability never multiplies a NaN/Inf bit pattern
-        if (key0 + PF_N > kv_hi) {
-            uint8_t *vd = sV + stage * PF_KV_BYTES;
-            if (mbar_wait_bounded(&bar_v[stage], kv_parity, PF_WAIT_LIMIT)) {
-                for (int idx = tid; idx < (key0 + PF_N - kv_hi) * 16; idx += 128) {
-                    const int r = (kv_hi - key0) + idx / 16, ch = idx % 16;
-                    *reinterpret_cast<uint4 *>(vd + (ch >> 3) * (PF_KV_BYTES / 2) + r * 128 + ((ch & 7) << 4)) =
-                        make_uint4(0, 0, 0, 0);
+        for (int it = 0; it < n_tiles; ++it) {
+            const int stage = it % PF_STAGES;
+            const uint32_t kv_parity = (uint32_t)((it / PF_STAGES) & 1);
+            const int key0 = kv_lo + it * PF_N;
+            const uint32_t tmem_s_it = tmem_s + (uint32_t)(it & 1) * PF_N;
+            PF_STAMP(0);
+            // tcgen05.ld/st are warp-wide (.sync.aligned): every decision that skips them is taken per warp
+            {
+                const bool ok = *abort_flag == 0 &&
+                                mbar_wait_bounded(&bar_s[it & 1], (uint32_t)((it >> 1) & 1), PF_WAIT_LIMIT);
+                if (!__all_sync(0xffffffffu, ok)) {
+                    aborted = true;
+                    break;
                 }
             }
-        }
-        fence_proxy_async_smem();  // P (and the zeroed V rows) must be visible to the tensor core
-        tc_fence_before();         // orders this thread's TMEM loads/stores before the next MMAs
-        __syncthreads();
-        aborted = *abort_flag != 0;
-        if (aborted) break;
+            tc_fence_after();
+            PF_STAMP(1);
 
-        // ---- O (+)= P V(it), and straight behind it S(it+1): the tensor pipe stays fed while
-        //      this CTA's threads wait, and the other CTA of the SM runs its softmax ------------
-        if (tid == 0) {
-            issue_pv(it);
-            if (it + 1 < n_tiles) issue_s(it + 1);
-        }
-    }
-
-    // ---- epilogue -----------------------------------------------------------------------------
-    const int t = t0 + row;
-    if (!aborted && n_tiles > 0) {
-        if (!mbar_wait_bounded(bar_o, (uint32_t)((n_tiles - 1) & 1), PF_WAIT_LIMIT)) {
-            *abort_flag = 1;
-            atomicOr(p.status, (int)NCKV_ST_TIMEOUT);
-            aborted = true;
-        }
-        tc_fence_after();
-    }
-    aborted = __any_sync(0xffffffffu, aborted);  // keep the warp together for the TMEM loads below
-    if (!aborted) {  // uniform over the CTA: the TMEM loads below are warp-wide instructions
-        const float inv = (n_tiles > 0 && l_run > 0.f) ? 1.f / l_run : 0.f;
-        uint4 *dst = reinterpret_cast<uint4 *>(p.out + (((long long)b * p.T_new + t) * p.Hq + hq) * NCKV_D);
+            float s_val[HN];
 #pragma unroll
-        for (int ch = 0; ch < NCKV_D / 32; ++ch) {
-            float c[32];
-            if (n_tiles > 0) {
-                tmem_ld32(tmem_o + lane_sel + ch * 32, c);
-            } else {
+            for (int ch = 0; ch < HN / 32; ++ch) {
+                float c[32];
+                tmem_ld32(tmem_s_it + lane_sel + half * HN + ch * 32, c);  // raw q.k, scaled inside the exponent
 #pragma unroll
-                for (int i = 0; i < 32; ++i) c[i] = 0.f;
+                for (int i = 0; i < 32; ++i) s_val[ch * 32 + i] = c[i];
             }
-            if (t < p.T_new) {  // rows past the end of the sequence are padding
+            // only tiles that touch the causal diagonal, the window edge or the end of the keys need
+            // per-element masking (uniform over the CTA)
+            const bool edge = (key0 + PF_N - 1 > L + t0) || (key0 + PF_N > kv_hi) ||
+                              (p.window_left >= 0 && key0 < L + t0 + PF_M - 1 - p.window_left);
+            if (edge) {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    uint4 v;
-                    v.x = pack_bf16x2(c[8 * i + 0] * inv, c[8 * i + 1] * inv);
-                    v.y = pack_bf16x2(c[8 * i + 2] * inv, c[8 * i + 3] * inv);
-                    v.z = pack_bf16x2(c[8 * i + 4] * inv, c[8 * i + 5] * inv);
-                    v.w = pack_bf16x2(c[8 * i + 6] * inv, c[8 * i + 7] * inv);
-                    dst[ch * 4 + i] = v;
+                for (int c = 0; c < HN; ++c) {
+                    const int j = key0 + half * HN + c;
+                    const bool visible = (j <= pos) && (j < kv_hi) && (p.window_left < 0 || pos - j <= p.window_left);
+                    s_val[c] = visible ? s_val[c] : -INFINITY;
+                }
+            }
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains instead of one
+#pragma unroll
+            for (int c = 0; c < HN; c += 4) {
+                mx4[0] = fmaxf(mx4[0], s_val[c]);
+                mx4[1] = fmaxf(mx4[1], s_val[c + 1]);
+                mx4[2] = fmaxf(mx4[2], s_val[c + 2]);
+                mx4[3] = fmaxf(mx4[3], s_val[c + 3]);
+            }
+            float mx_raw = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            if (PF_SPLIT == 2) {
+                // The row max needs both halves: exchange through shared memory, double buffered
+                // because a thread may run up to one tile ahead of its partner.  bf16 rounded UP: the
+                // reference point of the exponentials only has to be the same in both threads and
+                // not below the true max.
+                __nv_bfloat16 *xb = s_xchg + (it & 1) * 2 * PF_M;
+                const __nv_bfloat16 mine = __float2bfloat16_ru(mx_raw);
+                xb[half * PF_M + row] = mine;
+                asm volatile("bar.sync 1, %0;" ::"n"(PF_SOFTMAX_THREADS) : "memory");
+                mx_raw = fmaxf(__bfloat162float(mine), __bfloat162float(xb[(half ^ 1) * PF_M + row]));
+            }
+            PF_STAMP(2);
+            // the max is taken on raw scores and scaled once (the scale is positive)
+            const float mx = mx_raw * p.scale_log2;
+            const bool raise = mx > m_used + 8.f;  // also the first tile that shows this row a key (m_used = -inf)
+            const float alpha = raise ? ex2_approx(m_used - mx) : 1.f;  // 2^-inf = 0
+            if (raise) {
+                l_run *= alpha;
+                m_used = mx;
+            }
+            const float m_use = m_used == -INFINITY ? 0.f : m_used;  // a row that has seen no key yet
+            float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+            uint32_t pk[HN / 2];
+#pragma unroll
+            for (int c = 0; c < HN; c += 4) {
+                // one FFMA and one MUFU.EX2 per score: 2^(s * scale - m)
+                const float p0 = ex2_approx(fmaf(s_val[c], p.scale_log2, -m_use));
+                const float p1 = ex2_approx(fmaf(s_val[c + 1], p.scale_log2, -m_use));
+                const float p2 = ex2_approx(fmaf(s_val[c + 2], p.scale_log2, -m_use));
+                const float p3 = ex2_approx(fmaf(s_val[c + 3], p.scale_log2, -m_use));
+                rs4[0] += p0; rs4[1] += p1; rs4[2] += p2; rs4[3] += p3;
+                pk[c / 2] = pack_bf16x2(p0, p1);
+                pk[c / 2 + 1] = pack_bf16x2(p2, p3);
+            }
+            l_run += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);  // this thread's share of the row sum
+            PF_STAMP(3);
+
+            // P row -> TMEM, over the first 32 columns of this tile's S buffer (this lane's own scores,
+            // already in registers).  S of tile it+2 is issued behind P V(it) and lands on top of it.
+            tmem_st_words(tmem_s_it + lane_sel + half * (HN / 2), pk);
+            PF_STAMP(4);
+            // A raised scale: O (+)= P V of the previous tile must be complete before the O rows
+            // accumulated so far are brought to the new scale (tcgen05.ld / multiply / tcgen05.st).
+            // Every lane applies its own factor (1 for rows that keep their scale).
+            if (it > 0 && __any_sync(0xffffffffu, raise)) {
+                const bool ok = mbar_wait_bounded(&bar_o[(it - 1) & 1], (uint32_t)(((it - 1) >> 1) & 1), PF_WAIT_LIMIT);
+                if (!__all_sync(0xffffffffu, ok)) {
+                    if (!ok) timed_out();
+                    aborted = true;
+                    break;
+                }
+                tc_fence_after();
+#pragma unroll
+                for (int ch = 0; ch < OC / 32; ++ch) {
+                    float c[32];
+                    tmem_ld32(tmem_o + lane_sel + half * OC + ch * 32, c);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) c[i] *= alpha;
+                    tmem_st32(tmem_o + lane_sel + half * OC + ch * 32, c);
+                }
+            }
+            // rows of the V tile past the last key may hold stale bytes: zero them so that a zero
+            // probability never multiplies a NaN/Inf bit pattern
+            if (key0 + PF_N > kv_hi) {
+                uint8_t *vd = sV + stage * PF_KV_BYTES;
+                if (mbar_wait_bounded(&bar_v[stage], kv_parity, PF_WAIT_LIMIT)) {
+                    for (int idx = tid; idx < (key0 + PF_N - kv_hi) * 16; idx += PF_SOFTMAX_THREADS) {
+                        const int r = (kv_hi - key0) + idx / 16, ch = idx % 16;
+                        *reinterpret_cast<uint4 *>(vd + (ch >> 3) * (PF_KV_BYTES / 2) + r * 128 + ((ch & 7) << 4)) =
+                            make_uint4(0, 0, 0, 0);
+                    }
+                }
+                fence_proxy_async_smem();  // the zeroed V rows must be visible to the tensor core
+            }
+            PF_STAMP(5);
+            tc_fence_before();  // orders this thread's TMEM loads/stores before the next MMAs
+            __syncwarp();
+            if ((tid & 31) == 0) mbar_arrive(&bar_p[it & 1]);  // one arrival per warp
+            PF_STAMP(6);
+        }
+        if (aborted && *abort_flag == 0) timed_out();  // a wait ran out in this warp
+
+        // ---- epilogue ---------------------------------------------------------------------------
+        const int t = t0 + row;
+        if (!aborted && n_tiles > 0) {
+            const bool ok = mbar_wait_bounded(&bar_o[(n_tiles - 1) & 1], (uint32_t)(((n_tiles - 1) >> 1) & 1), PF_WAIT_LIMIT);
+            if (!ok) timed_out();
+            aborted = !__all_sync(0xffffffffu, ok);
+            tc_fence_after();
+        }
+        float l_row = l_run;
+        if (PF_SPLIT == 2) {  // the row sum is the sum of the two threads' shares
+            // every product has completed (or the CTA has given up): the first K stage is free
+            float *s_sum = reinterpret_cast<float *>(sK);
+            s_sum[half * PF_M + row] = l_run;
+            asm volatile("bar.sync 1, %0;" ::"n"(PF_SOFTMAX_THREADS) : "memory");
+            l_row += s_sum[(half ^ 1) * PF_M + row];
+        }
+        if (!aborted) {  // uniform over the warp: the TMEM loads below are warp-wide instructions
+            const float inv = (n_tiles > 0 && l_row > 0.f) ? 1.f / l_row : 0.f;
+            uint4 *dst = reinterpret_cast<uint4 *>(p.out + (((long long)b * p.T_new + t) * p.Hq + hq) * NCKV_D + half * OC);
+#pragma unroll
+            for (int ch = 0; ch < OC / 32; ++ch) {
+                float c[32];
+                if (n_tiles > 0) {
+                    tmem_ld32(tmem_o + lane_sel + half * OC + ch * 32, c);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) c[i] = 0.f;
+                }
+                if (t < p.T_new) {  // rows past the end of the sequence are padding
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        uint4 v;
+                        v.x = pack_bf16x2(c[8 * i + 0] * inv, c[8 * i + 1] * inv);
+                        v.y = pack_bf16x2(c[8 * i + 2] * inv, c[8 * i + 3] * inv);
+                        v.z = pack_bf16x2(c[8 * i + 4] * inv, c[8 * i + 5] * inv);
+                        v.w = pack_bf16x2(c[8 * i + 6] * inv, c[8 * i + 7] * inv);
+                        dst[ch * 4 + i] = v;
+                    }
                 }
             }
         }
@@ -421,10 +600,18 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 }
 
 static size_t prefill_smem_bytes() {
-    return PF_Q_BYTES + 2 * PF_STAGES * PF_KV_BYTES + PF_P_BYTES + 16 * sizeof(uint64_t);
+    return PF_Q_BYTES + 2 * PF_STAGES * PF_KV_BYTES + 12 * sizeof(uint64_t) +
+           (PF_SPLIT == 2 ? 4 * PF_M * sizeof(__nv_bfloat16) : 0);
 }
 
 }  // namespace nckv
+
+#ifdef NCKV_PF_TIMELINE
+extern "C" NCKV_API int nckv_debug_set_pf_timeline(void *ptr) {
+    long long *v = static_cast<long long *>(ptr);
+    return cudaMemcpyToSymbol(nckv::g_pf_tl, &v, sizeof(v)) == cudaSuccess ? 0 : -4;
+}
+#endif
 
 extern "C" int nckv_prefill_attn(const void *q, const void *k, const void *v, const int32_t *cache_seqlens,
                                  void *out, int B, int T_new, int Hq, int Hkv, int D, int T_k,
@@ -486,7 +673,7 @@ extern "C" int nckv_prefill_attn(const void *q, const void *k, const void *v, co
     const int n_qtiles = (T_new + PF_M - 1) / PF_M;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(n_qtiles, Hq, B);
-    cfg.blockDim = dim3(128);
+    cfg.blockDim = dim3(PF_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = static_cast<cudaStream_t>(stream);
     cudaLaunchAttribute attr[1];
