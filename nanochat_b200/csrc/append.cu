@@ -110,10 +110,11 @@ __device__ __forceinline__ uint4 rope_norm_scale(const uint4 &xin, const uint4 &
 
 __global__ void __launch_bounds__(256) append_rope_norm_kernel(const AppendParams p) {
     // Programmatic dependent launch: this grid may have been scheduled while its predecessor was
-    // still running; its inputs come from that predecessor, so wait first.  The attention kernel
-    // that follows may be scheduled right away (it waits for this grid before reading the cache).
-    pdl_wait_prior_grids();
+    // still running; its inputs come from that predecessor, so wait before touching anything.
+    // The attention kernel that follows may be scheduled right away, even before that wait: it
+    // reads only cache_seqlens and older cache rows until it has itself waited for this grid.
     pdl_launch_dependents();
+    pdl_wait_prior_grids();
     const int lane = threadIdx.x & 31;
     const int j = lane & 15;
     const int heads_per_tok = (p.q_in ? p.Hq : 0) + 2 * p.Hkv;

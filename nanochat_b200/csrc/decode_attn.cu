@@ -291,12 +291,21 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
         for (int i = 0; i < DEC_WARPS * DEC_STAGES; ++i) mbar_init(&full_bar[i], 1);
         fence_mbar_init();
     }
-    // Everything from here on may depend on the kernel right before this one in the stream
-    // (cache_seqlens, q, the appended K/V rows): wait for it.  Only the launch itself and the
-    // lines above overlap its tail.
-    pdl_wait_prior_grids();
+    // Programmatic dependent launch: this grid may be running while the kernels before it in the
+    // stream (the append kernel; the tail and the merge kernel of a previous call) still are.
+    // What is read before wait_prior() below is only what none of them writes: cache_seqlens and
+    // keys/values older than the rows this step appended.  q, the appended rows, the run counter
+    // and every store come after it.  Dependents (the merge kernel) are released after the wait,
+    // so that a grid that can start early always finds its predecessor's predecessors complete.
     build_row_tables(p, s_start, s_end, s_pref, blockIdx.x == 0);
-    pdl_launch_dependents();  // the merge kernel may be scheduled and run its own set-up now
+    bool prior_done = false;
+    auto wait_prior = [&]() {  // called warp-uniformly
+        if (!prior_done) {
+            pdl_wait_prior_grids();
+            pdl_launch_dependents();  // the merge kernel may be scheduled and run its own set-up now
+            prior_done = true;
+        }
+    };
     TL_STAMP(1);
 
     RunGeometry geo;
@@ -304,15 +313,22 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
     const int gw = blockIdx.x * DEC_WARPS + warp;
     TL_STAMP(9);
 
-    // rows without any visible key: zero output, lse = -inf (only sharded calls can produce them)
-    for (int b = blockIdx.x; b < B; b += gridDim.x) {
-        if (s_pref[b + 1] != s_pref[b]) continue;
-        for (int i = tid; i < p.Hq * NCKV_D; i += blockDim.x) {
-            const long long o = (long long)b * p.Hq * NCKV_D + i;
-            p.out[o] = __float2bfloat16(0.0f);
-            if (p.out_f32) p.out_f32[o] = 0.0f;
+    {
+        // rows without any visible key: zero output, lse = -inf (only sharded calls can produce them)
+        bool any_empty = false;
+        for (int b = blockIdx.x; b < B; b += gridDim.x) any_empty |= s_pref[b + 1] == s_pref[b];
+        if (any_empty) {  // uniform over the CTA
+            wait_prior();
+            for (int b = blockIdx.x; b < B; b += gridDim.x) {
+                if (s_pref[b + 1] != s_pref[b]) continue;
+                for (int i = tid; i < p.Hq * NCKV_D; i += blockDim.x) {
+                    const long long o = (long long)b * p.Hq * NCKV_D + i;
+                    p.out[o] = __float2bfloat16(0.0f);
+                    if (p.out_f32) p.out_f32[o] = 0.0f;
+                }
+                if (p.lse) for (int i = tid; i < p.Hq; i += blockDim.x) p.lse[(long long)b * p.Hq + i] = -INFINITY;
+            }
         }
-        if (p.lse) for (int i = tid; i < p.Hq; i += blockDim.x) p.lse[(long long)b * p.Hq + i] = -INFINITY;
     }
     if (geo.total == 0) return;  // every warp of the grid takes this exit together
     TL_STAMP(10);
@@ -337,6 +353,7 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
             return gw;
         }
         if (!have_ticket) {  // only when the static run was empty
+            wait_prior();  // the counter belongs to the previous launch until that has completed
             if (lane == 0) next_ticket = atomicAdd(p.run_counter, 1);
             have_ticket = true;
         }
@@ -378,11 +395,13 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
             ++ring_push;
             __syncwarp();
         }
+        const int key0 = s_start[prod.b] + prod.j * DEC_TILE;
+        // a tile that reaches the rows appended by this step has to wait for the append kernel
+        if (!prior_done && key0 + DEC_TILE > s_end[prod.b] - p.seqlen_offset) wait_prior();
         if (lane == 0) {
             const int stage = issue_idx % DEC_STAGES;
             uint8_t *dst = my_stages + stage * DEC_STAGE_BYTES;
             uint64_t *bar = &my_bar[stage];
-            const int key0 = s_start[prod.b] + prod.j * DEC_TILE;
             // the only generic-proxy writes to a stage are the zeroed V rows of a tail tile; order
             // them before the bulk copy that reuses the stage
             if (stage_dirty & (1u << stage)) {
@@ -411,7 +430,12 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
         return true;
     };
 
+    // The first loads of the static run go out before the wait: they overlap the append kernel and,
+    // in back-to-back calls, the tail and the merge of the previous call.
     issue_one();
+    while (issue_idx < DEC_STAGES && prod_left > 0 && issue_one()) {
+    }
+    wait_prior();
     if (!have_ticket) {  // needed once the static run has been issued; by then it has long arrived
         if (lane == 0) next_ticket = atomicAdd(p.run_counter, 1);
         have_ticket = true;
