@@ -37,7 +37,7 @@ B, HQ, HKV, D, T_MAX = 32, 12, 12, 128, 2048
 NSETS = 4
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode_attn_kernel launch on this workload, from the ncu
 # capture summarised in profiles/decode_attn_config1.md
-TRAFFIC_BYTES_PER_LAUNCH = 201.70e6
+TRAFFIC_BYTES_PER_LAUNCH = 202.78e6
 METRIC = "decode tokens/s (KV append + decode attention, B=32 x 12 heads x 128, ragged cache)"
 WORKLOAD = "configs[1]: op-level KV append + decode attention, B=32, 12q/12kv heads, D=128, T_max=2048, ragged seqlens seed 2"
 

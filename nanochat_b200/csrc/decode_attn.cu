@@ -436,6 +436,7 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
     while (issue_idx < DEC_STAGES && prod_left > 0 && issue_one()) {
     }
     wait_prior();
+    TL_STAMP(4);
     if (!have_ticket) {  // needed once the static run has been issued; by then it has long arrived
         if (lane == 0) next_ticket = atomicAdd(p.run_counter, 1);
         have_ticket = true;
