@@ -98,6 +98,18 @@ NCKV_API int nckv_append_rope_norm_at(const void *q_in, const void *k_in, const 
                              int rope_len, float qk_scale, float eps, int32_t *status, void *stream);
 
 /*
+ * Introspection of kernel (b)'s work list: writes, for every row, the half-open range of key
+ * positions [key_begin[b], key_end[b]) the decode kernel would read for these arguments, computed on
+ * the device by the same routine the attention kernels call.  Restates the visible-key rule of
+ * flash_attention.py:83-88 (keys [max(0, L - w), L] of a row whose new token sits at position L),
+ * intersected with [kv_begin, kv_end) when that range is not empty.  Out-of-range lengths are clamped
+ * and flagged in *status like the attention entry points do.  Used by the parity tests.
+ */
+NCKV_API int nckv_decode_key_ranges(const int32_t *cache_seqlens, int B, int T_max, int seqlen_offset,
+                                    int window_left, int kv_begin, int kv_end, int32_t *key_begin,
+                                    int32_t *key_end, int32_t *status, void *stream);
+
+/*
  * Bookkeeping of the sequence-split long-context path (no counterpart in the reference): key
  * positions are owned block-cyclically, position p by shard (p / block) % world at local index
  * (p / (block*world)) * block + p % block.  From the global cache_seqlens (lengths before the new

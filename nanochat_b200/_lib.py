@@ -34,6 +34,7 @@ SIGNATURES = {
                          [c_void_p, c_size_t, c_void_p]),
     "nckv_decode_attn_static": (c_int, [c_void_p] * 7 + [c_int] * 5 + [c_i64, c_i64] + [c_int] * 4 +
                                 [ctypes.POINTER(c_void_p), c_void_p]),
+    "nckv_decode_key_ranges": (c_int, [c_void_p] + [c_int] * 6 + [c_void_p] * 4),
     "nckv_lse_combine": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_i64, c_i64, c_void_p, c_void_p, c_void_p]),
     "nckv_p2p_buffer_bytes": (c_size_t, [c_int, c_int, c_int]),
     "nckv_p2p_push": (c_int, [c_void_p, c_int, c_int, ctypes.POINTER(c_void_p), c_int, c_int, c_void_p, c_void_p]),

@@ -698,6 +698,17 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
     }
 }
 
+// The row tables of a launch, copied out for inspection.
+__global__ void __launch_bounds__(128) decode_key_ranges_kernel(const DecodeParams p, int32_t *key_begin,
+                                                                int32_t *key_end) {
+    __shared__ int s_start[DEC_MAX_B], s_end[DEC_MAX_B], s_pref[DEC_MAX_B + 1];
+    build_row_tables(p, s_start, s_end, s_pref, true);
+    for (int b = threadIdx.x; b < p.B; b += blockDim.x) {
+        key_begin[b] = s_start[b];
+        key_end[b] = s_end[b];
+    }
+}
+
 // Merge of the partial records: one warp per (row, q head).  Lane i looks after part base+i of a
 // chunk of 32 parts for the softmax statistics; for the O row every lane owns channels
 // 4*lane .. 4*lane+3.  Which records belong to a pair follows from cache_seqlens alone, so the
@@ -991,6 +1002,32 @@ int nckv_decode_attn(const void *q, const void *k_cache, const void *v_cache,
 // that loads the library carries it until the process exits.
 #define NCKV_STATIC_SCRATCH_BYTES (14u << 20)
 static __device__ __align__(256) unsigned char g_static_scratch[NCKV_STATIC_SCRATCH_BYTES];
+
+extern "C" int nckv_decode_key_ranges(const int32_t *cache_seqlens, int B, int T_max, int seqlen_offset,
+                                      int window_left, int kv_begin, int kv_end, int32_t *key_begin,
+                                      int32_t *key_end, int32_t *status, void *stream) {
+    using namespace nckv;
+    if (!cache_seqlens || !key_begin || !key_end || !status) {
+        set_error("decode_key_ranges: null pointer argument");
+        return NCKV_E_ARG;
+    }
+    if (B <= 0 || B > DEC_MAX_B || T_max <= 0) {
+        set_error("decode_key_ranges: B=%d must be in 1..%d and T_max=%d positive", B, DEC_MAX_B, T_max);
+        return NCKV_E_ARG;
+    }
+    DecodeParams p = {};
+    p.seqlens = cache_seqlens;
+    p.status = status;
+    p.B = B;
+    p.T_max = T_max;
+    p.seqlen_offset = seqlen_offset;
+    p.window_left = window_left;
+    p.kv_begin = kv_begin;
+    p.kv_end = kv_end;
+    decode_key_ranges_kernel<<<1, 128, 0, static_cast<cudaStream_t>(stream)>>>(p, key_begin, key_end);
+    NCKV_CUDA_CHECK(cudaGetLastError());
+    return NCKV_OK;
+}
 
 int nckv_decode_attn_static(const void *q, const void *k_cache, const void *v_cache,
                             const int32_t *cache_seqlens, void *out, float *out_f32, float *lse_out,

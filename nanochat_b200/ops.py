@@ -402,6 +402,21 @@ def kv_split_plan(cache_seqlens, world, rank, block, T_new=1):
     return local_len, slot
 
 
+def decode_key_ranges(cache_seqlens, T_max, seqlen_offset=1, window_left=-1, kv_begin=0, kv_end=0):
+    """Key positions [begin, end) per row that decode_attention reads for these arguments, as two
+    int32 tensors (computed on the device by the routine the attention kernels use)."""
+    _require_cuda("decode_key_ranges", cache_seqlens)
+    B = cache_seqlens.numel()
+    begin = torch.empty_like(cache_seqlens)
+    end = torch.empty_like(cache_seqlens)
+    idx = cache_seqlens.device.index
+    ws = workspace(cache_seqlens.device, 1, 1, 1)
+    with _device_guard(idx):
+        _lib.call("nckv_decode_key_ranges", cache_seqlens.data_ptr(), B, T_max, seqlen_offset, window_left, kv_begin,
+                  kv_end, begin.data_ptr(), end.data_ptr(), ws.data_ptr(), torch.cuda.current_stream(idx).cuda_stream)
+    return begin, end
+
+
 def prefill_attention(q, k, v, cache_seqlens=None, window_left=-1):
     """Dense causal attention of T_new query tokens per row against a cache view or plain k/v."""
     return _prefill_attn(q, k, v, cache_seqlens, window_left)
