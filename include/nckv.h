@@ -136,6 +136,11 @@ NCKV_API int nckv_append(const void *k_in, const void *v_in, void *k_cache, void
  * the same size; q_rot_dev, out_dev: device (B,Hq,D) bf16 scratch/result; out_host: pinned host
  * (B,Hq,D) bf16.  Performs H2D, nckv_append_rope_norm, nckv_decode_attn, D2H and a stream
  * synchronise; on return out_host holds the attention output.  cache_seqlens is not advanced.
+ * Mapped mode: with qkv_dev == NULL the append kernel reads the pinned host block itself (over
+ * PCIe, through the device alias of the host pointer) and no H2D copy is enqueued; with
+ * out_dev == NULL the attention kernels store the result straight into out_host and no D2H copy
+ * is enqueued.  Both blocks must then be page-locked memory the device can address
+ * (cudaHostAlloc / cudaHostRegister); anything else is rejected with NCKV_E_ARG.
  */
 NCKV_API int nckv_decode_step_host(const void *qkv_host, void *qkv_dev, void *q_rot_dev, void *out_dev, void *out_host,
                           void *k_cache, void *v_cache, const int32_t *cache_seqlens, const void *cos,

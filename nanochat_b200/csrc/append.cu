@@ -338,7 +338,7 @@ int nckv_decode_step_host(const void *qkv_host, void *qkv_dev, void *q_rot_dev, 
                           int64_t cache_token_stride, int rope_len, float qk_scale, float eps, int window_left,
                           void *workspace, size_t workspace_bytes, void *stream) {
     using namespace nckv;
-    if (!qkv_host || !qkv_dev || !q_rot_dev || !out_dev || !out_host || !workspace) {
+    if (!qkv_host || !q_rot_dev || !out_host || !workspace) {
         set_error("decode_step_host: null pointer argument");
         return NCKV_E_ARG;
     }
@@ -348,16 +348,34 @@ int nckv_decode_step_host(const void *qkv_host, void *qkv_dev, void *q_rot_dev, 
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const size_t nq = (size_t)B * Hq * D, nk = (size_t)B * Hkv * D;
-    NCKV_CUDA_CHECK(cudaMemcpyAsync(qkv_dev, qkv_host, (nq + 2 * nk) * 2, cudaMemcpyHostToDevice, s));
-    __nv_bfloat16 *base = static_cast<__nv_bfloat16 *>(qkv_dev);
+    const __nv_bfloat16 *base = static_cast<const __nv_bfloat16 *>(qkv_dev);
+    if (qkv_dev) {
+        NCKV_CUDA_CHECK(cudaMemcpyAsync(qkv_dev, qkv_host, (nq + 2 * nk) * 2, cudaMemcpyHostToDevice, s));
+    } else {  // mapped mode: the append kernel reads the host block through its device alias
+        void *alias = nullptr;
+        if (cudaHostGetDevicePointer(&alias, const_cast<void *>(qkv_host), 0) != cudaSuccess || !alias) {
+            (void)cudaGetLastError();
+            set_error("decode_step_host: qkv_host is not page-locked memory the device can address");
+            return NCKV_E_ARG;
+        }
+        base = static_cast<const __nv_bfloat16 *>(alias);
+    }
+    void *out_target = out_dev;
+    if (!out_dev) {  // mapped mode: the attention kernels store into the host block
+        if (cudaHostGetDevicePointer(&out_target, out_host, 0) != cudaSuccess || !out_target) {
+            (void)cudaGetLastError();
+            set_error("decode_step_host: out_host is not page-locked memory the device can address");
+            return NCKV_E_ARG;
+        }
+    }
     int rc = nckv_append_rope_norm(base, base + nq, base + nq + nk, q_rot_dev, k_cache, v_cache, cache_seqlens, cos, sin,
                                    B, 1, Hq, Hkv, D, T_max, cache_batch_stride, cache_token_stride, rope_len, qk_scale,
                                    eps, static_cast<int32_t *>(workspace), stream);
     if (rc != NCKV_OK) return rc;
-    rc = nckv_decode_attn(q_rot_dev, k_cache, v_cache, cache_seqlens, out_dev, nullptr, nullptr, B, Hq, Hkv, D, T_max,
+    rc = nckv_decode_attn(q_rot_dev, k_cache, v_cache, cache_seqlens, out_target, nullptr, nullptr, B, Hq, Hkv, D, T_max,
                           cache_batch_stride, cache_token_stride, 1, window_left, 0, 0, workspace, workspace_bytes, stream);
     if (rc != NCKV_OK) return rc;
-    NCKV_CUDA_CHECK(cudaMemcpyAsync(out_host, out_dev, nq * 2, cudaMemcpyDeviceToHost, s));
+    if (out_dev) NCKV_CUDA_CHECK(cudaMemcpyAsync(out_host, out_dev, nq * 2, cudaMemcpyDeviceToHost, s));
     NCKV_CUDA_CHECK(cudaStreamSynchronize(s));
     return NCKV_OK;
 }

@@ -246,6 +246,16 @@ def test_workspace_ticket_counter_returns_to_zero():
     assert ws[:256].view(torch.int32).abs().sum().item() == 0, "status word / ticket counter not back to zero"
 
 
+def test_decode_shapes_share_one_workspace():
+    """Calls of different shapes through one workspace: the counter and the records of one call must
+    not leak into the next."""
+    lens32 = torch.randint(1, 2048, (32,), generator=torch.Generator().manual_seed(2)).tolist()
+    for _ in range(2):
+        run_decode_case(32, 12, 12, 2048, lens32, -1, seed=3, check_eager=False)
+        run_decode_case(4, 16, 4, 4096, [4000, 17, 2500, 4095], -1, seed=4)
+        run_decode_case(3, 2, 2, 2048, [2000, 1, 999], 512, seed=5)
+
+
 # ------------------------------------------------------------------------------------------------
 # reference fixtures through the public wrapper
 # ------------------------------------------------------------------------------------------------
@@ -440,8 +450,10 @@ def test_registered_custom_ops_dispatch():
         torch.ops.nckv.decode_attn(q.cpu(), k_cache.cpu(), v_cache.cpu(), st.cpu(), 1, -1, 0, 0, False)
 
 
-def test_host_decode_step_matches_device_path():
-    """nckv_decode_step_host (H2D + append + attention + D2H in one call) == the two device ops."""
+@pytest.mark.parametrize("transfer", ["copy", "mapped"])
+def test_host_decode_step_matches_device_path(transfer):
+    """nckv_decode_step_host (H2D + append + attention + D2H in one call, or the kernels reading and
+    writing the pinned host blocks themselves) == the two device ops."""
     gen = torch.Generator(device=DEV).manual_seed(77)
     B, Hq, Hkv, T_max = 5, 8, 2, 200
     cos, sin = E.rotary_tables(T_max, 128, DEV, BF)
@@ -453,7 +465,7 @@ def test_host_decode_step_matches_device_path():
     kc2, vc2 = k_cache.clone(), v_cache.clone()
     q2 = ops().append_rope_norm(q, k, v, k_cache, v_cache, st, cos, sin)
     ref = ops().decode_attention(q2[:, 0], k_cache, v_cache, st, window_left=50)
-    step = ops().HostDecodeStep(B, Hq, Hkv, cos, sin, DEV)
+    step = ops().HostDecodeStep(B, Hq, Hkv, cos, sin, DEV, transfer=transfer)
     step.q.copy_(q[:, 0].cpu()); step.k.copy_(k[:, 0].cpu()); step.v.copy_(v[:, 0].cpu())
     out = step.run(kc2, vc2, st, 50)
     assert not out.is_cuda and torch.equal(bits(out), bits(ref.cpu()))
