@@ -39,7 +39,8 @@ namespace nckv {
 
 constexpr int PF_M = 128;  // query tokens per CTA
 constexpr int PF_N = 64;   // keys per tile
-constexpr int PF_STAGES = 2;
+constexpr int PF_STAGES = 2;    // K stages
+constexpr int PF_VSTAGES = 3;   // V stages
 constexpr int PF_SPLIT = 1;                           // softmax threads per query row (2 measured slower)
 constexpr int PF_SOFTMAX_THREADS = PF_M * PF_SPLIT;
 constexpr int PF_THREADS = PF_SOFTMAX_THREADS + 64;   // + one warp that issues the MMAs + one that issues the TMA copies
@@ -211,20 +212,25 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     }
     uint8_t *sQ = smem;                                   // 32 KB
     uint8_t *sK = sQ + PF_Q_BYTES;                        // 2 x 16 KB
-    uint8_t *sV = sK + PF_STAGES * PF_KV_BYTES;           // 2 x 16 KB
-    uint64_t *bars = reinterpret_cast<uint64_t *>(sV + PF_STAGES * PF_KV_BYTES);
+    uint8_t *sV = sK + PF_STAGES * PF_KV_BYTES;           // 3 x 16 KB
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sV + PF_VSTAGES * PF_KV_BYTES);
     uint64_t *bar_q = bars;          // Q landed
     uint64_t *bar_k = bars + 1;      // [PF_STAGES] K tile landed
-    uint64_t *bar_v = bars + 3;      // [PF_STAGES] V tile landed
-    uint64_t *bar_s = bars + 5;      // [2] S = QK^T complete (two S buffers in TMEM)
-    uint64_t *bar_o = bars + 7;      // [2] O (+)= P V(it) complete, on bar_o[it & 1]
+    uint64_t *bar_v = bars + 3;      // [PF_VSTAGES] V tile landed
+    // [2] S(it) = Q K(it)^T complete, on bar_s[it & 1].  Products complete in issue order and S(it) is
+    // issued behind O += P V(it-2), so this also says "P V(it-2) complete".
+    uint64_t *bar_s = bars + 6;
+    // [2] O += P V(it) complete, on bar_o[it & 1]: signalled only for the last two tiles, which no S
+    // follows.  Every tcgen05.commit costs tensor-pipe time (measured: groups of 4-8 instructions
+    // between commits run at about half the rate of an uninterrupted stream), so a tile gets one.
+    uint64_t *bar_o = bars + 8;
     // [2] P(it) in TMEM, S(it) read, O rescaled: one arrival per softmax warp on bar_p[it & 1].  Two
     // barriers because the softmax may finish tile it+1 before the issuer has looked at tile it.
-    uint64_t *bar_p = bars + 9;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 11);
+    uint64_t *bar_p = bars + 10;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 12);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     // PF_SPLIT == 2 only: [2 buffers][2][PF_M] row maxima exchanged between the threads of a row
-    __nv_bfloat16 *s_xchg = reinterpret_cast<__nv_bfloat16 *>(bars + 12);
+    __nv_bfloat16 *s_xchg = reinterpret_cast<__nv_bfloat16 *>(bars + 13);
     (void)s_xchg;
 
     const int tid = threadIdx.x, warp = tid >> 5;
@@ -256,10 +262,8 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         prefetch_tensormap(&tmap_k);
         prefetch_tensormap(&tmap_v);
         mbar_init(bar_q, 1);
-        for (int s = 0; s < PF_STAGES; ++s) {
-            mbar_init(&bar_k[s], 1);
-            mbar_init(&bar_v[s], 1);
-        }
+        for (int s = 0; s < PF_STAGES; ++s) mbar_init(&bar_k[s], 1);
+        for (int s = 0; s < PF_VSTAGES; ++s) mbar_init(&bar_v[s], 1);
         mbar_init(&bar_s[0], 1);
         mbar_init(&bar_s[1], 1);
         mbar_init(&bar_o[0], 1);
@@ -311,8 +315,8 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 tma_load_4d(kd, &tmap_k, &bar_k[stage], 0, hkv, key0, b);
                 tma_load_4d(kd + PF_KV_BYTES / 2, &tmap_k, &bar_k[stage], 64, hkv, key0, b);
             };
-            auto load_v = [&](int tile) {  // V(tile) -> stage tile % 2
-                const int stage = tile % PF_STAGES, key0 = kv_lo + tile * PF_N;
+            auto load_v = [&](int tile) {  // V(tile) -> stage tile % 3
+                const int stage = tile % PF_VSTAGES, key0 = kv_lo + tile * PF_N;
                 uint8_t *vd = sV + stage * PF_KV_BYTES;
                 mbar_arrive_expect_tx(&bar_v[stage], PF_KV_BYTES);
                 tma_load_4d(vd, &tmap_v, &bar_v[stage], 0, hkv, key0, b);
@@ -321,20 +325,22 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             mbar_arrive_expect_tx(bar_q, PF_Q_BYTES);
             tma_load_4d(sQ, &tmap_q, bar_q, 0, hq, t0, b);
             tma_load_4d(sQ + PF_Q_BYTES / 2, &tmap_q, bar_q, 64, hq, t0, b);
-            for (int i = 0; i < PF_STAGES && i < n_tiles; ++i) {
-                load_k(i);
-                load_v(i);
-            }
+            for (int i = 0; i < PF_STAGES && i < n_tiles; ++i) load_k(i);
+            for (int i = 0; i < PF_VSTAGES && i < n_tiles; ++i) load_v(i);
             bool ok = true;
-            for (int it = 0; it + PF_STAGES < n_tiles && ok; ++it) {
-                // S(it) complete: its K stage is free for K(it+2)
-                ok = mbar_wait_bounded(&bar_s[it & 1], (uint32_t)((it >> 1) & 1), PF_WAIT_LIMIT);
+            for (int t = 0; t + 2 < n_tiles && ok; ++t) {
+                // S(t) complete: K(t)'s stage is free for K(t+2); and, being issued behind it,
+                // O += P V(t-2) is complete too: V(t-2)'s stage is free for V(t+1)
+                ok = mbar_wait_bounded(&bar_s[t & 1], (uint32_t)((t >> 1) & 1), PF_WAIT_LIMIT);
                 if (!ok) break;
-                load_k(it + PF_STAGES);
-                // P V(it) complete: its V stage is free for V(it+2)
-                ok = mbar_wait_bounded(&bar_o[it & 1], (uint32_t)((it >> 1) & 1), PF_WAIT_LIMIT);
-                if (!ok) break;
-                load_v(it + PF_STAGES);
+                load_k(t + 2);
+                if (t + 1 >= PF_VSTAGES) load_v(t + 1);
+            }
+            // V of the last tile: its stage is the one of V(n-4), free once S(n-2) has completed
+            if (ok && n_tiles - 1 >= PF_VSTAGES && n_tiles >= 2) {
+                const int t = n_tiles - 2;
+                ok = mbar_wait_bounded(&bar_s[t & 1], (uint32_t)((t >> 1) & 1), PF_WAIT_LIMIT);
+                if (ok) load_v(n_tiles - 1);
             }
             if (!ok) timed_out();
         }
@@ -374,9 +380,9 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 return true;
             };
             // O (+)= P V(tile) into TMEM columns [128, 256), then arrive on bar_o[tile & 1]
-            auto issue_pv = [&](int tile) -> bool {
-                const int stage = tile % PF_STAGES;
-                if (!wait_all(&bar_v[stage], (uint32_t)((tile / PF_STAGES) & 1))) return false;
+            auto issue_pv = [&](int tile, bool commit_now) -> bool {
+                const int stage = tile % PF_VSTAGES;
+                if (!wait_all(&bar_v[stage], (uint32_t)((tile / PF_VSTAGES) & 1))) return false;
                 tc_fence_after();
                 // V in place: N (channels) contiguous, the two 64-channel halves PF_KV_BYTES/2 apart
                 // (leading offset), 8-key groups 1024 B apart (stride offset)
@@ -388,7 +394,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                     const uint64_t db = dv + (uint64_t)((ks * 16 * 128) >> 4);
                     if (leader) umma_bf16_a_tmem(tmem_o, pbase + (uint32_t)ks * 8, db, IDESC_O, (tile > 0 || ks > 0) ? 1u : 0u);
                 }
-                if (leader) umma_commit(&bar_o[tile & 1]);
+                if (leader && commit_now) umma_commit(&bar_o[tile & 1]);
                 __syncwarp();
                 return true;
             };
@@ -403,9 +409,12 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 if (!ok) break;
                 tc_fence_after();
                 PF_STAMP(3);
-                ok = issue_pv(it);
+                // S(it+2) goes into the S buffer every thread has just finished reading; its commit also
+                // covers O += P V(it).  The last two tiles have no S behind them and signal bar_o.
+                const bool s_follows = it + 2 < n_tiles;
+                ok = issue_pv(it, !s_follows);
                 PF_STAMP(4);
-                if (ok && it + 2 < n_tiles) ok = issue_s(it + 2);
+                if (ok && s_follows) ok = issue_s(it + 2);
                 PF_STAMP(5);
             }
             if (!ok && leader) timed_out();
@@ -424,8 +433,8 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         constexpr int OC = NCKV_D / PF_SPLIT;  // output channels per thread
 
         for (int it = 0; it < n_tiles; ++it) {
-            const int stage = it % PF_STAGES;
-            const uint32_t kv_parity = (uint32_t)((it / PF_STAGES) & 1);
+            const int stage = it % PF_VSTAGES;
+            const uint32_t kv_parity = (uint32_t)((it / PF_VSTAGES) & 1);
             const int key0 = kv_lo + it * PF_N;
             const uint32_t tmem_s_it = tmem_s + (uint32_t)(it & 1) * PF_N;
             PF_STAMP(0);
@@ -515,7 +524,11 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             // accumulated so far are brought to the new scale (tcgen05.ld / multiply / tcgen05.st).
             // Every lane applies its own factor (1 for rows that keep their scale).
             if (it > 0 && __any_sync(0xffffffffu, raise)) {
-                const bool ok = mbar_wait_bounded(&bar_o[(it - 1) & 1], (uint32_t)(((it - 1) >> 1) & 1), PF_WAIT_LIMIT);
+                // O += P V(it-1) complete: told by S(it+1), which was issued behind it, or by bar_o
+                // when tile it is the last one
+                const bool ok = it + 1 < n_tiles
+                                    ? mbar_wait_bounded(&bar_s[(it + 1) & 1], (uint32_t)(((it + 1) >> 1) & 1), PF_WAIT_LIMIT)
+                                    : mbar_wait_bounded(&bar_o[(it - 1) & 1], 0, PF_WAIT_LIMIT);
                 if (!__all_sync(0xffffffffu, ok)) {
                     if (!ok) timed_out();
                     aborted = true;
@@ -555,7 +568,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         // ---- epilogue ---------------------------------------------------------------------------
         const int t = t0 + row;
         if (!aborted && n_tiles > 0) {
-            const bool ok = mbar_wait_bounded(&bar_o[(n_tiles - 1) & 1], (uint32_t)(((n_tiles - 1) >> 1) & 1), PF_WAIT_LIMIT);
+            const bool ok = mbar_wait_bounded(&bar_o[(n_tiles - 1) & 1], 0, PF_WAIT_LIMIT);
             if (!ok) timed_out();
             aborted = !__all_sync(0xffffffffu, ok);
             tc_fence_after();
@@ -600,7 +613,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 }
 
 static size_t prefill_smem_bytes() {
-    return PF_Q_BYTES + 2 * PF_STAGES * PF_KV_BYTES + 12 * sizeof(uint64_t) +
+    return PF_Q_BYTES + (PF_STAGES + PF_VSTAGES) * PF_KV_BYTES + 13 * sizeof(uint64_t) +
            (PF_SPLIT == 2 ? 4 * PF_M * sizeof(__nv_bfloat16) : 0);
 }
 
