@@ -2,7 +2,7 @@
 
 Run once in a container that has the reference checkout (it is not needed to run the tests):
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path of the reference checkout>
 
 The reference's tokenizer module imports the `rustbpe` wheel, which this path never uses; a stub
 module stands in for it.  Everything else is the reference's own code, unmodified: the functions
@@ -200,4 +200,6 @@ def main(ref_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <path of the reference checkout>")
+    main(sys.argv[1])
