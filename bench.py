@@ -508,6 +508,69 @@ def run_case(args):
                    ms_per_step=ms, eager_ms_per_step=eager_ms, prefill_s=prefill_s, context=ctx,
                    roofline_ms=(kv_step + w_bytes) / (peak * 1e9) * 1e3, kv_bytes_per_step=kv_step, weight_bytes=w_bytes,
                    config={"model": f"d{n_layer}", "B": Bc, "prompt": T0, "steps": n_new})
+    elif args.case in ("engine_d32", "engine_d32_small"):
+        # configs[3]: nanochat d32 with GQA (32 x 2048, 16 query / 4 kv heads), random-init bf16, 256 rows with
+        # ragged prompt lengths U[128, 2048], capacity 4096, top-k 50 sampling at temperature 1; per-row
+        # positions (the reference loop cannot run this batch), decode step replayed from a CUDA graph.
+        # Prefill: uniform 2048-token chunks, each row then truncated to its own length (causal, so the cache
+        # rows below that length are those of the shorter prompt).
+        from nanochat_b200.engine import GraphedDecodeStep, KVCache, sample_next_token
+        from nanochat_b200.gpt import GPT, GPTConfig, rms
+        small = args.case.endswith("small")
+        n_layer, Bc, Tp, cap, chunk = (4, 16, 256, 512, 8) if small else (32, 256, 2048, 4096, 16)
+        cfg = GPTConfig(sequence_len=cap, vocab_size=32768, n_layer=n_layer, n_head=16, n_kv_head=4, n_embd=2048)
+        torch.manual_seed(4)
+        with torch.device("meta"):
+            model = GPT(cfg, compute_dtype=bf)
+        model.to_empty(device=dev)
+        model.init_weights()
+        model.to(bf)
+        model.window_sizes = [(cap // 2, 0) if (i % 4) != 3 else (cap, 0) for i in range(n_layer)]
+        model.window_sizes[-1] = (cap, 0)
+        g4 = torch.Generator().manual_seed(4)
+        lens = torch.randint(Tp // 16, Tp + 1, (Bc,), generator=g4, dtype=torch.int32)
+        prompts = torch.randint(0, 32768, (Bc, Tp), generator=g4)
+        cache = KVCache(batch_size=Bc, num_heads=4, seq_len=cap, head_dim=128, num_layers=n_layer, device=dev, dtype=bf)
+        t0 = time.perf_counter()
+        prev, first = [], []
+        for r0 in range(0, Bc, chunk):
+            part = KVCache(batch_size=chunk, num_heads=4, seq_len=Tp, head_dim=128, num_layers=n_layer, device=dev, dtype=bf)
+            ids_c = prompts[r0:r0 + chunk].to(dev)
+            logits_c = model.forward(ids_c, kv_cache=part)
+            cache.k_cache[:, r0:r0 + chunk, :Tp] = part.k_cache
+            cache.v_cache[:, r0:r0 + chunk, :Tp] = part.v_cache
+            rows = torch.arange(chunk, device=dev)
+            last = (lens[r0:r0 + chunk].to(dev) - 1).long()
+            first.append(logits_c[rows, last])                      # logits at each row's own last prompt token
+            prev.append(rms(model.transformer.wte(ids_c[rows, last]).to(bf)).unsqueeze(1))  # smear state of the model's forward
+            del part, logits_c
+        cache.cache_seqlens.copy_(lens.to(dev))
+        cache.prev_embedding = torch.cat(prev, 0)
+        torch.cuda.synchronize()
+        prefill_s = time.perf_counter() - t0
+        rng = torch.Generator(device=dev).manual_seed(4)
+        ids = sample_next_token(torch.cat(first, 0).float(), rng, temperature=1.0, top_k=50)
+        n_new = max(args.steps, 8)
+        graphed = GraphedDecodeStep(model, cache, ids)
+        for _ in range(3):
+            ids = sample_next_token(graphed.step(ids).float(), rng, temperature=1.0, top_k=50)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n_new):
+            ids = sample_next_token(graphed.step(ids).float(), rng, temperature=1.0, top_k=50)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / n_new
+        now = cache.cache_seqlens.long().cpu()
+        kv_step = sum(4 * 4 * D * int(torch.clamp(now, max=w[0] + 1).sum()) for w in model.window_sizes)
+        w_bytes = 2 * sum(p_.numel() for n_, p_ in model.named_parameters() if "wte" not in n_ and "value_embeds" not in n_)
+        out.update(metric="decode tokens/s (whole model, ragged rows, top-k sampling, CUDA-graphed step)",
+                   value=Bc / (ms * 1e-3), unit="tokens/s", ms_per_step=ms, prefill_s=prefill_s,
+                   mean_context=float(now.float().mean()), roofline_ms=(kv_step + w_bytes) / (peak * 1e9) * 1e3,
+                   kv_bytes_per_step=kv_step, weight_bytes=w_bytes,
+                   config={"model": f"d{n_layer} GQA 16/4", "B": Bc, "prompt": f"U[{Tp // 16},{Tp}]", "capacity": cap,
+                           "steps": n_new, "sampling": "top-k 50, temperature 1"})
     elif args.case == "prefill":            # dense causal attention, d24 shape: 12 heads, T=2048
         Bc, T, Hq, Hkv = 8, 2048, 12, 12
         q, k, v = rnd(Bc, T, Hq, D), rnd(Bc, T, Hkv, D), rnd(Bc, T, Hkv, D)
@@ -556,7 +619,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--case", default=None,
                     help="secondary op-level measurement instead of the headline workload: decode_long, decode_gqa, "
-                         "decode_gqa_window, decode_d24, prefill, broadcast, append, engine_d24, engine_d24_small")
+                         "decode_gqa_window, decode_d24, prefill, broadcast, append, engine_d24, engine_d24_small, engine_d32, "
+                         "engine_d32_small")
     args = ap.parse_args()
     if args.case:
         run_case(args)
