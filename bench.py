@@ -145,6 +145,12 @@ def max_over_ranks(x, world, device):
 # ------------------------------------------------------------------------------------------------
 def cpu_reference_run(steps, warmup, budget_s=25.0):
     from oracle import torch_ref as R
+    # all the host cores this process may use (torchrun exports OMP_NUM_THREADS=1 to its ranks)
+    try:
+        usable = len(os.sched_getaffinity(0))
+    except AttributeError:
+        usable = os.cpu_count() or 1
+    torch.set_num_threads(max(usable, 1))
     threads = torch.get_num_threads()
     gen = torch.Generator().manual_seed(2)
     seqlens = seqlens_cpu()
