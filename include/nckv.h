@@ -160,6 +160,11 @@ NCKV_API int nckv_decode_step_host(const void *qkv_host, void *qkv_dev, void *q_
  * the natural-log sum-exp per (b, h) as fp32 (-inf for an empty key range, out = 0), and
  * when out_f32 != NULL the normalised output is also written there as fp32 (for the
  * cross-GPU combine).  workspace: see nckv_workspace_bytes().
+ * Ordering: the kernels start while the kernel launched before them in the stream may still be
+ * running (programmatic dependent launch) and read cache_seqlens and all but the last
+ * max(seqlen_offset, 1) visible positions of every row before they wait for it.  A libnckv append
+ * directly in front of this call must therefore not have written older positions than those (a
+ * decode step appends exactly that one position); any other kernel is waited for in full.
  */
 NCKV_API int nckv_decode_attn(const void *q, const void *k_cache, const void *v_cache,
                      const int32_t *cache_seqlens, void *out, float *out_f32, float *lse_out,

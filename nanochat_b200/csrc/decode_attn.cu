@@ -294,7 +294,8 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
     // Programmatic dependent launch: this grid may be running while the kernels before it in the
     // stream (the append kernel; the tail and the merge kernel of a previous call) still are.
     // What is read before wait_prior() below is only what none of them writes: cache_seqlens and
-    // keys/values older than the rows this step appended.  q, the appended rows, the run counter
+    // keys/values older than the last max(seqlen_offset, 1) visible positions of a row (the rows a
+    // decode step's append kernel may have written).  q, the appended rows, the run counter
     // and every store come after it.  Dependents (the merge kernel) are released after the wait,
     // so that a grid that can start early always finds its predecessor's predecessors complete.
     build_row_tables(p, s_start, s_end, s_pref, blockIdx.x == 0);
@@ -396,8 +397,10 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
             __syncwarp();
         }
         const int key0 = s_start[prod.b] + prod.j * DEC_TILE;
-        // a tile that reaches the rows appended by this step has to wait for the append kernel
-        if (!prior_done && key0 + DEC_TILE > s_end[prod.b] - p.seqlen_offset) wait_prior();
+        // A tile that reaches the rows appended by this step has to wait for the append kernel.
+        // With seqlen_offset == 0 the caller has already counted the new token in cache_seqlens
+        // (the sequence-split path does): the last visible position is then the appended one.
+        if (!prior_done && key0 + DEC_TILE > s_end[prod.b] - max(p.seqlen_offset, 1)) wait_prior();
         if (lane == 0) {
             const int stage = issue_idx % DEC_STAGES;
             uint8_t *dst = my_stages + stage * DEC_STAGE_BYTES;

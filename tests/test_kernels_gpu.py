@@ -246,6 +246,31 @@ def test_workspace_ticket_counter_returns_to_zero():
     assert ws[:256].view(torch.int32).abs().sum().item() == 0, "status word / ticket counter not back to zero"
 
 
+def test_decode_right_behind_append_sees_the_appended_row():
+    """The attention kernels start while the append kernel in front of them may still be running
+    and prefetch older keys early; the tile that holds the appended position must wait.  Lengths
+    are multiples of the 48-key tile and already count the new token (seqlen_offset = 0, the
+    sequence-split convention), the case in which the appended row is the last row of a full tile."""
+    gen = torch.Generator(device=DEV).manual_seed(21)
+    B, Hq, Hkv, T_max = 64, 4, 4, 480
+    cos, sin = E.rotary_tables(T_max, 128, DEV, BF)
+    after = torch.tensor([48 * (1 + (b % 9)) for b in range(B)], device=DEV, dtype=torch.int32)  # lengths incl. new token
+    before = after - 1
+    slots = before.clone()
+    k_cache, v_cache = make_cache(B, T_max, Hkv, None, gen)
+    for it in range(40):
+        q = torch.randn(B, 1, Hq, 128, generator=gen, device=DEV).to(BF)
+        k = torch.randn(B, 1, Hkv, 128, generator=gen, device=DEV).to(BF) * (1 + it)
+        v = torch.randn(B, 1, Hkv, 128, generator=gen, device=DEV).to(BF) * (1 + it)
+        q2 = ops().append_rope_norm(q, k, v, k_cache, v_cache, before, cos, sin, write_slots=slots)
+        out = ops().decode_attention(q2[:, 0], k_cache, v_cache, after, seqlen_offset=0)
+        torch.cuda.synchronize()
+        settled = ops().decode_attention(q2[:, 0], k_cache, v_cache, after, seqlen_offset=0)  # nothing in flight before it
+        torch.cuda.synchronize()
+        assert torch.equal(bits(out), bits(settled)), f"iteration {it}: attention ran ahead of the append"
+    assert ops().read_status(DEV) == 0
+
+
 def test_decode_shapes_share_one_workspace():
     """Calls of different shapes through one workspace: the counter and the records of one call must
     not leak into the next."""
