@@ -258,12 +258,27 @@ def test_decode_right_behind_append_sees_the_appended_row():
     before = after - 1
     slots = before.clone()
     k_cache, v_cache = make_cache(B, T_max, Hkv, None, gen)
-    for it in range(40):
-        q = torch.randn(B, 1, Hq, 128, generator=gen, device=DEV).to(BF)
-        k = torch.randn(B, 1, Hkv, 128, generator=gen, device=DEV).to(BF) * (1 + it)
-        v = torch.randn(B, 1, Hkv, 128, generator=gen, device=DEV).to(BF) * (1 + it)
+    q = torch.randn(B, 1, Hq, 128, generator=gen, device=DEV).to(BF)
+    k = torch.randn(B, 1, Hkv, 128, generator=gen, device=DEV).to(BF)
+    v = torch.randn(B, 1, Hkv, 128, generator=gen, device=DEV).to(BF)
+
+    def pair():
         q2 = ops().append_rope_norm(q, k, v, k_cache, v_cache, before, cos, sin, write_slots=slots)
-        out = ops().decode_attention(q2[:, 0], k_cache, v_cache, after, seqlen_offset=0)
+        return q2, ops().decode_attention(q2[:, 0], k_cache, v_cache, after, seqlen_offset=0)
+
+    # the two calls back to back on the device (no host gap between the launches): a CUDA graph
+    side = torch.cuda.Stream(DEV)
+    with torch.cuda.stream(side):
+        pair()
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            q2, out = pair()
+    torch.cuda.synchronize()
+    for it in range(40):
+        k.copy_(torch.randn(B, 1, Hkv, 128, generator=gen, device=DEV).to(BF) * (1 + it))
+        v.copy_(torch.randn(B, 1, Hkv, 128, generator=gen, device=DEV).to(BF) * (1 + it))
+        graph.replay()
         torch.cuda.synchronize()
         settled = ops().decode_attention(q2[:, 0], k_cache, v_cache, after, seqlen_offset=0)  # nothing in flight before it
         torch.cuda.synchronize()
