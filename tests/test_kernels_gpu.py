@@ -246,17 +246,20 @@ def test_workspace_ticket_counter_returns_to_zero():
     assert ws[:256].view(torch.int32).abs().sum().item() == 0, "status word / ticket counter not back to zero"
 
 
-def test_decode_right_behind_append_sees_the_appended_row():
+@pytest.mark.parametrize("counted", [True, False])
+def test_decode_right_behind_append_sees_the_appended_row(counted):
     """The attention kernels start while the append kernel in front of them may still be running
     and prefetch older keys early; the tile that holds the appended position must wait.  Lengths
-    are multiples of the 48-key tile and already count the new token (seqlen_offset = 0, the
-    sequence-split convention), the case in which the appended row is the last row of a full tile."""
+    are multiples of the 48-key tile, the case in which the appended row is the last row of a full
+    tile; ``counted``: cache_seqlens already counts the new token (seqlen_offset = 0, the
+    sequence-split convention) or not (seqlen_offset = 1, the reference's convention)."""
     gen = torch.Generator(device=DEV).manual_seed(21)
     B, Hq, Hkv, T_max = 64, 4, 4, 480
     cos, sin = E.rotary_tables(T_max, 128, DEV, BF)
     after = torch.tensor([48 * (1 + (b % 9)) for b in range(B)], device=DEV, dtype=torch.int32)  # lengths incl. new token
     before = after - 1
     slots = before.clone()
+    lens, offset = (after, 0) if counted else (before, 1)
     k_cache, v_cache = make_cache(B, T_max, Hkv, None, gen)
     q = torch.randn(B, 1, Hq, 128, generator=gen, device=DEV).to(BF)
     k = torch.randn(B, 1, Hkv, 128, generator=gen, device=DEV).to(BF)
@@ -264,7 +267,7 @@ def test_decode_right_behind_append_sees_the_appended_row():
 
     def pair():
         q2 = ops().append_rope_norm(q, k, v, k_cache, v_cache, before, cos, sin, write_slots=slots)
-        return q2, ops().decode_attention(q2[:, 0], k_cache, v_cache, after, seqlen_offset=0)
+        return q2, ops().decode_attention(q2[:, 0], k_cache, v_cache, lens, seqlen_offset=offset)
 
     # the two calls back to back on the device (no host gap between the launches): a CUDA graph
     side = torch.cuda.Stream(DEV)
@@ -280,9 +283,56 @@ def test_decode_right_behind_append_sees_the_appended_row():
         v.copy_(torch.randn(B, 1, Hkv, 128, generator=gen, device=DEV).to(BF) * (1 + it))
         graph.replay()
         torch.cuda.synchronize()
-        settled = ops().decode_attention(q2[:, 0], k_cache, v_cache, after, seqlen_offset=0)  # nothing in flight before it
+        settled = ops().decode_attention(q2[:, 0], k_cache, v_cache, lens, seqlen_offset=offset)  # nothing in flight before it
         torch.cuda.synchronize()
         assert torch.equal(bits(out), bits(settled)), f"iteration {it}: attention ran ahead of the append"
+    assert ops().read_status(DEV) == 0
+
+
+def test_invalid_lengths_set_status_bits_and_spare_the_other_rows():
+    """Negative and over-capacity cache_seqlens: the kernels flag them in the status word (bit 4 bad
+    length, bit 1 overflow), touch nothing out of range, and the valid rows keep their results."""
+    from nanochat_b200 import _lib
+    gen = torch.Generator(device=DEV).manual_seed(31)
+    B, Hq, Hkv, T_max = 6, 4, 2, 300
+    good = [10, 0, 299, 150, 47, 48]
+    lens_ok = torch.tensor(good, device=DEV, dtype=torch.int32)
+    lens_bad = lens_ok.clone()
+    lens_bad[1] = -7          # bad length
+    lens_bad[3] = T_max + 50  # beyond the capacity
+    q = torch.randn(B, Hq, 128, generator=gen, device=DEV).to(BF)
+    k_cache, v_cache = make_cache(B, T_max, Hkv, None, gen)
+    ref = ops().decode_attention(q, k_cache, v_cache, lens_ok, seqlen_offset=1)
+    assert ops().read_status(DEV) & ~_lib.ST_OVERFLOW == 0  # row 2 (L + 1 == T_max) is legal
+    ops().read_status(DEV)
+    out = ops().decode_attention(q, k_cache, v_cache, lens_bad, seqlen_offset=1)
+    torch.cuda.synchronize()
+    st = ops().read_status(DEV)
+    assert st & _lib.ST_BAD_SEQLEN and st & _lib.ST_OVERFLOW, st
+    keep = [0, 2, 4, 5]
+    assert torch.equal(bits(out[keep]), bits(ref[keep]))
+    assert not torch.isnan(out.float()).any()
+    # append: rows with a bad or overflowing position are skipped, the others written
+    cos, sin = E.rotary_tables(T_max, 128, DEV, BF)
+    kq = torch.randn(B, 1, Hq, 128, generator=gen, device=DEV).to(BF)
+    kk = torch.randn(B, 1, Hkv, 128, generator=gen, device=DEV).to(BF)
+    kv = torch.randn(B, 1, Hkv, 128, generator=gen, device=DEV).to(BF)
+    kc2, vc2 = k_cache.clone(), v_cache.clone()
+    ops().append_rope_norm(kq, kk, kv, kc2, vc2, lens_bad, cos, sin)
+    torch.cuda.synchronize()
+    st = ops().read_status(DEV)
+    assert st & _lib.ST_BAD_SEQLEN and st & _lib.ST_OVERFLOW, st
+    for b in (1, 3):
+        assert torch.equal(bits(kc2[b]), bits(k_cache[b])) and torch.equal(bits(vc2[b]), bits(v_cache[b]))
+    for b in (0, 4, 5):
+        assert torch.equal(bits(vc2[b, good[b]]), bits(kv[b, 0]))
+    # prefill attention
+    T_new = 5
+    pq = torch.randn(B, T_new, Hq, 128, generator=gen, device=DEV).to(BF)
+    ops().prefill_attention(pq, k_cache, v_cache, lens_bad, -1)
+    torch.cuda.synchronize()
+    st = ops().read_status(DEV)
+    assert st & _lib.ST_BAD_SEQLEN and st & _lib.ST_OVERFLOW, st
     assert ops().read_status(DEV) == 0
 
 
