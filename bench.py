@@ -514,6 +514,56 @@ def run_case(args):
                    ms_per_step=ms, eager_ms_per_step=eager_ms, prefill_s=prefill_s, context=ctx,
                    roofline_ms=(kv_step + w_bytes) / (peak * 1e9) * 1e3, kv_bytes_per_step=kv_step, weight_bytes=w_bytes,
                    config={"model": f"d{n_layer}", "B": Bc, "prompt": T0, "steps": n_new})
+    elif args.case in ("engine_api_d24", "engine_api_small"):
+        # configs[2] through the public generation loop (Engine.generate: one prompt, 64 samples, greedy):
+        # per token one host round trip for the sampled ids and the Python row state machine, as in the
+        # reference (engine.py:230-280); the decode step itself is replayed from a CUDA graph or run eagerly
+        from nanochat_b200.engine import Engine
+        from nanochat_b200.gpt import GPT, GPTConfig
+        small = args.case.endswith("small")
+        n_layer, Bc, T0 = (4, 8, 64) if small else (24, 64, 512)
+        cfg = GPTConfig(sequence_len=2048, vocab_size=32768, n_layer=n_layer, n_head=12, n_kv_head=12, n_embd=1536)
+        torch.manual_seed(3)
+        with torch.device("meta"):
+            model = GPT(cfg, compute_dtype=bf)
+        model.to_empty(device=dev)
+        model.init_weights()
+        model.to(bf)
+        model.window_sizes = [(1024, 0) if (i % 4) != 3 else (2048, 0) for i in range(n_layer)]
+        model.window_sizes[-1] = (2048, 0)
+
+        class _Specials:  # special ids lie outside the vocabulary: no row ever stops early
+            def encode_special(self, name):
+                return 40000 + (hash(name) % 1000)
+
+            def get_bos_token_id(self):
+                return 39999
+
+            def encode(self, text):
+                return []
+
+            def decode(self, ids):
+                return ""
+
+        prompt = torch.randint(0, 32768, (T0,), generator=torch.Generator().manual_seed(3)).tolist()
+        n_new = max(args.steps, 24)
+        res = {}
+        for mode in (True, False):
+            eng = Engine(model, _Specials(), cuda_graph=mode)
+            gen_ = eng.generate(prompt, num_samples=Bc, max_tokens=n_new + 8, temperature=0.0)
+            for _ in range(8):  # prefill, first steps, graph capture
+                next(gen_)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(n_new):
+                next(gen_)
+            torch.cuda.synchronize()
+            res[mode] = (time.perf_counter() - t0) / n_new
+            gen_.close()
+        out.update(metric="tokens/s through Engine.generate (whole model, host loop included)",
+                   value=Bc / res[True], unit="tokens/s", ms_per_step=res[True] * 1e3,
+                   eager_ms_per_step=res[False] * 1e3, eager_tokens_per_s=Bc / res[False],
+                   config={"model": f"d{n_layer}", "num_samples": Bc, "prompt": T0, "steps": n_new})
     elif args.case in ("engine_d32", "engine_d32_small"):
         # configs[3]: nanochat d32 with GQA (32 x 2048, 16 query / 4 kv heads), random-init bf16, 256 rows with
         # ragged prompt lengths U[128, 2048], capacity 4096, top-k 50 sampling at temperature 1; per-row
@@ -626,7 +676,7 @@ def main():
     ap.add_argument("--case", default=None,
                     help="secondary op-level measurement instead of the headline workload: decode_long, decode_gqa, "
                          "decode_gqa_window, decode_d24, prefill, broadcast, append, engine_d24, engine_d24_small, engine_d32, "
-                         "engine_d32_small")
+                         "engine_d32_small, engine_api_d24, engine_api_small")
     args = ap.parse_args()
     if args.case:
         run_case(args)

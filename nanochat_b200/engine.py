@@ -140,9 +140,12 @@ class Engine:
     and ``forward(ids, kv_cache=...)``; the tokenizer only the special-token lookups, ``encode``
     and ``decode``."""
 
-    def __init__(self, model, tokenizer):
+    def __init__(self, model, tokenizer, cuda_graph=True):
         self.model = model
         self.tokenizer = tokenizer
+        # On a CUDA device the decode step is replayed from a CUDA graph once a generation is long
+        # enough to pay for the capture (same tokens, cache lengths and cache bytes as eager steps).
+        self.cuda_graph = cuda_graph
 
     @torch.inference_mode()
     def generate(self, tokens, num_samples=1, max_tokens=None, temperature=1.0, top_k=None, seed=42):
@@ -170,6 +173,7 @@ class Engine:
 
         rows = [RowState(tokens.copy()) for _ in range(num_samples)]
         produced = 0
+        graphed = None
         while (max_tokens is None or produced < max_tokens) and not all(r.completed for r in rows):
             sampled = sample_next_token(logits, rng, temperature, top_k)[:, 0].tolist()
             column, masks = [], []
@@ -197,7 +201,17 @@ class Engine:
             yield column, masks
             produced += 1
             ids = torch.tensor(column, dtype=torch.long, device=device).unsqueeze(1)
-            logits = self.model.forward(ids, kv_cache=cache)[:, -1, :]
+            if graphed is None and self.cuda_graph and device.type == "cuda" and produced >= 2:
+                # capture runs three throw-away steps behind the current position: needs that room,
+                # and only pays off if enough steps are still to come
+                room = capacity - (len(tokens) + produced)
+                left = (max_tokens - produced) if max_tokens is not None else room
+                if room >= 4 and left >= 16:
+                    graphed = GraphedDecodeStep(self.model, cache, ids)
+            if graphed is not None:
+                logits = graphed.step(ids)
+            else:
+                logits = self.model.forward(ids, kv_cache=cache)[:, -1, :]
 
     def generate_batch(self, tokens, num_samples=1, **kwargs):
         """Run ``generate`` to the end; returns (token lists, sampled/forced masks) without the
