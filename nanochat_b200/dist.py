@@ -37,6 +37,49 @@ def shard_rows(n_rows, rank, world_size):
     return lo, lo + q + (1 if rank < r else 0)
 
 
+def sharded_prefill(prompt_cache, local_cache, group=None, src=0):
+    """``KVCache.prefill`` (engine.py:123-137) when the sample rows are spread over ranks.
+
+    Rank ``src`` holds the batch-1 cache of the prompt (``prompt_cache``; the others pass None).
+    Its keys and values (and the smear state) are sent ONCE to every rank with a broadcast, land in
+    that rank's own memory, and each rank then fills its own rows from the local copy with the
+    broadcast-copy kernel -- no rank reads another GPU's memory inside a kernel.  ``local_cache``
+    is this rank's (empty) KVCache for its share of the rows (``shard_rows``).  Returns the prompt
+    length."""
+    import torch.distributed as dist
+    from .engine import KVCache
+    rank = dist.get_rank(group)
+    dev = local_cache.k_cache.device
+    meta = torch.zeros(2, dtype=torch.int64, device=dev)
+    if rank == src:
+        assert prompt_cache is not None and prompt_cache.batch_size == 1, "the source is a batch-1 prompt cache"
+        meta[0] = prompt_cache.get_pos()
+        meta[1] = 0 if prompt_cache.prev_embedding is None else prompt_cache.prev_embedding.size(-1)
+    dist.broadcast(meta, src=src, group=group)
+    p, emb = int(meta[0]), int(meta[1])
+    if rank == src:
+        staged = prompt_cache
+    else:
+        staged = KVCache(batch_size=1, num_heads=local_cache.n_heads, seq_len=max(p, 1), head_dim=local_cache.head_dim,
+                         num_layers=local_cache.n_layers, device=dev, dtype=local_cache.k_cache.dtype)
+        staged.cache_seqlens.fill_(p)
+        if emb:
+            staged.prev_embedding = torch.empty(1, 1, emb, device=dev, dtype=local_cache.k_cache.dtype)
+    if p > 0:
+        # only the filled part of the source travels: (L, 1, p, H, D) for K and for V
+        k_part = staged.k_cache[:, :, :p].contiguous()
+        v_part = staged.v_cache[:, :, :p].contiguous()
+        dist.broadcast(k_part, src=src, group=group)
+        dist.broadcast(v_part, src=src, group=group)
+        if rank != src:
+            staged.k_cache[:, :, :p] = k_part
+            staged.v_cache[:, :, :p] = v_part
+    if emb:
+        dist.broadcast(staged.prev_embedding, src=src, group=group)
+    local_cache.prefill(staged)
+    return p
+
+
 def kv_shard_range(capacity, rank, world_size, align=32):
     """Key range [begin, end) of ``rank`` in the contiguous layout: equal ranges, boundaries rounded
     up to a multiple of ``align`` tokens (the decode kernel's tile) so no tile straddles two ranks."""

@@ -9,7 +9,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from nanochat_b200.dist import KVSplitAttention, kv_shard_range, owned_below, shard_rows
+from nanochat_b200.dist import KVSplitAttention, kv_shard_range, owned_below, shard_rows, sharded_prefill
 from oracle import kv_oracle as O
 
 
@@ -97,3 +97,49 @@ def test_kv_split_exchange_matches_unsplit_attention(world, window):
     errs = ret.get(timeout=10)
     assert len(errs) == world and max(errs) < 1e-5, errs
 
+
+
+def _prefill_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from nanochat_b200.engine import KVCache
+        from tests.cpu_backend import oracle_backend
+        L, H, D, p, cap, rows_total = 3, 2, 16, 11, 20, 5
+        lo, hi = shard_rows(rows_total, rank, world)
+        g = torch.Generator().manual_seed(3)  # the same reference data on every rank (only rank 0 uses it as source)
+        src_k = torch.randn(L, 1, p, H, D, generator=g)
+        src_v = torch.randn(L, 1, p, H, D, generator=g)
+        emb = torch.randn(1, 1, 8, generator=g)
+        prompt = None
+        if rank == 0:
+            prompt = KVCache(batch_size=1, num_heads=H, seq_len=p, head_dim=D, num_layers=L, device="cpu", dtype=torch.float32)
+            prompt.k_cache.copy_(src_k)
+            prompt.v_cache.copy_(src_v)
+            prompt.cache_seqlens.fill_(p)
+            prompt.prev_embedding = emb.clone()
+        local = KVCache(batch_size=hi - lo, num_heads=H, seq_len=cap, head_dim=D, num_layers=L, device="cpu", dtype=torch.float32)
+        with oracle_backend():
+            got_p = sharded_prefill(prompt, local, src=0)
+        ok = got_p == p and local.cache_seqlens.tolist() == [p] * (hi - lo)
+        ok = ok and torch.equal(local.k_cache[:, :, :p], src_k.expand(L, hi - lo, p, H, D))
+        ok = ok and torch.equal(local.v_cache[:, :, :p], src_v.expand(L, hi - lo, p, H, D))
+        ok = ok and float(local.k_cache[:, :, p:].abs().sum()) == 0.0
+        ok = ok and torch.equal(local.prev_embedding, emb.expand(hi - lo, -1, -1))
+        ret.put(bool(ok))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_prefill_fills_every_ranks_rows_from_one_broadcast():
+    ctx = mp.get_context("spawn")
+    ret = ctx.Queue()
+    port = _free_port()
+    world = 2
+    procs = [ctx.Process(target=_prefill_worker, args=(r, world, port, ret)) for r in range(world)]
+    for pr in procs:
+        pr.start()
+    for pr in procs:
+        pr.join(120)
+        assert pr.exitcode == 0
+    assert all(ret.get(timeout=10) for _ in range(world))

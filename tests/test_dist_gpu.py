@@ -84,6 +84,32 @@ def _worker(rank, world, port, ret):
             torch.cuda.synchronize()
             full3, _ = O.attention_kvcache(q.float().numpy()[:, None], kc.float().numpy(), vc.float().numpy(), lens3.numpy())
             err = max(err, float(np.abs(out3.float().cpu().numpy() - full3[:, 0]).max() / np.abs(full3).max()))
+        # (4) prefill broadcast with the sample rows sharded over the ranks: the prompt cache of rank 0
+        # is broadcast once, every rank fills its own rows from its local copy (kernel (c))
+        from nanochat_b200.dist import shard_rows, sharded_prefill
+        from nanochat_b200.engine import KVCache
+        Lyr, Hh, pp, cap, rows_total = 3, 4, 777, 1024, 9
+        gp = torch.Generator().manual_seed(5)
+        src_k = torch.randn(Lyr, 1, pp, Hh, 128, generator=gp).to(torch.bfloat16)
+        src_v = torch.randn(Lyr, 1, pp, Hh, 128, generator=gp).to(torch.bfloat16)
+        emb = torch.randn(1, 1, 64, generator=gp).to(torch.bfloat16)
+        prompt = None
+        if rank == 0:
+            prompt = KVCache(batch_size=1, num_heads=Hh, seq_len=pp, head_dim=128, num_layers=Lyr, device=dev, dtype=torch.bfloat16)
+            prompt.k_cache.copy_(src_k)
+            prompt.v_cache.copy_(src_v)
+            prompt.cache_seqlens.fill_(pp)
+            prompt.prev_embedding = emb.to(dev)
+        lo, hi = shard_rows(rows_total, rank, world)
+        local = KVCache(batch_size=hi - lo, num_heads=Hh, seq_len=cap, head_dim=128, num_layers=Lyr, device=dev, dtype=torch.bfloat16)
+        got_p = sharded_prefill(prompt, local, src=0)
+        torch.cuda.synchronize()
+        same = (got_p == pp and local.cache_seqlens.tolist() == [pp] * (hi - lo)
+                and torch.equal(local.k_cache[:, :, :pp].cpu().view(torch.int16), src_k.expand(Lyr, hi - lo, pp, Hh, 128).contiguous().view(torch.int16))
+                and torch.equal(local.v_cache[:, :, :pp].cpu().view(torch.int16), src_v.expand(Lyr, hi - lo, pp, Hh, 128).contiguous().view(torch.int16))
+                and torch.equal(local.prev_embedding.cpu(), emb.expand(hi - lo, -1, -1)))
+        if not same:
+            err = float("inf")
         status = ops.read_status(dev)
         res = [None] * world
         dist.all_gather_object(res, (err, status))
