@@ -206,7 +206,7 @@ class Engine:
                 # and only pays off if enough steps are still to come
                 room = capacity - (len(tokens) + produced)
                 left = (max_tokens - produced) if max_tokens is not None else room
-                if room >= 4 and left >= 16:
+                if room >= 4 and left >= 16 and cache.prev_embedding is not None:
                     graphed = GraphedDecodeStep(self.model, cache, ids)
             if graphed is not None:
                 logits = graphed.step(ids)
