@@ -148,9 +148,19 @@ int nckv_p2p_push(const float *send, int rows, int D, void *const *peer_bufs, in
         set_error("p2p_push: send buffer must be 16-byte aligned");
         return NCKV_E_ARG;
     }
-    p2p_push_kernel<<<world, 1024, 0, static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const float4 *>(send),
-                                                                       p2p_per_floats(rows), pp, world, rank, step_counter);
-    NCKV_CUDA_CHECK(cudaGetLastError());
+    // programmatic dependent launch: the grid may be scheduled while its predecessor (the merge of
+    // the partial results) is still running; the kernel waits for it before it reads anything
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)world);
+    cfg.blockDim = dim3(1024);
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    NCKV_CUDA_CHECK(cudaLaunchKernelEx(&cfg, p2p_push_kernel, reinterpret_cast<const float4 *>(send), p2p_per_floats(rows), pp,
+                                       world, rank, static_cast<const unsigned *>(step_counter)));
     return NCKV_OK;
 }
 
@@ -168,11 +178,18 @@ int nckv_p2p_wait_combine(const void *local_buf, int world, int rows, int D, uin
     if (limit_ns == 0) limit_ns = NCKV_WAIT_LIMIT_NS;
     const int threads = 256;
     const long long blocks = ((long long)rows * 32 + threads - 1) / threads;
-    p2p_wait_combine_kernel<<<(unsigned)blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const float *>(local_buf), p2p_per_floats(rows), world, rows, step_counter,
-        static_cast<__nv_bfloat16 *>(out),
-        lse_out, status, (unsigned long long)limit_ns);
-    NCKV_CUDA_CHECK(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)blocks);
+    cfg.blockDim = dim3(threads);
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    NCKV_CUDA_CHECK(cudaLaunchKernelEx(&cfg, p2p_wait_combine_kernel, static_cast<const float *>(local_buf), p2p_per_floats(rows),
+                                       world, rows, static_cast<unsigned *>(step_counter), static_cast<__nv_bfloat16 *>(out),
+                                       lse_out, status, (unsigned long long)limit_ns));
     return NCKV_OK;
 }
 
