@@ -102,12 +102,15 @@ NCKV_API int nckv_append_rope_norm_at(const void *q_in, const void *k_in, const 
  * positions [key_begin[b], key_end[b]) the decode kernel would read for these arguments, computed on
  * the device by the same routine the attention kernels call.  Restates the visible-key rule of
  * flash_attention.py:83-88 (keys [max(0, L - w), L] of a row whose new token sits at position L),
- * intersected with [kv_begin, kv_end) when that range is not empty.  Out-of-range lengths are clamped
- * and flagged in *status like the attention entry points do.  Used by the parity tests.
+ * intersected with [kv_begin, kv_end) when that range is not empty.  With split_block > 0 the
+ * lengths are global and the ranges are local indices into shard split_rank's block-cyclic part (as
+ * nckv_decode_attn_split reads them).  Out-of-range lengths are clamped and flagged in *status like
+ * the attention entry points do.  Used by the parity tests.
  */
 NCKV_API int nckv_decode_key_ranges(const int32_t *cache_seqlens, int B, int T_max, int seqlen_offset,
-                                    int window_left, int kv_begin, int kv_end, int32_t *key_begin,
-                                    int32_t *key_end, int32_t *status, void *stream);
+                                    int window_left, int kv_begin, int kv_end, int split_world, int split_rank,
+                                    int split_block, int32_t *key_begin, int32_t *key_end, int32_t *status,
+                                    void *stream);
 
 /*
  * Bookkeeping of the sequence-split long-context path (no counterpart in the reference): key
@@ -115,9 +118,26 @@ NCKV_API int nckv_decode_key_ranges(const int32_t *cache_seqlens, int B, int T_m
  * (p / (block*world)) * block + p % block.  From the global cache_seqlens (lengths before the new
  * tokens) computes, for shard `rank`: local_len_after[b] = keys of row b this shard holds once the
  * T_new new tokens are in, and write_slot[b] = local index for the new token, or -1 if it is not ours.
+ * The *_split entry points below apply the same rule inside their kernels; this one exposes it (to
+ * the parity tests, and to callers that lay out their own caches).  Its kernel does not release its
+ * dependents early, so a libnckv kernel launched behind it sees the finished arrays.
  */
 NCKV_API int nckv_kv_split_plan(const int32_t *cache_seqlens, int B, int T_new, int world, int rank, int block,
                        int32_t *local_len_after, int32_t *write_slot, void *stream);
+
+/*
+ * nckv_append_rope_norm for shard `rank` of a block-cyclic sequence split (no counterpart in the
+ * reference): cache_seqlens are the GLOBAL lengths (they drive RoPE), the caches are this shard's
+ * compact part (capacity T_local), and k/v of row b are stored only if this shard owns position
+ * cache_seqlens[b], at the local index nckv_kv_split_plan would report.  q_out is always produced.
+ * T_new must be 1.
+ */
+NCKV_API int nckv_append_rope_norm_split(const void *q_in, const void *k_in, const void *v_in, void *q_out,
+                                void *k_cache, void *v_cache, const int32_t *cache_seqlens, const void *cos,
+                                const void *sin, int B, int T_new, int Hq, int Hkv, int D, int T_local,
+                                int64_t cache_batch_stride, int64_t cache_token_stride, int rope_len,
+                                float qk_scale, float eps, int world, int rank, int block, int32_t *status,
+                                void *stream);
 
 /*
  * Plain append (k already rotated/normalised by the caller): the cache write of
@@ -162,9 +182,12 @@ NCKV_API int nckv_decode_step_host(const void *qkv_host, void *qkv_dev, void *q_
  * cross-GPU combine).  workspace: see nckv_workspace_bytes().
  * Ordering: the kernels start while the kernel launched before them in the stream may still be
  * running (programmatic dependent launch) and read cache_seqlens and all but the last
- * max(seqlen_offset, 1) visible positions of every row before they wait for it.  A libnckv append
- * directly in front of this call must therefore not have written older positions than those (a
- * decode step appends exactly that one position); any other kernel is waited for in full.
+ * max(seqlen_offset, 1) visible positions of every row before they wait for it.  This only matters
+ * behind a kernel that releases its dependents before it has finished, which among ordinary
+ * kernels only libnckv's own appends do: an append directly in front of this call must not have
+ * written older positions than those (a decode step appends exactly that one position) and must
+ * not be what produces cache_seqlens.  A kernel that never releases early (every torch or library
+ * kernel, nckv_kv_split_plan) has completed before these kernels read anything.
  */
 NCKV_API int nckv_decode_attn(const void *q, const void *k_cache, const void *v_cache,
                      const int32_t *cache_seqlens, void *out, float *out_f32, float *lse_out,
@@ -172,6 +195,25 @@ NCKV_API int nckv_decode_attn(const void *q, const void *k_cache, const void *v_
                      int64_t cache_token_stride, int seqlen_offset, int window_left,
                      int kv_begin, int kv_end, void *workspace, size_t workspace_bytes,
                      void *stream);
+
+/*
+ * nckv_decode_attn over shard `rank` of a block-cyclic sequence split (no counterpart in the
+ * reference, which never splits the keys): cache_seqlens are the GLOBAL lengths, the caches are this
+ * shard's compact part (capacity T_local), and the keys read of row b are the local indices
+ * [0, owned_below(cache_seqlens[b] + seqlen_offset)) (full causal; windows need global indices, use
+ * kv_begin/kv_end of nckv_decode_attn for those).  part_out (B, Hq, D) fp32 receives the normalised
+ * partial output and part_lse (B, Hq) fp32 its natural-log sum-exp (-inf and zeros for a shard
+ * without keys of a row).
+ * With peer_bufs != NULL (world pointers: every rank's exchange buffer as mapped into this process,
+ * see nckv_p2p_buffer_bytes) the kernel that merges the split partials also stores the packed
+ * partial into this rank's slot of every peer's buffer and releases the step's flag there, which
+ * replaces a separate nckv_p2p_push; follow it with nckv_p2p_wait_combine.  Plain peer stores only.
+ */
+NCKV_API int nckv_decode_attn_split(const void *q, const void *k_cache, const void *v_cache,
+                           const int32_t *cache_seqlens, float *part_out, float *part_lse, int B, int Hq,
+                           int Hkv, int D, int T_local, int64_t cache_batch_stride, int64_t cache_token_stride,
+                           int seqlen_offset, int world, int rank, int block, void *const *peer_bufs,
+                           const uint32_t *step_counter, void *workspace, size_t workspace_bytes, void *stream);
 
 /*
  * Decode attention without any allocation (no counterpart in the reference; same computation and
@@ -185,8 +227,10 @@ NCKV_API int nckv_decode_attn(const void *q, const void *k_cache, const void *v_
  * routine.  Limits and rules:
  *   - shapes whose nckv_workspace_bytes() exceeds 14 MiB are rejected with NCKV_E_CAPACITY
  *     (group sizes Hq/Hkv up to 4 fit, any B up to the per-launch row limit);
- *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress); make
- *     that first call outside any stream capture;
+ *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress), which
+ *     is also when the CUDA runtime may first set the array up on that device (modules load
+ *     lazily).  Make that first call at start-up: before the process gives its free memory away,
+ *     and outside any stream capture;
  *   - all calls on a device share the one array: two calls whose kernels can overlap on the GPU
  *     (different streams, no ordering between them) race on it.  Serialise them;
  *   - if status_word != NULL it receives the device address of the status word, to be read with

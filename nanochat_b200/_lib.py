@@ -26,6 +26,8 @@ SIGNATURES = {
                                                              c_float, c_void_p, c_void_p]),
     "nckv_append_rope_norm_at": (c_int, [c_void_p] * 10 + [c_int] * 6 + [c_i64, c_i64, c_int, c_float, c_float,
                                                           c_void_p, c_void_p]),
+    "nckv_append_rope_norm_split": (c_int, [c_void_p] * 9 + [c_int] * 6 + [c_i64, c_i64, c_int, c_float, c_float] +
+                                    [c_int] * 3 + [c_void_p, c_void_p]),
     "nckv_kv_split_plan": (c_int, [c_void_p] + [c_int] * 5 + [c_void_p, c_void_p, c_void_p]),
     "nckv_append": (c_int, [c_void_p] * 5 + [c_int] * 5 + [c_i64, c_i64, c_void_p, c_void_p]),
     "nckv_decode_step_host": (c_int, [c_void_p] * 10 + [c_int] * 5 + [c_i64, c_i64, c_int, c_float, c_float, c_int,
@@ -34,7 +36,9 @@ SIGNATURES = {
                          [c_void_p, c_size_t, c_void_p]),
     "nckv_decode_attn_static": (c_int, [c_void_p] * 7 + [c_int] * 5 + [c_i64, c_i64] + [c_int] * 4 +
                                 [ctypes.POINTER(c_void_p), c_void_p]),
-    "nckv_decode_key_ranges": (c_int, [c_void_p] + [c_int] * 6 + [c_void_p] * 4),
+    "nckv_decode_attn_split": (c_int, [c_void_p] * 6 + [c_int] * 5 + [c_i64, c_i64] + [c_int] * 4 +
+                               [ctypes.POINTER(c_void_p), c_void_p, c_void_p, c_size_t, c_void_p]),
+    "nckv_decode_key_ranges": (c_int, [c_void_p] + [c_int] * 9 + [c_void_p] * 4),
     "nckv_lse_combine": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_i64, c_i64, c_void_p, c_void_p, c_void_p]),
     "nckv_p2p_buffer_bytes": (c_size_t, [c_int, c_int, c_int]),
     "nckv_p2p_push": (c_int, [c_void_p, c_int, c_int, ctypes.POINTER(c_void_p), c_int, c_int, c_void_p, c_void_p]),

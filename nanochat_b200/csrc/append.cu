@@ -30,6 +30,7 @@ struct AppendParams {
     int64_t cache_batch_stride, cache_token_stride;
     float qk_scale, eps;
     int transform_k;  // 0: k is stored as given (plain append)
+    KvSplit split;    // block > 0: block-cyclic sequence split, the owner of position cache_seqlens[b] stores k/v
 };
 
 __device__ __forceinline__ void unpack8(const uint4 &v, float (&f)[8]) {
@@ -132,7 +133,10 @@ __global__ void __launch_bounds__(256) append_rope_norm_kernel(const AppendParam
         const int t = (int)(bt % p.T_new);
         const int b = (int)(bt / p.T_new);
         const int len = p.cache_seqlens[b];          // sequence position of token 0 (drives RoPE)
-        const int wslot = p.write_slots ? p.write_slots[b] : len;  // cache index of token 0
+        int wslot = p.write_slots ? p.write_slots[b] : len;  // cache index of token 0
+        if (p.split.block > 0 && len >= 0)
+            wslot = (len / p.split.block) % p.split.world == p.split.rank
+                        ? owned_below(len, p.split.world, p.split.rank, p.split.block) : -1;
         const int pos = len + t;
         bool ok = live;
         if (len < 0 || wslot < -1) {
@@ -233,7 +237,7 @@ extern "C" {
 
 static int append_rope_norm_impl(const void *q_in, const void *k_in, const void *v_in, void *q_out,
                                  void *k_cache, void *v_cache, const int32_t *cache_seqlens,
-                                 const int32_t *write_slots, const void *cos, const void *sin, int B, int T_new,
+                                 const int32_t *write_slots, nckv::KvSplit split, const void *cos, const void *sin, int B, int T_new,
                                  int Hq, int Hkv, int D, int T_max, int64_t cache_batch_stride,
                                  int64_t cache_token_stride, int rope_len, float qk_scale, float eps,
                                  int32_t *status, void *stream) {
@@ -271,6 +275,7 @@ static int append_rope_norm_impl(const void *q_in, const void *k_in, const void 
     p.qk_scale = qk_scale;
     p.eps = eps;
     p.transform_k = 1;
+    p.split = split;
     return launch_append(p, static_cast<cudaStream_t>(stream));
 }
 
@@ -280,7 +285,7 @@ int nckv_append_rope_norm(const void *q_in, const void *k_in, const void *v_in, 
                           int D, int T_max, int64_t cache_batch_stride,
                           int64_t cache_token_stride, int rope_len, float qk_scale, float eps,
                           int32_t *status, void *stream) {
-    return append_rope_norm_impl(q_in, k_in, v_in, q_out, k_cache, v_cache, cache_seqlens, nullptr, cos, sin, B, T_new,
+    return append_rope_norm_impl(q_in, k_in, v_in, q_out, k_cache, v_cache, cache_seqlens, nullptr, nckv::KvSplit{0, 0, 0}, cos, sin, B, T_new,
                                  Hq, Hkv, D, T_max, cache_batch_stride, cache_token_stride, rope_len, qk_scale, eps,
                                  status, stream);
 }
@@ -294,9 +299,25 @@ int nckv_append_rope_norm_at(const void *q_in, const void *k_in, const void *v_i
         nckv::set_error("append_rope_norm_at: write_slots is required");
         return NCKV_E_ARG;
     }
-    return append_rope_norm_impl(q_in, k_in, v_in, q_out, k_cache, v_cache, positions, write_slots, cos, sin, B, T_new,
+    return append_rope_norm_impl(q_in, k_in, v_in, q_out, k_cache, v_cache, positions, write_slots, nckv::KvSplit{0, 0, 0}, cos, sin, B, T_new,
                                  Hq, Hkv, D, T_max, cache_batch_stride, cache_token_stride, rope_len, qk_scale, eps,
                                  status, stream);
+}
+
+int nckv_append_rope_norm_split(const void *q_in, const void *k_in, const void *v_in, void *q_out,
+                                void *k_cache, void *v_cache, const int32_t *cache_seqlens, const void *cos,
+                                const void *sin, int B, int T_new, int Hq, int Hkv, int D, int T_local,
+                                int64_t cache_batch_stride, int64_t cache_token_stride, int rope_len,
+                                float qk_scale, float eps, int world, int rank, int block, int32_t *status,
+                                void *stream) {
+    if (world <= 0 || rank < 0 || rank >= world || block <= 0 || T_new != 1) {
+        nckv::set_error("append_rope_norm_split: bad split (world=%d rank=%d block=%d) or T_new=%d != 1", world, rank,
+                        block, T_new);
+        return NCKV_E_ARG;
+    }
+    return append_rope_norm_impl(q_in, k_in, v_in, q_out, k_cache, v_cache, cache_seqlens, nullptr,
+                                 nckv::KvSplit{world, rank, block}, cos, sin, B, T_new, Hq, Hkv, D, T_local,
+                                 cache_batch_stride, cache_token_stride, rope_len, qk_scale, eps, status, stream);
 }
 
 int nckv_append(const void *k_in, const void *v_in, void *k_cache, void *v_cache,
@@ -325,6 +346,7 @@ int nckv_append(const void *k_in, const void *v_in, void *k_cache, void *v_cache
     p.qk_scale = 1.0f;
     p.eps = 0.0f;
     p.transform_k = 0;
+    p.split = KvSplit{0, 0, 0};
     return launch_append(p, static_cast<cudaStream_t>(stream));
 }
 

@@ -64,6 +64,10 @@ constexpr int DEC_DYN_PER_WARP = 4;                   // at most this many dynam
 #endif
 constexpr int DEC_STATIC_NUM = NCKV_DEC_STATIC_NUM, DEC_STATIC_DEN = 10; // statically assigned fraction of a slice
 constexpr int DEC_MIN_RUN = NCKV_DEC_MIN_RUN;  // tiles in the smallest dynamic run
+#ifndef NCKV_DEC_PREFETCH
+#define NCKV_DEC_PREFETCH 4
+#endif
+constexpr int DEC_PREFETCH = NCKV_DEC_PREFETCH;  // tiles of the static run a warp asks L2 for before it may start
 constexpr int MERGE_WARPS = 8;
 constexpr int MERGE_BATCH = 16; // O rows fetched per round trip
 constexpr int MERGE_PLAN = 4;  // chunks of 32 parts whose record slots a merge warp works out ahead of time
@@ -79,12 +83,10 @@ struct DecodeParams {
     float *partials;       // 2 records per run, rec_floats each
     int B, Hq, Hkv, G, T_max;
     int seqlen_offset, window_left, kv_begin, kv_end;
+    KvSplit split;         // block > 0: seqlens are global lengths, the cache holds this shard's block-cyclic part
     int rec_floats;
     int W;                 // warps of the streaming grid (the run geometry depends on it)
     float scale_log2;
-#ifdef NCKV_TIMELINE
-    unsigned long long *timeline;  // 16 stamps per warp of the grid (debug builds only)
-#endif
 };
 
 struct TileCursor {
@@ -208,6 +210,7 @@ __device__ __forceinline__ void build_row_tables(const DecodeParams &p, int *s_s
             if (report) atomicOr(p.status, (int)NCKV_ST_BAD_SEQLEN);
             n = 0;
         }
+        if (p.split.block > 0) n = owned_below(n, p.split.world, p.split.rank, p.split.block);
         if (n > p.T_max) {
             if (report) atomicOr(p.status, (int)NCKV_ST_OVERFLOW);
             n = p.T_max;
@@ -250,11 +253,6 @@ __device__ __forceinline__ void build_row_tables(const DecodeParams &p, int *s_s
     __syncthreads();
 }
 
-#ifdef NCKV_TIMELINE
-#define TL_STAMP(i) do { if (lane == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); tl[i] = t_; } } while (0)
-#else
-#define TL_STAMP(i)
-#endif
 
 // GHI: group size 9..16 (rows 8..15 of the MMA tile carry heads too).  MAP5: the tensor maps are the
 // 5-D form (one copy per K or V tile) instead of the 4-D form (one copy per 64-channel half).
@@ -277,12 +275,6 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
     const int warp = tid >> 5;
     const int lane = tid & 31;
     const int B = p.B, Hkv = p.Hkv, G = p.G;
-#ifdef NCKV_TIMELINE
-    unsigned long long *tl = p.timeline + ((long long)blockIdx.x * DEC_WARPS + warp) * 16;
-    long long tl_segend = 0;
-    int tl_tiles = 0, tl_runs = 0;
-    TL_STAMP(0);
-#endif
 
     // ---- set-up ---------------------------------------------------------------------------------
     if (tid == 0) {
@@ -307,12 +299,10 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
             prior_done = true;
         }
     };
-    TL_STAMP(1);
 
     RunGeometry geo;
     geo.init(Hkv * s_pref[B], p.W);
     const int gw = blockIdx.x * DEC_WARPS + warp;
-    TL_STAMP(9);
 
     {
         // rows without any visible key: zero output, lse = -inf (only sharded calls can produce them)
@@ -324,7 +314,7 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
                 if (s_pref[b + 1] != s_pref[b]) continue;
                 for (int i = tid; i < p.Hq * NCKV_D; i += blockDim.x) {
                     const long long o = (long long)b * p.Hq * NCKV_D + i;
-                    p.out[o] = __float2bfloat16(0.0f);
+                    if (p.out) p.out[o] = __float2bfloat16(0.0f);
                     if (p.out_f32) p.out_f32[o] = 0.0f;
                 }
                 if (p.lse) for (int i = tid; i < p.Hq; i += blockDim.x) p.lse[(long long)b * p.Hq + i] = -INFINITY;
@@ -332,7 +322,6 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
         }
     }
     if (geo.total == 0) return;  // every warp of the grid takes this exit together
-    TL_STAMP(10);
 
     uint8_t *my_stages = stages + warp * DEC_STAGES * DEC_STAGE_BYTES;
     uint64_t *my_bar = full_bar + warp * DEC_STAGES;
@@ -385,9 +374,6 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
             }
             prod = locate_tile(s_pref, B, Hkv, run_lo);
             prod_left = n;
-#ifdef NCKV_TIMELINE
-            if (issue_idx == 0) TL_STAMP(11);
-#endif
             if (lane == 0) {
                 RunEntry e;
                 e.k = k; e.n = n; e.start = prod;
@@ -424,9 +410,6 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
                 tma_load_4d_hint(dst + 3 * DEC_HALF_BYTES, &tmap_v, bar, 64, prod.h, key0, prod.b, kv_policy);
             }
         }
-#ifdef NCKV_TIMELINE
-        if (issue_idx == 0) TL_STAMP(12);
-#endif
         ++issue_idx;
         --prod_left;
         cursor_advance(prod, s_pref, B, Hkv);
@@ -438,15 +421,35 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
     issue_one();
     while (issue_idx < DEC_STAGES && prod_left > 0 && issue_one()) {
     }
+    // The ring is full, yet the kernels in front may need a few more microseconds (and, once this
+    // grid may go on, its first loads are behind it): ask L2 for the next tiles of the static run so
+    // that HBM keeps working through the hand-over.  Purely a hint; the copies into shared memory
+    // are issued as usual and then hit L2.  A prefetched line that the append kernel writes
+    // afterwards is updated in L2, which is where every later read of it is served from.
+    if (DEC_PREFETCH > 0 && lane == 0) {
+        TileCursor pc = prod;
+        int left = prod_left;
+        for (int i = 0; i < DEC_PREFETCH && left > 0; ++i, --left) {
+            const int key0 = s_start[pc.b] + pc.j * DEC_TILE;
+            if (MAP5) {
+                tma_prefetch_l2_5d(&tmap_k, 0, key0, 0, pc.h, pc.b);
+                tma_prefetch_l2_5d(&tmap_v, 0, key0, 0, pc.h, pc.b);
+            } else {
+                tma_prefetch_l2_4d(&tmap_k, 0, pc.h, key0, pc.b);
+                tma_prefetch_l2_4d(&tmap_k, 64, pc.h, key0, pc.b);
+                tma_prefetch_l2_4d(&tmap_v, 0, pc.h, key0, pc.b);
+                tma_prefetch_l2_4d(&tmap_v, 64, pc.h, key0, pc.b);
+            }
+            cursor_advance(pc, s_pref, B, Hkv);
+        }
+    }
     wait_prior();
-    TL_STAMP(4);
     if (!have_ticket) {  // needed once the static run has been issued; by then it has long arrived
         if (lane == 0) next_ticket = atomicAdd(p.run_counter, 1);
         have_ticket = true;
     }
     while (issue_idx < DEC_STAGES && issue_one()) {
     }
-    TL_STAMP(2);
 
     // ---- consuming side -----------------------------------------------------------------------
     const int g = lane >> 2;  // MMA row within 8 (query head within the group)
@@ -469,9 +472,6 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
             cons_k = e.k;
             cons_left = e.n;
             run_begin = true;
-#ifdef NCKV_TIMELINE
-            ++tl_runs;
-#endif
         }
         const int stage = cons_idx % DEC_STAGES;
         const uint32_t parity = (uint32_t)((cons_idx / DEC_STAGES) & 1);
@@ -502,10 +502,6 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
             timed_out = true;
             break;
         }
-#ifdef NCKV_TIMELINE
-        if (cons_idx == 0) TL_STAMP(3);
-        ++tl_tiles;
-#endif
 
         const uint32_t kbase = smem_u32(my_stages + stage * DEC_STAGE_BYTES);
         const uint32_t vbase = kbase + 2 * DEC_HALF_BYTES;
@@ -625,9 +621,6 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
         // ---- end of this pair's stretch inside the run? ----
         const bool seg_end = (cons_left == 0) || (cons.j == cons.nt - 1);
         if (seg_end) {
-#ifdef NCKV_TIMELINE
-            const long long tc0 = clock64();
-#endif
             float l0 = l_run[0], l1 = l_run[1];
             l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
             l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
@@ -646,13 +639,13 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
                     if (g < G) {
                         const long long o = (row_base + g) * NCKV_D + d;
                         const float v0 = o_acc[nd][0] * inv0, v1 = o_acc[nd][1] * inv0;
-                        *reinterpret_cast<uint32_t *>(p.out + o) = pack_bf16x2(v0, v1);
+                        if (p.out) *reinterpret_cast<uint32_t *>(p.out + o) = pack_bf16x2(v0, v1);
                         if (p.out_f32) *reinterpret_cast<float2 *>(p.out_f32 + o) = make_float2(v0, v1);
                     }
                     if (GHI && g + 8 < G) {
                         const long long o = (row_base + g + 8) * NCKV_D + d;
                         const float v0 = o_acc[nd][2] * inv1, v1 = o_acc[nd][3] * inv1;
-                        *reinterpret_cast<uint32_t *>(p.out + o) = pack_bf16x2(v0, v1);
+                        if (p.out) *reinterpret_cast<uint32_t *>(p.out + o) = pack_bf16x2(v0, v1);
                         if (p.out_f32) *reinterpret_cast<float2 *>(p.out_f32 + o) = make_float2(v0, v1);
                     }
                 }
@@ -678,16 +671,9 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
                     if (GHI && g + 8 < G) { rec[G * NCKV_D + g + 8] = m_run[1]; rec[G * NCKV_D + G + g + 8] = l1; }
                 }
             }
-#ifdef NCKV_TIMELINE
-            tl_segend += clock64() - tc0;
-#endif
         }
         cursor_advance(cons, s_pref, B, Hkv);
     }
-    TL_STAMP(5);
-#ifdef NCKV_TIMELINE
-    if (lane == 0) { tl[6] = (unsigned long long)tl_segend; tl[7] = (unsigned long long)tl_tiles; tl[8] = (unsigned long long)tl_runs; }
-#endif
 
     if (timed_out) {
         if (lane == 0) atomicOr(p.status, (int)NCKV_ST_TIMEOUT);
@@ -712,19 +698,28 @@ __global__ void __launch_bounds__(128) decode_key_ranges_kernel(const DecodePara
     }
 }
 
+// Where the merged result goes when the keys are split across GPUs: besides the local buffers, the
+// packed fp32 partial ([rows][128] output | [rows] log-sum-exp) is stored into slot (step parity,
+// rank) of every peer's exchange buffer with plain peer stores, and the last block to finish
+// releases the per-(parity, rank) flag on every peer with the step number.  world == 0: off.
+struct PushDesc {
+    PeerPtrs peers;
+    const unsigned *step_counter;  // completed exchange steps (advanced by the wait/combine kernel)
+    unsigned *done;                // blocks of the merge grid that have finished; zero on entry and exit
+    long long per;                 // floats per (parity, rank) slot
+    int world, rank, rows;
+};
+
 // Merge of the partial records: one warp per (row, q head).  Lane i looks after part base+i of a
 // chunk of 32 parts for the softmax statistics; for the O row every lane owns channels
 // 4*lane .. 4*lane+3.  Which records belong to a pair follows from cache_seqlens alone, so the
 // record slots of a warp's first item are worked out BEFORE the grid-dependency wait, while the
 // streaming kernel is still running; after the wait only loads, a few shuffles and the store remain.
-__global__ void __launch_bounds__(MERGE_WARPS * 32) decode_merge_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(MERGE_WARPS * 32) decode_merge_kernel(const DecodeParams p,
+                                                                        const __grid_constant__ PushDesc pd) {
     __shared__ int s_start[DEC_MAX_B], s_end[DEC_MAX_B], s_pref[DEC_MAX_B + 1];
     const int lane = threadIdx.x & 31;
     const int B = p.B, Hkv = p.Hkv, G = p.G;
-#ifdef NCKV_TIMELINE
-    unsigned long long *tl = p.timeline + (long long)p.W * 16 + blockIdx.x * 4;
-    if (threadIdx.x == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); tl[0] = t_; }
-#endif
     pdl_launch_dependents();  // whatever follows in the stream may be scheduled behind this grid
     // cache_seqlens is stable by now: the streaming kernel only lets this grid start after it has
     // itself waited for its predecessor
@@ -765,15 +760,30 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) decode_merge_kernel(const De
     if (geo.total > 0 && first_item < n_items) plan_n = plan(first_item, 0, plan_slots, plan_hg);
 
     pdl_wait_prior_grids();  // the streaming kernel has completed and its records are visible
-#ifdef NCKV_TIMELINE
-    if (threadIdx.x == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); tl[1] = t_; }
-#endif
-    if (geo.total == 0) return;
+    const bool push = pd.world > 0;
+    if (geo.total == 0 && !push) return;
+    // The exchange step this call belongs to.  The counter is only advanced by the wait/combine
+    // kernel of the previous step, which completed before the kernels in front of this grid ran.
+    const unsigned step = push ? *pd.step_counter + 1u : 0u;
+    const long long push_off = push ? ((long long)(step & 1u) * pd.world + pd.rank) * pd.per : 0;
+    auto push_row = [&](int item, const float4 &row, float lse_v) {
+        for (int r = 0; r < pd.world; ++r) {
+            float *dst = pd.peers.buf[r] + push_off;
+            reinterpret_cast<float4 *>(dst + (long long)item * NCKV_D)[lane] = row;
+            if (lane == 0) dst[(long long)pd.rows * NCKV_D + item] = lse_v;
+        }
+    };
 
     for (int item = first_item; item < n_items; item += item_stride) {
         int hg = plan_hg, nparts = plan_n;
-        if (item != first_item) nparts = plan(item, 0, plan_slots, hg);
-        if (nparts == 0) continue;
+        if (item != first_item) nparts = geo.total > 0 ? plan(item, 0, plan_slots, hg) : 0;
+        if (nparts == 0) {
+            // written by the streaming kernel itself (one run held the whole pair, or no key is visible)
+            if (push)
+                push_row(item, __ldcg(reinterpret_cast<const float4 *>(p.out_f32 + (long long)item * NCKV_D) + lane),
+                         __ldcg(p.lse + item));
+            continue;
+        }
         float M = -INFINITY, L = 0.f;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int base = 0; base < nparts; base += 32) {
@@ -831,14 +841,30 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) decode_merge_kernel(const De
         uint2 packed;
         packed.x = pack_bf16x2(acc.x, acc.y);
         packed.y = pack_bf16x2(acc.z, acc.w);
-        *reinterpret_cast<uint2 *>(p.out + o) = packed;
+        if (p.out) *reinterpret_cast<uint2 *>(p.out + o) = packed;
         if (p.out_f32) *reinterpret_cast<float4 *>(p.out_f32 + o) = acc;
-        if (p.lse && lane == 0) p.lse[item] = (M + log2f(L)) * 0.69314718055994531f;
+        const float lse_v = (M + log2f(L)) * 0.69314718055994531f;
+        if (p.lse && lane == 0) p.lse[item] = lse_v;
+        if (push) push_row(item, acc, lse_v);
     }
-#ifdef NCKV_TIMELINE
-    __syncthreads();
-    if (threadIdx.x == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); tl[2] = t_; }
-#endif
+    if (push) {
+        // every block's peer stores are ordered before its count; the last block orders all counts
+        // before the flags it releases
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const unsigned prev = atomicAdd(pd.done, 1u);
+            if (prev == gridDim.x - 1) {
+                *pd.done = 0;
+                __threadfence_system();
+                for (int r = 0; r < pd.world; ++r) {
+                    unsigned *flags = reinterpret_cast<unsigned *>(pd.peers.buf[r] + 2LL * pd.world * pd.per);
+                    unsigned *f = flags + (step & 1u) * pd.world + pd.rank;
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(step) : "memory");
+                }
+            }
+        }
+    }
 }
 
 static size_t decode_smem_bytes() {
@@ -855,9 +881,6 @@ static size_t ws_partial_bytes(int G) {
     return 2 * runs * (size_t)rec_floats_for(G) * sizeof(float);
 }
 
-#ifdef NCKV_TIMELINE
-static unsigned long long *g_timeline = nullptr;
-#endif
 
 template <typename Kernel, typename... Args>
 static cudaError_t launch_pdl(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool pdl,
@@ -879,9 +902,6 @@ static cudaError_t launch_pdl(Kernel kernel, dim3 grid, dim3 block, size_t smem,
 
 extern "C" {
 
-#ifdef NCKV_TIMELINE
-NCKV_API void nckv_debug_set_timeline(void *ptr) { nckv::g_timeline = static_cast<unsigned long long *>(ptr); }
-#endif
 
 size_t nckv_workspace_bytes(int B, int Hq, int Hkv, int D) {
     using namespace nckv;
@@ -889,14 +909,12 @@ size_t nckv_workspace_bytes(int B, int Hq, int Hkv, int D) {
     return DEC_STATUS_BYTES + ws_partial_bytes(Hq / Hkv);
 }
 
-int nckv_decode_attn(const void *q, const void *k_cache, const void *v_cache,
-                     const int32_t *cache_seqlens, void *out, float *out_f32, float *lse_out,
-                     int B, int Hq, int Hkv, int D, int T_max, int64_t cache_batch_stride,
-                     int64_t cache_token_stride, int seqlen_offset, int window_left,
-                     int kv_begin, int kv_end, void *workspace, size_t workspace_bytes,
-                     void *stream) {
+// Argument checks shared by the decode-attention entry points (nothing is enqueued here).
+static int decode_check(const void *q, const void *k_cache, const void *v_cache, const int32_t *cache_seqlens,
+                        const void *out, const float *out_f32, const void *workspace, int B, int Hq, int Hkv, int D,
+                        int T_max, size_t workspace_bytes) {
     using namespace nckv;
-    if (!q || !k_cache || !v_cache || !cache_seqlens || !out || !workspace) {
+    if (!q || !k_cache || !v_cache || !cache_seqlens || (!out && !out_f32) || !workspace) {
         set_error("decode_attn: null pointer argument");
         return NCKV_E_ARG;
     }
@@ -929,9 +947,23 @@ int nckv_decode_attn(const void *q, const void *k_cache, const void *v_cache,
         set_error("decode_attn: workspace of %zu bytes given, %zu needed", workspace_bytes, need);
         return NCKV_E_CAPACITY;
     }
+    return NCKV_OK;
+}
+
+static int decode_launch(const void *q, const void *k_cache, const void *v_cache, const int32_t *cache_seqlens,
+                         void *out, float *out_f32, float *lse_out, int B, int Hq, int Hkv, int D, int T_max,
+                         int64_t cache_batch_stride, int64_t cache_token_stride, int seqlen_offset, int window_left,
+                         int kv_begin, int kv_end, nckv::KvSplit split, const nckv::PushDesc &push, void *workspace,
+                         size_t workspace_bytes, void *stream) {
+    using namespace nckv;
+    int rc0 = decode_check(q, k_cache, v_cache, cache_seqlens, out, out_f32, workspace, B, Hq, Hkv, D, T_max,
+                           workspace_bytes);
+    if (rc0 != NCKV_OK) return rc0;
     const int G = Hq / Hkv;
     // Prefer the 5-D maps (one copy instruction per tile and tensor); if this driver does not accept
     // their stride order, use the 4-D maps (two per tile and tensor).  Decided once per process.
+    // (A plain int shared by all host threads: concurrent first calls would both probe and store the
+    // same answer.)
     static int map5_state = 0;  // 0 unknown, 1 usable, -1 refused
     CUtensorMap mk, mv;
     int rc = NCKV_E_CUDA;
@@ -966,15 +998,13 @@ int nckv_decode_attn(const void *q, const void *k_cache, const void *v_cache,
     p.window_left = window_left;
     p.kv_begin = kv_begin;
     p.kv_end = kv_end;
+    p.split = split;
     p.rec_floats = rec_floats_for(G);
     p.W = grid * DEC_WARPS;
     p.scale_log2 = (float)(1.4426950408889634 / sqrt((double)D));
-#ifdef NCKV_TIMELINE
-    p.timeline = g_timeline;
-#endif
 
     const size_t smem = decode_smem_bytes();
-    static bool attr_set[64] = {false};
+    static bool attr_set[64] = {false};  // per device; setting the attribute twice from racing threads is harmless
     int dev = 0;
     NCKV_CUDA_CHECK(cudaGetDevice(&dev));
     const bool ghi = G > 8;
@@ -996,8 +1026,64 @@ int nckv_decode_attn(const void *q, const void *k_cache, const void *v_cache,
     const int items = B * Hq;
     int merge_grid = (items + MERGE_WARPS - 1) / MERGE_WARPS;
     if (merge_grid > 4 * grid) merge_grid = 4 * grid;
-    NCKV_CUDA_CHECK(launch_pdl(decode_merge_kernel, dim3(merge_grid), dim3(MERGE_WARPS * 32), 0, s, true, p));
+    PushDesc pd = push;
+    pd.done = reinterpret_cast<unsigned *>(ws + 32);
+    NCKV_CUDA_CHECK(launch_pdl(decode_merge_kernel, dim3(merge_grid), dim3(MERGE_WARPS * 32), 0, s, true, p, pd));
     return NCKV_OK;
+}
+
+int nckv_decode_attn(const void *q, const void *k_cache, const void *v_cache,
+                     const int32_t *cache_seqlens, void *out, float *out_f32, float *lse_out,
+                     int B, int Hq, int Hkv, int D, int T_max, int64_t cache_batch_stride,
+                     int64_t cache_token_stride, int seqlen_offset, int window_left,
+                     int kv_begin, int kv_end, void *workspace, size_t workspace_bytes,
+                     void *stream) {
+    if (!out) {
+        nckv::set_error("decode_attn: null pointer argument");
+        return NCKV_E_ARG;
+    }
+    nckv::PushDesc none = {};
+    return decode_launch(q, k_cache, v_cache, cache_seqlens, out, out_f32, lse_out, B, Hq, Hkv, D, T_max,
+                         cache_batch_stride, cache_token_stride, seqlen_offset, window_left, kv_begin, kv_end,
+                         nckv::KvSplit{0, 0, 0}, none, workspace, workspace_bytes, stream);
+}
+
+int nckv_decode_attn_split(const void *q, const void *k_cache, const void *v_cache, const int32_t *cache_seqlens,
+                           float *part_out, float *part_lse, int B, int Hq, int Hkv, int D, int T_local,
+                           int64_t cache_batch_stride, int64_t cache_token_stride, int seqlen_offset, int world,
+                           int rank, int block, void *const *peer_bufs, const uint32_t *step_counter,
+                           void *workspace, size_t workspace_bytes, void *stream) {
+    using namespace nckv;
+    if (!part_out || !part_lse) {
+        set_error("decode_attn_split: part_out and part_lse are required");
+        return NCKV_E_ARG;
+    }
+    if (world <= 0 || world > NCKV_MAX_PEERS || rank < 0 || rank >= world || block <= 0) {
+        set_error("decode_attn_split: bad split (world=%d rank=%d block=%d)", world, rank, block);
+        return NCKV_E_ARG;
+    }
+    PushDesc pd = {};
+    if (peer_bufs) {
+        if (!step_counter) {
+            set_error("decode_attn_split: step_counter is required with peer_bufs");
+            return NCKV_E_ARG;
+        }
+        for (int i = 0; i < world; ++i) {
+            pd.peers.buf[i] = static_cast<float *>(peer_bufs[i]);
+            if (!pd.peers.buf[i] || ((uintptr_t)pd.peers.buf[i] & 15)) {
+                set_error("decode_attn_split: peer buffer %d is null or misaligned", i);
+                return NCKV_E_ARG;
+            }
+        }
+        pd.step_counter = step_counter;
+        pd.world = world;
+        pd.rank = rank;
+        pd.rows = B * Hq;
+        pd.per = p2p_per_floats(B * Hq);
+    }
+    return decode_launch(q, k_cache, v_cache, cache_seqlens, nullptr, part_out, part_lse, B, Hq, Hkv, D, T_local,
+                         cache_batch_stride, cache_token_stride, seqlen_offset, -1, 0, 0, KvSplit{world, rank, block},
+                         pd, workspace, workspace_bytes, stream);
 }
 
 // ---- decode attention for callers that must not allocate ----------------------------------------
@@ -1007,8 +1093,9 @@ int nckv_decode_attn(const void *q, const void *k_cache, const void *v_cache,
 static __device__ __align__(256) unsigned char g_static_scratch[NCKV_STATIC_SCRATCH_BYTES];
 
 extern "C" int nckv_decode_key_ranges(const int32_t *cache_seqlens, int B, int T_max, int seqlen_offset,
-                                      int window_left, int kv_begin, int kv_end, int32_t *key_begin,
-                                      int32_t *key_end, int32_t *status, void *stream) {
+                                      int window_left, int kv_begin, int kv_end, int split_world, int split_rank,
+                                      int split_block, int32_t *key_begin, int32_t *key_end, int32_t *status,
+                                      void *stream) {
     using namespace nckv;
     if (!cache_seqlens || !key_begin || !key_end || !status) {
         set_error("decode_key_ranges: null pointer argument");
@@ -1018,7 +1105,12 @@ extern "C" int nckv_decode_key_ranges(const int32_t *cache_seqlens, int B, int T
         set_error("decode_key_ranges: B=%d must be in 1..%d and T_max=%d positive", B, DEC_MAX_B, T_max);
         return NCKV_E_ARG;
     }
+    if (split_block < 0 || (split_block > 0 && (split_world <= 0 || split_rank < 0 || split_rank >= split_world))) {
+        set_error("decode_key_ranges: bad split (world=%d rank=%d block=%d)", split_world, split_rank, split_block);
+        return NCKV_E_ARG;
+    }
     DecodeParams p = {};
+    p.split = KvSplit{split_world, split_rank, split_block};
     p.seqlens = cache_seqlens;
     p.status = status;
     p.B = B;
@@ -1038,8 +1130,13 @@ int nckv_decode_attn_static(const void *q, const void *k_cache, const void *v_ca
                             int64_t cache_token_stride, int seqlen_offset, int window_left,
                             int kv_begin, int kv_end, void **status_word, void *stream) {
     using namespace nckv;
+    if (!out) {
+        set_error("decode_attn_static: null pointer argument");
+        return NCKV_E_ARG;
+    }
     // In host code `g_static_scratch` is only a handle; the address kernels can use has to be
-    // asked for, once per device, with that device current.
+    // asked for, once per device, with that device current.  (Racing first calls from two host
+    // threads would both store the same address.)
     static void *dev_ptr[64] = {nullptr};
     int dev = 0;
     NCKV_CUDA_CHECK(cudaGetDevice(&dev));
@@ -1061,6 +1158,10 @@ int nckv_decode_attn_static(const void *q, const void *k_cache, const void *v_ca
     }
     unsigned char *base = static_cast<unsigned char *>(dev_ptr[dev]);
     if (status_word) *status_word = base;
+    // reject bad arguments before anything touches the shared array
+    const int chk = decode_check(q, k_cache, v_cache, cache_seqlens, out, out_f32, base, B, Hq, Hkv, D, T_max,
+                                 NCKV_STATIC_SCRATCH_BYTES);
+    if (chk != NCKV_OK) return chk;
     // The array keeps whatever the previous call left.  The ticket counter must start at zero (it
     // returns to zero by itself unless a call was cut short); the partial records need no clearing,
     // every record that is read was written by the same call.

@@ -39,19 +39,12 @@ __global__ void __launch_bounds__(256) lse_combine_kernel(const float *__restric
     if (lse_out && lane == 0) lse_out[row] = M > -INFINITY ? M + logf(L) : -INFINITY;
 }
 
-// Block-cyclic ownership of key positions for the sequence-split path: position p belongs to shard
-// (p / block) % world and sits at local index (p / (block*world)) * block + p % block there.
-__device__ __forceinline__ int owned_below(int n, int world, int rank, int block) {
-    const int cycle = block * world;
-    const int full = n / cycle, rem = n - full * cycle;
-    return full * block + min(max(rem - rank * block, 0), block);
-}
-
+// The split bookkeeping as arrays (owned_below: nckv_common.cuh).  This kernel never releases its
+// dependents early: a kernel launched behind it with programmatic dependent launch may read its
+// outputs before its own grid-dependency wait (the decode kernels read cache_seqlens that early).
 __global__ void kv_split_plan_kernel(const int32_t *__restrict__ seqlens, int B, int T_new, int world, int rank,
                                      int block, int32_t *__restrict__ local_len_after,
                                      int32_t *__restrict__ write_slot) {
-    pdl_wait_prior_grids();
-    pdl_launch_dependents();
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= B) return;
     const int L = max(seqlens[b], 0);
@@ -70,8 +63,8 @@ extern "C" int nckv_kv_split_plan(const int32_t *cache_seqlens, int B, int T_new
         set_error("kv_split_plan: null pointer argument");
         return NCKV_E_ARG;
     }
-    if (B <= 0 || T_new <= 0 || world <= 0 || rank < 0 || rank >= world || block <= 0 || (block % 32) != 0) {
-        set_error("kv_split_plan: bad argument (B=%d T_new=%d world=%d rank=%d block=%d; block must be a multiple of 32)",
+    if (B <= 0 || T_new <= 0 || world <= 0 || rank < 0 || rank >= world || block <= 0) {
+        set_error("kv_split_plan: bad argument (B=%d T_new=%d world=%d rank=%d block=%d)",
                   B, T_new, world, rank, block);
         return NCKV_E_ARG;
     }

@@ -26,13 +26,36 @@ int cuda_fail(cudaError_t e, const char *what);
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
-// Encode a tiled tensor map over a (B, T, Hkv, D) bf16 view split as
-// dims (64 [d within half], T, 2 [half], Hkv, B) or plain 4-D; see tensor_map.cu.
+// Tiled tensor maps over a (B, T, Hkv, D) bf16 cache view (defined in host.cu): the 4-D form
+// (d, h, t, b) and the 5-D form (d within half [64], t, half [2], h, b).
 int make_kv_tensor_map(CUtensorMap *map, const void *base, int B, int T, int Hkv,
                        int64_t batch_stride, int64_t token_stride, int box_tokens);
 
 int make_kv_tensor_map_5d(CUtensorMap *map, const void *base, int B, int T, int Hkv,
                           int64_t batch_stride, int64_t token_stride, int box_tokens);
+
+// ---- sequence-split bookkeeping (shared by host checks and kernels) ---------------------------
+// Block-cyclic ownership of key positions: position p belongs to shard (p / block) % world and
+// sits at local index (p / (block*world)) * block + p % block there.  owned_below(n) = how many
+// positions p < n shard `rank` owns = the local index of position n when the shard owns it.
+__host__ __device__ inline int owned_below(int n, int world, int rank, int block) {
+    const int cycle = block * world;
+    const int full = n / cycle, rem = n - full * cycle;
+    int part = rem - rank * block;
+    part = part < 0 ? 0 : (part > block ? block : part);
+    return full * block + part;
+}
+struct KvSplit {  // block == 0: the cache is not split
+    int world, rank, block;
+};
+
+// Peer-memory exchange of the sequence-split path: one symmetric buffer per rank,
+//     data  [2][world][per] fp32, flags [2][world] u32   (per = p2p_per_floats(rows))
+#define NCKV_MAX_PEERS 16
+struct PeerPtrs {
+    float *buf[NCKV_MAX_PEERS];
+};
+__host__ __device__ inline long long p2p_per_floats(int rows) { return (long long)rows * NCKV_D + ((rows + 3) & ~3); }
 
 // ---- device helpers ----------------------------------------------------------------------
 #ifdef __CUDACC__
@@ -162,6 +185,17 @@ __device__ __forceinline__ void tma_load_5d_hint(void *smem_dst, const CUtensorM
         " [%0], [%1, {%2, %3, %4, %5, %6}], [%7], %8;" ::"r"(smem_u32(smem_dst)),
         "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(smem_u32(bar)), "l"(policy)
         : "memory");
+}
+// L2 prefetch of a tile (no shared-memory destination, no completion to wait for)
+__device__ __forceinline__ void tma_prefetch_l2_5d(const CUtensorMap *map, int c0, int c1, int c2, int c3, int c4) {
+    asm volatile("cp.async.bulk.prefetch.tensor.5d.L2.global.tile [%0, {%1, %2, %3, %4, %5}];" ::"l"(map), "r"(c0),
+                 "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_l2_4d(const CUtensorMap *map, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];" ::"l"(map), "r"(c0),
+                 "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
 }
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");

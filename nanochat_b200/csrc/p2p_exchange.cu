@@ -5,6 +5,9 @@
 //     flags [2][world]      u32    flag (parity, r) = number of the step whose data slot (parity, r) holds
 // per = rows*D normalised partial output + rows log-sum-exp values (padded to 4 floats).
 //
+//   (decode_merge_kernel)    in the fused form (nckv_decode_attn_split with peer buffers) the kernel that
+//                            merges the split partials stores each finished row straight into every
+//                            peer's slot and its last block releases the flags; no separate push.
 //   p2p_push_kernel          CTA p of rank r copies r's partial into peer p's slot (step&1, r) with
 //                            plain 16-byte stores through the peer mapping, fences at system scope
 //                            and then releases the flag with the step number (read from a device
@@ -19,15 +22,7 @@
 
 #include "nckv_common.cuh"
 
-#define NCKV_MAX_PEERS 16
-
 namespace nckv {
-
-struct PeerPtrs {
-    float *buf[NCKV_MAX_PEERS];
-};
-
-__host__ __device__ inline long long p2p_per_floats(int rows) { return (long long)rows * NCKV_D + ((rows + 3) & ~3); }
 
 __global__ void __launch_bounds__(1024) p2p_push_kernel(const float4 *__restrict__ send, long long per,
                                                         const __grid_constant__ PeerPtrs peers, int world, int rank,
@@ -57,8 +52,12 @@ __global__ void __launch_bounds__(256) p2p_wait_combine_kernel(const float *__re
                                                                float *__restrict__ lse_out, int32_t *status,
                                                                unsigned long long limit_ns) {
     __shared__ int s_ok;
-    pdl_wait_prior_grids();
-    const unsigned step = *step_counter + 1u;  // the step the push kernel before this grid delivered
+    // No grid-dependency wait yet: the flags are the synchronisation.  This grid may be resident while
+    // the kernels of its own step are still running (they release their dependents early); the step
+    // counter is stable by then, since those kernels only started after the previous step's
+    // wait/combine grid (the only writer of the counter) had completed.  The local rank's flag is set by
+    // the last block of its own push, so passing the poll implies the local partial is in place too.
+    const unsigned step = *step_counter + 1u;  // the step whose partials are awaited
     const unsigned parity = step & 1u;
     unsigned *done = step_counter + 1;         // blocks of this grid that have finished
     if (threadIdx.x == 0) s_ok = 1;
@@ -77,6 +76,7 @@ __global__ void __launch_bounds__(256) p2p_wait_combine_kernel(const float *__re
         if (!ok) s_ok = 0;
     }
     __syncthreads();
+    pdl_wait_prior_grids();  // `out` may still be read by an earlier kernel; nothing is written before this
     const int lane = threadIdx.x & 31;
     const long long row = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (!s_ok) {  // a peer never delivered: report, write nothing, keep the context usable

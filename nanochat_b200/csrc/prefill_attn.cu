@@ -189,16 +189,6 @@ __host__ __device__ constexpr uint32_t umma_idesc(int M, int N, int a_mn_major, 
            ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
-// Debug builds with -DNCKV_PF_TIMELINE record clock64() stamps of two CTAs' loop phases.
-#ifdef NCKV_PF_TIMELINE
-__device__ long long *g_pf_tl = nullptr;
-#define PF_STAMP(k)                                                                                  \
-    do {                                                                                             \
-        if (tl_slot >= 0 && it < 40) tl_ptr[((tl_slot * 40) + it) * 8 + (k)] = clock64();            \
-    } while (0)
-#else
-#define PF_STAMP(k)
-#endif
 
 __global__ void __launch_bounds__(PF_THREADS, 2)
 prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -289,17 +279,6 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     constexpr uint32_t IDESC_O = umma_idesc(PF_M, NCKV_D, 0, 1);
     const bool issuer_warp = warp == PF_SOFTMAX_THREADS / 32;
     bool aborted = false;
-#ifdef NCKV_PF_TIMELINE
-    int tl_slot = -1;
-    long long *const tl_ptr = g_pf_tl;
-    {
-        int cta = -1;
-        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) cta = 0;
-        if (blockIdx.x == 8 && blockIdx.y == 3 && blockIdx.z == 2) cta = 1;
-        int th = tid == 0 ? 0 : (tid == 64 ? 1 : (tid == PF_SOFTMAX_THREADS ? 2 : -1));
-        if (tl_ptr && cta >= 0 && th >= 0) tl_slot = cta * 3 + th;
-    }
-#endif
     auto timed_out = [&]() {
         *abort_flag = 1;
         atomicOr(p.status, (int)NCKV_ST_TIMEOUT);
@@ -403,19 +382,15 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             bool ok = issue_s(0);
             if (ok && n_tiles > 1) ok = issue_s(1);
             for (int it = 0; it < n_tiles && ok; ++it) {
-                PF_STAMP(0);
                 // P(it) is in TMEM, S(it) has been read, O carries the scale P was made with
                 ok = wait_all(&bar_p[it & 1], (uint32_t)((it >> 1) & 1));
                 if (!ok) break;
                 tc_fence_after();
-                PF_STAMP(3);
                 // S(it+2) goes into the S buffer every thread has just finished reading; its commit also
                 // covers O += P V(it).  The last two tiles have no S behind them and signal bar_o.
                 const bool s_follows = it + 2 < n_tiles;
                 ok = issue_pv(it, !s_follows);
-                PF_STAMP(4);
                 if (ok && s_follows) ok = issue_s(it + 2);
-                PF_STAMP(5);
             }
             if (!ok && leader) timed_out();
         }
@@ -437,7 +412,6 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             const uint32_t kv_parity = (uint32_t)((it / PF_VSTAGES) & 1);
             const int key0 = kv_lo + it * PF_N;
             const uint32_t tmem_s_it = tmem_s + (uint32_t)(it & 1) * PF_N;
-            PF_STAMP(0);
             // tcgen05.ld/st are warp-wide (.sync.aligned): every decision that skips them is taken per warp
             {
                 const bool ok = *abort_flag == 0 &&
@@ -448,7 +422,6 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 }
             }
             tc_fence_after();
-            PF_STAMP(1);
 
             float s_val[HN];
 #pragma unroll
@@ -490,7 +463,6 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 asm volatile("bar.sync 1, %0;" ::"n"(PF_SOFTMAX_THREADS) : "memory");
                 mx_raw = fmaxf(__bfloat162float(mine), __bfloat162float(xb[(half ^ 1) * PF_M + row]));
             }
-            PF_STAMP(2);
             // the max is taken on raw scores and scaled once (the scale is positive)
             const float mx = mx_raw * p.scale_log2;
             const bool raise = mx > m_used + 8.f;  // also the first tile that shows this row a key (m_used = -inf)
@@ -514,12 +486,10 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 pk[c / 2 + 1] = pack_bf16x2(p2, p3);
             }
             l_run += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);  // this thread's share of the row sum
-            PF_STAMP(3);
 
             // P row -> TMEM, over the first 32 columns of this tile's S buffer (this lane's own scores,
             // already in registers).  S of tile it+2 is issued behind P V(it) and lands on top of it.
             tmem_st_words(tmem_s_it + lane_sel + half * (HN / 2), pk);
-            PF_STAMP(4);
             // A raised scale: O (+)= P V of the previous tile must be complete before the O rows
             // accumulated so far are brought to the new scale (tcgen05.ld / multiply / tcgen05.st).
             // Every lane applies its own factor (1 for rows that keep their scale).
@@ -557,11 +527,9 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 }
                 fence_proxy_async_smem();  // the zeroed V rows must be visible to the tensor core
             }
-            PF_STAMP(5);
             tc_fence_before();  // orders this thread's TMEM loads/stores before the next MMAs
             __syncwarp();
             if ((tid & 31) == 0) mbar_arrive(&bar_p[it & 1]);  // one arrival per warp
-            PF_STAMP(6);
         }
         if (aborted && *abort_flag == 0) timed_out();  // a wait ran out in this warp
 
@@ -619,12 +587,6 @@ static size_t prefill_smem_bytes() {
 
 }  // namespace nckv
 
-#ifdef NCKV_PF_TIMELINE
-extern "C" NCKV_API int nckv_debug_set_pf_timeline(void *ptr) {
-    long long *v = static_cast<long long *>(ptr);
-    return cudaMemcpyToSymbol(nckv::g_pf_tl, &v, sizeof(v)) == cudaSuccess ? 0 : -4;
-}
-#endif
 
 extern "C" int nckv_prefill_attn(const void *q, const void *k, const void *v, const int32_t *cache_seqlens,
                                  void *out, int B, int T_new, int Hq, int Hkv, int D, int T_k,

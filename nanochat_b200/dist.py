@@ -1,6 +1,6 @@
 """Multi-GPU forms of the decode path (one process per GPU, torch.distributed for the plumbing).
 
-Two partitionings, both from BASELINE.json's north star:
+Two partitionings:
 
 * by sequence (``shard_rows``): rows are independent, every rank owns a contiguous block of rows
   with its own KVCache and nothing crosses GPUs on the data path.  This is the replica-per-GPU
@@ -82,7 +82,8 @@ def sharded_prefill(prompt_cache, local_cache, group=None, src=0):
 
 def kv_shard_range(capacity, rank, world_size, align=32):
     """Key range [begin, end) of ``rank`` in the contiguous layout: equal ranges, boundaries rounded
-    up to a multiple of ``align`` tokens (the decode kernel's tile) so no tile straddles two ranks."""
+    up to a multiple of ``align`` tokens.  (Any boundary is correct: a shard's tiles start at its own
+    first key.  The rounding only keeps the ranges tidy.)"""
     if not 0 <= rank < world_size:
         raise ValueError(f"rank {rank} outside world of {world_size}")
     per = -(-capacity // world_size)
@@ -105,10 +106,15 @@ class KVSplitAttention:
     in this rank's layout (see module docstring), cache_seqlens the GLOBAL lengths before the new
     token — returns the full attention output (B, Hq, D) bf16 on every rank.
     ``append_and_attend`` first runs the fused RoPE/norm/append for the rows this rank owns.
+
+    Kernels per step in the block-cyclic layout with ``exchange="p2p"``: append (works out the owner
+    and the local slot itself), streaming attention over the local part (works out the local
+    lengths itself), merge of the split partials (stores every finished row into all peers'
+    exchange buffers and releases the step's flags), wait + combine.  With ``exchange="nccl"`` the
+    third kernel only fills the local send buffer and an all-gather plus the combine kernel follow.
     """
 
-    def __init__(self, capacity, group=None, window_left=-1, block=1024, exchange="nccl", partial_fn=None,
-                 combine_fn=None):
+    def __init__(self, capacity, group=None, window_left=-1, block=1024, exchange="nccl"):
         import torch.distributed as dist
         self.dist = dist
         self.group = group
@@ -119,8 +125,8 @@ class KVSplitAttention:
         if block and window_left >= 0:
             raise ValueError("the block-cyclic layout stores keys compactly and cannot express a sliding window; "
                              "use block=0 (contiguous ranges) for windowed layers")
-        if block and block % 32:
-            raise ValueError("block must be a multiple of the 32-key tile")
+        if block < 0:
+            raise ValueError("block must be positive (block-cyclic) or 0 (contiguous ranges)")
         self.block = block
         if block:
             self.kv_begin = self.kv_end = 0
@@ -128,9 +134,6 @@ class KVSplitAttention:
         else:
             self.kv_begin, self.kv_end = kv_shard_range(capacity, self.rank, self.world)
             self.local_capacity = capacity
-        # injectable for CPU tests of the exchange logic; the product path is the CUDA ops
-        self._partial = partial_fn or self._partial_cuda
-        self._combine = combine_fn or ops.lse_combine
         self._gather = self._send = None
         if exchange not in ("nccl", "p2p"):
             raise ValueError("exchange must be 'nccl' (all-gather + combine kernel) or 'p2p' (peer-memory push + "
@@ -138,6 +141,11 @@ class KVSplitAttention:
         self.exchange = exchange if self.world > 1 else "nccl"
         self._symm = self._peer_ptrs = None
         self.wait_limit_ns = 0  # 0 = the library default (2 s)
+
+    @property
+    def split(self):
+        """(world, rank, block) as the *_split kernels take it."""
+        return self.world, self.rank, self.block
 
     # ---- buffers: [rows*D output | rows lse] per rank, padded to a multiple of 4 floats ----------
     def _buffers(self, rows, D, device):
@@ -147,12 +155,13 @@ class KVSplitAttention:
             self._send = torch.empty(per, dtype=torch.float32, device=device)
         return self._send[:rows * D], self._send[rows * D:rows * D + rows]
 
-    def _partial_cuda(self, q, k_cache, v_cache, cache_seqlens, out_f32, lse):
-        B, Hq, D = q.shape
+    def _partial(self, q, k_cache, v_cache, cache_seqlens, out_f32, lse, push):
+        """This rank's normalised partial output and log-sum-exp into out_f32 / lse; with ``push`` the
+        same kernels also deliver them to every peer (block-cyclic layout only)."""
         if self.block:
-            local_len, _ = ops.kv_split_plan(cache_seqlens, self.world, self.rank, self.block)
-            ops.decode_attention(q, k_cache, v_cache, local_len, seqlen_offset=0, window_left=-1, partial=True,
-                                 out_f32=out_f32, lse=lse)
+            ops.decode_attention_split(q, k_cache, v_cache, cache_seqlens, self.split, out_f32, lse, seqlen_offset=1,
+                                       peer_ptrs=self._peer_ptrs if push else None,
+                                       step_counter=self._step_ctr if push else None)
         elif self.kv_end <= self.kv_begin:  # more ranks than tiles: this rank has nothing
             out_f32.zero_()
             lse.fill_(float("-inf"))
@@ -160,12 +169,14 @@ class KVSplitAttention:
             ops.decode_attention(q, k_cache, v_cache, cache_seqlens, seqlen_offset=1, window_left=self.window_left,
                                  kv_begin=self.kv_begin, kv_end=self.kv_end, partial=True, out_f32=out_f32, lse=lse)
 
+    def _combine(self, parts_o, parts_lse):
+        return ops.lse_combine(parts_o, parts_lse)
+
     def append_and_attend(self, q, k, v, k_cache, v_cache, cache_seqlens, cos, sin):
         """q, k, v: (B, 1, H, D) raw projections.  RoPE/QK-norm/scale on q and k (positions are the
         global lengths), the owner of position L_b stores k/v, then ``attend``."""
         if self.block:
-            _, slots = ops.kv_split_plan(cache_seqlens, self.world, self.rank, self.block)
-            q2 = ops.append_rope_norm(q, k, v, k_cache, v_cache, cache_seqlens, cos, sin, write_slots=slots)
+            q2 = ops.append_rope_norm(q, k, v, k_cache, v_cache, cache_seqlens, cos, sin, split=self.split)
         else:  # global indices: every rank may write, only the owner's range is ever read
             q2 = ops.append_rope_norm(q, k, v, k_cache, v_cache, cache_seqlens, cos, sin)
         return self.attend(q2[:, 0], k_cache, v_cache, cache_seqlens)
@@ -174,18 +185,15 @@ class KVSplitAttention:
         B, Hq, D = q.shape
         rows = B * Hq
         out_f32, lse = self._buffers(rows, D, q.device)
-        res = self._partial(q, k_cache, v_cache, cache_seqlens, out_f32.view(B, Hq, D), lse.view(B, Hq))
-        if res is not None:  # an injected partial_fn may return fresh tensors instead of filling the buffers
-            o32, l32 = res
-            if o32.shape != (B, Hq, D) or l32.shape != (B, Hq):
-                raise RuntimeError(f"partial result has shape {tuple(o32.shape)} / {tuple(l32.shape)}, expected "
-                                   f"{(B, Hq, D)} / {(B, Hq)}")
-            out_f32.copy_(o32.reshape(-1))
-            lse.copy_(l32.reshape(-1))
+        p2p = self.exchange == "p2p"
+        if p2p and (self._symm is None or self._p2p_rows != rows):
+            self._setup_p2p(rows, D, q.device)
+        fused_push = p2p and bool(self.block)
+        self._partial(q, k_cache, v_cache, cache_seqlens, out_f32.view(B, Hq, D), lse.view(B, Hq), fused_push)
         if self.world == 1:
             return self._combine(out_f32.view(1, rows, D), lse.view(1, rows))[0].view(B, Hq, D)
-        if self.exchange == "p2p":
-            return self._exchange_p2p(rows, D, q.device).view(B, Hq, D)
+        if p2p:
+            return self._exchange_p2p(rows, D, q.device, pushed=fused_push).view(B, Hq, D)
         self.dist.all_gather_into_tensor(self._gather.view(-1), self._send, group=self.group)
         parts_o = self._gather[:, :rows * D].unflatten(1, (rows, D))
         parts_lse = self._gather[:, rows * D:rows * D + rows]
@@ -210,15 +218,14 @@ class KVSplitAttention:
         self._p2p_out = torch.empty(rows, D, dtype=torch.bfloat16, device=device)
         self._step_ctr = torch.zeros(2, dtype=torch.int32, device=device)  # [step, finished blocks]
 
-    def _exchange_p2p(self, rows, D, device):
+    def _exchange_p2p(self, rows, D, device, pushed):
         from . import _lib
-        if self._symm is None or self._p2p_rows != rows:
-            self._setup_p2p(rows, D, device)
         idx = device.index if device.index is not None else torch.cuda.current_device()
         stream = torch.cuda.current_stream(idx).cuda_stream
         ws = ops.workspace(device, 1, 1, 1)
-        _lib.call("nckv_p2p_push", self._send.data_ptr(), rows, D, self._peer_ptrs, self.world, self.rank,
-                  self._step_ctr.data_ptr(), stream)
+        if not pushed:
+            _lib.call("nckv_p2p_push", self._send.data_ptr(), rows, D, self._peer_ptrs, self.world, self.rank,
+                      self._step_ctr.data_ptr(), stream)
         _lib.call("nckv_p2p_wait_combine", self._symm.data_ptr(), self.world, rows, D, self._step_ctr.data_ptr(),
                   self._p2p_out.data_ptr(), None, ws.data_ptr(), self.wait_limit_ns, stream)
         return self._p2p_out

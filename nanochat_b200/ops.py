@@ -136,7 +136,7 @@ _NS.define("append_rope_norm(Tensor q, Tensor k, Tensor v, Tensor(a!) k_cache, T
            "Tensor cache_seqlens, Tensor cos, Tensor sin, float qk_scale, float eps) -> Tensor")
 
 
-def _append_rope_norm(q, k, v, k_cache, v_cache, cache_seqlens, cos, sin, qk_scale, eps, write_slots=None):
+def _append_rope_norm(q, k, v, k_cache, v_cache, cache_seqlens, cos, sin, qk_scale, eps, write_slots=None, split=None):
     name = "append_rope_norm"
     _require_cuda(name, q, k, v, k_cache, v_cache, cache_seqlens, cos, sin)
     _require_bf16(name, q, k, v, k_cache, v_cache, cos, sin)
@@ -159,7 +159,14 @@ def _append_rope_norm(q, k, v, k_cache, v_cache, cache_seqlens, cos, sin, qk_sca
     q_out = torch.empty_like(q)
     idx, stream, ws = _launch_ctx(q, B, Hq, Hkv)
     with _device_guard(idx):
-        if write_slots is None:
+        if split is not None:
+            world, rank, block = split
+            rc = _lib.lib.nckv_append_rope_norm_split(q.data_ptr(), k.data_ptr(), v.data_ptr(), q_out.data_ptr(),
+                                                      k_cache.data_ptr(), v_cache.data_ptr(), cache_seqlens.data_ptr(),
+                                                      cos2.data_ptr(), sin2.data_ptr(), B, T_new, Hq, Hkv, D,
+                                                      k_cache.size(1), sb, st, cos2.size(0), qk_scale, eps, world, rank,
+                                                      block, ws.data_ptr(), stream)
+        elif write_slots is None:
             rc = _F_APPEND_ROPE(q.data_ptr(), k.data_ptr(), v.data_ptr(), q_out.data_ptr(), k_cache.data_ptr(),
                                 v_cache.data_ptr(), cache_seqlens.data_ptr(), cos2.data_ptr(), sin2.data_ptr(), B, T_new,
                                 Hq, Hkv, D, k_cache.size(1), sb, st, cos2.size(0), qk_scale, eps, ws.data_ptr(), stream)
@@ -367,11 +374,49 @@ _NS.impl("lse_combine", _lse_combine, "CPU")
 
 
 def append_rope_norm(q, k, v, k_cache, v_cache, cache_seqlens, cos, sin, qk_scale=QK_SCALE, eps=RMS_EPS,
-                     write_slots=None):
+                     write_slots=None, split=None):
     """RoPE + QK-norm + scale on q and k, append k/v at ``cache_seqlens`` (per row); returns q'.
     With ``write_slots`` (int32 per row; sequence-split caches) the position still comes from
-    ``cache_seqlens`` but k/v are written at ``write_slots[b]``, or not at all where it is -1."""
-    return _append_rope_norm(q, k, v, k_cache, v_cache, cache_seqlens, cos, sin, qk_scale, eps, write_slots)
+    ``cache_seqlens`` but k/v are written at ``write_slots[b]``, or not at all where it is -1.
+    With ``split=(world, rank, block)`` the kernel works those slots out itself from the global
+    ``cache_seqlens`` (block-cyclic ownership; only the owner of the position stores k/v)."""
+    return _append_rope_norm(q, k, v, k_cache, v_cache, cache_seqlens, cos, sin, qk_scale, eps, write_slots, split)
+
+
+def decode_attention_split(q, k_cache, v_cache, cache_seqlens, split, part_out, part_lse, seqlen_offset=1,
+                           peer_ptrs=None, step_counter=None):
+    """One-token attention over this rank's block-cyclic part of the keys (``split = (world, rank,
+    block)``; ``cache_seqlens`` are the global lengths).  Fills ``part_out`` (B, Hq, D) fp32 and
+    ``part_lse`` (B, Hq) fp32.  With ``peer_ptrs`` (a ctypes array of every rank's exchange buffer)
+    the merge kernel also pushes the packed partial to all peers and releases the step's flags."""
+    name = "decode_attn_split"
+    _require_cuda(name, q, k_cache, v_cache, cache_seqlens, part_out, part_lse)
+    _require_bf16(name, q, k_cache, v_cache)
+    if cache_seqlens.dtype != torch.int32:
+        raise RuntimeError(f"nckv::{name}: cache_seqlens must be int32")
+    if q.dim() != 3 or q.size(2) != HEAD_DIM:
+        raise RuntimeError(f"nckv::{name}: q must be (B, Hq, {HEAD_DIM}), got {tuple(q.shape)}")
+    B, Hq, D = q.shape
+    if k_cache.shape != v_cache.shape or k_cache.stride() != v_cache.stride():
+        raise RuntimeError(f"nckv::{name}: k_cache and v_cache must share shape and strides")
+    Hkv = k_cache.size(2)
+    if k_cache.size(0) != B or Hq % Hkv:
+        raise RuntimeError(f"nckv::{name}: cache {tuple(k_cache.shape)} does not match q {tuple(q.shape)}")
+    if (part_out.dtype != torch.float32 or part_lse.dtype != torch.float32 or part_out.numel() != B * Hq * D or
+            part_lse.numel() != B * Hq or not part_out.is_contiguous() or not part_lse.is_contiguous()):
+        raise RuntimeError(f"nckv::{name}: part_out / part_lse buffers do not fit (B={B}, Hq={Hq})")
+    sb, st = _cache_strides(name, k_cache)
+    q = q.contiguous()
+    world, rank, block = split
+    idx, stream, ws = _launch_ctx(q, B, Hq, Hkv)
+    with _device_guard(idx):
+        rc = _lib.lib.nckv_decode_attn_split(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), cache_seqlens.data_ptr(),
+                                             part_out.data_ptr(), part_lse.data_ptr(), B, Hq, Hkv, D, k_cache.size(1), sb, st,
+                                             seqlen_offset, world, rank, block, peer_ptrs,
+                                             step_counter.data_ptr() if step_counter is not None else None,
+                                             ws.data_ptr(), ws.numel(), stream)
+    if rc < 0:
+        _lib.check("nckv_decode_attn_split", rc)
 
 
 def append_kv(k, v, k_cache, v_cache, cache_seqlens):
@@ -402,9 +447,10 @@ def kv_split_plan(cache_seqlens, world, rank, block, T_new=1):
     return local_len, slot
 
 
-def decode_key_ranges(cache_seqlens, T_max, seqlen_offset=1, window_left=-1, kv_begin=0, kv_end=0):
+def decode_key_ranges(cache_seqlens, T_max, seqlen_offset=1, window_left=-1, kv_begin=0, kv_end=0, split=(0, 0, 0)):
     """Key positions [begin, end) per row that decode_attention reads for these arguments, as two
-    int32 tensors (computed on the device by the routine the attention kernels use)."""
+    int32 tensors (computed on the device by the routine the attention kernels use).  With
+    ``split = (world, rank, block)`` the ranges are local indices of that block-cyclic shard."""
     _require_cuda("decode_key_ranges", cache_seqlens)
     B = cache_seqlens.numel()
     begin = torch.empty_like(cache_seqlens)
@@ -413,7 +459,7 @@ def decode_key_ranges(cache_seqlens, T_max, seqlen_offset=1, window_left=-1, kv_
     ws = workspace(cache_seqlens.device, 1, 1, 1)
     with _device_guard(idx):
         _lib.call("nckv_decode_key_ranges", cache_seqlens.data_ptr(), B, T_max, seqlen_offset, window_left, kv_begin,
-                  kv_end, begin.data_ptr(), end.data_ptr(), ws.data_ptr(), torch.cuda.current_stream(idx).cuda_stream)
+                  kv_end, int(split[0]), int(split[1]), int(split[2]), begin.data_ptr(), end.data_ptr(), ws.data_ptr(), torch.cuda.current_stream(idx).cuda_stream)
     return begin, end
 
 

@@ -53,18 +53,22 @@ def _worker(rank, world, port, B, Hq, Hkv, D, T, seqlens, window, ret):
         vc = torch.randn(B, T, Hkv, D, generator=g)
         lens = torch.tensor(seqlens, dtype=torch.int32)
 
-        def partial_fn(q_, kc_, vc_, lens_, out_buf=None, lse_buf=None):
-            o, l = O.attention_kvcache(q_.numpy()[:, None], kc_.numpy(), vc_.numpy(), lens_.numpy(), window_left=window,
-                                       kv_begin=att.kv_begin, kv_end=att.kv_end)
-            if att.kv_end <= att.kv_begin:
-                o[:], l[:] = 0.0, -np.inf
-            return torch.from_numpy(o[:, 0]), torch.from_numpy(l[:, 0])
+        class OracleSplit(KVSplitAttention):
+            """The exchange logic on CPU: the two kernel calls are replaced by the numpy oracle."""
 
-        def combine_fn(po, pl):
-            o, l = O.lse_combine(po.numpy(), pl.numpy())
-            return torch.from_numpy(o), torch.from_numpy(l)
+            def _partial(self, q_, kc_, vc_, lens_, out_buf, lse_buf, push):
+                o, l = O.attention_kvcache(q_.numpy()[:, None], kc_.numpy(), vc_.numpy(), lens_.numpy(),
+                                           window_left=window, kv_begin=self.kv_begin, kv_end=self.kv_end)
+                if self.kv_end <= self.kv_begin:
+                    o[:], l[:] = 0.0, -np.inf
+                out_buf.copy_(torch.from_numpy(o[:, 0]))
+                lse_buf.copy_(torch.from_numpy(l[:, 0]))
 
-        att = KVSplitAttention(T, window_left=window, block=0, partial_fn=partial_fn, combine_fn=combine_fn)
+            def _combine(self, po, pl):
+                o, l = O.lse_combine(po.numpy(), pl.numpy())
+                return torch.from_numpy(o), torch.from_numpy(l)
+
+        att = OracleSplit(T, window_left=window, block=0)
         # poison the keys this rank does not own: the result must not depend on them
         kc_local, vc_local = kc.clone(), vc.clone()
         kc_local[:, :att.kv_begin] = 1e4

@@ -1,5 +1,5 @@
-"""Key-split decode attention across 2 GPUs (NCCL all-gather + LSE combine) against the oracle.
-Needs two CUDA devices; skipped otherwise."""
+"""Key-split decode attention across 2 GPUs (NCCL all-gather + LSE combine, and the peer-memory
+exchange fused into the attention kernels) against the oracle.  Needs two CUDA devices; skipped otherwise."""
 import os
 import socket
 
@@ -84,6 +84,13 @@ def _worker(rank, world, port, ret):
             torch.cuda.synchronize()
             full3, _ = O.attention_kvcache(q.float().numpy()[:, None], kc.float().numpy(), vc.float().numpy(), lens3.numpy())
             err = max(err, float(np.abs(out3.float().cpu().numpy() - full3[:, 0]).max() / np.abs(full3).max()))
+        # (3b) the whole fused step over peer memory: owner-only append inside the append kernel, local
+        # lengths inside the attention kernel, push inside the merge kernel, then wait + combine
+        out4 = att3.append_and_attend(q_raw.to(dev), k_raw.to(dev), v_raw.to(dev), kl.to(dev), vl.to(dev), lens.to(dev),
+                                      cos.to(dev), sin.to(dev))
+        torch.cuda.synchronize()
+        err = max(err, float(np.abs(out4.float().cpu().numpy() - full2[:, 0]).max() / np.abs(full2).max()))
+        assert torch.equal(out4.view(torch.int16), out2.view(torch.int16)) or err <= 1e-2
         # (4) prefill broadcast with the sample rows sharded over the ranks: the prompt cache of rank 0
         # is broadcast once, every rank fills its own rows from its local copy (kernel (c))
         from nanochat_b200.dist import shard_rows, sharded_prefill

@@ -5,13 +5,16 @@ server that gave every free byte to the KV cache at start-up, or host code that 
 touch an allocator on its hot path.  For them the library carries its own scratch (a fixed device
 array) and this entry point uses it.  The test calls it through the C ABI exactly as such a caller
 would, twice in a row on the same shapes with different data, and checks each result against the
-regular entry point (which is given a workspace), to the tolerance the attention tests use.
-The file is named so that pytest collects it last.
+regular entry point (which is given a workspace) and against the numpy oracle, to the tolerance the
+attention tests use.  The file is named so that pytest collects it last.
 """
 import ctypes
 
+import numpy as np
 import pytest
 import torch
+
+from oracle import kv_oracle as O
 
 pytestmark = pytest.mark.gpu
 ATOL = RTOL = 1e-2  # the attention tolerance of tests/test_kernels_gpu.py
@@ -52,6 +55,9 @@ def test_static_scratch_entry_point_matches_regular_one(Hq, Hkv, window):
         assert not torch.isnan(got.float()).any(), f"call {call_no}: output rows were left unwritten"
         assert torch.allclose(got.float(), expect.float(), atol=ATOL, rtol=RTOL), \
             f"call {call_no}: max diff {(got.float() - expect.float()).abs().max().item()}"
+        ref, _ = O.attention_kvcache(q.float().cpu().numpy()[:, None], kc.float().cpu().numpy(), vc.float().cpu().numpy(),
+                                     seqlens.cpu().numpy(), window_left=window)
+        assert np.allclose(got.float().cpu().numpy(), ref[:, 0], atol=ATOL, rtol=RTOL), f"call {call_no}: differs from the oracle"
 
 
 def test_static_scratch_entry_point_rejects_oversized_shapes():
