@@ -50,7 +50,14 @@ namespace nckv {
 constexpr int DEC_TILE = NCKV_DEC_TILE;      // keys per tile (multiple of 16)
 constexpr int DEC_STAGES = NCKV_DEC_STAGES;  // tiles in flight per warp
 constexpr int DEC_WARPS = NCKV_DEC_WARPS;    // warps (independent streams) per CTA
-constexpr int DEC_MAX_B = 1024; // rows per launch (bounds the shared-memory row tables)
+#ifndef NCKV_DEC_CTAS_PER_SM
+#define NCKV_DEC_CTAS_PER_SM 1
+#endif
+constexpr int DEC_CTAS_PER_SM = NCKV_DEC_CTAS_PER_SM;  // CTAs of the persistent grid per SM
+#ifndef NCKV_DEC_MAX_B
+#define NCKV_DEC_MAX_B 1024
+#endif
+constexpr int DEC_MAX_B = NCKV_DEC_MAX_B; // rows per launch (bounds the shared-memory row tables)
 constexpr int DEC_HALF_BYTES = DEC_TILE * 128;        // one 64-channel half of a K or V tile
 constexpr int DEC_STAGE_BYTES = 4 * DEC_HALF_BYTES;   // K lo, K hi, V lo, V hi
 constexpr int DEC_STATUS_BYTES = 256;                 // status word, then the ticket counter at +16
@@ -65,7 +72,7 @@ constexpr int DEC_DYN_PER_WARP = 4;                   // at most this many dynam
 constexpr int DEC_STATIC_NUM = NCKV_DEC_STATIC_NUM, DEC_STATIC_DEN = 10; // statically assigned fraction of a slice
 constexpr int DEC_MIN_RUN = NCKV_DEC_MIN_RUN;  // tiles in the smallest dynamic run
 #ifndef NCKV_DEC_PREFETCH
-#define NCKV_DEC_PREFETCH 4
+#define NCKV_DEC_PREFETCH 2
 #endif
 constexpr int DEC_PREFETCH = NCKV_DEC_PREFETCH;  // tiles of the static run a warp asks L2 for before it may start
 constexpr int MERGE_WARPS = 8;
@@ -257,7 +264,7 @@ __device__ __forceinline__ void build_row_tables(const DecodeParams &p, int *s_s
 // GHI: group size 9..16 (rows 8..15 of the MMA tile carry heads too).  MAP5: the tensor maps are the
 // 5-D form (one copy per K or V tile) instead of the 4-D form (one copy per 64-channel half).
 template <bool GHI, bool MAP5>
-__global__ void __launch_bounds__(DEC_WARPS * 32, 1)
+__global__ void __launch_bounds__(DEC_WARPS * 32, DEC_CTAS_PER_SM)
 decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
                    const __grid_constant__ CUtensorMap tmap_v, const DecodeParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -877,7 +884,7 @@ static size_t decode_smem_bytes() {
 // One partial record: [G][128] fp32 O, then m[G] and l[G], padded so records stay 16-byte aligned.
 static int rec_floats_for(int G) { return G * NCKV_D + ((2 * G + 3) & ~3); }
 static size_t ws_partial_bytes(int G) {
-    const size_t runs = (size_t)(1 + DEC_DYN_PER_WARP) * sm_count() * DEC_WARPS + 2;
+    const size_t runs = (size_t)(1 + DEC_DYN_PER_WARP) * sm_count() * DEC_CTAS_PER_SM * DEC_WARPS + 2;
     return 2 * runs * (size_t)rec_floats_for(G) * sizeof(float);
 }
 
@@ -982,7 +989,7 @@ static int decode_launch(const void *q, const void *k_cache, const void *v_cache
         if (rc != NCKV_OK) return rc;
     }
 
-    const int grid = sm_count();
+    const int grid = sm_count() * DEC_CTAS_PER_SM;
     uint8_t *ws = static_cast<uint8_t *>(workspace);
     DecodeParams p;
     p.q = static_cast<const __nv_bfloat16 *>(q);

@@ -16,6 +16,15 @@ def pytest_configure(config):
         _build.build()
     except Exception as e:  # the import of the package then fails loudly in the tests that need it
         print(f"[conftest] could not build libnckv.so: {e}", file=sys.stderr)
+    # where the reference is mounted, (re)stage the checker's copy of its modules (oracle/_ref)
+    try:
+        import __graft_entry__ as entry
+        ref = entry.reference_checkout()
+        if ref is not None:
+            from oracle import make_ref
+            make_ref.stage(ref)
+    except Exception as e:
+        print(f"[conftest] could not stage oracle/_ref: {e}", file=sys.stderr)
 
 
 def pytest_collection_modifyitems(config, items):
