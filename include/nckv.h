@@ -297,6 +297,30 @@ NCKV_API int nckv_prefill_attn(const void *q, const void *k, const void *v, cons
                       int64_t kv_batch_stride, int64_t kv_token_stride, int window_left,
                       int32_t *status, void *stream);
 
+/*
+ * Decode-time glue of the transformer trunk around the KV branch: the elementwise ops between the
+ * matrix products of GPT.forward / Block.forward for one new token per row, fused per layer.  Each
+ * kernel rounds to bf16 exactly where the eager op sequence does, so results are bit-identical to it.
+ *
+ * nckv_glue_mix_norm, one launch for (rows, C) bf16 row vectors:
+ *     a = x                          or, with add != NULL,  a = bf16(x + add)      residual add, gpt.py:148-150
+ *     mode 0:  y = a
+ *     mode 1:  y = bf16(bf16(resid_lambda * a) + bf16(x0_lambda * x0))             gpt.py:457
+ *     mode 2:  y = bf16(a - bf16(backout_lambda * x_backout))                      gpt.py:466-467
+ *     out_norm = bf16(y * rsqrt(mean(y^2) + eps))   (norm, gpt.py:42-43)           gpt.py:149-150, 468
+ * out_sum (optional, needs add) receives a, out_x (optional) receives y, out_norm (optional) the
+ * normalised row; the fp32 sum of squares is accumulated in the order of torch's row kernel.
+ * nckv_glue_relu_sq: out = bf16(max(h, 0)^2) over n elements (n % 8 == 0), MLP.forward gpt.py:136.
+ * nckv_glue_ve_gate: v_out = bf16(v + bf16(bf16(3 * bf16(sigmoid(gate_lin))) * ve)) with v, ve (rows, Hkv, D)
+ * and gate_lin (rows, Hkv) the output of the gate's linear layer: the value residual of gpt.py:92-95.
+ */
+NCKV_API int nckv_glue_mix_norm(const void *x, const void *add, const void *x0, const void *x_backout, void *out_sum,
+                       void *out_x, void *out_norm, int rows, int C, int mode, float resid_lambda, float x0_lambda,
+                       float backout_lambda, float eps, void *stream);
+NCKV_API int nckv_glue_relu_sq(const void *h, void *out, int64_t n, void *stream);
+NCKV_API int nckv_glue_ve_gate(const void *v, const void *gate_lin, const void *ve, void *v_out, int rows, int Hkv, int D,
+                      void *stream);
+
 #ifdef __cplusplus
 }
 #endif

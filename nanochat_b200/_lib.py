@@ -44,6 +44,9 @@ SIGNATURES = {
     "nckv_p2p_push": (c_int, [c_void_p, c_int, c_int, ctypes.POINTER(c_void_p), c_int, c_int, c_void_p, c_void_p]),
     "nckv_p2p_wait_combine": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                       ctypes.c_uint64, c_void_p]),
+    "nckv_glue_mix_norm": (c_int, [c_void_p] * 7 + [c_int] * 3 + [c_float] * 4 + [c_void_p]),
+    "nckv_glue_relu_sq": (c_int, [c_void_p, c_void_p, c_i64, c_void_p]),
+    "nckv_glue_ve_gate": (c_int, [c_void_p] * 4 + [c_int] * 3 + [c_void_p]),
     "nckv_prefill_broadcast": (c_int, [c_void_p] * 5 + [c_int] * 7 + [c_void_p]),
     "nckv_prefill_attn": (c_int, [c_void_p] * 5 + [c_int] * 6 + [c_i64, c_i64, c_int, c_void_p, c_void_p]),
 }

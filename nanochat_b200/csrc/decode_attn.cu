@@ -3,17 +3,18 @@
 // Work decomposition.  Keys of row b are cut into tiles of DEC_TILE tokens starting at the first
 // visible key; the tiles of all (row, kv-head) pairs form one flat sequence (row outer, head
 // middle, tile inner) of `total` tiles.  The sequence is handed out as RUNS of consecutive tiles:
-//   * the sequence is cut into one equal slice per warp of the persistent grid (one CTA per SM,
-//     DEC_WARPS warps each); the first 70% of a slice is that warp's static run, so a warp starts
-//     without any global traffic;
-//   * the last 30% of every slice is cut into small runs that warps claim from an atomic ticket counter (drawn one
+//   * the sequence is cut into one equal slice per warp of the persistent grid (DEC_CTAS_PER_SM CTAs
+//     per SM, DEC_WARPS warps each); the first 60% of a slice is that warp's static run, so a warp
+//     starts without any global traffic;
+//   * the last 40% of every slice is cut into small runs that warps claim from an atomic ticket counter (drawn one
 //     run ahead, so the round trip is hidden) when they finish what they have.  SMs do not all
 //     see the same HBM bandwidth (two dies, distance to the stacks); the dynamic part lets the
 //     fast ones absorb the difference.
 // A warp is a self-contained stream processor: lane 0 issues TMA tile loads (K and V, 128-byte
 // swizzle, L2 evict-first) into the warp's private ring of DEC_STAGES shared-memory stages (48 keys x
-// 512 B = 24 KB each; 4 warps x 2 stages = 192 KB in flight per SM; measured best of the
-// tile/stage/warp splits of that budget on B200),
+// 512 B = 24 KB each; 2 CTAs x 2 warps x 2 stages = 192 KB in flight per SM; measured best of the
+// tile/stage/warp splits of that budget on B200.  Two small CTAs per SM instead of one large one let
+// the next launch's CTAs move in, and start their first loads, as soon as half an SM is done),
 // completion is signalled on the warp's own mbarriers, and the loads run ahead across pair and
 // run boundaries.  There is no CTA-wide synchronisation after set-up and no fence or wait on
 // another warp anywhere in the stream.
@@ -45,13 +46,13 @@ namespace nckv {
 #define NCKV_DEC_STAGES 2
 #endif
 #ifndef NCKV_DEC_WARPS
-#define NCKV_DEC_WARPS 4
+#define NCKV_DEC_WARPS 2
 #endif
 constexpr int DEC_TILE = NCKV_DEC_TILE;      // keys per tile (multiple of 16)
 constexpr int DEC_STAGES = NCKV_DEC_STAGES;  // tiles in flight per warp
 constexpr int DEC_WARPS = NCKV_DEC_WARPS;    // warps (independent streams) per CTA
 #ifndef NCKV_DEC_CTAS_PER_SM
-#define NCKV_DEC_CTAS_PER_SM 1
+#define NCKV_DEC_CTAS_PER_SM 2
 #endif
 constexpr int DEC_CTAS_PER_SM = NCKV_DEC_CTAS_PER_SM;  // CTAs of the persistent grid per SM
 #ifndef NCKV_DEC_MAX_B
@@ -64,7 +65,7 @@ constexpr int DEC_STATUS_BYTES = 256;                 // status word, then the t
 constexpr int DEC_RING = 4;                           // runs a warp may have claimed but not finished
 constexpr int DEC_DYN_PER_WARP = 4;                   // at most this many dynamic runs per warp of the grid
 #ifndef NCKV_DEC_STATIC_NUM
-#define NCKV_DEC_STATIC_NUM 7
+#define NCKV_DEC_STATIC_NUM 6
 #endif
 #ifndef NCKV_DEC_MIN_RUN
 #define NCKV_DEC_MIN_RUN 2
@@ -141,7 +142,7 @@ __device__ __forceinline__ TileCursor locate_tile(const int *s_pref, int B, int 
 // How the flat tile sequence [0, total) is cut into runs.  A pure function of (total, W), so the
 // streaming kernel and the merge kernel agree on it.
 //   slice w (w < W) = q + (w < r) consecutive tiles, q = total / W, r = total % W
-//   static run w    = the first 70% of slice w (all of it when the slice is shorter than 4 tiles)
+//   static run w    = the first 60% of slice w (all of it when the slice is shorter than 4 tiles)
 //   dynamic runs    = the rest of each slice in chunks of CH tiles, numbered in tile order
 // Interleaving static and dynamic stretches keeps the number of runs that touch any one
 // (row, head) pair small, which bounds the work of the merge.
@@ -205,6 +206,11 @@ struct RunGeometry {
         return W + (w < r ? w * d_big : r * d_big + (w - r) * d_small) + c;
     }
 };
+
+// Entries per shared-memory row table of a launch with B rows (B + 1 are used; a multiple of 32 keeps
+// the tables aligned).  Sizing them by the launch instead of by DEC_MAX_B keeps room on the SM for the
+// merge grid to be resident beside the streaming CTAs at ordinary batch sizes.
+__host__ __device__ inline int table_rows(int B) { return (B + 1 + 31) & ~31; }
 
 // Per-row visible key range [s_start, s_end) and the exclusive prefix sum of tiles per row
 // (s_pref, B + 1 entries), computed by a whole CTA.  Ends with a __syncthreads().
@@ -274,9 +280,9 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
     uint8_t *stages = smem;  // [DEC_WARPS][DEC_STAGES][DEC_STAGE_BYTES]
     uint64_t *full_bar = reinterpret_cast<uint64_t *>(stages + DEC_WARPS * DEC_STAGES * DEC_STAGE_BYTES);
     RunEntry *rings = reinterpret_cast<RunEntry *>(full_bar + DEC_WARPS * DEC_STAGES);  // [DEC_WARPS][DEC_RING]
-    int *s_start = reinterpret_cast<int *>(rings + DEC_WARPS * DEC_RING);
-    int *s_end = s_start + DEC_MAX_B;
-    int *s_pref = s_end + DEC_MAX_B;  // B + 1 entries
+    int *s_start = reinterpret_cast<int *>(rings + DEC_WARPS * DEC_RING);  // three tables of table_rows(B) entries
+    int *s_end = s_start + table_rows(p.B);
+    int *s_pref = s_end + table_rows(p.B);  // B + 1 entries
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -697,7 +703,8 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
 // The row tables of a launch, copied out for inspection.
 __global__ void __launch_bounds__(128) decode_key_ranges_kernel(const DecodeParams p, int32_t *key_begin,
                                                                 int32_t *key_end) {
-    __shared__ int s_start[DEC_MAX_B], s_end[DEC_MAX_B], s_pref[DEC_MAX_B + 1];
+    extern __shared__ int s_tables[];
+    int *s_start = s_tables, *s_end = s_start + table_rows(p.B), *s_pref = s_end + table_rows(p.B);
     build_row_tables(p, s_start, s_end, s_pref, true);
     for (int b = threadIdx.x; b < p.B; b += blockDim.x) {
         key_begin[b] = s_start[b];
@@ -724,7 +731,8 @@ struct PushDesc {
 // streaming kernel is still running; after the wait only loads, a few shuffles and the store remain.
 __global__ void __launch_bounds__(MERGE_WARPS * 32) decode_merge_kernel(const DecodeParams p,
                                                                         const __grid_constant__ PushDesc pd) {
-    __shared__ int s_start[DEC_MAX_B], s_end[DEC_MAX_B], s_pref[DEC_MAX_B + 1];
+    extern __shared__ int s_tables[];
+    int *s_start = s_tables, *s_end = s_start + table_rows(p.B), *s_pref = s_end + table_rows(p.B);
     const int lane = threadIdx.x & 31;
     const int B = p.B, Hkv = p.Hkv, G = p.G;
     pdl_launch_dependents();  // whatever follows in the stream may be scheduled behind this grid
@@ -874,9 +882,10 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) decode_merge_kernel(const De
     }
 }
 
-static size_t decode_smem_bytes() {
+static size_t table_smem_bytes(int B) { return 3 * (size_t)table_rows(B) * sizeof(int); }
+static size_t decode_smem_bytes(int B) {
     return 1024 + (size_t)DEC_WARPS * DEC_STAGES * DEC_STAGE_BYTES + DEC_WARPS * DEC_STAGES * sizeof(uint64_t) +
-           DEC_WARPS * DEC_RING * sizeof(RunEntry) + (3 * DEC_MAX_B + 4) * sizeof(int);
+           DEC_WARPS * DEC_RING * sizeof(RunEntry) + table_smem_bytes(B);
 }
 
 // Workspace layout: [0,256) status word and ticket counter; then the partial records, two per run,
@@ -1010,16 +1019,16 @@ static int decode_launch(const void *q, const void *k_cache, const void *v_cache
     p.W = grid * DEC_WARPS;
     p.scale_log2 = (float)(1.4426950408889634 / sqrt((double)D));
 
-    const size_t smem = decode_smem_bytes();
+    const size_t smem = decode_smem_bytes(B), smem_max = decode_smem_bytes(DEC_MAX_B);
     static bool attr_set[64] = {false};  // per device; setting the attribute twice from racing threads is harmless
     int dev = 0;
     NCKV_CUDA_CHECK(cudaGetDevice(&dev));
     const bool ghi = G > 8;
     if (dev < 64 && !attr_set[dev]) {
-        NCKV_CUDA_CHECK(cudaFuncSetAttribute(decode_attn_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        NCKV_CUDA_CHECK(cudaFuncSetAttribute(decode_attn_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        NCKV_CUDA_CHECK(cudaFuncSetAttribute(decode_attn_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        NCKV_CUDA_CHECK(cudaFuncSetAttribute(decode_attn_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        NCKV_CUDA_CHECK(cudaFuncSetAttribute(decode_attn_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max));
+        NCKV_CUDA_CHECK(cudaFuncSetAttribute(decode_attn_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max));
+        NCKV_CUDA_CHECK(cudaFuncSetAttribute(decode_attn_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max));
+        NCKV_CUDA_CHECK(cudaFuncSetAttribute(decode_attn_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max));
         attr_set[dev] = true;
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -1035,7 +1044,7 @@ static int decode_launch(const void *q, const void *k_cache, const void *v_cache
     if (merge_grid > 4 * grid) merge_grid = 4 * grid;
     PushDesc pd = push;
     pd.done = reinterpret_cast<unsigned *>(ws + 32);
-    NCKV_CUDA_CHECK(launch_pdl(decode_merge_kernel, dim3(merge_grid), dim3(MERGE_WARPS * 32), 0, s, true, p, pd));
+    NCKV_CUDA_CHECK(launch_pdl(decode_merge_kernel, dim3(merge_grid), dim3(MERGE_WARPS * 32), table_smem_bytes(B), s, true, p, pd));
     return NCKV_OK;
 }
 
@@ -1126,7 +1135,7 @@ extern "C" int nckv_decode_key_ranges(const int32_t *cache_seqlens, int B, int T
     p.window_left = window_left;
     p.kv_begin = kv_begin;
     p.kv_end = kv_end;
-    decode_key_ranges_kernel<<<1, 128, 0, static_cast<cudaStream_t>(stream)>>>(p, key_begin, key_end);
+    decode_key_ranges_kernel<<<1, 128, table_smem_bytes(B), static_cast<cudaStream_t>(stream)>>>(p, key_begin, key_end);
     NCKV_CUDA_CHECK(cudaGetLastError());
     return NCKV_OK;
 }

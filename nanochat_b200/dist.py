@@ -118,8 +118,10 @@ class KVSplitAttention:
         import torch.distributed as dist
         self.dist = dist
         self.group = group
-        self.rank = dist.get_rank(group)
-        self.world = dist.get_world_size(group)
+        # without a process group this is the single-rank case (same kernels, no exchange)
+        alone = not (dist.is_available() and dist.is_initialized())
+        self.rank = 0 if alone else dist.get_rank(group)
+        self.world = 1 if alone else dist.get_world_size(group)
         self.capacity = capacity
         self.window_left = window_left
         if block and window_left >= 0:

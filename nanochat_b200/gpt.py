@@ -194,6 +194,11 @@ class GPT(nn.Module):
         kv_dim = config.n_kv_head * head_dim
         self.value_embeds = nn.ModuleDict({str(i): nn.Embedding(padded, kv_dim) for i in range(config.n_layer)
                                            if layer_has_value_embedding(i, config.n_layer)})
+        # Decode steps (one new token per row, CUDA, bf16) run the elementwise glue between the matrix
+        # products through the fused kernels of libnckv (bit-identical to the eager ops); set False to
+        # run the eager op sequence everywhere.
+        self.fused_glue = True
+        self._lambda_cache = None
         self.rotary_seq_len = config.sequence_len * 10  # same over-allocation as gpt.py:195
         self.register_buffer("cos", torch.empty(0), persistent=False)
         self.register_buffer("sin", torch.empty(0), persistent=False)
@@ -277,6 +282,8 @@ class GPT(nn.Module):
         backout_at = self.config.n_layer // 2
         x_backout = None
         rope_tables = (self.cos, self.sin)
+        if self.fused_glue and T == 1 and kv_cache is not None and x.is_cuda and x.dtype == torch.bfloat16:
+            return self._decode_trunk_fused(idx, x, kv_cache, rope_tables)
         for i, block in enumerate(self.transformer.h):
             x = self.resid_lambdas[i] * x + self.x0_lambdas[i] * x0
             ve = self.value_embeds[str(i)](idx).to(x.dtype) if str(i) in self.value_embeds else None
@@ -287,6 +294,55 @@ class GPT(nn.Module):
             x = x - self.backout_lambda.to(x.dtype) * x_backout
         x = rms(x)
         logits = self.lm_head(x)[..., :self.config.vocab_size].float()
+        return 15 * torch.tanh(logits / 15)
+
+    def _lambdas(self):
+        """Host copies of the per-layer scalars, read once (a device read per step would synchronise).
+        resid/x0 lambdas multiply as 0-dim tensors, i.e. with their stored value; the backout lambda is
+        cast to the activation dtype first (gpt.py:467), so it is rounded to bf16 here."""
+        key = (self.resid_lambdas.data_ptr(), self.resid_lambdas._version, self.x0_lambdas._version,
+               self.backout_lambda._version, self.resid_lambdas.dtype)
+        if self._lambda_cache is None or self._lambda_cache[0] != key:
+            self._lambda_cache = (key, self.resid_lambdas.detach().float().tolist(), self.x0_lambdas.detach().float().tolist(),
+                                  float(self.backout_lambda.detach().to(torch.bfloat16).float().item()))
+        return self._lambda_cache[1:]
+
+    def _decode_trunk_fused(self, idx, x, kv_cache, rope_tables):
+        """The layer loop of ``forward`` for one new token per row with the elementwise glue fused:
+        per layer one launch for [previous MLP residual add + lambda mix + norm], one for [attention
+        residual add + norm], one for relu^2 (and one for the value-embedding gate where a layer has
+        one), instead of about a dozen eager launches.  Same matrix products, same roundings."""
+        B = idx.size(0)
+        C = x.size(-1)
+        resid, x0l, backout = self._lambdas()
+        n_layer = self.config.n_layer
+        backout_at = n_layer // 2
+        x = x.contiguous()
+        x0 = x
+        pending = None      # MLP output of the previous layer, not yet added to the residual stream
+        x_backout = None
+        for i, block in enumerate(self.transformer.h):
+            # the residual stream after layer backout_at is needed later: keep the sum when the add happens
+            x_sum, x, xn = ops.glue_mix_norm(x, add=pending, x0=x0, resid_lambda=resid[i], x0_lambda=x0l[i],
+                                             want_sum=(i == backout_at + 1))
+            if i == backout_at + 1:
+                x_backout = x_sum
+            attn = block.attn
+            q = attn.c_q(xn).view(B, 1, attn.n_head, attn.head_dim)
+            k = attn.c_k(xn).view(B, 1, attn.n_kv_head, attn.head_dim)
+            v = attn.c_v(xn).view(B, 1, attn.n_kv_head, attn.head_dim)
+            if str(i) in self.value_embeds:
+                ve = self.value_embeds[str(i)](idx).to(x.dtype)
+                v = ops.glue_ve_gate(v, attn.ve_gate(xn[..., :attn.ve_gate_channels]), ve)
+            y = kv_attention(q, k, v, rope_tables, self.window_sizes[i], kv_cache, i)
+            _, x, xn = ops.glue_mix_norm(x, add=attn.c_proj(y.view(B, 1, C)))
+            pending = block.mlp.c_proj(ops.glue_relu_sq(block.mlp.c_fc(xn)))
+        if backout_at == n_layer - 1:  # only a one-layer model: the backout operand is the final sum itself
+            x_backout, _, _ = ops.glue_mix_norm(x, add=pending, want_sum=True, want_x=False, want_norm=False)
+            _, _, xn = ops.glue_mix_norm(x_backout, x_backout=x_backout, backout_lambda=backout, want_x=False)
+        else:
+            _, _, xn = ops.glue_mix_norm(x, add=pending, x_backout=x_backout, backout_lambda=backout, want_x=False)
+        logits = self.lm_head(xn)[..., :self.config.vocab_size].float()
         return 15 * torch.tanh(logits / 15)
 
     @torch.inference_mode()

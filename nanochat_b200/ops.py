@@ -478,6 +478,69 @@ def lse_combine(parts_o, parts_lse):
     return _lse_combine(parts_o, parts_lse)
 
 
+# ------------------------------------------------------------------------------------------------
+# decode-time glue of the trunk (bit-exact fusions of the eager elementwise ops)
+# ------------------------------------------------------------------------------------------------
+def _rows(name, t, C):
+    if not t.is_cuda or t.dtype != torch.bfloat16 or t.size(-1) != C or not t.is_contiguous():
+        raise RuntimeError(f"nckv::{name} needs contiguous CUDA bfloat16 rows of {C} channels, got {tuple(t.shape)} "
+                           f"{t.dtype} on {t.device}")
+    return t.data_ptr()
+
+
+def glue_mix_norm(x, add=None, x0=None, x_backout=None, resid_lambda=1.0, x0_lambda=0.0, backout_lambda=0.0,
+                  want_sum=False, want_x=True, want_norm=True, eps=RMS_EPS):
+    """One launch for the elementwise ops between two matrix products of the trunk, on (..., C) rows:
+    ``a = x (+ add)``; then ``resid_lambda * a + x0_lambda * x0`` (when ``x0`` is given) or
+    ``a - backout_lambda * x_backout`` (when ``x_backout`` is given); then rms-norm.  Every step
+    rounds to bf16 like the eager op it stands for.  Returns (a or None, y or None, norm or None)."""
+    name = "glue_mix_norm"
+    C = x.size(-1)
+    px = _rows(name, x, C)
+    rows = x.numel() // C
+    mode = 1 if x0 is not None else (2 if x_backout is not None else 0)
+    out_sum = torch.empty_like(x) if (want_sum and add is not None) else None
+    out_x = torch.empty_like(x) if want_x else None
+    out_norm = torch.empty_like(x) if want_norm else None
+    idx = x.device.index
+    with _device_guard(idx):
+        _lib.call("nckv_glue_mix_norm", px, _rows(name, add, C) if add is not None else None,
+                  _rows(name, x0, C) if x0 is not None else None,
+                  _rows(name, x_backout, C) if x_backout is not None else None,
+                  _ptr(out_sum), _ptr(out_x), _ptr(out_norm), rows, C, mode, float(resid_lambda), float(x0_lambda),
+                  float(backout_lambda), float(eps), torch.cuda.current_stream(idx).cuda_stream)
+    return out_sum, out_x, out_norm
+
+
+def glue_relu_sq(h):
+    """relu(h)^2 in one launch (MLP.forward, gpt.py:136), bf16 rounding after each of the two eager ops."""
+    if not h.is_cuda or h.dtype != torch.bfloat16 or not h.is_contiguous():
+        raise RuntimeError("nckv::glue_relu_sq needs a contiguous CUDA bfloat16 tensor")
+    out = torch.empty_like(h)
+    idx = h.device.index
+    with _device_guard(idx):
+        _lib.call("nckv_glue_relu_sq", h.data_ptr(), out.data_ptr(), h.numel(), torch.cuda.current_stream(idx).cuda_stream)
+    return out
+
+
+def glue_ve_gate(v, gate_lin, ve):
+    """v + 3 * sigmoid(gate_lin)[..., None] * ve in one launch (gpt.py:92-95); v, ve: (..., Hkv, 128),
+    gate_lin: (..., Hkv) — the output of the gate's linear layer."""
+    for t in (v, gate_lin, ve):
+        if not t.is_cuda or t.dtype != torch.bfloat16 or not t.is_contiguous():
+            raise RuntimeError("nckv::glue_ve_gate needs contiguous CUDA bfloat16 tensors")
+    Hkv, Dh = v.size(-2), v.size(-1)
+    rows = v.numel() // (Hkv * Dh)
+    if gate_lin.numel() != rows * Hkv or ve.numel() != v.numel():
+        raise RuntimeError(f"nckv::glue_ve_gate: shapes {tuple(v.shape)} / {tuple(gate_lin.shape)} / {tuple(ve.shape)} do not match")
+    out = torch.empty_like(v)
+    idx = v.device.index
+    with _device_guard(idx):
+        _lib.call("nckv_glue_ve_gate", v.data_ptr(), gate_lin.data_ptr(), ve.data_ptr(), out.data_ptr(), rows, Hkv, Dh,
+                  torch.cuda.current_stream(idx).cuda_stream)
+    return out
+
+
 class HostDecodeStep:
     """A decode step of one layer for activations that live in host memory.
 
