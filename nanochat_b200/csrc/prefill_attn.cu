@@ -54,6 +54,7 @@ struct PrefillParams {
     __nv_bfloat16 *out;
     int32_t *status;
     int B, T_new, Hq, Hkv, T_k;
+    int group_pairs;  // (row, q head) pairs per scheduling group, see the work order in the kernel
     int window_left;
     float scale_log2;
 };
@@ -224,9 +225,20 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     (void)s_xchg;
 
     const int tid = threadIdx.x, warp = tid >> 5;
+    // Work order.  CTAs are handed to the SMs in block-index order, which makes the grid a work queue.
+    // Causal query tiles differ in length by up to n_qtiles x, so the order decides the tail: the
+    // (row, q head) pairs are taken in groups of group_pairs (sized on the host so that a group's K/V
+    // stays in L2 while its query tiles reuse it); inside a group all pairs' longest tiles come first,
+    // their shortest last, with the pairs (and so the q heads that share a kv head) adjacent.
     const int n_qtiles = (p.T_new + PF_M - 1) / PF_M;
-    const int qt = n_qtiles - 1 - (int)blockIdx.x;  // long tiles first
-    const int hq = blockIdx.y, b = blockIdx.z;
+    const int n_pairs = p.Hq * p.B;
+    const int per_group = p.group_pairs * n_qtiles;
+    const int grp = (int)blockIdx.x / per_group;
+    const int in_grp = (int)blockIdx.x - grp * per_group;
+    const int grp_pairs = min(p.group_pairs, n_pairs - grp * p.group_pairs);
+    const int qt = n_qtiles - 1 - in_grp / grp_pairs;  // long tiles first
+    const int pair = grp * p.group_pairs + in_grp % grp_pairs;
+    const int hq = pair % p.Hq, b = pair / p.Hq;
     const int hkv = hq / (p.Hq / p.Hkv);
     const int t0 = qt * PF_M;
 
@@ -613,8 +625,9 @@ extern "C" int nckv_prefill_attn(const void *q, const void *k, const void *v, co
         set_error("prefill_attn: T_new=%d exceeds the key capacity T_k=%d", T_new, T_k);
         return NCKV_E_CAPACITY;
     }
-    if (B > 65535 || Hq > 65535) {
-        set_error("prefill_attn: B=%d / Hq=%d exceed the grid limits", B, Hq);
+    const int n_qtiles = (T_new + PF_M - 1) / PF_M;
+    if ((long long)n_qtiles * Hq * B > 0x7fffffffLL) {
+        set_error("prefill_attn: B=%d x Hq=%d x %d query tiles exceed the grid limit", B, Hq, n_qtiles);
         return NCKV_E_UNSUPPORTED;
     }
     if (((uintptr_t)q | (uintptr_t)out) & 15) {
@@ -636,6 +649,15 @@ extern "C" int nckv_prefill_attn(const void *q, const void *k, const void *v, co
     p.B = B; p.T_new = T_new; p.Hq = Hq; p.Hkv = Hkv; p.T_k = T_k;
     p.window_left = window_left;
     p.scale_log2 = (float)(1.4426950408889634 / sqrt((double)D));
+    {
+        // pairs per group: about 48 MB of K and V rows (512 B per key and kv head, shared by Hq / Hkv
+        // q heads) leaves room in the 126 MB L2 for two groups in flight and everything else
+        const long long keys = window_left >= 0 && window_left + PF_M < T_k ? window_left + PF_M : T_k;
+        const long long bytes_per_pair = keys * 512 / (Hq / Hkv) + 1;
+        long long g = (48LL << 20) / bytes_per_pair;
+        g -= g % (Hq / Hkv);  // keep the q heads of a kv head in one group
+        p.group_pairs = (int)(g < Hq / Hkv ? Hq / Hkv : (g > (long long)Hq * B ? (long long)Hq * B : g));
+    }
 
     const size_t smem = prefill_smem_bytes();
     static bool attr_set[64] = {false};
@@ -645,9 +667,8 @@ extern "C" int nckv_prefill_attn(const void *q, const void *k, const void *v, co
         NCKV_CUDA_CHECK(cudaFuncSetAttribute(prefill_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attr_set[dev] = true;
     }
-    const int n_qtiles = (T_new + PF_M - 1) / PF_M;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(n_qtiles, Hq, B);
+    cfg.gridDim = dim3((unsigned)(n_qtiles * Hq * B));
     cfg.blockDim = dim3(PF_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = static_cast<cudaStream_t>(stream);

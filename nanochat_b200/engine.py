@@ -174,8 +174,43 @@ class Engine:
         rows = [RowState(tokens.copy()) for _ in range(num_samples)]
         produced = 0
         graphed = None
+        on_gpu = device.type == "cuda"
+        staged = torch.empty(num_samples, dtype=torch.long, pin_memory=True) if on_gpu else None
+        arrived = torch.cuda.Event() if on_gpu else None
+
+        def run_step(ids, n_done):
+            """One forward of the new tokens ids (B, 1) on the device, the n_done-th generated column;
+            returns the logits (B, vocab)."""
+            nonlocal graphed
+            if graphed is None and self.cuda_graph and on_gpu and n_done >= 2:
+                # capture runs three throw-away steps behind the current position: needs that room,
+                # and only pays off if enough steps are still to come
+                room = capacity - (len(tokens) + n_done)
+                left = (max_tokens - n_done) if max_tokens is not None else room
+                if room >= 4 and left >= 16 and cache.prev_embedding is not None:
+                    graphed = GraphedDecodeStep(self.model, cache, ids)
+            if graphed is not None:
+                return graphed.step(ids)
+            return self.model.forward(ids, kv_cache=cache)[:, -1, :]
+
         while (max_tokens is None or produced < max_tokens) and not all(r.completed for r in rows):
-            sampled = sample_next_token(logits, rng, temperature, top_k)[:, 0].tolist()
+            drawn_dev = sample_next_token(logits, rng, temperature, top_k)  # (B, 1), stays on the device
+            # Unless a row has tool output waiting to be injected, the tokens the model sees next are
+            # exactly the ones just drawn: the next forward is enqueued straight from the device tensor,
+            # before the host has looked at them, and the host-side bookkeeping below (token lists, the
+            # tool-use state machine, the caller's work between yields) overlaps with it.  The reference
+            # reads the tokens first (engine.py:240) and only then launches; the tokens are the same.
+            ahead = not any(r.forced_tokens for r in rows)
+            if on_gpu:
+                staged.copy_(drawn_dev[:, 0], non_blocking=True)
+                arrived.record()
+            if ahead:
+                logits = run_step(drawn_dev, produced + 1)
+            if on_gpu:
+                arrived.synchronize()
+                sampled = staged.tolist()
+            else:
+                sampled = drawn_dev[:, 0].tolist()
             column, masks = [], []
             for row, drawn in zip(rows, sampled):
                 forced = len(row.forced_tokens) > 0
@@ -200,18 +235,12 @@ class Engine:
                     row.python_expr_tokens.append(tok)
             yield column, masks
             produced += 1
-            ids = torch.tensor(column, dtype=torch.long, device=device).unsqueeze(1)
-            if graphed is None and self.cuda_graph and device.type == "cuda" and produced >= 2:
-                # capture runs three throw-away steps behind the current position: needs that room,
-                # and only pays off if enough steps are still to come
-                room = capacity - (len(tokens) + produced)
-                left = (max_tokens - produced) if max_tokens is not None else room
-                if room >= 4 and left >= 16 and cache.prev_embedding is not None:
-                    graphed = GraphedDecodeStep(self.model, cache, ids)
-            if graphed is not None:
-                logits = graphed.step(ids)
-            else:
-                logits = self.model.forward(ids, kv_cache=cache)[:, -1, :]
+            if not ahead:
+                logits = run_step(torch.tensor(column, dtype=torch.long, device=device).unsqueeze(1), produced)
+            if on_gpu and produced % 64 == 0:
+                ops.check_status(device)  # capacity / RoPE-range overflow raises like the reference's slice-assign
+        if on_gpu:
+            ops.check_status(device)
 
     def generate_batch(self, tokens, num_samples=1, **kwargs):
         """Run ``generate`` to the end; returns (token lists, sampled/forced masks) without the

@@ -297,14 +297,15 @@ class GPT(nn.Module):
         return 15 * torch.tanh(logits / 15)
 
     def _lambdas(self):
-        """Host copies of the per-layer scalars, read once (a device read per step would synchronise).
-        resid/x0 lambdas multiply as 0-dim tensors, i.e. with their stored value; the backout lambda is
-        cast to the activation dtype first (gpt.py:467), so it is rounded to bf16 here."""
+        """Host copies of the per-layer scalars, read once (a device read per step would synchronise),
+        rounded to bf16: the eager multiply converts a 0-dim parameter to the activation dtype before it
+        multiplies (and gpt.py:467 casts the backout lambda explicitly)."""
         key = (self.resid_lambdas.data_ptr(), self.resid_lambdas._version, self.x0_lambdas._version,
                self.backout_lambda._version, self.resid_lambdas.dtype)
         if self._lambda_cache is None or self._lambda_cache[0] != key:
-            self._lambda_cache = (key, self.resid_lambdas.detach().float().tolist(), self.x0_lambdas.detach().float().tolist(),
-                                  float(self.backout_lambda.detach().to(torch.bfloat16).float().item()))
+            as_bf16 = lambda t: t.detach().to(torch.bfloat16).float()
+            self._lambda_cache = (key, as_bf16(self.resid_lambdas).tolist(), as_bf16(self.x0_lambdas).tolist(),
+                                  float(as_bf16(self.backout_lambda).item()))
         return self._lambda_cache[1:]
 
     def _decode_trunk_fused(self, idx, x, kv_cache, rope_tables):

@@ -28,20 +28,22 @@ def test_mix_norm_is_bit_identical_to_the_eager_ops(C, lambda_dtype):
     gen = torch.Generator(device=DEV).manual_seed(C)
     rows = 257
     x, add, x0, xb = (_rand(gen, rows, 1, C, scale=s) for s in (1.0, 0.3, 1.0, 2.0))
-    lam = torch.tensor([1.0826, 0.1337, 0.2], device=DEV).to(lambda_dtype)  # parameters as the model holds them
+    # parameters as the model holds them (fp32 by default, bf16 after model.to(bfloat16)); a 0-dim parameter is
+    # converted to the activation dtype by the eager multiply, so the kernel takes the bf16-rounded value
+    lam = torch.tensor([1.0826, 0.1337, 0.2], device=DEV).to(lambda_dtype)
     rl, xl, bl = lam[0], lam[1], lam[2:3]
     # lambda mix behind a residual add (a layer in the middle of the trunk)
     a = x + add
     y = rl * a + xl * x0
-    got_sum, got_x, got_norm = ops.glue_mix_norm(x, add=add, x0=x0, resid_lambda=float(rl.float()),
-                                                 x0_lambda=float(xl.float()), want_sum=True)
+    got_sum, got_x, got_norm = ops.glue_mix_norm(x, add=add, x0=x0, resid_lambda=float(rl.to(BF).float()),
+                                                 x0_lambda=float(xl.to(BF).float()), want_sum=True)
     assert torch.equal(_bits(got_sum), _bits(a))
     assert torch.equal(_bits(got_x), _bits(y))
     bad = (_bits(got_norm) != _bits(_rms(y))).sum().item()
     assert bad == 0, f"{bad} of {y.numel()} normalised elements differ"
     # first layer: no pending add
     y = rl * x + xl * x0
-    _, got_x, got_norm = ops.glue_mix_norm(x, x0=x0, resid_lambda=float(rl.float()), x0_lambda=float(xl.float()))
+    _, got_x, got_norm = ops.glue_mix_norm(x, x0=x0, resid_lambda=float(rl.to(BF).float()), x0_lambda=float(xl.to(BF).float()))
     assert torch.equal(_bits(got_x), _bits(y)) and torch.equal(_bits(got_norm), _bits(_rms(y)))
     # attention residual + norm
     y = x + add
