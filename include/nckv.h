@@ -45,6 +45,7 @@ extern "C" {
 #define NCKV_ST_OVERFLOW 1u   /* cache_seqlens[b] + T_new > T_max, or position >= rope_len: row skipped */
 #define NCKV_ST_TIMEOUT 2u    /* a bounded wait on a shared-memory barrier ran out */
 #define NCKV_ST_BAD_SEQLEN 4u /* negative cache_seqlens[b] */
+#define NCKV_ST_BAD_PAGE 8u   /* a block-table entry outside the page pool: the tile was read as zeros / the row not written */
 
 /* Library version and the SM architecture the kernels were compiled for ("sm_100a"). */
 NCKV_API int nckv_version(void);
@@ -281,6 +282,37 @@ NCKV_API int nckv_p2p_wait_combine(const void *local_buf, int world, int rows, i
 NCKV_API int nckv_prefill_broadcast(const void *src_k, const void *src_v, void *dst_k, void *dst_v,
                            int32_t *dst_seqlens, int L, int B, int p, int Hkv, int D, int T_src,
                            int T_dst, void *stream);
+
+/*
+ * Paged KV storage (the "next" format after the dense (L, B, T_max, H, D) tensors of engine.py:98-100;
+ * no counterpart in the reference).  One layer's K or V is a pool of pages (n_pages, page_tokens, Hkv,
+ * D) with element strides (page_stride, token_stride, D, 1); block_table is int32 (B, max_pages): token t
+ * of row b lives in page block_table[b][t / page_tokens] at index t % page_tokens.  page_tokens must be a
+ * multiple of nckv_paged_tile_tokens() so that a tile of keys never straddles two pages.  Rows may
+ * share pages they only read (a common prompt).  A table entry outside [0, n_pages) met by a kernel
+ * sets NCKV_ST_BAD_PAGE and is skipped (read as zeros / not written).
+ *   nckv_append_rope_norm_paged   nckv_append_rope_norm with the k/v rows written through the table
+ *   nckv_decode_attn_paged        nckv_decode_attn (all of its semantics except kv_begin/kv_end) reading
+ *                                 through the table
+ *   nckv_paged_fill               KVCache.prefill (engine.py:123-137) into pages: n_jobs jobs of three
+ *                                 int32 (page, first source token, tokens) copy runs of the batch-1 source
+ *                                 cache (L, 1, T_src, Hkv, D) into pages of the pools (L, n_pages,
+ *                                 page_tokens, Hkv, D), K and V in one launch.  With the full prompt pages
+ *                                 shared between the rows this writes each of them once instead of B times.
+ */
+NCKV_API int nckv_paged_tile_tokens(void);
+NCKV_API int nckv_append_rope_norm_paged(const void *q_in, const void *k_in, const void *v_in, void *q_out, void *k_pool,
+                                void *v_pool, const int32_t *block_table, const int32_t *cache_seqlens,
+                                const void *cos, const void *sin, int B, int T_new, int Hq, int Hkv, int D,
+                                int page_tokens, int max_pages, int n_pages, int64_t page_stride, int64_t token_stride,
+                                int rope_len, float qk_scale, float eps, int32_t *status, void *stream);
+NCKV_API int nckv_decode_attn_paged(const void *q, const void *k_pool, const void *v_pool, const int32_t *block_table,
+                           const int32_t *cache_seqlens, void *out, float *out_f32, float *lse_out, int B, int Hq,
+                           int Hkv, int D, int page_tokens, int max_pages, int n_pages, int64_t page_stride,
+                           int64_t token_stride, int seqlen_offset, int window_left, void *workspace,
+                           size_t workspace_bytes, void *stream);
+NCKV_API int nckv_paged_fill(const void *src_k, const void *src_v, void *k_pool, void *v_pool, const int32_t *jobs,
+                    int n_jobs, int L, int Hkv, int D, int T_src, int page_tokens, int n_pages, void *stream);
 
 /*
  * Dense (T_new >= 1) causal attention over a cache or plain k/v, tcgen05/TMEM tiles.

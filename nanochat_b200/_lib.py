@@ -47,12 +47,18 @@ SIGNATURES = {
     "nckv_glue_mix_norm": (c_int, [c_void_p] * 7 + [c_int] * 3 + [c_float] * 4 + [c_void_p]),
     "nckv_glue_relu_sq": (c_int, [c_void_p, c_void_p, c_i64, c_void_p]),
     "nckv_glue_ve_gate": (c_int, [c_void_p] * 4 + [c_int] * 3 + [c_void_p]),
+    "nckv_paged_tile_tokens": (c_int, []),
+    "nckv_append_rope_norm_paged": (c_int, [c_void_p] * 10 + [c_int] * 8 + [c_i64, c_i64, c_int, c_float, c_float,
+                                                             c_void_p, c_void_p]),
+    "nckv_decode_attn_paged": (c_int, [c_void_p] * 8 + [c_int] * 7 + [c_i64, c_i64, c_int, c_int, c_void_p, c_size_t,
+                                                        c_void_p]),
+    "nckv_paged_fill": (c_int, [c_void_p] * 5 + [c_int] * 7 + [c_void_p]),
     "nckv_prefill_broadcast": (c_int, [c_void_p] * 5 + [c_int] * 7 + [c_void_p]),
     "nckv_prefill_attn": (c_int, [c_void_p] * 5 + [c_int] * 6 + [c_i64, c_i64, c_int, c_void_p, c_void_p]),
 }
 
 ERROR_NAMES = {-1: "NCKV_E_ARG", -2: "NCKV_E_UNSUPPORTED", -3: "NCKV_E_CAPACITY", -4: "NCKV_E_CUDA"}
-ST_OVERFLOW, ST_TIMEOUT, ST_BAD_SEQLEN = 1, 2, 4
+ST_OVERFLOW, ST_TIMEOUT, ST_BAD_SEQLEN, ST_BAD_PAGE = 1, 2, 4, 8
 
 
 class NckvError(RuntimeError):

@@ -31,6 +31,10 @@ struct AppendParams {
     float qk_scale, eps;
     int transform_k;  // 0: k is stored as given (plain append)
     KvSplit split;    // block > 0: block-cyclic sequence split, the owner of position cache_seqlens[b] stores k/v
+    // paged storage (block_table != null): the caches are page pools (n_pages, page_tokens, Hkv, D);
+    // T_max is then max_pages * page_tokens and cache_batch_stride the distance between pages
+    const int32_t *block_table;
+    int page_tokens, max_pages, n_pages;
 };
 
 __device__ __forceinline__ void unpack8(const uint4 &v, float (&f)[8]) {
@@ -170,10 +174,21 @@ __global__ void __launch_bounds__(256) append_rope_norm_kernel(const AppendParam
                 p.q_out[src_idx] = o;
             } else if (write_kv) {
                 __nv_bfloat16 *cache = kind == 1 ? p.k_cache : p.v_cache;
-                uint4 *dst = reinterpret_cast<uint4 *>(cache + (long long)b * p.cache_batch_stride +
-                                                       (long long)(wslot + t) * p.cache_token_stride +
-                                                       (long long)h * NCKV_D);
-                dst[j] = o;
+                long long outer = b, tok = wslot + t;
+                if (p.block_table) {  // row -> page
+                    const int idx = (int)(tok / p.page_tokens);
+                    tok -= (long long)idx * p.page_tokens;
+                    outer = p.block_table[(long long)b * p.max_pages + idx];
+                    if (outer < 0 || outer >= p.n_pages) {
+                        if (j == 0 && h == 0 && kind == 1) atomicOr(p.status, (int)NCKV_ST_BAD_PAGE);
+                        outer = -1;
+                    }
+                }
+                if (outer >= 0) {
+                    uint4 *dst = reinterpret_cast<uint4 *>(cache + outer * p.cache_batch_stride +
+                                                           tok * p.cache_token_stride + (long long)h * NCKV_D);
+                    dst[j] = o;
+                }
             }
         }
     }
@@ -240,7 +255,8 @@ static int append_rope_norm_impl(const void *q_in, const void *k_in, const void 
                                  const int32_t *write_slots, nckv::KvSplit split, const void *cos, const void *sin, int B, int T_new,
                                  int Hq, int Hkv, int D, int T_max, int64_t cache_batch_stride,
                                  int64_t cache_token_stride, int rope_len, float qk_scale, float eps,
-                                 int32_t *status, void *stream) {
+                                 int32_t *status, void *stream, const int32_t *block_table = nullptr,
+                                 int page_tokens = 0, int max_pages = 0, int n_pages = 0) {
     using namespace nckv;
     int rc = check_common(k_in, v_in, k_cache, v_cache, cache_seqlens, B, T_new, Hkv, D, T_max,
                           cache_batch_stride, cache_token_stride, status);
@@ -276,6 +292,8 @@ static int append_rope_norm_impl(const void *q_in, const void *k_in, const void 
     p.eps = eps;
     p.transform_k = 1;
     p.split = split;
+    p.block_table = block_table;
+    p.page_tokens = page_tokens; p.max_pages = max_pages; p.n_pages = n_pages;
     return launch_append(p, static_cast<cudaStream_t>(stream));
 }
 
@@ -320,6 +338,22 @@ int nckv_append_rope_norm_split(const void *q_in, const void *k_in, const void *
                                  cache_batch_stride, cache_token_stride, rope_len, qk_scale, eps, status, stream);
 }
 
+int nckv_append_rope_norm_paged(const void *q_in, const void *k_in, const void *v_in, void *q_out, void *k_pool,
+                                void *v_pool, const int32_t *block_table, const int32_t *cache_seqlens,
+                                const void *cos, const void *sin, int B, int T_new, int Hq, int Hkv, int D,
+                                int page_tokens, int max_pages, int n_pages, int64_t page_stride, int64_t token_stride,
+                                int rope_len, float qk_scale, float eps, int32_t *status, void *stream) {
+    if (!block_table || page_tokens <= 0 || max_pages <= 0 || n_pages <= 0 ||
+        (long long)page_tokens * max_pages > 0x3fffffffLL) {
+        nckv::set_error("append_rope_norm_paged: bad paging (page_tokens=%d max_pages=%d n_pages=%d)", page_tokens,
+                        max_pages, n_pages);
+        return NCKV_E_ARG;
+    }
+    return append_rope_norm_impl(q_in, k_in, v_in, q_out, k_pool, v_pool, cache_seqlens, nullptr, nckv::KvSplit{0, 0, 0},
+                                 cos, sin, B, T_new, Hq, Hkv, D, page_tokens * max_pages, page_stride, token_stride,
+                                 rope_len, qk_scale, eps, status, stream, block_table, page_tokens, max_pages, n_pages);
+}
+
 int nckv_append(const void *k_in, const void *v_in, void *k_cache, void *v_cache,
                 const int32_t *cache_seqlens, int B, int T_new, int Hkv, int D, int T_max,
                 int64_t cache_batch_stride, int64_t cache_token_stride, int32_t *status,
@@ -347,6 +381,8 @@ int nckv_append(const void *k_in, const void *v_in, void *k_cache, void *v_cache
     p.eps = 0.0f;
     p.transform_k = 0;
     p.split = KvSplit{0, 0, 0};
+    p.block_table = nullptr;
+    p.page_tokens = p.max_pages = p.n_pages = 0;
     return launch_append(p, static_cast<cudaStream_t>(stream));
 }
 

@@ -92,6 +92,12 @@ struct DecodeParams {
     int B, Hq, Hkv, G, T_max;
     int seqlen_offset, window_left, kv_begin, kv_end;
     KvSplit split;         // block > 0: seqlens are global lengths, the cache holds this shard's block-cyclic part
+    // paged storage (block_table != null): the caches are pools of pages (n_pages, page_tokens, Hkv, D);
+    // token t of row b lives in page block_table[b * max_pages + t / page_tokens] at t % page_tokens.
+    // page_tokens is a multiple of DEC_TILE and tiles are cut on the DEC_TILE grid, so a tile never
+    // straddles two pages.
+    const int32_t *block_table;
+    int page_tokens, max_pages, n_pages;
     int rec_floats;
     int W;                 // warps of the streaming grid (the run geometry depends on it)
     float scale_log2;
@@ -214,8 +220,10 @@ __host__ __device__ inline int table_rows(int B) { return (B + 1 + 31) & ~31; }
 
 // Per-row visible key range [s_start, s_end) and the exclusive prefix sum of tiles per row
 // (s_pref, B + 1 entries), computed by a whole CTA.  Ends with a __syncthreads().
+// With paged storage s_start is the tile origin (the first visible key rounded down to the tile grid)
+// and s_head the number of keys of tile 0 in front of the first visible one (0 otherwise).
 __device__ __forceinline__ void build_row_tables(const DecodeParams &p, int *s_start, int *s_end, int *s_pref,
-                                                 bool report) {
+                                                 int *s_head, bool report) {
     const int tid = threadIdx.x, lane = tid & 31, B = p.B;
     for (int b = tid; b < B; b += blockDim.x) {
         int n = p.seqlens[b] + p.seqlen_offset;
@@ -235,8 +243,10 @@ __device__ __forceinline__ void build_row_tables(const DecodeParams &p, int *s_s
             hi = min(hi, p.kv_end);
         }
         if (hi < lo) hi = lo;
-        s_start[b] = lo;
+        const int origin = p.block_table ? (hi > lo ? (lo / DEC_TILE) * DEC_TILE : lo) : lo;
+        s_start[b] = origin;
         s_end[b] = hi;
+        s_head[b] = lo - origin;
     }
     __syncthreads();
     if (tid < 32) {  // exclusive prefix sum of tiles per row
@@ -267,9 +277,22 @@ __device__ __forceinline__ void build_row_tables(const DecodeParams &p, int *s_s
 }
 
 
+// Paged storage: tile starting at key `key0` of row b -> (token inside its page, page).  A page number
+// outside the pool is reported and replaced by the pool size, a coordinate the copy fills with zeros.
+__device__ __forceinline__ void page_coords(const DecodeParams &p, int b, int key0, int &tok, int &page) {
+    const int idx = key0 / p.page_tokens;
+    tok = key0 - idx * p.page_tokens;
+    page = __ldg(p.block_table + (long long)b * p.max_pages + idx);
+    if (page < 0 || page >= p.n_pages) {
+        atomicOr(p.status, (int)NCKV_ST_BAD_PAGE);
+        page = p.n_pages;
+    }
+}
+
 // GHI: group size 9..16 (rows 8..15 of the MMA tile carry heads too).  MAP5: the tensor maps are the
 // 5-D form (one copy per K or V tile) instead of the 4-D form (one copy per 64-channel half).
-template <bool GHI, bool MAP5>
+// PAGED: block-table storage (always with the 5-D maps, whose outermost coordinate is then the page).
+template <bool GHI, bool MAP5, bool PAGED = false>
 __global__ void __launch_bounds__(DEC_WARPS * 32, DEC_CTAS_PER_SM)
 decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
                    const __grid_constant__ CUtensorMap tmap_v, const DecodeParams p) {
@@ -280,9 +303,10 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
     uint8_t *stages = smem;  // [DEC_WARPS][DEC_STAGES][DEC_STAGE_BYTES]
     uint64_t *full_bar = reinterpret_cast<uint64_t *>(stages + DEC_WARPS * DEC_STAGES * DEC_STAGE_BYTES);
     RunEntry *rings = reinterpret_cast<RunEntry *>(full_bar + DEC_WARPS * DEC_STAGES);  // [DEC_WARPS][DEC_RING]
-    int *s_start = reinterpret_cast<int *>(rings + DEC_WARPS * DEC_RING);  // three tables of table_rows(B) entries
+    int *s_start = reinterpret_cast<int *>(rings + DEC_WARPS * DEC_RING);  // four tables of table_rows(B) entries
     int *s_end = s_start + table_rows(p.B);
     int *s_pref = s_end + table_rows(p.B);  // B + 1 entries
+    int *s_head = s_pref + table_rows(p.B);
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -303,7 +327,7 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
     // decode step's append kernel may have written).  q, the appended rows, the run counter
     // and every store come after it.  Dependents (the merge kernel) are released after the wait,
     // so that a grid that can start early always finds its predecessor's predecessors complete.
-    build_row_tables(p, s_start, s_end, s_pref, blockIdx.x == 0);
+    build_row_tables(p, s_start, s_end, s_pref, s_head, blockIdx.x == 0);
     bool prior_done = false;
     auto wait_prior = [&]() {  // called warp-uniformly
         if (!prior_done) {
@@ -396,6 +420,8 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
             __syncwarp();
         }
         const int key0 = s_start[prod.b] + prod.j * DEC_TILE;
+        int tok = key0, outer = prod.b;  // token and outermost (row or page) coordinate of the tile
+        if (PAGED) page_coords(p, prod.b, key0, tok, outer);
         // A tile that reaches the rows appended by this step has to wait for the append kernel.
         // With seqlen_offset == 0 the caller has already counted the new token in cache_seqlens
         // (the sequence-split path does): the last visible position is then the appended one.
@@ -414,8 +440,8 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
             // K/V bytes are used once: evict-first keeps them from flushing q and the partial
             // records out of L2
             if (MAP5) {
-                tma_load_5d_hint(dst, &tmap_k, bar, 0, key0, 0, prod.h, prod.b, kv_policy);
-                tma_load_5d_hint(dst + 2 * DEC_HALF_BYTES, &tmap_v, bar, 0, key0, 0, prod.h, prod.b, kv_policy);
+                tma_load_5d_hint(dst, &tmap_k, bar, 0, tok, 0, prod.h, outer, kv_policy);
+                tma_load_5d_hint(dst + 2 * DEC_HALF_BYTES, &tmap_v, bar, 0, tok, 0, prod.h, outer, kv_policy);
             } else {
                 tma_load_4d_hint(dst, &tmap_k, bar, 0, prod.h, key0, prod.b, kv_policy);
                 tma_load_4d_hint(dst + DEC_HALF_BYTES, &tmap_k, bar, 64, prod.h, key0, prod.b, kv_policy);
@@ -445,8 +471,10 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
         for (int i = 0; i < DEC_PREFETCH && left > 0; ++i, --left) {
             const int key0 = s_start[pc.b] + pc.j * DEC_TILE;
             if (MAP5) {
-                tma_prefetch_l2_5d(&tmap_k, 0, key0, 0, pc.h, pc.b);
-                tma_prefetch_l2_5d(&tmap_v, 0, key0, 0, pc.h, pc.b);
+                int tok = key0, outer = pc.b;
+                if (PAGED) page_coords(p, pc.b, key0, tok, outer);
+                tma_prefetch_l2_5d(&tmap_k, 0, tok, 0, pc.h, outer);
+                tma_prefetch_l2_5d(&tmap_v, 0, tok, 0, pc.h, outer);
             } else {
                 tma_prefetch_l2_4d(&tmap_k, 0, pc.h, key0, pc.b);
                 tma_prefetch_l2_4d(&tmap_k, 64, pc.h, key0, pc.b);
@@ -520,6 +548,7 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
         const uint32_t vbase = kbase + 2 * DEC_HALF_BYTES;
         const int key0 = s_start[cons.b] + cons.j * DEC_TILE;
         const int nvalid = min(DEC_TILE, s_end[cons.b] - key0);
+        const int nskip = (PAGED && cons.j == 0) ? s_head[cons.b] : 0;  // keys of the tile in front of the window
 
         if (nvalid < DEC_TILE) {
             // Tail tile: rows past the last visible key may hold stale bytes; zero V there so a
@@ -565,8 +594,8 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmap_k,
 #pragma unroll
         for (int nb = 0; nb < DEC_TILE / 8; ++nb) {
             const int k0 = nb * 8 + 2 * t4;
-            if (k0 >= nvalid) { s_acc[nb][0] = -INFINITY; s_acc[nb][2] = -INFINITY; }
-            if (k0 + 1 >= nvalid) { s_acc[nb][1] = -INFINITY; s_acc[nb][3] = -INFINITY; }
+            if (k0 >= nvalid || (PAGED && k0 < nskip)) { s_acc[nb][0] = -INFINITY; s_acc[nb][2] = -INFINITY; }
+            if (k0 + 1 >= nvalid || (PAGED && k0 + 1 < nskip)) { s_acc[nb][1] = -INFINITY; s_acc[nb][3] = -INFINITY; }
             mx0 = fmaxf(mx0, fmaxf(s_acc[nb][0], s_acc[nb][1]));
             if (GHI) mx1 = fmaxf(mx1, fmaxf(s_acc[nb][2], s_acc[nb][3]));
         }
@@ -705,9 +734,10 @@ __global__ void __launch_bounds__(128) decode_key_ranges_kernel(const DecodePara
                                                                 int32_t *key_end) {
     extern __shared__ int s_tables[];
     int *s_start = s_tables, *s_end = s_start + table_rows(p.B), *s_pref = s_end + table_rows(p.B);
-    build_row_tables(p, s_start, s_end, s_pref, true);
+    int *s_head = s_pref + table_rows(p.B);
+    build_row_tables(p, s_start, s_end, s_pref, s_head, true);
     for (int b = threadIdx.x; b < p.B; b += blockDim.x) {
-        key_begin[b] = s_start[b];
+        key_begin[b] = s_start[b] + s_head[b];
         key_end[b] = s_end[b];
     }
 }
@@ -724,6 +754,12 @@ struct PushDesc {
     int world, rank, rows;
 };
 
+// Block-table storage of a launch (table == null: dense caches).
+struct PagedDesc {
+    const int32_t *table;
+    int page_tokens, max_pages, n_pages;
+};
+
 // Merge of the partial records: one warp per (row, q head).  Lane i looks after part base+i of a
 // chunk of 32 parts for the softmax statistics; for the O row every lane owns channels
 // 4*lane .. 4*lane+3.  Which records belong to a pair follows from cache_seqlens alone, so the
@@ -733,12 +769,13 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) decode_merge_kernel(const De
                                                                         const __grid_constant__ PushDesc pd) {
     extern __shared__ int s_tables[];
     int *s_start = s_tables, *s_end = s_start + table_rows(p.B), *s_pref = s_end + table_rows(p.B);
+    int *s_head = s_pref + table_rows(p.B);
     const int lane = threadIdx.x & 31;
     const int B = p.B, Hkv = p.Hkv, G = p.G;
     pdl_launch_dependents();  // whatever follows in the stream may be scheduled behind this grid
     // cache_seqlens is stable by now: the streaming kernel only lets this grid start after it has
     // itself waited for its predecessor
-    build_row_tables(p, s_start, s_end, s_pref, false);
+    build_row_tables(p, s_start, s_end, s_pref, s_head, false);
     RunGeometry geo;
     geo.init(Hkv * s_pref[B], p.W);
     const int n_items = B * p.Hq;
@@ -882,7 +919,7 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) decode_merge_kernel(const De
     }
 }
 
-static size_t table_smem_bytes(int B) { return 3 * (size_t)table_rows(B) * sizeof(int); }
+static size_t table_smem_bytes(int B) { return 4 * (size_t)table_rows(B) * sizeof(int); }
 static size_t decode_smem_bytes(int B) {
     return 1024 + (size_t)DEC_WARPS * DEC_STAGES * DEC_STAGE_BYTES + DEC_WARPS * DEC_STAGES * sizeof(uint64_t) +
            DEC_WARPS * DEC_RING * sizeof(RunEntry) + table_smem_bytes(B);
@@ -970,12 +1007,14 @@ static int decode_launch(const void *q, const void *k_cache, const void *v_cache
                          void *out, float *out_f32, float *lse_out, int B, int Hq, int Hkv, int D, int T_max,
                          int64_t cache_batch_stride, int64_t cache_token_stride, int seqlen_offset, int window_left,
                          int kv_begin, int kv_end, nckv::KvSplit split, const nckv::PushDesc &push, void *workspace,
-                         size_t workspace_bytes, void *stream) {
+                         size_t workspace_bytes, void *stream, nckv::PagedDesc paged = nckv::PagedDesc{nullptr, 0, 0, 0}) {
     using namespace nckv;
     int rc0 = decode_check(q, k_cache, v_cache, cache_seqlens, out, out_f32, workspace, B, Hq, Hkv, D, T_max,
                            workspace_bytes);
     if (rc0 != NCKV_OK) return rc0;
     const int G = Hq / Hkv;
+    // dense: the maps span (rows, T_max tokens); paged: (pages of the pool, page_tokens tokens)
+    const int map_outer = paged.table ? paged.n_pages : B, map_tokens = paged.table ? paged.page_tokens : T_max;
     // Prefer the 5-D maps (one copy instruction per tile and tensor); if this driver does not accept
     // their stride order, use the 4-D maps (two per tile and tensor).  Decided once per process.
     // (A plain int shared by all host threads: concurrent first calls would both probe and store the
@@ -984,13 +1023,17 @@ static int decode_launch(const void *q, const void *k_cache, const void *v_cache
     CUtensorMap mk, mv;
     int rc = NCKV_E_CUDA;
     if (map5_state >= 0) {
-        rc = make_kv_tensor_map_5d(&mk, k_cache, B, T_max, Hkv, cache_batch_stride, cache_token_stride, DEC_TILE);
+        rc = make_kv_tensor_map_5d(&mk, k_cache, map_outer, map_tokens, Hkv, cache_batch_stride, cache_token_stride, DEC_TILE);
         if (rc == NCKV_OK)
-            rc = make_kv_tensor_map_5d(&mv, v_cache, B, T_max, Hkv, cache_batch_stride, cache_token_stride, DEC_TILE);
+            rc = make_kv_tensor_map_5d(&mv, v_cache, map_outer, map_tokens, Hkv, cache_batch_stride, cache_token_stride, DEC_TILE);
         if (rc == NCKV_E_ARG) return rc;
         if (map5_state == 0) map5_state = rc == NCKV_OK ? 1 : -1;
     }
     const bool map5 = rc == NCKV_OK;
+    if (!map5 && paged.table) {
+        set_error("decode_attn_paged: this driver does not accept the 5-D tensor maps the paged kernels use");
+        return NCKV_E_UNSUPPORTED;
+    }
     if (!map5) {
         rc = make_kv_tensor_map(&mk, k_cache, B, T_max, Hkv, cache_batch_stride, cache_token_stride, DEC_TILE);
         if (rc != NCKV_OK) return rc;
@@ -1015,6 +1058,10 @@ static int decode_launch(const void *q, const void *k_cache, const void *v_cache
     p.kv_begin = kv_begin;
     p.kv_end = kv_end;
     p.split = split;
+    p.block_table = paged.table;
+    p.page_tokens = paged.page_tokens;
+    p.max_pages = paged.max_pages;
+    p.n_pages = paged.n_pages;
     p.rec_floats = rec_floats_for(G);
     p.W = grid * DEC_WARPS;
     p.scale_log2 = (float)(1.4426950408889634 / sqrt((double)D));
@@ -1029,13 +1076,17 @@ static int decode_launch(const void *q, const void *k_cache, const void *v_cache
         NCKV_CUDA_CHECK(cudaFuncSetAttribute(decode_attn_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max));
         NCKV_CUDA_CHECK(cudaFuncSetAttribute(decode_attn_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max));
         NCKV_CUDA_CHECK(cudaFuncSetAttribute(decode_attn_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max));
+        NCKV_CUDA_CHECK(cudaFuncSetAttribute(decode_attn_kernel<true, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max));
+        NCKV_CUDA_CHECK(cudaFuncSetAttribute(decode_attn_kernel<false, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max));
         attr_set[dev] = true;
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // Both launches allow programmatic overlap with their predecessor in the stream: each kernel
     // runs its set-up early and waits (griddepcontrol.wait) before it touches dependent data.
     const dim3 g3(grid), b3(DEC_WARPS * 32);
-    if (ghi && map5) NCKV_CUDA_CHECK(launch_pdl(decode_attn_kernel<true, true>, g3, b3, smem, s, true, mk, mv, p));
+    if (paged.table && ghi) NCKV_CUDA_CHECK(launch_pdl(decode_attn_kernel<true, true, true>, g3, b3, smem, s, true, mk, mv, p));
+    else if (paged.table) NCKV_CUDA_CHECK(launch_pdl(decode_attn_kernel<false, true, true>, g3, b3, smem, s, true, mk, mv, p));
+    else if (ghi && map5) NCKV_CUDA_CHECK(launch_pdl(decode_attn_kernel<true, true>, g3, b3, smem, s, true, mk, mv, p));
     else if (ghi) NCKV_CUDA_CHECK(launch_pdl(decode_attn_kernel<true, false>, g3, b3, smem, s, true, mk, mv, p));
     else if (map5) NCKV_CUDA_CHECK(launch_pdl(decode_attn_kernel<false, true>, g3, b3, smem, s, true, mk, mv, p));
     else NCKV_CUDA_CHECK(launch_pdl(decode_attn_kernel<false, false>, g3, b3, smem, s, true, mk, mv, p));
@@ -1063,6 +1114,33 @@ int nckv_decode_attn(const void *q, const void *k_cache, const void *v_cache,
                          cache_batch_stride, cache_token_stride, seqlen_offset, window_left, kv_begin, kv_end,
                          nckv::KvSplit{0, 0, 0}, none, workspace, workspace_bytes, stream);
 }
+
+int nckv_decode_attn_paged(const void *q, const void *k_pool, const void *v_pool, const int32_t *block_table,
+                           const int32_t *cache_seqlens, void *out, float *out_f32, float *lse_out, int B, int Hq,
+                           int Hkv, int D, int page_tokens, int max_pages, int n_pages, int64_t page_stride,
+                           int64_t token_stride, int seqlen_offset, int window_left, void *workspace,
+                           size_t workspace_bytes, void *stream) {
+    using namespace nckv;
+    if (!out || !block_table) {
+        set_error("decode_attn_paged: null pointer argument");
+        return NCKV_E_ARG;
+    }
+    if (page_tokens <= 0 || (page_tokens % DEC_TILE) != 0 || max_pages <= 0 || n_pages <= 0) {
+        set_error("decode_attn_paged: page_tokens=%d must be a positive multiple of %d, max_pages=%d and n_pages=%d positive",
+                  page_tokens, DEC_TILE, max_pages, n_pages);
+        return NCKV_E_ARG;
+    }
+    if ((long long)page_tokens * max_pages > 0x3fffffffLL) {
+        set_error("decode_attn_paged: page_tokens * max_pages too large");
+        return NCKV_E_UNSUPPORTED;
+    }
+    PushDesc none = {};
+    return decode_launch(q, k_pool, v_pool, cache_seqlens, out, out_f32, lse_out, B, Hq, Hkv, D, page_tokens * max_pages,
+                         page_stride, token_stride, seqlen_offset, window_left, 0, 0, KvSplit{0, 0, 0}, none, workspace,
+                         workspace_bytes, stream, PagedDesc{block_table, page_tokens, max_pages, n_pages});
+}
+
+int nckv_paged_tile_tokens(void) { return nckv::DEC_TILE; }
 
 int nckv_decode_attn_split(const void *q, const void *k_cache, const void *v_cache, const int32_t *cache_seqlens,
                            float *part_out, float *part_lse, int B, int Hq, int Hkv, int D, int T_local,

@@ -57,7 +57,75 @@ __global__ void __launch_bounds__(BC_THREADS) prefill_broadcast_kernel(const Bro
     }
 }
 
+// The same prefill into a paged cache.  Pages that hold a whole page of prompt tokens are shared by
+// all rows (the block tables point at them), so the copy is a list of jobs "fill page P with n tokens
+// of the prompt starting at token t0": one job per shared page plus one per row for the page that
+// holds the prompt's tail, which each row needs for itself because it appends there.
+struct PagedFillParams {
+    const uint4 *src[2];
+    uint4 *dst[2];
+    const int32_t *jobs;  // n_jobs x (page, first source token, tokens)
+    int L, n_pages;
+    long long tok_vecs;        // Hkv*D / 8
+    long long src_layer_vecs;  // T_src*Hkv*D / 8
+    long long page_vecs;       // page_tokens*Hkv*D / 8
+};
+
+__global__ void __launch_bounds__(BC_THREADS) paged_fill_kernel(const PagedFillParams q) {
+    const int job = blockIdx.y;
+    const int which = blockIdx.z & 1, layer = blockIdx.z >> 1;
+    const int page = q.jobs[3 * job], t0 = q.jobs[3 * job + 1], n = q.jobs[3 * job + 2];
+    if (page < 0 || page >= q.n_pages || n <= 0) return;
+    const long long run = (long long)n * q.tok_vecs;
+    const uint4 *s = (which ? q.src[1] : q.src[0]) + layer * q.src_layer_vecs + (long long)t0 * q.tok_vecs;
+    uint4 *d = (which ? q.dst[1] : q.dst[0]) + ((long long)layer * q.n_pages + page) * q.page_vecs;
+    const long long v0 = (long long)blockIdx.x * BC_THREADS * BC_VEC;
+#pragma unroll
+    for (int i = 0; i < BC_VEC; ++i) {
+        const long long v = v0 + (long long)i * BC_THREADS + threadIdx.x;
+        if (v < run) __stcs(d + v, __ldg(s + v));
+    }
+}
+
 }  // namespace nckv
+
+extern "C" int nckv_paged_fill(const void *src_k, const void *src_v, void *k_pool, void *v_pool, const int32_t *jobs,
+                               int n_jobs, int L, int Hkv, int D, int T_src, int page_tokens, int n_pages,
+                               void *stream) {
+    using namespace nckv;
+    if (!src_k || !src_v || !k_pool || !v_pool || !jobs) {
+        set_error("paged_fill: null pointer argument");
+        return NCKV_E_ARG;
+    }
+    if (n_jobs <= 0 || n_jobs > 65535 || L <= 0 || 2 * L > 65535 || Hkv <= 0 || T_src <= 0 || page_tokens <= 0 || n_pages <= 0) {
+        set_error("paged_fill: bad size (n_jobs=%d L=%d Hkv=%d T_src=%d page_tokens=%d n_pages=%d)", n_jobs, L, Hkv, T_src,
+                  page_tokens, n_pages);
+        return NCKV_E_ARG;
+    }
+    if ((D % 8) != 0) {
+        set_error("paged_fill: head_dim %d must be a multiple of 8", D);
+        return NCKV_E_UNSUPPORTED;
+    }
+    if (((uintptr_t)src_k | (uintptr_t)src_v | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) {
+        set_error("paged_fill: tensors must be 16-byte aligned");
+        return NCKV_E_ARG;
+    }
+    PagedFillParams q;
+    q.src[0] = static_cast<const uint4 *>(src_k);
+    q.src[1] = static_cast<const uint4 *>(src_v);
+    q.dst[0] = static_cast<uint4 *>(k_pool);
+    q.dst[1] = static_cast<uint4 *>(v_pool);
+    q.jobs = jobs;
+    q.L = L; q.n_pages = n_pages;
+    q.tok_vecs = (long long)Hkv * D / 8;
+    q.src_layer_vecs = (long long)T_src * q.tok_vecs;
+    q.page_vecs = (long long)page_tokens * q.tok_vecs;
+    const long long chunk_vecs = (long long)BC_THREADS * BC_VEC;
+    const dim3 grid((unsigned)((q.page_vecs + chunk_vecs - 1) / chunk_vecs), (unsigned)n_jobs, (unsigned)(2 * L));
+    paged_fill_kernel<<<grid, BC_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(q);
+    NCKV_CUDA_CHECK(cudaGetLastError());
+    return NCKV_OK;
+}
 
 extern "C" int nckv_prefill_broadcast(const void *src_k, const void *src_v, void *dst_k, void *dst_v,
                                       int32_t *dst_seqlens, int L, int B, int p, int Hkv, int D,

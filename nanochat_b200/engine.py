@@ -68,6 +68,124 @@ class KVCache:
             self.prev_embedding = other.prev_embedding.expand(self.batch_size, -1, -1).clone()
 
 
+class PagedKVCache:
+    """KV storage in pages with a per-row block table: the compact successor of the dense
+    (n_layers, B, T_max, Hkv, D) tensors of engine.py:98-100, behind the same methods.
+
+    ``k_cache`` / ``v_cache`` are pools of shape (n_layers, n_pages, page_tokens, Hkv, D);
+    ``block_table`` is int32 (B, max_pages): token t of row b lives in page ``block_table[b, t //
+    page_tokens]``.  Pages are handed out from a free list on the host, ahead of need: ``reserve(n)``
+    makes every row able to hold n tokens (the caller knows an upper bound of every row's length; the
+    device-side ``cache_seqlens`` is never read back for this).  What the format buys:
+      * rows take pages as they grow, so ``n_pages`` can be sized for the tokens a batch really holds
+        instead of B x T_max;
+      * ``prefill`` shares the prompt: the pages that hold a whole page of prompt tokens are written
+        once and referenced by every row's table; only the page with the prompt's tail is copied per
+        row (rows append there).  Shared pages are never written again, so no copy-on-write is needed.
+    CUDA only: the kernels that read and write through the table have no CPU implementation."""
+
+    paged = True
+
+    def __init__(self, batch_size, num_heads, seq_len, head_dim, num_layers, device, dtype, page_tokens=192,
+                 n_pages=None):
+        if page_tokens % ops.PAGE_TILE:
+            raise ValueError(f"page_tokens must be a multiple of {ops.PAGE_TILE}")
+        self.batch_size = batch_size
+        self.max_seq_len = seq_len
+        self.n_layers = num_layers
+        self.n_heads = num_heads
+        self.head_dim = head_dim
+        self.page_tokens = page_tokens
+        self.max_pages = -(-seq_len // page_tokens)
+        self.n_pages = n_pages if n_pages is not None else batch_size * self.max_pages
+        shape = (num_layers, self.n_pages, page_tokens, num_heads, head_dim)
+        # not zero-filled: nothing beyond cache_seqlens is ever attended
+        self.k_cache = torch.empty(shape, device=device, dtype=dtype)
+        self.v_cache = torch.empty(shape, device=device, dtype=dtype)
+        self.cache_seqlens = torch.zeros(batch_size, dtype=torch.int32, device=device)
+        self.block_table = torch.full((batch_size, self.max_pages), -1, dtype=torch.int32, device=device)
+        self._table_host = torch.full((batch_size, self.max_pages), -1, dtype=torch.int32)
+        if torch.device(device).type == "cuda":
+            self._table_host = self._table_host.pin_memory()
+        self._free = list(range(self.n_pages - 1, -1, -1))
+        self._rows = [[] for _ in range(batch_size)]   # pages of each row, in order
+        self._shared = 0                                # leading pages of every row that are shared
+        self.prev_embedding = None
+
+    # ---- the reference's KVCache methods -------------------------------------------------------
+    def reset(self):
+        for b, pages in enumerate(self._rows):
+            own = pages[self._shared:] if b else pages  # shared pages are returned once (by row 0)
+            self._free.extend(reversed(own))
+            self._rows[b] = []
+        self._shared = 0
+        self._table_host.fill_(-1)
+        self.block_table.fill_(-1)
+        self.cache_seqlens.zero_()
+        self.prev_embedding = None
+
+    def get_pos(self):
+        return int(self.cache_seqlens[0].item())
+
+    def get_layer_cache(self, layer_idx):
+        """(k_pool, v_pool) of one layer, each (n_pages, page_tokens, Hkv, D)."""
+        return self.k_cache[layer_idx], self.v_cache[layer_idx]
+
+    def advance(self, num_tokens):
+        self.cache_seqlens += num_tokens
+
+    # ---- page bookkeeping (host) ---------------------------------------------------------------
+    def pages_in_use(self):
+        return self.n_pages - len(self._free)
+
+    def reserve(self, n_tokens):
+        """Give every row the pages for positions < n_tokens.  Cheap when nothing has to be added."""
+        need = -(-min(n_tokens, self.max_pages * self.page_tokens) // self.page_tokens)
+        changed = False
+        for b, pages in enumerate(self._rows):
+            while len(pages) < need:
+                if not self._free:
+                    raise RuntimeError(f"PagedKVCache: page pool of {self.n_pages} pages exhausted "
+                                       f"(row {b} needs page {len(pages)} for {n_tokens} tokens)")
+                page = self._free.pop()
+                self._table_host[b, len(pages)] = page
+                pages.append(page)
+                changed = True
+        if changed:
+            self.block_table.copy_(self._table_host, non_blocking=True)
+
+    def prefill(self, other):
+        """KVCache.prefill (engine.py:123-137) from a dense batch-1 prompt cache, sharing the prompt's
+        full pages between the rows."""
+        assert self.pages_in_use() == 0 and not any(self._rows), "Cannot prefill a non-empty KV cache"
+        assert self.n_layers == other.n_layers and self.n_heads == other.n_heads and self.head_dim == other.head_dim
+        assert self.max_seq_len >= other.max_seq_len
+        assert other.batch_size == 1 and not getattr(other, "paged", False), "prefill takes a dense batch-1 cache"
+        p = other.get_pos()
+        pt = self.page_tokens
+        n_full, tail = divmod(p, pt)
+        if len(self._free) < n_full + (self.batch_size if tail else 0):
+            raise RuntimeError(f"PagedKVCache: {n_full} shared + {self.batch_size} private pages do not fit the pool")
+        shared = [self._free.pop() for _ in range(n_full)]
+        jobs = [(page, i * pt, pt) for i, page in enumerate(shared)]
+        for b in range(self.batch_size):
+            self._rows[b] = list(shared)
+            self._table_host[b, :n_full] = torch.tensor(shared, dtype=torch.int32) if n_full else self._table_host[b, :0]
+            if tail:
+                page = self._free.pop()
+                self._rows[b].append(page)
+                self._table_host[b, n_full] = page
+                jobs.append((page, n_full * pt, tail))
+        self._shared = n_full
+        self.block_table.copy_(self._table_host, non_blocking=True)
+        if jobs:
+            ops.paged_fill(other.k_cache, other.v_cache, self.k_cache, self.v_cache,
+                           torch.tensor(jobs, dtype=torch.int32).to(self.block_table.device))
+        self.cache_seqlens.fill_(p)
+        if other.prev_embedding is not None:
+            self.prev_embedding = other.prev_embedding.expand(self.batch_size, -1, -1).clone()
+
+
 # ------------------------------------------------------------------------------------------------
 # The caller of the hot path: token-level generation (nanochat/engine.py:141-304)
 # ------------------------------------------------------------------------------------------------
@@ -140,9 +258,12 @@ class Engine:
     and ``forward(ids, kv_cache=...)``; the tokenizer only the special-token lookups, ``encode``
     and ``decode``."""
 
-    def __init__(self, model, tokenizer, cuda_graph=True):
+    def __init__(self, model, tokenizer, cuda_graph=True, page_tokens=None):
         self.model = model
         self.tokenizer = tokenizer
+        # page_tokens: keep the decode cache in pages of that many tokens (PagedKVCache; the prompt's
+        # pages are shared between the samples) instead of dense rows.  CUDA only.
+        self.page_tokens = page_tokens
         # On a CUDA device the decode step is replayed from a CUDA graph once a generation is long
         # enough to pay for the capture (same tokens, cache lengths and cache bytes as eager steps).
         self.cuda_graph = cuda_graph
@@ -167,7 +288,14 @@ class Engine:
         logits = self.model.forward(ids, kv_cache=prompt_cache)[:, -1, :].expand(num_samples, -1)
 
         capacity = (len(tokens) + max_tokens) if max_tokens is not None else cfg.sequence_len
-        cache = KVCache(batch_size=num_samples, seq_len=capacity, device=device, dtype=dtype, **geometry)
+        if self.page_tokens:
+            # shared prompt pages + per row the pages its own continuation can need
+            pt = self.page_tokens
+            own = -(-capacity // pt) - len(tokens) // pt
+            cache = PagedKVCache(batch_size=num_samples, seq_len=capacity, device=device, dtype=dtype, page_tokens=pt,
+                                 n_pages=len(tokens) // pt + num_samples * own, **geometry)
+        else:
+            cache = KVCache(batch_size=num_samples, seq_len=capacity, device=device, dtype=dtype, **geometry)
         cache.prefill(prompt_cache)
         del prompt_cache
 
@@ -182,6 +310,8 @@ class Engine:
             """One forward of the new tokens ids (B, 1) on the device, the n_done-th generated column;
             returns the logits (B, vocab)."""
             nonlocal graphed
+            if self.page_tokens:  # pages for this step's token (and the throw-away steps of a capture)
+                cache.reserve(min(capacity, len(tokens) + n_done + 4))
             if graphed is None and self.cuda_graph and on_gpu and n_done >= 2:
                 # capture runs three throw-away steps behind the current position: needs that room,
                 # and only pays off if enough steps are still to come

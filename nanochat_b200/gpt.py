@@ -63,9 +63,19 @@ def kv_attention(q, k, v, cos_sin_tables, window_size, kv_cache, layer_idx):
     k_cache, v_cache = kv_cache.get_layer_cache(layer_idx)
     seqlens = kv_cache.cache_seqlens
     T = q.size(1)
-    q2 = ops.append_rope_norm(q, k, v, k_cache, v_cache, seqlens, cos, sin)
     left = int(window_size[0])
     left = left if left >= 0 else -1
+    if getattr(kv_cache, "paged", False):  # page pools + block table instead of dense rows
+        if T != 1:
+            raise NotImplementedError("a paged cache takes one new token per row; prefill the prompt into a dense "
+                                      "batch-1 KVCache and hand it over with PagedKVCache.prefill")
+        q2 = ops.append_rope_norm_paged(q, k, v, k_cache, v_cache, kv_cache.block_table, seqlens, cos, sin)
+        y = ops.decode_attention_paged(q2[:, 0], k_cache, v_cache, kv_cache.block_table, seqlens, seqlen_offset=1,
+                                       window_left=left).unsqueeze(1)
+        if layer_idx == kv_cache.n_layers - 1:
+            kv_cache.advance(T)
+        return y
+    q2 = ops.append_rope_norm(q, k, v, k_cache, v_cache, seqlens, cos, sin)
     if T == 1:
         y = ops.decode_attention(q2[:, 0], k_cache, v_cache, seqlens, seqlen_offset=1, window_left=left).unsqueeze(1)
     else:

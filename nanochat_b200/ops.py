@@ -111,7 +111,7 @@ def workspace(device, B, Hq, Hkv):
 
 def read_status(device, clear=True):
     """Synchronously read (and by default clear) the device status word of the current stream's
-    workspace; 0 means no guard fired.  Bits: 1 overflow, 2 timeout, 4 bad cache_seqlens."""
+    workspace; 0 means no guard fired.  Bits: 1 overflow, 2 timeout, 4 bad cache_seqlens, 8 bad page."""
     device = torch.device(device)
     idx = device.index if device.index is not None else torch.cuda.current_device()
     key = (idx, torch.cuda.current_stream(idx).cuda_stream)
@@ -125,7 +125,8 @@ def read_status(device, clear=True):
 def check_status(device):
     st = read_status(device, clear=True)
     if st:
-        names = [n for bit, n in ((1, "capacity overflow"), (2, "barrier timeout"), (4, "negative cache_seqlens")) if st & bit]
+        names = [n for bit, n in ((1, "capacity overflow"), (2, "barrier timeout"), (4, "negative cache_seqlens"),
+                                  (8, "block-table entry outside the page pool")) if st & bit]
         raise RuntimeError("nckv device status: " + ", ".join(names))
 
 
@@ -476,6 +477,97 @@ def prefill_broadcast(src_k, src_v, dst_k, dst_v, dst_seqlens, p):
 def lse_combine(parts_o, parts_lse):
     """Merge partial attention results over disjoint key ranges; returns (bf16 out, fp32 lse)."""
     return _lse_combine(parts_o, parts_lse)
+
+
+# ------------------------------------------------------------------------------------------------
+# paged KV storage: pools (n_pages, page_tokens, Hkv, D) + an int32 block table (B, max_pages)
+# ------------------------------------------------------------------------------------------------
+PAGE_TILE = _lib.lib.nckv_paged_tile_tokens()  # page_tokens must be a multiple of this
+
+
+def _pool_strides(name, pool, table, B):
+    if pool.dim() != 4 or pool.size(3) != HEAD_DIM or pool.stride(3) != 1 or pool.stride(2) != HEAD_DIM:
+        raise RuntimeError(f"nckv::{name}: pool must be (n_pages, page_tokens, Hkv, {HEAD_DIM}) with packed heads, got "
+                           f"{tuple(pool.shape)} / {pool.stride()}")
+    if table.dtype != torch.int32 or table.dim() != 2 or table.size(0) != B or not table.is_contiguous() or not table.is_cuda:
+        raise RuntimeError(f"nckv::{name}: block_table must be a contiguous CUDA int32 (B={B}, max_pages) tensor")
+    if pool.size(1) % PAGE_TILE:
+        raise RuntimeError(f"nckv::{name}: page_tokens={pool.size(1)} must be a multiple of {PAGE_TILE}")
+    return pool.stride(0), pool.stride(1)
+
+
+def append_rope_norm_paged(q, k, v, k_pool, v_pool, block_table, cache_seqlens, cos, sin, qk_scale=QK_SCALE, eps=RMS_EPS):
+    """``append_rope_norm`` into paged storage: k/v of row b's token at position p go to page
+    ``block_table[b, p // page_tokens]``.  Returns q'."""
+    name = "append_rope_norm_paged"
+    _require_cuda(name, q, k, v, k_pool, v_pool, cache_seqlens, cos, sin)
+    _require_bf16(name, q, k, v, k_pool, v_pool, cos, sin)
+    if cache_seqlens.dtype != torch.int32:
+        raise RuntimeError(f"nckv::{name}: cache_seqlens must be int32")
+    B, T_new, Hq, D = q.shape
+    Hkv = k.size(2)
+    if k.shape != (B, T_new, Hkv, D) or v.shape != k.shape:
+        raise RuntimeError(f"nckv::{name}: k/v shapes {tuple(k.shape)}/{tuple(v.shape)} do not match q {tuple(q.shape)}")
+    if k_pool.shape != v_pool.shape or k_pool.stride() != v_pool.stride() or k_pool.size(2) != Hkv:
+        raise RuntimeError(f"nckv::{name}: pools must share shape and strides and hold {Hkv} kv heads")
+    sp, st = _pool_strides(name, k_pool, block_table, B)
+    cos2, sin2 = cos.reshape(-1, D // 2), sin.reshape(-1, D // 2)
+    if not (cos2.is_contiguous() and sin2.is_contiguous()):
+        cos2, sin2 = cos2.contiguous(), sin2.contiguous()
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    q_out = torch.empty_like(q)
+    idx, stream, ws = _launch_ctx(q, B, Hq, Hkv)
+    with _device_guard(idx):
+        _lib.call("nckv_append_rope_norm_paged", q.data_ptr(), k.data_ptr(), v.data_ptr(), q_out.data_ptr(),
+                  k_pool.data_ptr(), v_pool.data_ptr(), block_table.data_ptr(), cache_seqlens.data_ptr(), cos2.data_ptr(),
+                  sin2.data_ptr(), B, T_new, Hq, Hkv, D, k_pool.size(1), block_table.size(1), k_pool.size(0), sp, st,
+                  cos2.size(0), qk_scale, eps, ws.data_ptr(), stream)
+    return q_out
+
+
+def decode_attention_paged(q, k_pool, v_pool, block_table, cache_seqlens, seqlen_offset=1, window_left=-1):
+    """``decode_attention`` over paged storage. q: (B, Hq, D); returns (B, Hq, D) bf16."""
+    name = "decode_attn_paged"
+    _require_cuda(name, q, k_pool, v_pool, cache_seqlens)
+    _require_bf16(name, q, k_pool, v_pool)
+    if cache_seqlens.dtype != torch.int32:
+        raise RuntimeError(f"nckv::{name}: cache_seqlens must be int32")
+    if q.dim() != 3 or q.size(2) != HEAD_DIM:
+        raise RuntimeError(f"nckv::{name}: q must be (B, Hq, {HEAD_DIM}), got {tuple(q.shape)}")
+    B, Hq, D = q.shape
+    Hkv = k_pool.size(2)
+    if k_pool.shape != v_pool.shape or k_pool.stride() != v_pool.stride() or Hq % Hkv:
+        raise RuntimeError(f"nckv::{name}: pools {tuple(k_pool.shape)} / {tuple(v_pool.shape)} do not fit q {tuple(q.shape)}")
+    sp, st = _pool_strides(name, k_pool, block_table, B)
+    q = q.contiguous()
+    out = torch.empty_like(q)
+    idx, stream, ws = _launch_ctx(q, B, Hq, Hkv)
+    with _device_guard(idx):
+        _lib.call("nckv_decode_attn_paged", q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), block_table.data_ptr(),
+                  cache_seqlens.data_ptr(), out.data_ptr(), None, None, B, Hq, Hkv, D, k_pool.size(1), block_table.size(1),
+                  k_pool.size(0), sp, st, seqlen_offset, window_left, ws.data_ptr(), ws.numel(), stream)
+    return out
+
+
+def paged_fill(src_k, src_v, k_pool, v_pool, jobs):
+    """Copy runs of a batch-1 (L, 1, T, Hkv, D) cache into pages of (L, n_pages, page_tokens, Hkv, D)
+    pools; ``jobs`` is a CUDA int32 (n_jobs, 3) tensor of (page, first source token, tokens)."""
+    name = "paged_fill"
+    _require_cuda(name, src_k, src_v, k_pool, v_pool, jobs)
+    for t in (src_k, src_v, k_pool, v_pool):
+        if t.dim() != 5 or not t.is_contiguous() or t.element_size() != 2 or t.dtype != k_pool.dtype:
+            raise RuntimeError(f"nckv::{name}: caches must be contiguous 5-d tensors of one 16-bit dtype")
+    L, n_pages, page_tokens, Hkv, D = k_pool.shape
+    if src_k.shape != src_v.shape or v_pool.shape != k_pool.shape or src_k.size(0) != L or src_k.size(1) != 1 or \
+            src_k.shape[3:] != k_pool.shape[3:]:
+        raise RuntimeError(f"nckv::{name}: source {tuple(src_k.shape)} does not match pools {tuple(k_pool.shape)}")
+    if jobs.dtype != torch.int32 or jobs.dim() != 2 or jobs.size(1) != 3 or not jobs.is_contiguous():
+        raise RuntimeError(f"nckv::{name}: jobs must be a contiguous int32 (n, 3) tensor")
+    if jobs.size(0) == 0:
+        return
+    with torch.cuda.device(k_pool.device):
+        _lib.call("nckv_paged_fill", _ptr(src_k), _ptr(src_v), _ptr(k_pool), _ptr(v_pool), _ptr(jobs), jobs.size(0), L, Hkv, D,
+                  src_k.size(2), page_tokens, n_pages, _stream(k_pool.device))
 
 
 # ------------------------------------------------------------------------------------------------
