@@ -760,17 +760,25 @@ struct PagedDesc {
     int page_tokens, max_pages, n_pages;
 };
 
-// Merge of the partial records: one warp per (row, q head).  Lane i looks after part base+i of a
-// chunk of 32 parts for the softmax statistics; for the O row every lane owns channels
-// 4*lane .. 4*lane+3.  Which records belong to a pair follows from cache_seqlens alone, so the
-// record slots of a warp's first item are worked out BEFORE the grid-dependency wait, while the
-// streaming kernel is still running; after the wait only loads, a few shuffles and the store remain.
+// Merge of the partial records.  An item is one (row, q head); WPI warps work on it (1: a warp per
+// item, for batches of many short pairs; MERGE_WARPS: a block per item, for few long pairs whose
+// tiles were spread over dozens of runs).  Which records belong to a pair follows from cache_seqlens
+// alone.  The runs that can touch the pair's tile range [P0, P1) are enumerated as CANDIDATES
+// (slice w, r) with r = 0 the static run of the slice and r = 1.. its dynamic runs, D1 = 1 + d_big
+// per slice; candidate c = 32 * chunk + lane is looked after by one lane, which works out on its own
+// (no walk over the runs) whether that run exists and meets the pair, and in which record slot it left
+// its partial.  The slots of a warp's first chunks are worked out BEFORE the grid-dependency wait,
+// while the streaming kernel is still running; after the wait only loads, shuffles and the store remain.
+// Candidates are merged in index order, so the result does not depend on timing.
+template <int WPI>
 __global__ void __launch_bounds__(MERGE_WARPS * 32) decode_merge_kernel(const DecodeParams p,
                                                                         const __grid_constant__ PushDesc pd) {
     extern __shared__ int s_tables[];
     int *s_start = s_tables, *s_end = s_start + table_rows(p.B), *s_pref = s_end + table_rows(p.B);
     int *s_head = s_pref + table_rows(p.B);
-    const int lane = threadIdx.x & 31;
+    // WPI > 1: the warps' partial merges (M, L, 128 channels) and their part counts
+    float *s_comb = reinterpret_cast<float *>(s_head + table_rows(p.B));
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int B = p.B, Hkv = p.Hkv, G = p.G;
     pdl_launch_dependents();  // whatever follows in the stream may be scheduled behind this grid
     // cache_seqlens is stable by now: the streaming kernel only lets this grid start after it has
@@ -779,37 +787,64 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) decode_merge_kernel(const De
     RunGeometry geo;
     geo.init(Hkv * s_pref[B], p.W);
     const int n_items = B * p.Hq;
-    const int first_item = blockIdx.x * MERGE_WARPS + (threadIdx.x >> 5);
-    const int item_stride = gridDim.x * MERGE_WARPS;
+    const int first_item = WPI == 1 ? blockIdx.x * MERGE_WARPS + warp : blockIdx.x;
+    const int item_stride = WPI == 1 ? gridDim.x * MERGE_WARPS : gridDim.x;
+    const int sub = WPI == 1 ? 0 : warp;  // this warp's share of an item's chunks: sub, sub + WPI, ...
+    const int D1 = 1 + geo.d_big;
 
-    // Walks the runs that intersect the pair of `item`; lane i keeps the record slots of parts
-    // base + i, base + 32 + i, ... (MERGE_PLAN chunks of 32).  Returns the number of parts
-    // (0: nothing to merge).
-    auto plan = [&](int item, int base, int (&slots)[MERGE_PLAN], int &hg) -> int {
+    struct ItemRange {
+        int P0, P1, w0, n_chunks, hg;
+    };
+    auto item_range = [&](int item) -> ItemRange {
+        ItemRange r;
         const int b = item / p.Hq, hq = item - b * p.Hq;
         const int h = hq / G;
-        hg = hq - h * G;
-#pragma unroll
-        for (int c = 0; c < MERGE_PLAN; ++c) slots[c] = 0;
+        r.hg = hq - h * G;
         const int nt = s_pref[b + 1] - s_pref[b];
-        if (nt == 0) return 0;  // no visible key: the streaming kernel wrote zeros
-        const int P0 = Hkv * s_pref[b] + h * nt, P1 = P0 + nt;
-        int n = 0;
-        for (int x = P0; x < P1; ++n) {
-            const int k = geo.run_of(x);
-            int lo, len;
-            geo.run_range(k, lo, len);
-            const int rel = n - base - lane;
-#pragma unroll
-            for (int c = 0; c < MERGE_PLAN; ++c)
-                if (rel == 32 * c) slots[c] = 2 * k + (lo <= P0 ? 1 : 0);
-            x = lo + len;
+        r.P0 = Hkv * s_pref[b] + h * nt;
+        r.P1 = r.P0 + nt;
+        r.w0 = 0;
+        r.n_chunks = 0;
+        if (nt > 0 && geo.total > 0) {  // nt == 0: no visible key, the streaming kernel wrote zeros
+            r.w0 = geo.slice_of(r.P0);
+            r.n_chunks = ((geo.slice_of(r.P1 - 1) - r.w0 + 1) * D1 + 31) >> 5;
         }
-        return n == 1 ? 0 : n;  // a single run held the whole pair and wrote the output itself
+        return r;
+    };
+    // record slot of candidate `cand` of the item, or -1 if that run does not exist or misses the pair
+    auto cand_slot = [&](const ItemRange &r, int cand) -> int {
+        const int w = r.w0 + cand / D1, rr = cand - (cand / D1) * D1;
+        if (w >= geo.W) return -1;
+        const int st = w < geo.r ? geo.s_big : geo.s_small;
+        const int slice_lo = geo.slice_lo(w), slice_len = geo.slice_len(w);
+        int k, lo, len;
+        if (rr == 0) {
+            k = w;
+            lo = slice_lo;
+            len = st;
+        } else {
+            const int c = rr - 1;
+            if (c >= (w < geo.r ? geo.d_big : geo.d_small)) return -1;
+            k = geo.W + (w < geo.r ? w * geo.d_big : geo.r * geo.d_big + (w - geo.r) * geo.d_small) + c;
+            lo = slice_lo + st + c * geo.CH;
+            len = min(geo.CH, slice_len - st - c * geo.CH);
+        }
+        if (len <= 0 || lo >= r.P1 || lo + len <= r.P0) return -1;
+        return 2 * k + (lo <= r.P0 ? 1 : 0);
     };
 
-    int plan_slots[MERGE_PLAN], plan_hg = 0, plan_n = 0;
-    if (geo.total > 0 && first_item < n_items) plan_n = plan(first_item, 0, plan_slots, plan_hg);
+    ItemRange cur = {0, 0, 0, 0, 0};
+    int plan_slots[MERGE_PLAN];
+#pragma unroll
+    for (int c = 0; c < MERGE_PLAN; ++c) plan_slots[c] = -1;
+    if (first_item < n_items) {
+        cur = item_range(first_item);
+#pragma unroll
+        for (int c = 0; c < MERGE_PLAN; ++c) {
+            const int chunk = sub + c * WPI;
+            if (chunk < cur.n_chunks) plan_slots[c] = cand_slot(cur, chunk * 32 + lane);
+        }
+    }
 
     pdl_wait_prior_grids();  // the streaming kernel has completed and its records are visible
     const bool push = pd.world > 0;
@@ -827,65 +862,104 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) decode_merge_kernel(const De
     };
 
     for (int item = first_item; item < n_items; item += item_stride) {
-        int hg = plan_hg, nparts = plan_n;
-        if (item != first_item) nparts = geo.total > 0 ? plan(item, 0, plan_slots, hg) : 0;
-        if (nparts == 0) {
-            // written by the streaming kernel itself (one run held the whole pair, or no key is visible)
-            if (push)
-                push_row(item, __ldcg(reinterpret_cast<const float4 *>(p.out_f32 + (long long)item * NCKV_D) + lane),
-                         __ldcg(p.lse + item));
-            continue;
-        }
+        if (item != first_item) cur = item_range(item);
+        const int hg = cur.hg;
         float M = -INFINITY, L = 0.f;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int base = 0; base < nparts; base += 32) {
-            if (base > 0 && (base / 32) % MERGE_PLAN == 0) plan(item, base, plan_slots, hg);  // beyond the planned window
-            int my_slot = plan_slots[0];
+        int nparts = 0;
+        for (int ci = 0, chunk = sub; chunk < cur.n_chunks; ++ci, chunk += WPI) {
+            int my_slot;
+            if (item == first_item && ci < MERGE_PLAN) {
+                my_slot = plan_slots[0];
 #pragma unroll
-            for (int c = 1; c < MERGE_PLAN; ++c)
-                if ((base / 32) % MERGE_PLAN == c) my_slot = plan_slots[c];
-            const int i = base + lane;
-            const int cnt = min(32, nparts - base);
+                for (int c = 1; c < MERGE_PLAN; ++c)
+                    if (ci == c) my_slot = plan_slots[c];
+            } else {
+                my_slot = cand_slot(cur, chunk * 32 + lane);
+            }
+            const unsigned live = __ballot_sync(0xffffffffu, my_slot >= 0);
+            if (live == 0) continue;
+            nparts += __popc(live);
             float m_i = -INFINITY, l_i = 0.f;
-            if (i < nparts) {
+            if (my_slot >= 0) {
                 const float *r2 = p.partials + (long long)my_slot * p.rec_floats;
                 m_i = __ldcg(r2 + G * NCKV_D + hg);
                 l_i = __ldcg(r2 + G * NCKV_D + G + hg);
             }
-            // O rows in batches of MERGE_BATCH predicated loads issued back to back (one round trip per
-            // batch instead of one per part); the first batch is in flight during the reductions
+            // O rows of the live candidates in batches of MERGE_BATCH loads issued back to back (one round
+            // trip per batch instead of one per part); the first batch is in flight during the reductions
             float4 v[MERGE_BATCH];
-            auto fetch8 = [&](int jb) {
+            unsigned todo = live;
+            int src[MERGE_BATCH];
+            auto fetch = [&]() {
 #pragma unroll
                 for (int u = 0; u < MERGE_BATCH; ++u) {
-                    const int slot_j = __shfl_sync(0xffffffffu, my_slot, (jb + u) & 31);
+                    src[u] = todo ? __ffs(todo) - 1 : -1;
+                    if (todo) todo &= todo - 1;
+                    const int slot_j = __shfl_sync(0xffffffffu, my_slot, src[u] < 0 ? 0 : src[u]);
                     v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (jb + u < cnt)
+                    if (src[u] >= 0)
                         v[u] = __ldcg(reinterpret_cast<const float4 *>(p.partials + (long long)slot_j * p.rec_floats + hg * NCKV_D) + lane);
                 }
             };
-            fetch8(0);
+            fetch();
             float cm = m_i;
 #pragma unroll
             for (int off = 16; off >= 1; off >>= 1) cm = fmaxf(cm, __shfl_xor_sync(0xffffffffu, cm, off));
             const float newM = fmaxf(M, cm);
             const float rescale = exp2f(M - newM);  // first chunk: exp2(-inf) = 0
-            const float sc = i < nparts ? exp2f(m_i - newM) : 0.f;
+            const float sc = my_slot >= 0 ? exp2f(m_i - newM) : 0.f;
             float cl = sc * l_i;
 #pragma unroll
             for (int off = 16; off >= 1; off >>= 1) cl += __shfl_xor_sync(0xffffffffu, cl, off);
             L = L * rescale + cl;
             acc.x *= rescale; acc.y *= rescale; acc.z *= rescale; acc.w *= rescale;
             M = newM;
-            for (int jb = 0; jb < cnt; jb += MERGE_BATCH) {
-                if (jb > 0) fetch8(jb);
+            for (;;) {
 #pragma unroll
                 for (int u = 0; u < MERGE_BATCH; ++u) {
-                    const float s_j = __shfl_sync(0xffffffffu, sc, (jb + u) & 31);  // 0 for lanes past the chunk
-                    acc.x = fmaf(s_j, v[u].x, acc.x); acc.y = fmaf(s_j, v[u].y, acc.y);
-                    acc.z = fmaf(s_j, v[u].z, acc.z); acc.w = fmaf(s_j, v[u].w, acc.w);
+                    const float s_j = __shfl_sync(0xffffffffu, sc, src[u] < 0 ? 0 : src[u]);
+                    if (src[u] >= 0) {
+                        acc.x = fmaf(s_j, v[u].x, acc.x); acc.y = fmaf(s_j, v[u].y, acc.y);
+                        acc.z = fmaf(s_j, v[u].z, acc.z); acc.w = fmaf(s_j, v[u].w, acc.w);
+                    }
+                }
+                if (todo == 0) break;
+                fetch();
+            }
+        }
+        if (WPI > 1) {
+            // combine the warps' shares in warp order: [warp][M, L, count, pad, 128 channels]
+            float *mine = s_comb + warp * (NCKV_D + 4);
+            if (lane == 0) { mine[0] = M; mine[1] = L; mine[2] = (float)nparts; }
+            reinterpret_cast<float4 *>(mine + 4)[lane] = acc;
+            __syncthreads();
+            if (warp == 0) {
+                M = -INFINITY; L = 0.f; nparts = 0;
+                acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int w2 = 0; w2 < WPI; ++w2) {
+                    const float *o = s_comb + w2 * (NCKV_D + 4);
+                    const float m2 = o[0], l2 = o[1];
+                    nparts += (int)o[2];
+                    if (m2 == -INFINITY) continue;
+                    const float newM = fmaxf(M, m2);
+                    const float ra = exp2f(M - newM), rb = exp2f(m2 - newM);
+                    const float4 v2 = reinterpret_cast<const float4 *>(o + 4)[lane];
+                    acc.x = acc.x * ra + v2.x * rb; acc.y = acc.y * ra + v2.y * rb;
+                    acc.z = acc.z * ra + v2.z * rb; acc.w = acc.w * ra + v2.w * rb;
+                    L = L * ra + l2 * rb;
+                    M = newM;
                 }
             }
+            __syncthreads();
+            if (warp != 0) continue;
+        }
+        if (nparts <= 1) {
+            // written by the streaming kernel itself (one run held the whole pair, or no key is visible)
+            if (push)
+                push_row(item, __ldcg(reinterpret_cast<const float4 *>(p.out_f32 + (long long)item * NCKV_D) + lane),
+                         __ldcg(p.lse + item));
+            continue;
         }
         const float inv = 1.f / L;
         acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
@@ -1091,11 +1165,19 @@ static int decode_launch(const void *q, const void *k_cache, const void *v_cache
     else if (map5) NCKV_CUDA_CHECK(launch_pdl(decode_attn_kernel<false, true>, g3, b3, smem, s, true, mk, mv, p));
     else NCKV_CUDA_CHECK(launch_pdl(decode_attn_kernel<false, false>, g3, b3, smem, s, true, mk, mv, p));
     const int items = B * Hq;
-    int merge_grid = (items + MERGE_WARPS - 1) / MERGE_WARPS;
-    if (merge_grid > 4 * grid) merge_grid = 4 * grid;
     PushDesc pd = push;
     pd.done = reinterpret_cast<unsigned *>(ws + 32);
-    NCKV_CUDA_CHECK(launch_pdl(decode_merge_kernel, dim3(merge_grid), dim3(MERGE_WARPS * 32), table_smem_bytes(B), s, true, p, pd));
+    // Few long (row, kv head) pairs: their tiles are spread over many runs each (about 4 runs per slice
+    // of the W a pair spans), so a block merges one item; otherwise a warp does.
+    const size_t merge_smem = table_smem_bytes(B) + MERGE_WARPS * (NCKV_D + 4) * sizeof(float);
+    if ((long long)B * Hkv * 4 <= p.W) {
+        const int merge_grid = items < 8 * sm_count() ? items : 8 * sm_count();
+        NCKV_CUDA_CHECK(launch_pdl(decode_merge_kernel<MERGE_WARPS>, dim3(merge_grid), dim3(MERGE_WARPS * 32), merge_smem, s, true, p, pd));
+    } else {
+        int merge_grid = (items + MERGE_WARPS - 1) / MERGE_WARPS;
+        if (merge_grid > 4 * sm_count()) merge_grid = 4 * sm_count();
+        NCKV_CUDA_CHECK(launch_pdl(decode_merge_kernel<1>, dim3(merge_grid), dim3(MERGE_WARPS * 32), merge_smem, s, true, p, pd));
+    }
     return NCKV_OK;
 }
 
