@@ -187,7 +187,12 @@ def spread(region_ms, per):
     return statistics.median(v), pick(0.1), pick(0.9)
 
 
+REGIONS_OVERRIDE = None  # --regions: a fixed number of regions (profiling runs want few launches)
+
+
 def repeats_for(region_s, target_s=1.0, lo=50, hi=3000):
+    if REGIONS_OVERRIDE:
+        return REGIONS_OVERRIDE
     return int(min(hi, max(lo, math.ceil(target_s / max(region_s, 1e-6)))))
 
 
@@ -590,7 +595,7 @@ def run_ours(args):
 
         for i in range(max(W, 3)):
             host_step.run(sets[i % NSETS][0], sets[i % NSETS][1], seqlens, -1)
-        reps = int(min(300, max(5, math.ceil(0.5 / (K * 80e-6)))))
+        reps = REGIONS_OVERRIDE or int(min(300, max(5, math.ceil(0.5 / (K * 80e-6)))))
         t0 = time.perf_counter()
         med, p10, p90 = spread(timed_regions(region, reps, world, dev), K)
         wall_ms = 1e3 * (time.perf_counter() - t0) / (reps * K)
@@ -936,6 +941,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--regions", type=int, default=None,
+                    help="time this many K-step regions instead of about a second's worth (at least 50)")
     ap.add_argument("--no-extras", action="store_true",
                     help="headline workload only: skip the long_context, d24_sharded and gpu_reference legs")
     ap.add_argument("--case", default=None,
@@ -943,6 +950,8 @@ def main():
                          "decode_gqa_window, decode_d24, prefill, broadcast, append, engine_d24, engine_d24_small, engine_d32, "
                          "engine_d32_small, engine_api_d24, engine_api_small")
     args = ap.parse_args()
+    global REGIONS_OVERRIDE
+    REGIONS_OVERRIDE = args.regions
     if args.case:
         run_case(args)
     elif args.impl == "reference":

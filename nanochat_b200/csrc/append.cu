@@ -136,6 +136,18 @@ __global__ void __launch_bounds__(256) append_rope_norm_kernel(const AppendParam
         const long long bt = r / heads_per_tok;
         const int t = (int)(bt % p.T_new);
         const int b = (int)(bt / p.T_new);
+        // kind: 0 = q head, 1 = k head, 2 = v head.  The two half-warps of a warp may hold
+        // different kinds, so the transform (which shuffles across the warp) runs unconditionally
+        // and its result is selected afterwards.
+        const int kind = slot < q_heads ? 0 : (slot < q_heads + p.Hkv ? 1 : 2);
+        const int h = kind == 0 ? slot : (kind == 1 ? slot - q_heads : slot - q_heads - p.Hkv);
+        const bool transform = kind == 0 || (kind == 1 && p.transform_k);
+        const uint4 *src = kind == 0 ? p.q_in : (kind == 1 ? p.k_in : p.v_in);
+        const long long src_idx = (bt * (kind == 0 ? p.Hq : p.Hkv) + h) * 16 + j;
+        // the input row does not depend on the row's length: its load goes out together with the
+        // length's, one round trip ahead of the table rows that do
+        uint4 x = make_uint4(0, 0, 0, 0);
+        if (live) x = src[src_idx];
         const int len = p.cache_seqlens[b];          // sequence position of token 0 (drives RoPE)
         int wslot = p.write_slots ? p.write_slots[b] : len;  // cache index of token 0
         if (p.split.block > 0 && len >= 0)
@@ -152,17 +164,8 @@ __global__ void __launch_bounds__(256) append_rope_norm_kernel(const AppendParam
         }
         const bool write_kv = ok && wslot >= 0;  // -1: this row's token belongs to another shard
         const int safe_pos = ok ? pos : 0;
-        // kind: 0 = q head, 1 = k head, 2 = v head.  The two half-warps of a warp may hold
-        // different kinds, so the transform (which shuffles across the warp) runs unconditionally
-        // and its result is selected afterwards.
-        const int kind = slot < q_heads ? 0 : (slot < q_heads + p.Hkv ? 1 : 2);
-        const int h = kind == 0 ? slot : (kind == 1 ? slot - q_heads : slot - q_heads - p.Hkv);
-        const bool transform = kind == 0 || (kind == 1 && p.transform_k);
-        const uint4 *src = kind == 0 ? p.q_in : (kind == 1 ? p.k_in : p.v_in);
-        const long long src_idx = (bt * (kind == 0 ? p.Hq : p.Hkv) + h) * 16 + j;
-        uint4 x = make_uint4(0, 0, 0, 0);
-        uint4 cv = x, sv = x;
-        if (ok) x = src[src_idx];
+        uint4 cv = make_uint4(0, 0, 0, 0), sv = cv;
+        if (!ok) x = cv;
         if (ok && transform) {
             cv = p.cos[(long long)safe_pos * 8 + (j & 7)];
             sv = p.sin[(long long)safe_pos * 8 + (j & 7)];
