@@ -51,8 +51,8 @@ B, HQ, HKV, D, T_MAX = 32, 12, 12, 128, 2048
 NSETS = 4
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode_attn_kernel launch on this workload
 # (one `ncu --set full` capture of this file's default command, summarised beside the other kernel profiles)
-TRAFFIC_BYTES_PER_LAUNCH = 202.78e6
-TRAFFIC_CAPTURE = "ncu --set full capture of decode_attn_kernel<0,1>, 2026-11-25, kernel source of commit 9cc5280"
+TRAFFIC_BYTES_PER_LAUNCH = 202.63e6
+TRAFFIC_CAPTURE = "ncu --set full capture of decode_attn_kernel<0,1,0> on this workload, 2026-11-25 (198.64 MB read + 4.00 MB written)"
 METRIC = "decode tokens/s (KV append + decode attention, B=32 x 12 heads x 128, ragged cache)"
 WORKLOAD = "configs[1]: op-level KV append + decode attention, B=32, 12q/12kv heads, D=128, T_max=2048, ragged seqlens seed 2"
 
