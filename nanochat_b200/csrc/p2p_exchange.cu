@@ -57,6 +57,11 @@ __global__ void __launch_bounds__(256) p2p_wait_combine_kernel(const float *__re
     // counter is stable by then, since those kernels only started after the previous step's
     // wait/combine grid (the only writer of the counter) had completed.  The local rank's flag is set by
     // the last block of its own push, so passing the poll implies the local partial is in place too.
+    // Whatever follows in the stream may be scheduled now: a libnckv append (and the attention kernel
+    // behind it) then runs its own prologue, and loads the first key tiles of the next step, while this
+    // grid waits for the peers.  Nothing a dependent reads before its own grid-dependency wait is
+    // written here.
+    pdl_launch_dependents();
     const unsigned step = *step_counter + 1u;  // the step whose partials are awaited
     const unsigned parity = step & 1u;
     unsigned *done = step_counter + 1;         // blocks of this grid that have finished
