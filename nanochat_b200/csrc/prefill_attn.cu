@@ -56,6 +56,7 @@ struct PrefillParams {
     int32_t *status;
     int B, T_new, Hq, Hkv, T_k;
     int group_pairs;  // (row, q head) pairs per scheduling group, see the work order in the kernel
+    int pair_major;   // order inside a group: 1 pair by pair, 0 longest tiles of all pairs first
     int window_left;
     float scale_log2;
 };
@@ -97,18 +98,26 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 
     const int tid = threadIdx.x, warp = tid >> 5;
     // Work order.  CTAs are handed to the SMs in block-index order, which makes the grid a work queue.
-    // Causal query tiles differ in length by up to n_qtiles x, so the order decides the tail: the
-    // (row, q head) pairs are taken in groups of group_pairs (sized on the host so that a group's K/V
-    // stays in L2 while its query tiles reuse it); inside a group all pairs' longest tiles come first,
-    // their shortest last, with the pairs (and so the q heads that share a kv head) adjacent.
+    // Causal query tiles differ in length by up to n_qtiles x, so the order decides both the tail and
+    // which tiles share an SM.  The (row, q head) pairs are taken in groups of group_pairs (sized on the
+    // host so that a group's K/V stays in L2 while its query tiles reuse it).  Inside a group either
+    // pair by pair with a pair's long tiles first (long and short tiles then meet on an SM and fill each
+    // other's gaps: best while a pair has few tiles), or all pairs' longest tiles first and their shortest
+    // last (bounds the tail when one tile is a large share of an SM's work: long sequences).
     const int n_qtiles = (p.T_new + PF_M - 1) / PF_M;
     const int n_pairs = p.Hq * p.B;
     const int per_group = p.group_pairs * n_qtiles;
     const int grp = (int)blockIdx.x / per_group;
     const int in_grp = (int)blockIdx.x - grp * per_group;
     const int grp_pairs = min(p.group_pairs, n_pairs - grp * p.group_pairs);
-    const int qt = n_qtiles - 1 - in_grp / grp_pairs;  // long tiles first
-    const int pair = grp * p.group_pairs + in_grp % grp_pairs;
+    int qt, pair;
+    if (p.pair_major) {  // pair by pair, a pair's long tiles first
+        pair = grp * p.group_pairs + in_grp / n_qtiles;
+        qt = n_qtiles - 1 - in_grp % n_qtiles;
+    } else {             // all pairs' longest tiles first, their shortest last
+        qt = n_qtiles - 1 - in_grp / grp_pairs;
+        pair = grp * p.group_pairs + in_grp % grp_pairs;
+    }
     const int hq = pair % p.Hq, b = pair / p.Hq;
     const int hkv = hq / (p.Hq / p.Hkv);
     const int t0 = qt * PF_M;
@@ -230,14 +239,16 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 tc_fence_after();
                 const uint64_t dk = desc_k + (uint64_t)((stage * PF_KV_BYTES) >> 4);
                 const uint32_t ds = tmem_s + (uint32_t)(tile & 1) * PF_N;
+                if (leader) {  // one thread runs the whole burst: nothing diverges and reconverges between the instructions
 #pragma unroll
-                for (int kk = 0; kk < NCKV_D / 16; ++kk) {
-                    const uint32_t off = (uint32_t)(kk & 3) * 32;
-                    const uint64_t da = desc_q + (uint64_t)(((kk >> 2) * (PF_Q_BYTES / 2) + off) >> 4);
-                    const uint64_t db = dk + (uint64_t)(((kk >> 2) * (PF_KV_BYTES / 2) + off) >> 4);
-                    if (leader) umma_bf16(ds, da, db, IDESC_S, kk > 0 ? 1u : 0u);
+                    for (int kk = 0; kk < NCKV_D / 16; ++kk) {
+                        const uint32_t off = (uint32_t)(kk & 3) * 32;
+                        const uint64_t da = desc_q + (uint64_t)(((kk >> 2) * (PF_Q_BYTES / 2) + off) >> 4);
+                        const uint64_t db = dk + (uint64_t)(((kk >> 2) * (PF_KV_BYTES / 2) + off) >> 4);
+                        umma_bf16(ds, da, db, IDESC_S, kk > 0 ? 1u : 0u);
+                    }
+                    umma_commit(&bar_s[tile & 1]);
                 }
-                if (leader) umma_commit(&bar_s[tile & 1]);
                 __syncwarp();
                 return true;
             };
@@ -250,13 +261,15 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 // (leading offset), 8-key groups 1024 B apart (stride offset)
                 const uint64_t dv = desc_v + (uint64_t)((stage * PF_KV_BYTES) >> 4);
                 const uint32_t pbase = tmem_s + (uint32_t)(tile & 1) * PF_N;
+                if (leader) {
 #pragma unroll
-                for (int ks = 0; ks < PF_N / 16; ++ks) {
-                    // P(tile) sits in the first 32 columns of its S buffer; 16 keys = 8 columns
-                    const uint64_t db = dv + (uint64_t)((ks * 16 * 128) >> 4);
-                    if (leader) umma_bf16_a_tmem(tmem_o, pbase + (uint32_t)ks * 8, db, IDESC_O, (tile > 0 || ks > 0) ? 1u : 0u);
+                    for (int ks = 0; ks < PF_N / 16; ++ks) {
+                        // P(tile) sits in the first 32 columns of its S buffer; 16 keys = 8 columns
+                        const uint64_t db = dv + (uint64_t)((ks * 16 * 128) >> 4);
+                        umma_bf16_a_tmem(tmem_o, pbase + (uint32_t)ks * 8, db, IDESC_O, (tile > 0 || ks > 0) ? 1u : 0u);
+                    }
+                    if (commit_now) umma_commit(&bar_o[tile & 1]);
                 }
-                if (leader && commit_now) umma_commit(&bar_o[tile & 1]);
                 __syncwarp();
                 return true;
             };
@@ -319,12 +332,11 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             const bool edge = (key0 + PF_N - 1 > L + t0) || (key0 + PF_N > kv_hi) ||
                               (p.window_left >= 0 && key0 < L + t0 + PF_M - 1 - p.window_left);
             if (edge) {
+                // this row sees columns [c_lo, c_hi) of its share of the tile
+                const int c_hi = min(pos, kv_hi - 1) - (key0 + half * HN) + 1;
+                const int c_lo = p.window_left >= 0 ? pos - p.window_left - (key0 + half * HN) : 0;
 #pragma unroll
-                for (int c = 0; c < HN; ++c) {
-                    const int j = key0 + half * HN + c;
-                    const bool visible = (j <= pos) && (j < kv_hi) && (p.window_left < 0 || pos - j <= p.window_left);
-                    s_val[c] = visible ? s_val[c] : -INFINITY;
-                }
+                for (int c = 0; c < HN; ++c) s_val[c] = (c >= c_lo && c < c_hi) ? s_val[c] : -INFINITY;
             }
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains instead of one
 #pragma unroll
@@ -529,6 +541,8 @@ extern "C" int nckv_prefill_attn(const void *q, const void *k, const void *v, co
         g -= g % (Hq / Hkv);  // keep the q heads of a kv head in one group
         p.group_pairs = (int)(g < Hq / Hkv ? Hq / Hkv : (g > (long long)Hq * B ? (long long)Hq * B : g));
     }
+
+    p.pair_major = n_qtiles <= 16;  // measured on B200: 2048-token rows and shorter prefer it, 4096 and longer do not
 
     const size_t smem = prefill_smem_bytes();
     static bool attr_set[64] = {false};
