@@ -919,6 +919,46 @@ def run_case(args):
         out.update(metric="prefill broadcast GB/s (written + read)", value=nbytes / sec / 1e9, unit="GB/s",
                    us_per_call=sec * 1e6, algorithmic_bytes=nbytes, frac=nbytes / sec / 1e9 / peak, peak=peak,
                    peak_kind=f"of {peak_kind}", config={"L": L, "B": Bc, "p": p, "Hkv": Hkv})
+    elif args.case == "decode_paged":       # one layer of configs[3] in pages of 192 tokens: same rows, scattered pages
+        Bc, Hq, Hkv, T, pt = 256, 16, 4, 4096, 192
+        lens = torch.randint(128, 4095, (Bc,), dtype=torch.int32, generator=torch.Generator().manual_seed(5))
+        pages_of = [-(-(int(L) + 1) // pt) for L in lens.tolist()]
+        n_pages = sum(pages_of)
+        max_pages = -(-T // pt)
+        perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(6)).to(torch.int32)
+        table = torch.full((Bc, max_pages), -1, dtype=torch.int32)
+        at = 0
+        for b_, n_ in enumerate(pages_of):
+            table[b_, :n_] = perm[at:at + n_]
+            at += n_
+        kp, vp = rnd(n_pages, pt, Hkv, D), rnd(n_pages, pt, Hkv, D)
+        q = rnd(Bc, Hq, D)
+        table_d, lens_d = table.to(dev), lens.to(dev)
+        sec = _time_cuda(lambda i: ops.decode_attention_paged(q, kp, vp, table_d, lens_d, 1, -1), iters)
+        nbytes = 4 * Hkv * D * int((lens.long() + 1).sum()) + 4 * Bc * Hq * D + 4 * Bc
+        out.update(metric="decode attention KV-read GB/s (paged storage)", value=nbytes / sec / 1e9, unit="GB/s", us_per_call=sec * 1e6,
+                   algorithmic_bytes=nbytes, frac=nbytes / sec / 1e9 / peak, peak=peak, peak_kind=f"of {peak_kind}",
+                   pool_bytes=2 * n_pages * pt * Hkv * D * 2, dense_bytes=2 * Bc * T * Hkv * D * 2,
+                   config={"B": Bc, "Hq": Hq, "Hkv": Hkv, "T_max": T, "page_tokens": pt, "pages": n_pages})
+    elif args.case == "prefill_paged":      # configs[4] broadcast into a paged cache: prompt pages shared by the 64 rows
+        from nanochat_b200.engine import KVCache, PagedKVCache
+        L, Bc, p_, Hkv, pt, cap = 1, 64, 8192, 4, 192, 8192 + 1024
+        prompt = KVCache(1, Hkv, p_, D, L, dev, bf)
+        prompt.k_cache.copy_(rnd(*prompt.k_cache.shape))
+        prompt.v_cache.copy_(rnd(*prompt.v_cache.shape))
+        prompt.advance(p_)
+        own = -(-cap // pt) - p_ // pt
+        cache = PagedKVCache(Bc, Hkv, cap, D, L, dev, bf, page_tokens=pt, n_pages=p_ // pt + Bc * own)
+
+        def fill(i):
+            cache.reset()
+            cache.prefill(prompt)
+
+        sec = _time_cuda(fill, iters)
+        written = 2 * L * cache.pages_in_use() * pt * Hkv * D * 2
+        out.update(metric="prefill into a paged cache, us per call (host bookkeeping included)", value=sec * 1e6, unit="us",
+                   bytes_written_upper_bound=written, dense_broadcast_bytes=2 * L * Bc * p_ * Hkv * D * 2,
+                   pages_in_use=cache.pages_in_use(), config={"L": L, "B": Bc, "p": p_, "Hkv": Hkv, "page_tokens": pt})
     elif args.case == "append":             # configs[1] append alone
         kc, vc = rnd(B, T_MAX, HKV, D), rnd(B, T_MAX, HKV, D)
         q, k, v = rnd(B, 1, HQ, D), rnd(B, 1, HKV, D), rnd(B, 1, HKV, D)
@@ -947,7 +987,7 @@ def main():
                     help="headline workload only: skip the long_context, d24_sharded and gpu_reference legs")
     ap.add_argument("--case", default=None,
                     help="secondary op-level measurement instead of the headline workload: decode_long, decode_gqa, "
-                         "decode_gqa_window, decode_d24, prefill, broadcast, append, engine_d24, engine_d24_small, engine_d32, "
+                         "decode_gqa_window, decode_d24, decode_paged, prefill, prefill_paged, broadcast, append, engine_d24, engine_d24_small, engine_d32, "
                          "engine_d32_small, engine_api_d24, engine_api_small")
     args = ap.parse_args()
     global REGIONS_OVERRIDE

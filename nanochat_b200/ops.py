@@ -22,6 +22,10 @@ _F_APPEND = _lib.lib.nckv_append
 _F_DECODE = _lib.lib.nckv_decode_attn
 _F_PREFILL = _lib.lib.nckv_prefill_attn
 _workspaces = {}  # (device index, stream id) -> uint8 tensor
+# Workspaces that a larger one has replaced.  They are kept alive for the life of the process: a CUDA
+# graph captured while one of them was current still launches kernels that point at it.  A (device,
+# stream) pair only ever grows its workspace a handful of times (the size depends on Hq / Hkv alone).
+_retired_workspaces = []
 
 
 def _ptr(t):
@@ -104,6 +108,8 @@ def workspace(device, B, Hq, Hkv):
     key = (idx, torch.cuda.current_stream(idx).cuda_stream)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < need:
+        if ws is not None:
+            _retired_workspaces.append(ws)
         ws = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=torch.device("cuda", idx))
         _workspaces[key] = ws
     return ws
@@ -119,7 +125,11 @@ def read_status(device, clear=True):
     if ws is None:
         return 0
     with torch.cuda.device(idx):
-        return _lib.call("nckv_read_status", _ptr(ws), int(bool(clear)), _stream(idx))
+        st = _lib.call("nckv_read_status", _ptr(ws), int(bool(clear)), _stream(idx))
+        for old in _retired_workspaces:  # graphs captured earlier report into the workspace they were captured with
+            if old.device.index == idx:
+                st |= _lib.call("nckv_read_status", _ptr(old), int(bool(clear)), _stream(idx))
+    return st
 
 
 def check_status(device):
