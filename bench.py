@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-extras]
 
-Headline workload (BASELINE configs[1]): B=32 rows, 12 q heads, 12 kv heads, head_dim 128, cache
+Headline workload (benchmark configuration 1, "configs[1]"): B=32 rows, 12 q heads, 12 kv heads, head_dim 128, cache
 capacity 2048, cache_seqlens uniform in [1, 2047] (torch CPU generator, seed 2), caches and new
 q/k/v ~ N(0,1) bf16, one new token per row, full causal.  One "step" is one pass of the hot path
 over that batch: the fused RoPE + QK-norm + append launch followed by the split-KV decode
@@ -25,10 +25,10 @@ come from HBM.
             on the same device and data, beside the kernels that replace it
 
 Two more legs ride in the same JSON line (skipped with --no-extras):
-  long_context  BASELINE configs[4] (B=8, 16/4 heads, T_max=65536, lengths U[32768,65536]) with the keys
+  long_context  benchmark configuration 4 ("configs[4]") (B=8, 16/4 heads, T_max=65536, lengths U[32768,65536]) with the keys
             split block-cyclically over the N ranks and the log-sum-exp exchange over NVLink peer memory
             (and over NCCL), checked in-run against the unsplit single-GPU result on the same data
-  d24_sharded   BASELINE configs[2] (d24 model, 64 sequences, 512-token prompts, greedy decode) with the
+  d24_sharded   benchmark configuration 2 ("configs[2]") (d24 model, 64 sequences, 512-token prompts, greedy decode) with the
             fixed batch sharded by sequence over the N ranks (strong scaling, weights replicated)
 """
 import argparse
@@ -664,7 +664,7 @@ def run_ours(args):
 
 
 # ------------------------------------------------------------------------------------------------
-# secondary cases (one JSON line each): the other kernels and the other BASELINE configs, op level
+# secondary cases (one JSON line each): the other kernels and the other benchmark configurations, op level
 # ------------------------------------------------------------------------------------------------
 def _time_cuda(fn, iters, warmup=3):
     for i in range(warmup):

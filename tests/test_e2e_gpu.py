@@ -1,4 +1,4 @@
-"""End to end on the GPU: BASELINE configs[0] (depth-4 GPT, 32-token prompt, 4 samples, 64 greedy
+"""End to end on the GPU: benchmark configuration 0 (depth-4 GPT, 32-token prompt, 4 samples, 64 greedy
 tokens) through Engine + GPT with the CUDA kernels, against the same model driven through the
 torch-eager port of the reference path (its bf16 GPU path: eager RoPE/norm/scale ops, slice-assign
 append, SDPA)."""

@@ -207,7 +207,7 @@ def test_engine_calculator_tool_forces_tokens():
 
 
 # ------------------------------------------------------------------------------------------------
-# GPT glue + Engine against the reference's own greedy streams (BASELINE configs[0])
+# GPT glue + Engine against the reference's own greedy streams (benchmark configuration 0)
 # ------------------------------------------------------------------------------------------------
 def _config0_model(binding):
     cfg = GPTConfig(sequence_len=2048, vocab_size=32768, n_layer=4, n_head=2, n_kv_head=2, n_embd=256,

@@ -174,7 +174,7 @@ def test_decode_attention_window_edges(window):
 
 
 def test_decode_attention_config1_shape_and_split_invariance():
-    """BASELINE configs[1]: B=32, 12/12 heads, capacity 2048, lengths uniform in [1, 2047] (seed 2)."""
+    """Benchmark configuration 1: B=32, 12/12 heads, capacity 2048, lengths uniform in [1, 2047] (seed 2)."""
     seqlens = torch.randint(1, 2048, (32,), dtype=torch.int32, generator=torch.Generator().manual_seed(2)).tolist()
     out = run_decode_case(32, 12, 12, 2048, seqlens, -1, seed=2)
     # same rows evaluated alone (different slicing of the tile sequence) must agree closely

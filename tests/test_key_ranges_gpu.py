@@ -3,7 +3,7 @@
 ``nckv_decode_key_ranges`` dumps the per-row key ranges from the routine the decode kernels themselves
 call (visible-key rule of nanochat/flash_attention.py:83-88 and :94-100); ``nckv_kv_split_plan`` dumps
 the block-cyclic owner rule that the *_split kernels apply.  Both are compared with
-``oracle.kv_oracle.visible_range`` / ``nanochat_b200.dist.owned_below`` for every BASELINE
+``oracle.kv_oracle.visible_range`` / ``nanochat_b200.dist.owned_below`` for every benchmark
 configuration's seeded lengths and for the edge lengths around each window.
 """
 import numpy as np
@@ -28,7 +28,7 @@ def _expected_ranges(lens, T_max, window, kv_begin, kv_end):
 
 
 def _seeded_lengths():
-    """cache_seqlens of every BASELINE configuration, drawn as its description says."""
+    """cache_seqlens of every benchmark configuration, drawn as its description says."""
     g = lambda s: torch.Generator().manual_seed(s)
     return {
         "configs[0] decode steps": (np.arange(32, 96, dtype=np.int32), 96),

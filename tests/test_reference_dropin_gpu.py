@@ -8,7 +8,7 @@ mirrors, exactly as an integrator would do it:
     nanochat.gpt.flash_attn   -> nanochat_b200.flash_attention.flash_attn
     nanochat.engine.KVCache   -> nanochat_b200.engine.KVCache
 
-Model: BASELINE configs[0] (depth 4, 2 heads x 128, vocab 32768, SSSL), 32-token prompt, 4 samples,
+Model: benchmark configuration 0 (depth 4, 2 heads x 128, vocab 32768, SSSL), 32-token prompt, 4 samples,
 64 greedy tokens; the stock initialisation and the "binding" one (c_proj re-drawn so that attention
 reaches the logits).  These tests FAIL when oracle/_ref is missing; they do not skip.
 """
