@@ -108,16 +108,14 @@ class PagedKVCache:
         if torch.device(device).type == "cuda":
             self._table_host = self._table_host.pin_memory()
         self._free = list(range(self.n_pages - 1, -1, -1))
-        self._rows = [[] for _ in range(batch_size)]   # pages of each row, in order
-        self._shared = 0                                # leading pages of every row that are shared
+        self._count = [0] * batch_size   # pages in each row's table, shared ones included
+        self._shared = 0                 # leading pages of every row that all rows share
         self.prev_embedding = None
 
     # ---- the reference's KVCache methods -------------------------------------------------------
     def reset(self):
-        for b, pages in enumerate(self._rows):
-            own = pages[self._shared:] if b else pages  # shared pages are returned once (by row 0)
-            self._free.extend(reversed(own))
-            self._rows[b] = []
+        self._free = list(range(self.n_pages - 1, -1, -1))
+        self._count = [0] * self.batch_size
         self._shared = 0
         self._table_host.fill_(-1)
         self.block_table.fill_(-1)
@@ -138,52 +136,62 @@ class PagedKVCache:
     def pages_in_use(self):
         return self.n_pages - len(self._free)
 
+    def _take(self, n):
+        if n > len(self._free):
+            raise RuntimeError(f"PagedKVCache: page pool of {self.n_pages} pages exhausted ({n} more pages needed, "
+                               f"{len(self._free)} free)")
+        taken = self._free[len(self._free) - n:]
+        del self._free[len(self._free) - n:]
+        taken.reverse()
+        return taken
+
     def reserve(self, n_tokens):
         """Give every row the pages for positions < n_tokens.  Cheap when nothing has to be added."""
         need = -(-min(n_tokens, self.max_pages * self.page_tokens) // self.page_tokens)
-        changed = False
-        for b, pages in enumerate(self._rows):
-            while len(pages) < need:
-                if not self._free:
-                    raise RuntimeError(f"PagedKVCache: page pool of {self.n_pages} pages exhausted "
-                                       f"(row {b} needs page {len(pages)} for {n_tokens} tokens)")
-                page = self._free.pop()
-                self._table_host[b, len(pages)] = page
-                pages.append(page)
-                changed = True
-        if changed:
-            self.block_table.copy_(self._table_host, non_blocking=True)
+        lo = min(self._count)
+        if lo >= need:
+            return
+        if lo == max(self._count):  # the usual case: rows grow in lock step, one block of table columns
+            fresh = self._take(self.batch_size * (need - lo))
+            self._table_host[:, lo:need] = torch.tensor(fresh, dtype=torch.int32).view(self.batch_size, need - lo)
+            self._count = [need] * self.batch_size
+        else:
+            for b, have in enumerate(self._count):
+                if have < need:
+                    self._table_host[b, have:need] = torch.tensor(self._take(need - have), dtype=torch.int32)
+                    self._count[b] = need
+        self.block_table.copy_(self._table_host, non_blocking=True)
 
     def prefill(self, other):
         """KVCache.prefill (engine.py:123-137) from a dense batch-1 prompt cache, sharing the prompt's
         full pages between the rows."""
-        assert self.pages_in_use() == 0 and not any(self._rows), "Cannot prefill a non-empty KV cache"
+        assert self.pages_in_use() == 0 and max(self._count) == 0, "Cannot prefill a non-empty KV cache"
         assert self.n_layers == other.n_layers and self.n_heads == other.n_heads and self.head_dim == other.head_dim
         assert self.max_seq_len >= other.max_seq_len
         assert other.batch_size == 1 and not getattr(other, "paged", False), "prefill takes a dense batch-1 cache"
         p = other.get_pos()
         pt = self.page_tokens
         n_full, tail = divmod(p, pt)
-        if len(self._free) < n_full + (self.batch_size if tail else 0):
-            raise RuntimeError(f"PagedKVCache: {n_full} shared + {self.batch_size} private pages do not fit the pool")
-        shared = [self._free.pop() for _ in range(n_full)]
-        jobs = [(page, i * pt, pt) for i, page in enumerate(shared)]
-        for b in range(self.batch_size):
-            self._rows[b] = list(shared)
-            self._table_host[b, :n_full] = torch.tensor(shared, dtype=torch.int32) if n_full else self._table_host[b, :0]
-            if tail:
-                page = self._free.pop()
-                self._rows[b].append(page)
-                self._table_host[b, n_full] = page
-                jobs.append((page, n_full * pt, tail))
+        B = self.batch_size
+        pages = torch.tensor(self._take(n_full + (B if tail else 0)), dtype=torch.int32)
+        shared, private = pages[:n_full], pages[n_full:]
+        jobs = torch.empty(pages.numel(), 3, dtype=torch.int32)
+        jobs[:, 0] = pages
+        jobs[:n_full, 1] = torch.arange(n_full, dtype=torch.int32) * pt
+        jobs[:n_full, 2] = pt
+        jobs[n_full:, 1] = n_full * pt
+        jobs[n_full:, 2] = tail
+        self._table_host[:, :n_full] = shared
+        if tail:
+            self._table_host[:, n_full] = private
         self._shared = n_full
+        self._count = [n_full + (1 if tail else 0)] * B
         self.block_table.copy_(self._table_host, non_blocking=True)
-        if jobs:
-            ops.paged_fill(other.k_cache, other.v_cache, self.k_cache, self.v_cache,
-                           torch.tensor(jobs, dtype=torch.int32).to(self.block_table.device))
+        if pages.numel():
+            ops.paged_fill(other.k_cache, other.v_cache, self.k_cache, self.v_cache, jobs.to(self.block_table.device))
         self.cache_seqlens.fill_(p)
         if other.prev_embedding is not None:
-            self.prev_embedding = other.prev_embedding.expand(self.batch_size, -1, -1).clone()
+            self.prev_embedding = other.prev_embedding.expand(B, -1, -1).clone()
 
 
 # ------------------------------------------------------------------------------------------------
