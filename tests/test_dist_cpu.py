@@ -84,6 +84,64 @@ def _worker(rank, world, port, B, Hq, Hkv, D, T, seqlens, window, ret):
         dist.destroy_process_group()
 
 
+def _cyclic_worker(rank, world, port, block, seqlens, ret):
+    """Block-cyclic ownership: every rank attends over the keys it owns (stored compactly), partials are
+    exchanged and combined; the kernels are replaced by the numpy oracle."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        B, Hq, Hkv, D, T = len(seqlens), 4, 2, 16, 160
+        g = torch.Generator().manual_seed(3)
+        q = torch.randn(B, Hq, D, generator=g)
+        kc = torch.randn(B, T, Hkv, D, generator=g)
+        vc = torch.randn(B, T, Hkv, D, generator=g)
+        lens = torch.tensor(seqlens, dtype=torch.int32)
+        mine = torch.tensor([p for p in range(T) if (p // block) % world == rank], dtype=torch.long)
+
+        class OracleSplit(KVSplitAttention):
+            def _partial(self, q_, kc_, vc_, lens_, out_buf, lse_buf, push):
+                assert self.split == (world, rank, block) and not push
+                local = torch.tensor([owned_below(int(L) + 1, world, rank, block) for L in lens_], dtype=torch.int32)
+                # the oracle takes lengths before the new token; the local caches already hold it
+                o, l = O.attention_kvcache(q_.numpy()[:, None], kc_.numpy(), vc_.numpy(), (local - 1).clamp(min=-1).numpy())
+                empty = (local == 0).numpy()
+                o[empty], l[empty] = 0.0, -np.inf
+                out_buf.copy_(torch.from_numpy(o[:, 0]))
+                lse_buf.copy_(torch.from_numpy(l[:, 0]))
+
+            def _combine(self, po, pl):
+                o, l = O.lse_combine(po.numpy(), pl.numpy())
+                return torch.from_numpy(o), torch.from_numpy(l)
+
+        att = OracleSplit(T, block=block)
+        assert att.local_capacity == owned_below(T, world, rank, block) == mine.numel()
+        out = att.attend(q, kc[:, mine].contiguous(), vc[:, mine].contiguous(), lens)
+        full, _ = O.attention_kvcache(q.numpy()[:, None], kc.numpy(), vc.numpy(), lens.numpy())
+        err = float(np.abs(out.numpy() - full[:, 0]).max())
+        gathered = [None] * world
+        dist.all_gather_object(gathered, err)
+        if rank == 0:
+            ret.put(gathered)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,block", [(2, 16), (3, 32)])
+def test_block_cyclic_split_matches_unsplit_attention(world, block):
+    ctx = mp.get_context("spawn")
+    ret = ctx.Queue()
+    port = _free_port()
+    seqlens = [159, 3, 40, 95]  # row 1 lives on the first rank only
+    procs = [ctx.Process(target=_cyclic_worker, args=(r, world, port, block, seqlens, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    errs = ret.get(timeout=10)
+    assert len(errs) == world and max(errs) < 1e-5, errs
+
+
 @pytest.mark.parametrize("world,window", [(2, -1), (2, 40), (3, -1)])
 def test_kv_split_exchange_matches_unsplit_attention(world, window):
     ctx = mp.get_context("spawn")

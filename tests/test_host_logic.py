@@ -249,3 +249,50 @@ def test_config0_greedy_streams_equal_reference(golden_dir, binding):
         model.window_sizes = [(8, 0), (8, 0), (8, 0), (2048, 0)]
         res, _ = eng.generate_batch(prompt, num_samples=2, max_tokens=24, temperature=0.0)
         assert np.array_equal(np.array(res), g[tag + "_w8"])
+
+
+# ------------------------------------------------------------------------------------------------
+# paged cache: host-side page bookkeeping (the copy kernel replaced by a torch stand-in)
+# ------------------------------------------------------------------------------------------------
+def test_paged_cache_tables_sharing_and_growth(monkeypatch):
+    from nanochat_b200 import ops
+    from nanochat_b200.engine import PagedKVCache
+
+    def fill_on_host(src_k, src_v, k_pool, v_pool, jobs):
+        for page, t0, n in jobs.tolist():
+            k_pool[:, page, :n] = src_k[:, 0, t0:t0 + n]
+            v_pool[:, page, :n] = src_v[:, 0, t0:t0 + n]
+
+    monkeypatch.setattr(ops, "paged_fill", fill_on_host)
+    L, B, H, D, pt, p, cap = 2, 3, 2, 8, ops.PAGE_TILE, 2 * ops.PAGE_TILE + 5, 5 * ops.PAGE_TILE
+    prompt = KVCache(1, H, p, D, L, "cpu", torch.float32)
+    prompt.k_cache.copy_(torch.randn(prompt.k_cache.shape))
+    prompt.v_cache.copy_(torch.randn(prompt.v_cache.shape))
+    prompt.advance(p)
+    prompt.prev_embedding = torch.randn(1, 1, 4)
+    cache = PagedKVCache(B, H, cap, D, L, "cpu", torch.float32, page_tokens=pt, n_pages=2 + B * 2 + 1)
+    assert cache.block_table.shape == (B, 5) and cache.pages_in_use() == 0
+    cache.prefill(prompt)
+    t = cache.block_table
+    assert cache.cache_seqlens.tolist() == [p] * B and cache.pages_in_use() == 2 + B
+    assert all(t[b, :2].tolist() == t[0, :2].tolist() for b in range(B))           # full prompt pages: shared
+    assert len(set(t[:, 2].tolist())) == B and (t[:, 3:] == -1).all()              # tail page: one per row
+    for b in range(B):                                                              # every token readable through the table
+        for tok in (0, pt - 1, pt, p - 1):
+            page, off = int(t[b, tok // pt]), tok % pt
+            assert torch.equal(cache.k_cache[:, page, off], prompt.k_cache[:, 0, tok])
+            assert torch.equal(cache.v_cache[:, page, off], prompt.v_cache[:, 0, tok])
+    assert cache.prev_embedding.shape == (B, 1, 4)
+    cache.reserve(p + 1)                                                            # still inside the tail page
+    assert cache.pages_in_use() == 2 + B
+    cache.reserve(3 * pt + 1)                                                       # one more page per row
+    assert cache.pages_in_use() == 2 + 2 * B and (cache.block_table[:, 3] >= 0).all()
+    assert len(set(cache.block_table[cache.block_table >= 0].tolist())) == 2 + 2 * B  # no page handed out twice
+    with pytest.raises(RuntimeError, match="exhausted"):
+        cache.reserve(cap + 10 * pt)                                                # clamps to capacity: 5 pages per row, one page short
+    with pytest.raises(AssertionError):
+        cache.prefill(prompt)                                                       # not empty
+    cache.reset()
+    assert cache.pages_in_use() == 0 and (cache.block_table == -1).all() and cache.get_pos() == 0
+    with pytest.raises(ValueError):
+        PagedKVCache(1, H, cap, D, L, "cpu", torch.float32, page_tokens=pt + 1)
