@@ -2,10 +2,13 @@
 // prefill, flash_attn_func), on the 5th-generation tensor cores: tcgen05.mma with Q, K, V in
 // shared memory (TMA, 128-byte swizzle), the probabilities and the accumulators in tensor memory.
 //
-// One CTA owns a tile of PF_M = 128 query tokens of one (row, q head) and walks the visible keys
-// in tiles of PF_N = 64.  Three roles, connected by mbarriers only (no CTA-wide barrier in the loop):
-//   producer warp     one lane issues the TMA copies: Q once, K and V through two stages each; a
-//                     stage is refilled as soon as the product that read it has completed
+// A work item is a tile of PF_M = 128 query tokens of one (row, q head) with the keys it sees, walked
+// in tiles of PF_N = 64.  The CTAs are persistent, two per SM, and each works through a fixed list of
+// items as ONE stream of key tiles: the copies and the first score products of the next item are
+// issued while the softmax of the current item's last tiles and its output are still under way.
+// Three roles, connected by mbarriers only (no CTA-wide barrier in the loop):
+//   producer warp     one lane issues the TMA copies: Q per item, K through two and V through three
+//                     stages; a stage is refilled as soon as the product that read it has completed
 //   MMA warp          one lane issues, per tile,
 //                       S = Q K^T   8 x tcgen05.mma (M128 N64 K16) into one of two S buffers in
 //                                   TMEM (columns [0, 64) and [64, 128)), two tiles ahead of the softmax
@@ -23,8 +26,9 @@
 //                     touch the accumulator.  O is read once, at the end.
 // Products issued by one thread execute in order: S of tile it+2 is issued behind O += P V(it)
 // and may therefore overwrite the buffer P(it) was read from.
-// Two CTAs fit on an SM (about 96 KB of shared memory and 256 of the 512 TMEM columns each), so
-// one CTA's softmax overlaps the other's tensor work.
+// Two CTAs fit on an SM (112 KB of shared memory and 256 of the 512 TMEM columns each), so one
+// CTA's softmax overlaps the other's tensor work.  mbarrier waits are made by one lane per warp:
+// a poll by 32 lanes is served lane after lane, and even a satisfied wait costs about 100 cycles.
 // Every barrier wait is bounded; a wait that runs out sets NCKV_ST_TIMEOUT, the CTA stops issuing
 // work, frees its TMEM and returns.
 //
@@ -55,13 +59,84 @@ struct PrefillParams {
     __nv_bfloat16 *out;
     int32_t *status;
     int B, T_new, Hq, Hkv, T_k;
-    int group_pairs;  // (row, q head) pairs per scheduling group, see the work order in the kernel
-    int pair_major;   // order inside a group: 1 pair by pair, 0 longest tiles of all pairs first
+    int n_qtiles, n_items;
+    int group_pairs;  // (row, q head) pairs per scheduling group, see the work order below
+    int n_groups;     // the last group takes the remaining pairs (fewer than 2 group_pairs)
     int window_left;
     float scale_log2;
 };
 
+// One work item: PF_M query tokens of one (row, q head) and the key tiles they see.
+struct PfItem {
+    int hq, b, hkv, t0, L;
+    int kv_lo, kv_hi;  // keys any row of the tile may see: [kv_lo, kv_hi)
+    int n_tiles;
+};
 
+// Work order.  The CTAs are persistent (two per SM) and each takes a fixed subsequence of the item
+// list, so every role of a CTA can enumerate its items without talking to the others.  Causal
+// items differ in length by up to n_qtiles x; the list is ordered longest first inside groups of
+// group_pairs (row, q head) pairs (sized on the host so that a group's K/V stays in L2 while its
+// query tiles reuse it), and the list is dealt out back and forth (round r: item r G + c to CTA c
+// when r is even, r G + G - 1 - c when odd), which evens out the sums without a shared counter.
+__device__ __forceinline__ int pf_item_index(const PrefillParams &p, int seq) {
+    const int G = (int)gridDim.x, c = (int)blockIdx.x;
+    const long long base = (long long)seq * G;
+    const long long idx = base + ((seq & 1) ? G - 1 - c : c);
+    return idx < p.n_items ? (int)idx : -1;
+}
+
+__device__ __forceinline__ PfItem pf_item(const PrefillParams &p, int idx) {
+    PfItem it;
+    const int n_pairs = p.Hq * p.B;
+    const int per_group = p.group_pairs * p.n_qtiles;
+    const int grp = min(idx / per_group, p.n_groups - 1);
+    const int in_grp = idx - grp * per_group;
+    const int grp_pairs = grp == p.n_groups - 1 ? n_pairs - grp * p.group_pairs : p.group_pairs;
+    const int qt = p.n_qtiles - 1 - in_grp / grp_pairs;  // all pairs' longest tiles first
+    const int pair = grp * p.group_pairs + in_grp % grp_pairs;
+    it.hq = pair % p.Hq;
+    it.b = pair / p.Hq;
+    it.hkv = it.hq / (p.Hq / p.Hkv);
+    it.t0 = qt * PF_M;
+    int L = p.seqlens ? p.seqlens[it.b] : 0;
+    if (L < 0) L = 0;  // reported once by the set-up code
+    it.L = L;
+    int Tk = L + p.T_new;  // keys present after the append
+    if (Tk > p.T_k) Tk = p.T_k;
+    const int last_t = min(it.t0 + PF_M, p.T_new) - 1;
+    it.kv_hi = min(Tk, L + last_t + 1);
+    it.kv_lo = p.window_left >= 0 ? max(0, L + it.t0 - p.window_left) : 0;
+    it.n_tiles = it.kv_hi > it.kv_lo ? (it.kv_hi - it.kv_lo + PF_N - 1) / PF_N : 0;
+    return it;
+}
+
+// Position in a CTA's stream of key tiles: item number `seq` of the CTA, tile `t` inside it.  Items
+// without any visible key are skipped (only the softmax warps look at them, to write zeros).
+struct PfCursor {
+    PfItem it;
+    int seq, t;
+    bool valid;
+    __device__ __forceinline__ void load(const PrefillParams &p, int from_seq) {  // first non-empty item at or after from_seq
+        t = 0;
+        for (seq = from_seq;; ++seq) {
+            const int idx = pf_item_index(p, seq);
+            if (idx < 0) {
+                valid = false;
+                return;
+            }
+            it = pf_item(p, idx);
+            if (it.n_tiles > 0) {
+                valid = true;
+                return;
+            }
+        }
+    }
+    __device__ __forceinline__ void advance(const PrefillParams &p) {
+        if (++t >= it.n_tiles) load(p, seq + 1);
+    }
+    __device__ __forceinline__ bool last_of_item() const { return t == it.n_tiles - 1; }
+};
 
 __global__ void __launch_bounds__(PF_THREADS, 2)
 prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -77,68 +152,25 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     uint8_t *sK = sQ + PF_Q_BYTES;                        // 2 x 16 KB
     uint8_t *sV = sK + PF_STAGES * PF_KV_BYTES;           // 3 x 16 KB
     uint64_t *bars = reinterpret_cast<uint64_t *>(sV + PF_VSTAGES * PF_KV_BYTES);
-    uint64_t *bar_q = bars;          // Q landed
+    // All tile barriers are indexed by the GLOBAL tile number g of the CTA's stream (its items' tiles one
+    // after the other): stage g % 2 or g % 3, buffer g & 1, and the phase parity follows from g as well.
+    uint64_t *bar_q = bars;          // Q of an item landed (one phase per item)
     uint64_t *bar_k = bars + 1;      // [PF_STAGES] K tile landed
     uint64_t *bar_v = bars + 3;      // [PF_VSTAGES] V tile landed
-    // [2] S(it) = Q K(it)^T complete, on bar_s[it & 1].  Products complete in issue order and S(it) is
-    // issued behind O += P V(it-2), so this also says "P V(it-2) complete".
+    // [2] S(g) = Q K(g)^T complete, on bar_s[g & 1].  Products complete in issue order and S(g) is
+    // issued behind O += P V(g-2), so this also says "P V(g-2) complete".
     uint64_t *bar_s = bars + 6;
-    // [2] O += P V(it) complete, on bar_o[it & 1]: signalled only for the last two tiles, which no S
-    // follows.  Every tcgen05.commit costs tensor-pipe time (measured: groups of 4-8 instructions
-    // between commits run at about half the rate of an uninterrupted stream), so a tile gets one.
+    // [2] O += P V complete for the last (bar_o[0]) and the second last (bar_o[1]) tile of an item: no S
+    // of the same item follows them.  One phase per item (bar_o[1]: per item of two or more tiles).
     uint64_t *bar_o = bars + 8;
-    // [2] P(it) in TMEM, S(it) read, O rescaled: one arrival per softmax warp on bar_p[it & 1].  Two
-    // barriers because the softmax may finish tile it+1 before the issuer has looked at tile it.
+    // [2] P(g) in TMEM, S(g) read, O rescaled: one arrival per softmax warp on bar_p[g & 1].
     uint64_t *bar_p = bars + 10;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 12);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
-    // PF_SPLIT == 2 only: [2 buffers][2][PF_M] row maxima exchanged between the threads of a row
-    __nv_bfloat16 *s_xchg = reinterpret_cast<__nv_bfloat16 *>(bars + 13);
-    (void)s_xchg;
 
     const int tid = threadIdx.x, warp = tid >> 5;
-    // Work order.  CTAs are handed to the SMs in block-index order, which makes the grid a work queue.
-    // Causal query tiles differ in length by up to n_qtiles x, so the order decides both the tail and
-    // which tiles share an SM.  The (row, q head) pairs are taken in groups of group_pairs (sized on the
-    // host so that a group's K/V stays in L2 while its query tiles reuse it).  Inside a group either
-    // pair by pair with a pair's long tiles first (long and short tiles then meet on an SM and fill each
-    // other's gaps: best while a pair has few tiles), or all pairs' longest tiles first and their shortest
-    // last (bounds the tail when one tile is a large share of an SM's work: long sequences).
-    const int n_qtiles = (p.T_new + PF_M - 1) / PF_M;
-    const int n_pairs = p.Hq * p.B;
-    const int per_group = p.group_pairs * n_qtiles;
-    const int grp = (int)blockIdx.x / per_group;
-    const int in_grp = (int)blockIdx.x - grp * per_group;
-    const int grp_pairs = min(p.group_pairs, n_pairs - grp * p.group_pairs);
-    int qt, pair;
-    if (p.pair_major) {  // pair by pair, a pair's long tiles first
-        pair = grp * p.group_pairs + in_grp / n_qtiles;
-        qt = n_qtiles - 1 - in_grp % n_qtiles;
-    } else {             // all pairs' longest tiles first, their shortest last
-        qt = n_qtiles - 1 - in_grp / grp_pairs;
-        pair = grp * p.group_pairs + in_grp % grp_pairs;
-    }
-    const int hq = pair % p.Hq, b = pair / p.Hq;
-    const int hkv = hq / (p.Hq / p.Hkv);
-    const int t0 = qt * PF_M;
 
     pdl_wait_prior_grids();
-    int L = p.seqlens ? p.seqlens[b] : 0;
-    if (L < 0) {
-        if (tid == 0) atomicOr(p.status, (int)NCKV_ST_BAD_SEQLEN);
-        L = 0;
-    }
-    int Tk = L + p.T_new;  // keys present after the append
-    if (Tk > p.T_k) {
-        if (tid == 0) atomicOr(p.status, (int)NCKV_ST_OVERFLOW);
-        Tk = p.T_k;
-    }
-    // keys any row of this tile may see: [kv_lo, kv_hi)
-    const int last_t = min(t0 + PF_M, p.T_new) - 1;
-    const int kv_hi = min(Tk, L + last_t + 1);
-    const int kv_lo = p.window_left >= 0 ? max(0, L + t0 - p.window_left) : 0;
-    const int n_tiles = kv_hi > kv_lo ? (kv_hi - kv_lo + PF_N - 1) / PF_N : 0;
-
     if (tid == 0) {
         prefetch_tensormap(&tmap_q);
         prefetch_tensormap(&tmap_k);
@@ -155,6 +187,13 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         *abort_flag = 0;
         fence_mbar_init();
     }
+    if (blockIdx.x == 0 && p.seqlens) {  // lengths out of range: reported once
+        for (int b = tid; b < p.B; b += blockDim.x) {
+            const int L = p.seqlens[b];
+            if (L < 0) atomicOr(p.status, (int)NCKV_ST_BAD_SEQLEN);
+            else if (L + p.T_new > p.T_k) atomicOr(p.status, (int)NCKV_ST_OVERFLOW);
+        }
+    }
     if (warp == 0) {
         tmem_alloc(tmem_slot, PF_TMEM_COLS);
         tmem_relinquish();
@@ -170,293 +209,294 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     constexpr uint32_t IDESC_S = umma_idesc(PF_M, PF_N, 0, 0);
     constexpr uint32_t IDESC_O = umma_idesc(PF_M, NCKV_D, 0, 1);
     const bool issuer_warp = warp == PF_SOFTMAX_THREADS / 32;
-    bool aborted = false;
     auto timed_out = [&]() {
         *abort_flag = 1;
         atomicOr(p.status, (int)NCKV_ST_TIMEOUT);
     };
+    auto par2 = [](uint32_t g) -> uint32_t { return (g >> 1) & 1u; };  // phase of a barrier indexed g & 1
 
     if (warp == PF_SOFTMAX_THREADS / 32 + 1) {
-        // =============== one lane moves the tiles: Q once, K and V through two stages each =======
-        if ((tid & 31) == 0 && n_tiles > 0) {
-            auto load_k = [&](int tile) {  // K(tile) -> stage tile % 2
-                const int stage = tile % PF_STAGES, key0 = kv_lo + tile * PF_N;
+        // =============== one lane moves the tiles ===================================================
+        if ((tid & 31) == 0) {
+            PfCursor kc, vc, wc;  // next K tile to load, next V tile to load, tile whose score product is awaited
+            kc.load(p, 0);
+            vc = kc;
+            wc = kc;
+            uint32_t gk = 0, gv = 0;
+            auto load_k = [&]() {
+                const int stage = (int)(gk % PF_STAGES), key0 = kc.it.kv_lo + kc.t * PF_N;
                 uint8_t *kd = sK + stage * PF_KV_BYTES;
                 mbar_arrive_expect_tx(&bar_k[stage], PF_KV_BYTES);
-                tma_load_4d(kd, &tmap_k, &bar_k[stage], 0, hkv, key0, b);
-                tma_load_4d(kd + PF_KV_BYTES / 2, &tmap_k, &bar_k[stage], 64, hkv, key0, b);
+                tma_load_4d(kd, &tmap_k, &bar_k[stage], 0, kc.it.hkv, key0, kc.it.b);
+                tma_load_4d(kd + PF_KV_BYTES / 2, &tmap_k, &bar_k[stage], 64, kc.it.hkv, key0, kc.it.b);
+                kc.advance(p);
+                ++gk;
             };
-            auto load_v = [&](int tile) {  // V(tile) -> stage tile % 3
-                const int stage = tile % PF_VSTAGES, key0 = kv_lo + tile * PF_N;
+            auto load_v = [&]() {
+                const int stage = (int)(gv % PF_VSTAGES), key0 = vc.it.kv_lo + vc.t * PF_N;
                 uint8_t *vd = sV + stage * PF_KV_BYTES;
                 mbar_arrive_expect_tx(&bar_v[stage], PF_KV_BYTES);
-                tma_load_4d(vd, &tmap_v, &bar_v[stage], 0, hkv, key0, b);
-                tma_load_4d(vd + PF_KV_BYTES / 2, &tmap_v, &bar_v[stage], 64, hkv, key0, b);
+                tma_load_4d(vd, &tmap_v, &bar_v[stage], 0, vc.it.hkv, key0, vc.it.b);
+                tma_load_4d(vd + PF_KV_BYTES / 2, &tmap_v, &bar_v[stage], 64, vc.it.hkv, key0, vc.it.b);
+                vc.advance(p);
+                ++gv;
             };
-            mbar_arrive_expect_tx(bar_q, PF_Q_BYTES);
-            tma_load_4d(sQ, &tmap_q, bar_q, 0, hq, t0, b);
-            tma_load_4d(sQ + PF_Q_BYTES / 2, &tmap_q, bar_q, 64, hq, t0, b);
-            for (int i = 0; i < PF_STAGES && i < n_tiles; ++i) load_k(i);
-            for (int i = 0; i < PF_VSTAGES && i < n_tiles; ++i) load_v(i);
+            auto load_q = [&](const PfItem &it) {
+                mbar_arrive_expect_tx(bar_q, PF_Q_BYTES);
+                tma_load_4d(sQ, &tmap_q, bar_q, 0, it.hq, it.t0, it.b);
+                tma_load_4d(sQ + PF_Q_BYTES / 2, &tmap_q, bar_q, 64, it.hq, it.t0, it.b);
+            };
             bool ok = true;
-            for (int t = 0; t + 2 < n_tiles && ok; ++t) {
-                // S(t) complete: K(t)'s stage is free for K(t+2); and, being issued behind it,
-                // O += P V(t-2) is complete too: V(t-2)'s stage is free for V(t+1)
-                ok = mbar_wait_bounded(&bar_s[t & 1], (uint32_t)((t >> 1) & 1), PF_WAIT_LIMIT);
-                if (!ok) break;
-                load_k(t + 2);
-                if (t + 1 >= PF_VSTAGES) load_v(t + 1);
-            }
-            // V of the last tile: its stage is the one of V(n-4), free once S(n-2) has completed
-            if (ok && n_tiles - 1 >= PF_VSTAGES && n_tiles >= 2) {
-                const int t = n_tiles - 2;
-                ok = mbar_wait_bounded(&bar_s[t & 1], (uint32_t)((t >> 1) & 1), PF_WAIT_LIMIT);
-                if (ok) load_v(n_tiles - 1);
+            if (wc.valid) {
+                load_q(wc.it);
+                while (gk < PF_STAGES && kc.valid) load_k();
+                while (gv < PF_VSTAGES && vc.valid) load_v();
+                for (uint32_t g = 0; wc.valid && ok; ++g) {
+                    // what S(g)'s completion releases: the Q buffer if g ends its item, K(g)'s stage for
+                    // K(g+2) and, P V(g-2) being complete too, V(g-2)'s stage for V(g+1)
+                    PfCursor nx;
+                    nx.valid = false;
+                    if (wc.last_of_item()) nx.load(p, wc.seq + 1);
+                    if (!kc.valid && !vc.valid && !nx.valid) break;
+                    ok = mbar_wait_bounded(&bar_s[g & 1], par2(g), PF_WAIT_LIMIT);
+                    if (!ok) break;
+                    if (nx.valid) load_q(nx.it);
+                    if (kc.valid) load_k();
+                    if (vc.valid && gv <= g + 1) load_v();
+                    wc.advance(p);
+                }
             }
             if (!ok) timed_out();
         }
         __syncwarp();
     } else if (issuer_warp) {
-        // =============== one warp feeds the tensor core ============================================
-        // The whole warp runs this loop so that control flow and every MMA operand (descriptors,
-        // TMEM addresses) stay warp-uniform; only the tcgen05.mma / tcgen05.commit instructions
-        // themselves are executed by a single lane.
-        if (n_tiles > 0) {
-            const bool leader = (tid & 31) == 0;
+        // =============== one thread feeds the tensor core ==========================================
+        // tcgen05.mma / tcgen05.commit are single-thread instructions and an mbarrier poll by 32 lanes
+        // is 32 polls, one after the other: lane 0 runs this role alone.
+        if ((tid & 31) == 0) {
             // Descriptors differ only in the start-address field (address >> 4 in the low 14 bits),
             // so they are built once and advanced by adding the byte offset >> 4.
             const uint64_t desc_q = smem_desc_sw128(smem_u32(sQ), 16, 1024);
             const uint64_t desc_k = smem_desc_sw128(smem_u32(sK), 16, 1024);
             const uint64_t desc_v = smem_desc_sw128(smem_u32(sV), PF_KV_BYTES / 2, 1024);
-            auto wait_all = [&](uint64_t *bar, uint32_t parity) -> bool {
-                return __all_sync(0xffffffffu, mbar_wait_bounded(bar, parity, PF_WAIT_LIMIT));
-            };
-            // S(tile) = Q K(tile)^T into S buffer tile & 1, then arrive on bar_s[tile & 1]
-            auto issue_s = [&](int tile) -> bool {
-                const int stage = tile % PF_STAGES;
-                if (tile == 0 && !wait_all(bar_q, 0)) return false;
-                if (!wait_all(&bar_k[stage], (uint32_t)((tile / PF_STAGES) & 1))) return false;
+            PfCursor sc, pc;  // tile of the next score product, tile of the next P V product
+            sc.load(p, 0);
+            pc = sc;
+            uint32_t gs = 0, gp = 0;
+            uint32_t n_q = 0;  // items whose Q has been waited for
+            // S(gs) = Q K(gs)^T into S buffer gs & 1, then arrive on bar_s[gs & 1]
+            auto issue_s = [&]() -> bool {
+                const uint32_t stage = gs % PF_STAGES;
+                if (sc.t == 0) {  // first tile of an item: its Q
+                    if (!mbar_wait_bounded(bar_q, n_q & 1u, PF_WAIT_LIMIT)) return false;
+                    ++n_q;
+                }
+                if (!mbar_wait_bounded(&bar_k[stage], (gs / PF_STAGES) & 1u, PF_WAIT_LIMIT)) return false;
                 tc_fence_after();
                 const uint64_t dk = desc_k + (uint64_t)((stage * PF_KV_BYTES) >> 4);
-                const uint32_t ds = tmem_s + (uint32_t)(tile & 1) * PF_N;
-                if (leader) {  // one thread runs the whole burst: nothing diverges and reconverges between the instructions
+                const uint32_t ds = tmem_s + (gs & 1u) * PF_N;
 #pragma unroll
-                    for (int kk = 0; kk < NCKV_D / 16; ++kk) {
-                        const uint32_t off = (uint32_t)(kk & 3) * 32;
-                        const uint64_t da = desc_q + (uint64_t)(((kk >> 2) * (PF_Q_BYTES / 2) + off) >> 4);
-                        const uint64_t db = dk + (uint64_t)(((kk >> 2) * (PF_KV_BYTES / 2) + off) >> 4);
-                        umma_bf16(ds, da, db, IDESC_S, kk > 0 ? 1u : 0u);
-                    }
-                    umma_commit(&bar_s[tile & 1]);
+                for (int kk = 0; kk < NCKV_D / 16; ++kk) {
+                    const uint32_t off = (uint32_t)(kk & 3) * 32;
+                    const uint64_t da = desc_q + (uint64_t)(((kk >> 2) * (PF_Q_BYTES / 2) + off) >> 4);
+                    const uint64_t db = dk + (uint64_t)(((kk >> 2) * (PF_KV_BYTES / 2) + off) >> 4);
+                    umma_bf16(ds, da, db, IDESC_S, kk > 0 ? 1u : 0u);
                 }
-                __syncwarp();
+                umma_commit(&bar_s[gs & 1u]);
+                sc.advance(p);
+                ++gs;
                 return true;
             };
-            // O (+)= P V(tile) into TMEM columns [128, 256), then arrive on bar_o[tile & 1]
-            auto issue_pv = [&](int tile, bool commit_now) -> bool {
-                const int stage = tile % PF_VSTAGES;
-                if (!wait_all(&bar_v[stage], (uint32_t)((tile / PF_VSTAGES) & 1))) return false;
+            // S runs two tiles ahead of the softmax
+            bool ok = true;
+            if (sc.valid) ok = issue_s();
+            if (ok && sc.valid) ok = issue_s();
+            while (pc.valid && ok) {
+                // P(gp) is in TMEM, S(gp) has been read, O carries the scale P was made with
+                const uint32_t vstage = gp % PF_VSTAGES;
+                ok = mbar_wait_bounded(&bar_p[gp & 1u], par2(gp), PF_WAIT_LIMIT) &&
+                     mbar_wait_bounded(&bar_v[vstage], (gp / PF_VSTAGES) & 1u, PF_WAIT_LIMIT);
+                if (!ok) break;
                 tc_fence_after();
                 // V in place: N (channels) contiguous, the two 64-channel halves PF_KV_BYTES/2 apart
                 // (leading offset), 8-key groups 1024 B apart (stride offset)
-                const uint64_t dv = desc_v + (uint64_t)((stage * PF_KV_BYTES) >> 4);
-                const uint32_t pbase = tmem_s + (uint32_t)(tile & 1) * PF_N;
-                if (leader) {
+                const uint64_t dv = desc_v + (uint64_t)((vstage * PF_KV_BYTES) >> 4);
+                const uint32_t pbase = tmem_s + (gp & 1u) * PF_N;
 #pragma unroll
-                    for (int ks = 0; ks < PF_N / 16; ++ks) {
-                        // P(tile) sits in the first 32 columns of its S buffer; 16 keys = 8 columns
-                        const uint64_t db = dv + (uint64_t)((ks * 16 * 128) >> 4);
-                        umma_bf16_a_tmem(tmem_o, pbase + (uint32_t)ks * 8, db, IDESC_O, (tile > 0 || ks > 0) ? 1u : 0u);
-                    }
-                    if (commit_now) umma_commit(&bar_o[tile & 1]);
+                for (int ks = 0; ks < PF_N / 16; ++ks) {
+                    // P(gp) sits in the first 32 columns of its S buffer; 16 keys = 8 columns
+                    const uint64_t db = dv + (uint64_t)((ks * 16 * 128) >> 4);
+                    umma_bf16_a_tmem(tmem_o, pbase + (uint32_t)ks * 8, db, IDESC_O, (pc.t > 0 || ks > 0) ? 1u : 0u);
                 }
-                __syncwarp();
-                return true;
-            };
-
-            // S runs two tiles ahead of the softmax
-            bool ok = issue_s(0);
-            if (ok && n_tiles > 1) ok = issue_s(1);
-            for (int it = 0; it < n_tiles && ok; ++it) {
-                // P(it) is in TMEM, S(it) has been read, O carries the scale P was made with
-                ok = wait_all(&bar_p[it & 1], (uint32_t)((it >> 1) & 1));
-                if (!ok) break;
-                tc_fence_after();
-                // S(it+2) goes into the S buffer every thread has just finished reading; its commit also
-                // covers O += P V(it).  The last two tiles have no S behind them and signal bar_o.
-                const bool s_follows = it + 2 < n_tiles;
-                ok = issue_pv(it, !s_follows);
-                if (ok && s_follows) ok = issue_s(it + 2);
+                // S(gp+2), issued behind this product into the S buffer P(gp) sits in, tells of its completion
+                // too; the last two tiles of an item tell it themselves (the S behind them belongs to the next
+                // item and may have to wait for that item's Q).
+                const int from_end = pc.it.n_tiles - 1 - pc.t;
+                if (from_end < 2) umma_commit(&bar_o[from_end]);
+                if (sc.valid) ok = issue_s();
+                pc.advance(p);
+                ++gp;
             }
-            if (!ok && leader) timed_out();
+            if (!ok) timed_out();
         }
         __syncwarp();
     } else {
-        // =============== softmax threads: PF_SPLIT per query row =================================
-        // Softmax state of this thread's row.  P is scaled by m_used, which follows the true running
-        // max lazily: it is only raised (and the O row in TMEM rescaled) when the max has grown by
-        // more than 2^8, so exp2(s - m_used) stays <= 256 and most tiles need no rescale at all.
-        float m_used = -INFINITY, l_run = 0.f;
+        // =============== softmax threads: one per query row =========================================
         const int row = tid & (PF_M - 1);  // query row inside the tile == TMEM lane
-        const int half = tid / PF_M;       // which share of the tile's scores (and of the output channels) is mine
-        const int pos = L + t0 + row;      // absolute position of this row's token
-        constexpr int HN = PF_N / PF_SPLIT;    // scores per thread and tile
-        constexpr int OC = NCKV_D / PF_SPLIT;  // output channels per thread
-
-        for (int it = 0; it < n_tiles; ++it) {
-            const int stage = it % PF_VSTAGES;
-            const uint32_t kv_parity = (uint32_t)((it / PF_VSTAGES) & 1);
-            const int key0 = kv_lo + it * PF_N;
-            const uint32_t tmem_s_it = tmem_s + (uint32_t)(it & 1) * PF_N;
-            // tcgen05.ld/st are warp-wide (.sync.aligned): every decision that skips them is taken per warp
-            {
-                const bool ok = *abort_flag == 0 &&
-                                mbar_wait_bounded(&bar_s[it & 1], (uint32_t)((it >> 1) & 1), PF_WAIT_LIMIT);
-                if (!__all_sync(0xffffffffu, ok)) {
-                    aborted = true;
-                    break;
-                }
-            }
-            tc_fence_after();
-
-            float s_val[HN];
-#pragma unroll
-            for (int ch = 0; ch < HN / 32; ++ch) {
-                float c[32];
-                tmem_ld32(tmem_s_it + lane_sel + half * HN + ch * 32, c);  // raw q.k, scaled inside the exponent
-#pragma unroll
-                for (int i = 0; i < 32; ++i) s_val[ch * 32 + i] = c[i];
-            }
-            // only tiles that touch the causal diagonal, the window edge or the end of the keys need
-            // per-element masking (uniform over the CTA)
-            const bool edge = (key0 + PF_N - 1 > L + t0) || (key0 + PF_N > kv_hi) ||
-                              (p.window_left >= 0 && key0 < L + t0 + PF_M - 1 - p.window_left);
-            if (edge) {
-                // this row sees columns [c_lo, c_hi) of its share of the tile
-                const int c_hi = min(pos, kv_hi - 1) - (key0 + half * HN) + 1;
-                const int c_lo = p.window_left >= 0 ? pos - p.window_left - (key0 + half * HN) : 0;
-#pragma unroll
-                for (int c = 0; c < HN; ++c) s_val[c] = (c >= c_lo && c < c_hi) ? s_val[c] : -INFINITY;
-            }
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains instead of one
-#pragma unroll
-            for (int c = 0; c < HN; c += 4) {
-                mx4[0] = fmaxf(mx4[0], s_val[c]);
-                mx4[1] = fmaxf(mx4[1], s_val[c + 1]);
-                mx4[2] = fmaxf(mx4[2], s_val[c + 2]);
-                mx4[3] = fmaxf(mx4[3], s_val[c + 3]);
-            }
-            float mx_raw = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            if (PF_SPLIT == 2) {
-                // The row max needs both halves: exchange through shared memory, double buffered
-                // because a thread may run up to one tile ahead of its partner.  bf16 rounded UP: the
-                // reference point of the exponentials only has to be the same in both threads and
-                // not below the true max.
-                __nv_bfloat16 *xb = s_xchg + (it & 1) * 2 * PF_M;
-                const __nv_bfloat16 mine = __float2bfloat16_ru(mx_raw);
-                xb[half * PF_M + row] = mine;
-                asm volatile("bar.sync 1, %0;" ::"n"(PF_SOFTMAX_THREADS) : "memory");
-                mx_raw = fmaxf(__bfloat162float(mine), __bfloat162float(xb[(half ^ 1) * PF_M + row]));
-            }
-            // the max is taken on raw scores and scaled once (the scale is positive)
-            const float mx = mx_raw * p.scale_log2;
-            const bool raise = mx > m_used + 8.f;  // also the first tile that shows this row a key (m_used = -inf)
-            const float alpha = raise ? ex2_approx(m_used - mx) : 1.f;  // 2^-inf = 0
-            if (raise) {
-                l_run *= alpha;
-                m_used = mx;
-            }
-            const float m_use = m_used == -INFINITY ? 0.f : m_used;  // a row that has seen no key yet
-            float rs4[4] = {0.f, 0.f, 0.f, 0.f};
-            uint32_t pk[HN / 2];
-#pragma unroll
-            for (int c = 0; c < HN; c += 4) {
-                // one FFMA and one MUFU.EX2 per score: 2^(s * scale - m)
-                const float p0 = ex2_approx(fmaf(s_val[c], p.scale_log2, -m_use));
-                const float p1 = ex2_approx(fmaf(s_val[c + 1], p.scale_log2, -m_use));
-                const float p2 = ex2_approx(fmaf(s_val[c + 2], p.scale_log2, -m_use));
-                const float p3 = ex2_approx(fmaf(s_val[c + 3], p.scale_log2, -m_use));
-                rs4[0] += p0; rs4[1] += p1; rs4[2] += p2; rs4[3] += p3;
-                pk[c / 2] = pack_bf16x2(p0, p1);
-                pk[c / 2 + 1] = pack_bf16x2(p2, p3);
-            }
-            l_run += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);  // this thread's share of the row sum
-
-            // P row -> TMEM, over the first 32 columns of this tile's S buffer (this lane's own scores,
-            // already in registers).  S of tile it+2 is issued behind P V(it) and lands on top of it.
-            tmem_st_words(tmem_s_it + lane_sel + half * (HN / 2), pk);
-            // A raised scale: O (+)= P V of the previous tile must be complete before the O rows
-            // accumulated so far are brought to the new scale (tcgen05.ld / multiply / tcgen05.st).
-            // Every lane applies its own factor (1 for rows that keep their scale).
-            if (it > 0 && __any_sync(0xffffffffu, raise)) {
-                // O += P V(it-1) complete: told by S(it+1), which was issued behind it, or by bar_o
-                // when tile it is the last one
-                const bool ok = it + 1 < n_tiles
-                                    ? mbar_wait_bounded(&bar_s[(it + 1) & 1], (uint32_t)(((it + 1) >> 1) & 1), PF_WAIT_LIMIT)
-                                    : mbar_wait_bounded(&bar_o[(it - 1) & 1], 0, PF_WAIT_LIMIT);
-                if (!__all_sync(0xffffffffu, ok)) {
-                    if (!ok) timed_out();
+        bool aborted = false;
+        uint32_t g = 0;  // global tile number of the current item's tile 0
+        uint32_t n_o0 = 0, n_o1 = 0;  // phases of bar_o[0] / bar_o[1] used up by the items before this one
+        // one lane polls (32 lanes polling one mbarrier are served one after the other), the warp follows
+        auto warp_wait = [&](uint64_t *bar, uint32_t parity) -> bool {
+            int ok = 1;
+            if ((tid & 31) == 0) ok = mbar_wait_bounded(bar, parity, PF_WAIT_LIMIT) ? 1 : 0;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            __syncwarp();  // orders the lanes' later reads of the tile behind lane 0's observation
+            return ok != 0;
+        };
+        for (int seq = 0; !aborted; ++seq) {
+            const int idx = pf_item_index(p, seq);
+            if (idx < 0) break;
+            const PfItem it = pf_item(p, idx);
+            const int n_tiles = it.n_tiles;
+            const int pos = it.L + it.t0 + row;  // absolute position of this row's token
+            // P V of the item's tile t complete: told by S of tile t+2, issued behind it, or by bar_o for the
+            // item's last two tiles
+            auto pv_done = [&](int t) -> bool {
+                const int from_end = n_tiles - 1 - t;
+                const uint32_t x = g + (uint32_t)t;
+                return from_end >= 2 ? warp_wait(&bar_s[(x + 2) & 1u], par2(x + 2)) : warp_wait(&bar_o[from_end], (from_end == 0 ? n_o0 : n_o1) & 1u);
+            };
+            // Softmax state of this thread's row.  P is scaled by m_used, which follows the true running
+            // max lazily: it is only raised (and the O row in TMEM rescaled) when the max has grown by
+            // more than 2^8, so exp2(s - m_used) stays <= 256 and most tiles need no rescale at all.
+            float m_used = -INFINITY, l_run = 0.f;
+            for (int t = 0; t < n_tiles; ++t) {
+                const uint32_t gt = g + (uint32_t)t;
+                const int stage = (int)(gt % PF_VSTAGES);
+                const int key0 = it.kv_lo + t * PF_N;
+                const uint32_t tmem_s_it = tmem_s + (uint32_t)(gt & 1) * PF_N;
+                // tcgen05.ld/st are warp-wide (.sync.aligned): every decision that skips them is taken per warp
+                if (*abort_flag != 0 || !warp_wait(&bar_s[gt & 1u], par2(gt))) {  // both uniform over the warp
                     aborted = true;
                     break;
                 }
                 tc_fence_after();
+
+                float s_val[PF_N];
 #pragma unroll
-                for (int ch = 0; ch < OC / 32; ++ch) {
+                for (int ch = 0; ch < PF_N / 32; ++ch) {
                     float c[32];
-                    tmem_ld32(tmem_o + lane_sel + half * OC + ch * 32, c);
+                    tmem_ld32(tmem_s_it + lane_sel + ch * 32, c);  // raw q.k, scaled inside the exponent
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) c[i] *= alpha;
-                    tmem_st32(tmem_o + lane_sel + half * OC + ch * 32, c);
+                    for (int i = 0; i < 32; ++i) s_val[ch * 32 + i] = c[i];
                 }
-            }
-            // rows of the V tile past the last key may hold stale bytes: zero them so that a zero
-            // probability never multiplies a NaN/Inf bit pattern
-            if (key0 + PF_N > kv_hi) {
-                uint8_t *vd = sV + stage * PF_KV_BYTES;
-                if (mbar_wait_bounded(&bar_v[stage], kv_parity, PF_WAIT_LIMIT)) {
-                    for (int idx = tid; idx < (key0 + PF_N - kv_hi) * 16; idx += PF_SOFTMAX_THREADS) {
-                        const int r = (kv_hi - key0) + idx / 16, ch = idx % 16;
-                        *reinterpret_cast<uint4 *>(vd + (ch >> 3) * (PF_KV_BYTES / 2) + r * 128 + ((ch & 7) << 4)) =
-                            make_uint4(0, 0, 0, 0);
+                // only tiles that touch the causal diagonal, the window edge or the end of the keys need
+                // per-element masking (uniform over the CTA)
+                const bool edge = (key0 + PF_N - 1 > it.L + it.t0) || (key0 + PF_N > it.kv_hi) ||
+                                  (p.window_left >= 0 && key0 < it.L + it.t0 + PF_M - 1 - p.window_left);
+                if (edge) {
+                    // this row sees columns [c_lo, c_hi) of the tile
+                    const int c_hi = min(pos, it.kv_hi - 1) - key0 + 1;
+                    const int c_lo = p.window_left >= 0 ? pos - p.window_left - key0 : 0;
+#pragma unroll
+                    for (int c = 0; c < PF_N; ++c) s_val[c] = (c >= c_lo && c < c_hi) ? s_val[c] : -INFINITY;
+                }
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains instead of one
+#pragma unroll
+                for (int c = 0; c < PF_N; c += 4) {
+                    mx4[0] = fmaxf(mx4[0], s_val[c]);
+                    mx4[1] = fmaxf(mx4[1], s_val[c + 1]);
+                    mx4[2] = fmaxf(mx4[2], s_val[c + 2]);
+                    mx4[3] = fmaxf(mx4[3], s_val[c + 3]);
+                }
+                // the max is taken on raw scores and scaled once (the scale is positive)
+                const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
+                const bool raise = mx > m_used + 8.f;  // also the first tile that shows this row a key (m_used = -inf)
+                const float alpha = raise ? ex2_approx(m_used - mx) : 1.f;  // 2^-inf = 0
+                if (raise) {
+                    l_run *= alpha;
+                    m_used = mx;
+                }
+                const float m_use = m_used == -INFINITY ? 0.f : m_used;  // a row that has seen no key yet
+                float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+                uint32_t pk[PF_N / 2];
+#pragma unroll
+                for (int c = 0; c < PF_N; c += 4) {
+                    // one FFMA and one MUFU.EX2 per score: 2^(s * scale - m)
+                    const float p0 = ex2_approx(fmaf(s_val[c], p.scale_log2, -m_use));
+                    const float p1 = ex2_approx(fmaf(s_val[c + 1], p.scale_log2, -m_use));
+                    const float p2 = ex2_approx(fmaf(s_val[c + 2], p.scale_log2, -m_use));
+                    const float p3 = ex2_approx(fmaf(s_val[c + 3], p.scale_log2, -m_use));
+                    rs4[0] += p0; rs4[1] += p1; rs4[2] += p2; rs4[3] += p3;
+                    pk[c / 2] = pack_bf16x2(p0, p1);
+                    pk[c / 2 + 1] = pack_bf16x2(p2, p3);
+                }
+                l_run += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+
+                // P row -> TMEM, over the first 32 columns of this tile's S buffer (this lane's own scores,
+                // already in registers).  S of tile g+2 is issued behind P V(g) and lands on top of it.
+                tmem_st_words(tmem_s_it + lane_sel, pk);
+                // A raised scale: O (+)= P V of the previous tile must be complete before the O rows
+                // accumulated so far are brought to the new scale (tcgen05.ld / multiply / tcgen05.st).
+                // Every lane applies its own factor (1 for rows that keep their scale).
+                if (t > 0 && __any_sync(0xffffffffu, raise)) {
+                    if (!pv_done(t - 1)) {
+                        timed_out();
+                        aborted = true;
+                        break;
+                    }
+                    tc_fence_after();
+#pragma unroll
+                    for (int ch = 0; ch < NCKV_D / 32; ++ch) {
+                        float c[32];
+                        tmem_ld32(tmem_o + lane_sel + ch * 32, c);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) c[i] *= alpha;
+                        tmem_st32(tmem_o + lane_sel + ch * 32, c);
                     }
                 }
-                fence_proxy_async_smem();  // the zeroed V rows must be visible to the tensor core
+                // rows of the V tile past the last key may hold stale bytes: zero them so that a zero
+                // probability never multiplies a NaN/Inf bit pattern
+                if (key0 + PF_N > it.kv_hi) {
+                    uint8_t *vd = sV + stage * PF_KV_BYTES;
+                    if (warp_wait(&bar_v[stage], (gt / PF_VSTAGES) & 1u)) {
+                        for (int i = tid; i < (key0 + PF_N - it.kv_hi) * 16; i += PF_SOFTMAX_THREADS) {
+                            const int r = (it.kv_hi - key0) + i / 16, ch = i % 16;
+                            *reinterpret_cast<uint4 *>(vd + (ch >> 3) * (PF_KV_BYTES / 2) + r * 128 + ((ch & 7) << 4)) =
+                                make_uint4(0, 0, 0, 0);
+                        }
+                    }
+                    fence_proxy_async_smem();  // the zeroed V rows must be visible to the tensor core
+                }
+                tc_fence_before();  // orders this thread's TMEM loads/stores before the next MMAs
+                __syncwarp();
+                if ((tid & 31) == 0) mbar_arrive(&bar_p[gt & 1]);  // one arrival per warp
             }
-            tc_fence_before();  // orders this thread's TMEM loads/stores before the next MMAs
-            __syncwarp();
-            if ((tid & 31) == 0) mbar_arrive(&bar_p[it & 1]);  // one arrival per warp
-        }
-        if (aborted && *abort_flag == 0) timed_out();  // a wait ran out in this warp
+            if (aborted) break;
 
-        // ---- epilogue ---------------------------------------------------------------------------
-        const int t = t0 + row;
-        if (!aborted && n_tiles > 0) {
-            const bool ok = mbar_wait_bounded(&bar_o[(n_tiles - 1) & 1], 0, PF_WAIT_LIMIT);
-            if (!ok) timed_out();
-            aborted = !__all_sync(0xffffffffu, ok);
-            tc_fence_after();
-        }
-        float l_row = l_run;
-        if (PF_SPLIT == 2) {  // the row sum is the sum of the two threads' shares
-            // every product has completed (or the CTA has given up): the first K stage is free
-            float *s_sum = reinterpret_cast<float *>(sK);
-            s_sum[half * PF_M + row] = l_run;
-            asm volatile("bar.sync 1, %0;" ::"n"(PF_SOFTMAX_THREADS) : "memory");
-            l_row += s_sum[(half ^ 1) * PF_M + row];
-        }
-        if (!aborted) {  // uniform over the warp: the TMEM loads below are warp-wide instructions
-            const float inv = (n_tiles > 0 && l_row > 0.f) ? 1.f / l_row : 0.f;
-            uint4 *dst = reinterpret_cast<uint4 *>(p.out + (((long long)b * p.T_new + t) * p.Hq + hq) * NCKV_D + half * OC);
+            // ---- epilogue of the item -------------------------------------------------------------
+            const int tq = it.t0 + row;
+            if (n_tiles > 0) {
+                if (!pv_done(n_tiles - 1)) {
+                    timed_out();
+                    aborted = true;
+                    break;
+                }
+                tc_fence_after();
+            }
+            const float inv = (n_tiles > 0 && l_run > 0.f) ? 1.f / l_run : 0.f;
+            uint4 *dst = reinterpret_cast<uint4 *>(p.out + (((long long)it.b * p.T_new + tq) * p.Hq + it.hq) * NCKV_D);
 #pragma unroll
-            for (int ch = 0; ch < OC / 32; ++ch) {
+            for (int ch = 0; ch < NCKV_D / 32; ++ch) {
                 float c[32];
                 if (n_tiles > 0) {
-                    tmem_ld32(tmem_o + lane_sel + half * OC + ch * 32, c);
+                    tmem_ld32(tmem_o + lane_sel + ch * 32, c);
                 } else {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) c[i] = 0.f;
                 }
-                if (t < p.T_new) {  // rows past the end of the sequence are padding
+                if (tq < p.T_new) {  // rows past the end of the sequence are padding
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         uint4 v;
@@ -468,7 +508,14 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                     }
                 }
             }
+            // O is read: order those loads before the first P V of the next item, which overwrites it and
+            // is only issued after this thread's next arrival on bar_p
+            tc_fence_before();
+            g += (uint32_t)n_tiles;
+            n_o0 += n_tiles >= 1;
+            n_o1 += n_tiles >= 2;
         }
+        if (aborted && *abort_flag == 0) timed_out();  // a wait ran out in this warp
     }
     tc_fence_before();
     __syncthreads();
@@ -532,17 +579,35 @@ extern "C" int nckv_prefill_attn(const void *q, const void *k, const void *v, co
     p.B = B; p.T_new = T_new; p.Hq = Hq; p.Hkv = Hkv; p.T_k = T_k;
     p.window_left = window_left;
     p.scale_log2 = (float)(1.4426950408889634 / sqrt((double)D));
+    const int n_items = n_qtiles * Hq * B;
+    const int grid = n_items < 2 * sm_count() ? n_items : 2 * sm_count();  // two CTAs per SM, persistent
+    p.n_qtiles = n_qtiles;
+    p.n_items = n_items;
     {
-        // pairs per group: about 48 MB of K and V rows (512 B per key and kv head, shared by Hq / Hkv
-        // q heads) leaves room in the 126 MB L2 for two groups in flight and everything else
+        // Pairs per group.  Everything in one group when all K and V rows (512 B per key and kv head,
+        // shared by Hq / Hkv q heads) are 40 MB or less, a third of L2; else groups of about that size,
+        // rounded down to one whose item count is a multiple of twice the grid, so that the
+        // back-and-forth deal hands every CTA the same mix of long and short tiles.  The last group
+        // takes the remainder as well.
         const long long keys = window_left >= 0 && window_left + PF_M < T_k ? window_left + PF_M : T_k;
         const long long bytes_per_pair = keys * 512 / (Hq / Hkv) + 1;
-        long long g = (48LL << 20) / bytes_per_pair;
-        g -= g % (Hq / Hkv);  // keep the q heads of a kv head in one group
-        p.group_pairs = (int)(g < Hq / Hkv ? Hq / Hkv : (g > (long long)Hq * B ? (long long)Hq * B : g));
+        const long long pairs = (long long)Hq * B;
+        const long long rep = Hq / Hkv;  // keep the q heads of a kv head in one group
+        long long g = pairs;
+        if (pairs * bytes_per_pair > (40LL << 20)) {
+            g = (40LL << 20) / bytes_per_pair;
+            g -= g % rep;
+            long long a = 2LL * grid, b = n_qtiles;
+            while (b) { const long long t = a % b; a = b; b = t; }  // a = gcd(2 grid, n_qtiles)
+            long long unit = 2LL * grid / a;                         // pairs per balanced deal
+            { long long x = unit, y = rep; while (y) { const long long t = x % y; x = y; y = t; } unit = unit / x * rep; }
+            if (g >= unit) g -= g % unit;
+            if (g < rep) g = rep;
+            if (g > pairs) g = pairs;
+        }
+        p.n_groups = (int)(pairs / g);  // >= 1; the last group also takes the pairs / g remainder
+        p.group_pairs = (int)g;
     }
-
-    p.pair_major = n_qtiles <= 16;  // measured on B200: 2048-token rows and shorter prefer it, 4096 and longer do not
 
     const size_t smem = prefill_smem_bytes();
     static bool attr_set[64] = {false};
@@ -553,7 +618,7 @@ extern "C" int nckv_prefill_attn(const void *q, const void *k, const void *v, co
         attr_set[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(n_qtiles * Hq * B));
+    cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3(PF_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = static_cast<cudaStream_t>(stream);
