@@ -44,10 +44,10 @@ namespace nckv {
 
 constexpr int PF_M = 128;  // query tokens per CTA
 constexpr int PF_N = 64;   // keys per tile
+static_assert(PF_N == 64, "the softmax loads a tile's scores with one 64-column tcgen05.ld");
 constexpr int PF_STAGES = 2;    // K stages
 constexpr int PF_VSTAGES = 3;   // V stages
-constexpr int PF_SPLIT = 1;                           // softmax threads per query row (2 measured slower)
-constexpr int PF_SOFTMAX_THREADS = PF_M * PF_SPLIT;
+constexpr int PF_SOFTMAX_THREADS = PF_M;               // one softmax thread per query row (two, each with half a tile's scores, measured slower)
 constexpr int PF_THREADS = PF_SOFTMAX_THREADS + 64;   // + one warp that issues the MMAs + one that issues the TMA copies
 constexpr int PF_Q_BYTES = PF_M * NCKV_D * 2;        // 32 KB: two 64-channel halves of [128][128 B]
 constexpr int PF_KV_BYTES = PF_N * NCKV_D * 2;       // 16 KB: two halves of [64][128 B]
@@ -384,13 +384,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 tc_fence_after();
 
                 float s_val[PF_N];
-#pragma unroll
-                for (int ch = 0; ch < PF_N / 32; ++ch) {
-                    float c[32];
-                    tmem_ld32(tmem_s_it + lane_sel + ch * 32, c);  // raw q.k, scaled inside the exponent
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) s_val[ch * 32 + i] = c[i];
-                }
+                tmem_ld64(tmem_s_it + lane_sel, s_val);  // raw q.k, scaled inside the exponent; one load, one wait
                 // only tiles that touch the causal diagonal, the window edge or the end of the keys need
                 // per-element masking (uniform over the CTA)
                 const bool edge = (key0 + PF_N - 1 > it.L + it.t0) || (key0 + PF_N > it.kv_hi) ||
@@ -404,11 +398,11 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 }
                 float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains instead of one
 #pragma unroll
-                for (int c = 0; c < PF_N; c += 4) {
-                    mx4[0] = fmaxf(mx4[0], s_val[c]);
-                    mx4[1] = fmaxf(mx4[1], s_val[c + 1]);
-                    mx4[2] = fmaxf(mx4[2], s_val[c + 2]);
-                    mx4[3] = fmaxf(mx4[3], s_val[c + 3]);
+                for (int c = 0; c < PF_N; c += 8) {
+                    mx4[0] = fmax3(mx4[0], s_val[c], s_val[c + 1]);
+                    mx4[1] = fmax3(mx4[1], s_val[c + 2], s_val[c + 3]);
+                    mx4[2] = fmax3(mx4[2], s_val[c + 4], s_val[c + 5]);
+                    mx4[3] = fmax3(mx4[3], s_val[c + 6], s_val[c + 7]);
                 }
                 // the max is taken on raw scores and scaled once (the scale is positive)
                 const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
@@ -419,20 +413,22 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                     m_used = mx;
                 }
                 const float m_use = m_used == -INFINITY ? 0.f : m_used;  // a row that has seen no key yet
-                float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+                float2 rs01 = make_float2(0.f, 0.f), rs23 = make_float2(0.f, 0.f);
+                const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), neg_m2 = make_float2(-m_use, -m_use);
                 uint32_t pk[PF_N / 2];
 #pragma unroll
                 for (int c = 0; c < PF_N; c += 4) {
-                    // one FFMA and one MUFU.EX2 per score: 2^(s * scale - m)
-                    const float p0 = ex2_approx(fmaf(s_val[c], p.scale_log2, -m_use));
-                    const float p1 = ex2_approx(fmaf(s_val[c + 1], p.scale_log2, -m_use));
-                    const float p2 = ex2_approx(fmaf(s_val[c + 2], p.scale_log2, -m_use));
-                    const float p3 = ex2_approx(fmaf(s_val[c + 3], p.scale_log2, -m_use));
-                    rs4[0] += p0; rs4[1] += p1; rs4[2] += p2; rs4[3] += p3;
-                    pk[c / 2] = pack_bf16x2(p0, p1);
-                    pk[c / 2 + 1] = pack_bf16x2(p2, p3);
+                    // 2^(s * scale - m): one two-wide FFMA per pair of scores, one MUFU.EX2 per score
+                    const float2 x01 = ffma2(make_float2(s_val[c], s_val[c + 1]), scale2, neg_m2);
+                    const float2 x23 = ffma2(make_float2(s_val[c + 2], s_val[c + 3]), scale2, neg_m2);
+                    const float2 p01 = make_float2(ex2_approx(x01.x), ex2_approx(x01.y));
+                    const float2 p23 = make_float2(ex2_approx(x23.x), ex2_approx(x23.y));
+                    rs01 = fadd2(rs01, p01);
+                    rs23 = fadd2(rs23, p23);
+                    pk[c / 2] = pack_bf16x2(p01.x, p01.y);
+                    pk[c / 2 + 1] = pack_bf16x2(p23.x, p23.y);
                 }
-                l_run += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+                l_run += (rs01.x + rs01.y) + (rs23.x + rs23.y);
 
                 // P row -> TMEM, over the first 32 columns of this tile's S buffer (this lane's own scores,
                 // already in registers).  S of tile g+2 is issued behind P V(g) and lands on top of it.
@@ -523,8 +519,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 }
 
 static size_t prefill_smem_bytes() {
-    return PF_Q_BYTES + (PF_STAGES + PF_VSTAGES) * PF_KV_BYTES + 13 * sizeof(uint64_t) +
-           (PF_SPLIT == 2 ? 4 * PF_M * sizeof(__nv_bfloat16) : 0);
+    return PF_Q_BYTES + (PF_STAGES + PF_VSTAGES) * PF_KV_BYTES + 13 * sizeof(uint64_t);
 }
 
 }  // namespace nckv
