@@ -330,6 +330,24 @@ NCKV_API int nckv_prefill_attn(const void *q, const void *k, const void *v, cons
                       int32_t *status, void *stream);
 
 /*
+ * flash_attn_func for training (flash_attention.py:107-128, caller gpt.py:108): causal attention with a
+ * left window over plain (B, T, H, D) bf16 tensors, forward with the log-sum-exp kept, and backward.
+ * Replaces F.scaled_dot_product_attention and the autograd graph behind it on this path.
+ *   nckv_flash_attn_fwd   out (B, T, Hq, D) and lse (B, Hq, T) fp32, the natural log of each row's sum of
+ *                         exponentials of the scaled scores.  Same kernel as nckv_prefill_attn; `status` is
+ *                         the first word of a zero-initialised workspace as there.
+ *   nckv_flash_attn_bwd   dq (B, T, Hq, D), dk and dv (B, T, Hkv, D) from q, k, v, out, dout and lse.
+ *                         `workspace` holds nckv_flash_attn_bwd_workspace_bytes(B, T, Hq) bytes of scratch
+ *                         (rowsum(dout * out)); no atomics are used, results do not depend on scheduling.
+ */
+NCKV_API int nckv_flash_attn_fwd(const void *q, const void *k, const void *v, void *out, float *lse, int B, int T,
+                        int Hq, int Hkv, int D, int window_left, int32_t *status, void *stream);
+NCKV_API size_t nckv_flash_attn_bwd_workspace_bytes(int B, int T, int Hq);
+NCKV_API int nckv_flash_attn_bwd(const void *q, const void *k, const void *v, const void *out, const void *dout,
+                        const float *lse, void *dq, void *dk, void *dv, void *workspace, int B, int T, int Hq,
+                        int Hkv, int D, int window_left, void *stream);
+
+/*
  * Decode-time glue of the transformer trunk around the KV branch: the elementwise ops between the
  * matrix products of GPT.forward / Block.forward for one new token per row, fused per layer.  Each
  * kernel rounds to bf16 exactly where the eager op sequence does, so results are bit-identical to it.

@@ -55,6 +55,9 @@ SIGNATURES = {
     "nckv_paged_fill": (c_int, [c_void_p] * 5 + [c_int] * 7 + [c_void_p]),
     "nckv_prefill_broadcast": (c_int, [c_void_p] * 5 + [c_int] * 7 + [c_void_p]),
     "nckv_prefill_attn": (c_int, [c_void_p] * 5 + [c_int] * 6 + [c_i64, c_i64, c_int, c_void_p, c_void_p]),
+    "nckv_flash_attn_fwd": (c_int, [c_void_p] * 5 + [c_int] * 6 + [c_void_p, c_void_p]),
+    "nckv_flash_attn_bwd_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "nckv_flash_attn_bwd": (c_int, [c_void_p] * 10 + [c_int] * 6 + [c_void_p]),
 }
 
 ERROR_NAMES = {-1: "NCKV_E_ARG", -2: "NCKV_E_UNSUPPORTED", -3: "NCKV_E_CAPACITY", -4: "NCKV_E_CUDA"}

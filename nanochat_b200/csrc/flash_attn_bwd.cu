@@ -1,0 +1,352 @@
+// Backward of flash_attn_func (training): dq, dk, dv of causal / sliding-window attention over plain
+// (B, T, H, D) tensors, from q, k, v, the forward output, its gradient and the forward's log-sum-exp.
+//
+//   P  = exp(scale * Q K^T - lse)            (recomputed per tile, never stored)
+//   dV = P^T dO
+//   dP = dO V^T,   delta = rowsum(dO * O),   dS = P * (dP - delta)
+//   dQ = scale * dS K,    dK = scale * dS^T Q
+//
+// Three kernels.  `delta` is one warp per (row, token, head).  The dK/dV kernel gives a CTA one tile
+// of 64 keys of one (row, kv head) and walks the query tiles (of every q head of the group) that see
+// them; the dQ kernel gives a CTA one tile of 64 queries of one (row, q head) and walks its key
+// tiles.  Scores are recomputed in both (7 matrix products per tile pair instead of 5) so that no
+// gradient needs atomics: results do not depend on scheduling.  The products run on the warp-level
+// tensor-core path (16x16x16 bf16 fragments, fp32 accumulation), operands staged in shared memory;
+// this path is a first, correct version and makes no claim on the tensor-core roofline.
+//
+// Replaces: autograd through F.scaled_dot_product_attention as reached from flash_attn_func
+// (flash_attention.py:107-128, caller gpt.py:108) when training.
+#include <math.h>
+#include <mma.h>
+
+#include "nckv_common.cuh"
+
+namespace nckv {
+
+namespace wm = nvcuda::wmma;
+
+constexpr int BW_T = 64;             // queries and keys per tile
+constexpr int BW_THREADS = 256;      // 8 warps
+constexpr int BW_LD = NCKV_D + 8;    // bf16 row stride of the 64 x 128 operand tiles (272 B: no bank conflicts)
+constexpr int BW_LDS = BW_T + 8;     // row stride of the 64 x 64 score tiles (fp32 and bf16)
+
+struct BwdParams {
+    const __nv_bfloat16 *q, *k, *v, *dout;
+    const float *lse, *delta;
+    __nv_bfloat16 *dq, *dk, *dv;
+    int B, T, Hq, Hkv;
+    int window_left;
+    float scale, scale_log2;
+};
+
+struct BwdSmem {
+    __nv_bfloat16 q[BW_T * BW_LD];
+    __nv_bfloat16 dout[BW_T * BW_LD];
+    __nv_bfloat16 k[BW_T * BW_LD];
+    __nv_bfloat16 v[BW_T * BW_LD];
+    float s[BW_T * BW_LDS];   // scores, then (with dp, contiguous) staging of a 64 x 128 fp32 result
+    float dp[BW_T * BW_LDS];
+    __nv_bfloat16 p[BW_T * BW_LDS];
+    __nv_bfloat16 ds[BW_T * BW_LDS];
+    float lse2[BW_T];   // log-sum-exp in powers of two
+    float delta[BW_T];
+};
+static_assert(2 * BW_T * BW_LDS >= BW_T * NCKV_D, "the result staging area spans s and dp");
+
+// 64 rows x 256 bytes of a (B, T, H, D) tensor into a padded shared-memory tile; rows at or beyond T are zero.
+__device__ __forceinline__ void load_tile(__nv_bfloat16 *dst, const __nv_bfloat16 *src, int b, int t0, int h, int T,
+                                          int H) {
+    for (int i = threadIdx.x; i < BW_T * (NCKV_D / 8); i += BW_THREADS) {
+        const int r = i / (NCKV_D / 8), c = i % (NCKV_D / 8);
+        const int t = t0 + r;
+        uint4 val = make_uint4(0, 0, 0, 0);
+        if (t < T) val = *reinterpret_cast<const uint4 *>(src + (((long long)b * T + t) * H + h) * NCKV_D + c * 8);
+        *reinterpret_cast<uint4 *>(dst + r * BW_LD + c * 8) = val;
+    }
+}
+
+// S = Q K^T and dP = dO V^T for the staged tiles: 4 x 4 output fragments each, two per warp and product.
+__device__ __forceinline__ void scores_and_dp(BwdSmem &sm, int warp) {
+    const int r = warp >> 1, c0 = (warp & 1) * 2;
+    wm::fragment<wm::accumulator, 16, 16, 16, float> acc_s[2], acc_p[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        wm::fill_fragment(acc_s[j], 0.f);
+        wm::fill_fragment(acc_p[j], 0.f);
+    }
+#pragma unroll
+    for (int kk = 0; kk < NCKV_D / 16; ++kk) {
+        wm::fragment<wm::matrix_a, 16, 16, 16, __nv_bfloat16, wm::row_major> a_q, a_do;
+        wm::load_matrix_sync(a_q, sm.q + r * 16 * BW_LD + kk * 16, BW_LD);
+        wm::load_matrix_sync(a_do, sm.dout + r * 16 * BW_LD + kk * 16, BW_LD);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            // B(k = channel, n = key) sits at tile[key][channel]: column-major with the tile's row stride
+            wm::fragment<wm::matrix_b, 16, 16, 16, __nv_bfloat16, wm::col_major> b_k, b_v;
+            wm::load_matrix_sync(b_k, sm.k + (c0 + j) * 16 * BW_LD + kk * 16, BW_LD);
+            wm::load_matrix_sync(b_v, sm.v + (c0 + j) * 16 * BW_LD + kk * 16, BW_LD);
+            wm::mma_sync(acc_s[j], a_q, b_k, acc_s[j]);
+            wm::mma_sync(acc_p[j], a_do, b_v, acc_p[j]);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        wm::store_matrix_sync(sm.s + r * 16 * BW_LDS + (c0 + j) * 16, acc_s[j], BW_LDS, wm::mem_row_major);
+        wm::store_matrix_sync(sm.dp + r * 16 * BW_LDS + (c0 + j) * 16, acc_p[j], BW_LDS, wm::mem_row_major);
+    }
+}
+
+// P and dS of the staged score tile (queries q0.., keys k0..), rounded to bf16 for the products that follow.
+__device__ __forceinline__ void probabilities(BwdSmem &sm, const BwdParams &p, int q0, int k0) {
+    for (int i = threadIdx.x; i < BW_T * BW_T; i += BW_THREADS) {
+        const int r = i / BW_T, c = i % BW_T;
+        const int tq = q0 + r, tk = k0 + c;
+        const bool visible = tq < p.T && tk <= tq && (p.window_left < 0 || tq - tk <= p.window_left);
+        float pr = 0.f, ds = 0.f;
+        if (visible) {
+            pr = exp2f(sm.s[r * BW_LDS + c] * p.scale_log2 - sm.lse2[r]);
+            ds = pr * (sm.dp[r * BW_LDS + c] - sm.delta[r]) * p.scale;
+        }
+        sm.p[r * BW_LDS + c] = __float2bfloat16(pr);
+        sm.ds[r * BW_LDS + c] = __float2bfloat16(ds);
+    }
+}
+
+__device__ __forceinline__ void load_row_stats(BwdSmem &sm, const BwdParams &p, int b, int hq, int q0) {
+    for (int r = threadIdx.x; r < BW_T; r += BW_THREADS) {
+        const int t = q0 + r;
+        const long long o = ((long long)b * p.Hq + hq) * p.T + t;
+        // a row without keys (lse = -inf) cannot occur under a causal mask; keep exp2 finite anyway
+        const float l = t < p.T ? p.lse[o] : 0.f;
+        sm.lse2[r] = l == -INFINITY ? 0.f : l * 1.4426950408889634f;
+        sm.delta[r] = t < p.T ? p.delta[o] : 0.f;
+    }
+}
+
+// fp32 64 x 128 result in the staging area -> bf16 rows of a (B, T, H, D) tensor
+__device__ __forceinline__ void store_result(const float *stage, __nv_bfloat16 *dst, int b, int t0, int h, int T,
+                                             int H) {
+    for (int i = threadIdx.x; i < BW_T * (NCKV_D / 8); i += BW_THREADS) {
+        const int r = i / (NCKV_D / 8), c = i % (NCKV_D / 8);
+        const int t = t0 + r;
+        if (t >= T) continue;
+        const float *src = stage + r * NCKV_D + c * 8;
+        uint4 val;
+        val.x = pack_bf16x2(src[0], src[1]);
+        val.y = pack_bf16x2(src[2], src[3]);
+        val.z = pack_bf16x2(src[4], src[5]);
+        val.w = pack_bf16x2(src[6], src[7]);
+        *reinterpret_cast<uint4 *>(dst + (((long long)b * T + t) * H + h) * NCKV_D + c * 8) = val;
+    }
+}
+
+// delta[b, h, t] = sum_c dO[b, t, h, c] * O[b, t, h, c]
+__global__ void __launch_bounds__(256) attn_bwd_delta_kernel(const __nv_bfloat16 *out, const __nv_bfloat16 *dout,
+                                                             float *delta, int B, int T, int Hq) {
+    const long long row = (long long)blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5);  // (b, t, h) flattened
+    if (row >= (long long)B * T * Hq) return;
+    const int lane = threadIdx.x & 31;
+    const uint2 o = *reinterpret_cast<const uint2 *>(out + row * NCKV_D + lane * 4);
+    const uint2 g = *reinterpret_cast<const uint2 *>(dout + row * NCKV_D + lane * 4);
+    const __nv_bfloat162 *o2 = reinterpret_cast<const __nv_bfloat162 *>(&o);
+    const __nv_bfloat162 *g2 = reinterpret_cast<const __nv_bfloat162 *>(&g);
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const float2 a = __bfloat1622float2(o2[i]), c = __bfloat1622float2(g2[i]);
+        acc += a.x * c.x + a.y * c.y;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (lane == 0) {
+        const int h = (int)(row % Hq);
+        const long long bt = row / Hq;
+        const int t = (int)(bt % T), b = (int)(bt / T);
+        delta[((long long)b * Hq + h) * T + t] = acc;
+    }
+}
+
+// One CTA: 64 keys of one (row, kv head).  grid = (key tiles, Hkv, B)
+__global__ void __launch_bounds__(BW_THREADS) attn_bwd_dkdv_kernel(const BwdParams p) {
+    extern __shared__ __align__(128) uint8_t bw_smem[];
+    BwdSmem &sm = *reinterpret_cast<BwdSmem *>(bw_smem);
+    const int warp = threadIdx.x >> 5;
+    const int k0 = blockIdx.x * BW_T, hkv = blockIdx.y, b = blockIdx.z;
+    const int rep = p.Hq / p.Hkv;
+
+    load_tile(sm.k, p.k, b, k0, hkv, p.T, p.Hkv);
+    load_tile(sm.v, p.v, b, k0, hkv, p.T, p.Hkv);
+
+    // output fragments: 4 (key blocks) x 8 (channel blocks); warp w owns channel block w
+    wm::fragment<wm::accumulator, 16, 16, 16, float> acc_dk[4], acc_dv[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        wm::fill_fragment(acc_dk[r], 0.f);
+        wm::fill_fragment(acc_dv[r], 0.f);
+    }
+    // query tiles that see any of these keys: positions k0 .. (last key + window)
+    const int last_key = min(k0 + BW_T, p.T) - 1;
+    const int q_hi = p.window_left >= 0 ? min(p.T - 1, last_key + p.window_left) : p.T - 1;
+    for (int g = 0; g < rep; ++g) {
+        const int hq = hkv * rep + g;
+        for (int q0 = k0; q0 <= q_hi; q0 += BW_T) {  // causal: queries at or after the tile's first key
+            __syncthreads();  // the previous iteration's products have read q, dout, p, ds
+            load_tile(sm.q, p.q, b, q0, hq, p.T, p.Hq);
+            load_tile(sm.dout, p.dout, b, q0, hq, p.T, p.Hq);
+            load_row_stats(sm, p, b, hq, q0);
+            __syncthreads();
+            scores_and_dp(sm, warp);
+            __syncthreads();
+            probabilities(sm, p, q0, k0);
+            __syncthreads();
+#pragma unroll
+            for (int qq = 0; qq < BW_T / 16; ++qq) {
+                wm::fragment<wm::matrix_b, 16, 16, 16, __nv_bfloat16, wm::row_major> b_do, b_q;
+                wm::load_matrix_sync(b_do, sm.dout + qq * 16 * BW_LD + warp * 16, BW_LD);
+                wm::load_matrix_sync(b_q, sm.q + qq * 16 * BW_LD + warp * 16, BW_LD);
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    // A(m = key, k = query) sits at tile[query][key]: column-major
+                    wm::fragment<wm::matrix_a, 16, 16, 16, __nv_bfloat16, wm::col_major> a_p, a_ds;
+                    wm::load_matrix_sync(a_p, sm.p + qq * 16 * BW_LDS + r * 16, BW_LDS);
+                    wm::load_matrix_sync(a_ds, sm.ds + qq * 16 * BW_LDS + r * 16, BW_LDS);
+                    wm::mma_sync(acc_dv[r], a_p, b_do, acc_dv[r]);
+                    wm::mma_sync(acc_dk[r], a_ds, b_q, acc_dk[r]);
+                }
+            }
+        }
+    }
+    __syncthreads();
+    float *stage = sm.s;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) wm::store_matrix_sync(stage + r * 16 * NCKV_D + warp * 16, acc_dk[r], NCKV_D, wm::mem_row_major);
+    __syncthreads();
+    store_result(stage, p.dk, b, k0, hkv, p.T, p.Hkv);
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < 4; ++r) wm::store_matrix_sync(stage + r * 16 * NCKV_D + warp * 16, acc_dv[r], NCKV_D, wm::mem_row_major);
+    __syncthreads();
+    store_result(stage, p.dv, b, k0, hkv, p.T, p.Hkv);
+}
+
+// One CTA: 64 queries of one (row, q head).  grid = (query tiles, Hq, B)
+__global__ void __launch_bounds__(BW_THREADS) attn_bwd_dq_kernel(const BwdParams p) {
+    extern __shared__ __align__(128) uint8_t bw_smem[];
+    BwdSmem &sm = *reinterpret_cast<BwdSmem *>(bw_smem);
+    const int warp = threadIdx.x >> 5;
+    // longest tiles first: the last query tile sees the most keys
+    const int q0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * BW_T, hq = blockIdx.y, b = blockIdx.z;
+    const int hkv = hq / (p.Hq / p.Hkv);
+
+    load_tile(sm.q, p.q, b, q0, hq, p.T, p.Hq);
+    load_tile(sm.dout, p.dout, b, q0, hq, p.T, p.Hq);
+    load_row_stats(sm, p, b, hq, q0);
+
+    wm::fragment<wm::accumulator, 16, 16, 16, float> acc_dq[4];  // 4 (query blocks) x channel block `warp`
+#pragma unroll
+    for (int r = 0; r < 4; ++r) wm::fill_fragment(acc_dq[r], 0.f);
+
+    const int last_q = min(q0 + BW_T, p.T) - 1;
+    int k_lo = p.window_left >= 0 ? max(0, q0 - p.window_left) : 0;
+    k_lo -= k_lo % BW_T;
+    for (int k0 = k_lo; k0 <= last_q; k0 += BW_T) {
+        __syncthreads();  // the previous iteration's product has read k and ds
+        load_tile(sm.k, p.k, b, k0, hkv, p.T, p.Hkv);
+        load_tile(sm.v, p.v, b, k0, hkv, p.T, p.Hkv);
+        __syncthreads();
+        scores_and_dp(sm, warp);
+        __syncthreads();
+        probabilities(sm, p, q0, k0);
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BW_T / 16; ++kk) {
+            wm::fragment<wm::matrix_b, 16, 16, 16, __nv_bfloat16, wm::row_major> b_k;  // B(k = key, n = channel)
+            wm::load_matrix_sync(b_k, sm.k + kk * 16 * BW_LD + warp * 16, BW_LD);
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                wm::fragment<wm::matrix_a, 16, 16, 16, __nv_bfloat16, wm::row_major> a_ds;
+                wm::load_matrix_sync(a_ds, sm.ds + r * 16 * BW_LDS + kk * 16, BW_LDS);
+                wm::mma_sync(acc_dq[r], a_ds, b_k, acc_dq[r]);
+            }
+        }
+    }
+    __syncthreads();
+    float *stage = sm.s;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) wm::store_matrix_sync(stage + r * 16 * NCKV_D + warp * 16, acc_dq[r], NCKV_D, wm::mem_row_major);
+    __syncthreads();
+    store_result(stage, p.dq, b, q0, hq, p.T, p.Hq);
+}
+
+}  // namespace nckv
+
+extern "C" size_t nckv_flash_attn_bwd_workspace_bytes(int B, int T, int Hq) {
+    return (size_t)B * (size_t)T * (size_t)Hq * sizeof(float);
+}
+
+extern "C" int nckv_flash_attn_bwd(const void *q, const void *k, const void *v, const void *out, const void *dout,
+                                   const float *lse, void *dq, void *dk, void *dv, void *workspace, int B, int T,
+                                   int Hq, int Hkv, int D, int window_left, void *stream) {
+    using namespace nckv;
+    if (!q || !k || !v || !out || !dout || !lse || !dq || !dk || !dv || !workspace) {
+        set_error("flash_attn_bwd: null pointer argument");
+        return NCKV_E_ARG;
+    }
+    if (B <= 0 || T <= 0 || Hq <= 0 || Hkv <= 0) {
+        set_error("flash_attn_bwd: non-positive size (B=%d T=%d Hq=%d Hkv=%d)", B, T, Hq, Hkv);
+        return NCKV_E_ARG;
+    }
+    if (D != NCKV_D) {
+        set_error("flash_attn_bwd: head_dim %d unsupported (kernels are built for 128)", D);
+        return NCKV_E_UNSUPPORTED;
+    }
+    if (Hq % Hkv != 0) {
+        set_error("flash_attn_bwd: Hq=%d must be a multiple of Hkv=%d", Hq, Hkv);
+        return NCKV_E_UNSUPPORTED;
+    }
+    const int n_tiles = (T + BW_T - 1) / BW_T;
+    if (Hq > 65535 || B > 65535) {
+        set_error("flash_attn_bwd: B=%d or Hq=%d exceeds the grid limit 65535", B, Hq);
+        return NCKV_E_UNSUPPORTED;
+    }
+    if ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out | (uintptr_t)dout | (uintptr_t)dq | (uintptr_t)dk |
+          (uintptr_t)dv) & 15) != 0) {
+        set_error("flash_attn_bwd: tensors must be 16-byte aligned");
+        return NCKV_E_ARG;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    BwdParams p;
+    p.q = static_cast<const __nv_bfloat16 *>(q);
+    p.k = static_cast<const __nv_bfloat16 *>(k);
+    p.v = static_cast<const __nv_bfloat16 *>(v);
+    p.dout = static_cast<const __nv_bfloat16 *>(dout);
+    p.lse = lse;
+    p.delta = static_cast<const float *>(workspace);
+    p.dq = static_cast<__nv_bfloat16 *>(dq);
+    p.dk = static_cast<__nv_bfloat16 *>(dk);
+    p.dv = static_cast<__nv_bfloat16 *>(dv);
+    p.B = B; p.T = T; p.Hq = Hq; p.Hkv = Hkv;
+    p.window_left = window_left;
+    p.scale = (float)(1.0 / sqrt((double)D));
+    p.scale_log2 = (float)(1.4426950408889634 / sqrt((double)D));
+
+    const long long rows = (long long)B * T * Hq;
+    attn_bwd_delta_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(out), p.dout,
+                                                                       static_cast<float *>(workspace), B, T, Hq);
+    NCKV_CUDA_CHECK(cudaGetLastError());
+
+    const size_t smem = sizeof(BwdSmem);
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    NCKV_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 64 && !attr_set[dev]) {
+        NCKV_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        NCKV_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_set[dev] = true;
+    }
+    attn_bwd_dkdv_kernel<<<dim3((unsigned)n_tiles, (unsigned)Hkv, (unsigned)B), BW_THREADS, smem, st>>>(p);
+    NCKV_CUDA_CHECK(cudaGetLastError());
+    attn_bwd_dq_kernel<<<dim3((unsigned)n_tiles, (unsigned)Hq, (unsigned)B), BW_THREADS, smem, st>>>(p);
+    NCKV_CUDA_CHECK(cudaGetLastError());
+    return NCKV_OK;
+}

@@ -57,6 +57,7 @@ constexpr unsigned long long PF_WAIT_LIMIT = NCKV_WAIT_LIMIT_NS;
 struct PrefillParams {
     const int32_t *seqlens;  // may be null (all zero)
     __nv_bfloat16 *out;
+    float *lse;  // optional (B, Hq, T_new): natural log of each row's sum of exponentials, -inf for a row without keys
     int32_t *status;
     int B, T_new, Hq, Hkv, T_k;
     int n_qtiles, n_items;
@@ -482,6 +483,9 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 tc_fence_after();
             }
             const float inv = (n_tiles > 0 && l_run > 0.f) ? 1.f / l_run : 0.f;
+            if (p.lse && tq < p.T_new)  // m_used and l_run are in powers of two
+                p.lse[((long long)it.b * p.Hq + it.hq) * p.T_new + tq] =
+                    (n_tiles > 0 && l_run > 0.f) ? (m_used + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
             uint4 *dst = reinterpret_cast<uint4 *>(p.out + (((long long)it.b * p.T_new + tq) * p.Hq + it.hq) * NCKV_D);
 #pragma unroll
             for (int ch = 0; ch < NCKV_D / 32; ++ch) {
@@ -525,10 +529,9 @@ static size_t prefill_smem_bytes() {
 }  // namespace nckv
 
 
-extern "C" int nckv_prefill_attn(const void *q, const void *k, const void *v, const int32_t *cache_seqlens,
-                                 void *out, int B, int T_new, int Hq, int Hkv, int D, int T_k,
-                                 int64_t kv_batch_stride, int64_t kv_token_stride, int window_left,
-                                 int32_t *status, void *stream) {
+static int prefill_launch(const void *q, const void *k, const void *v, const int32_t *cache_seqlens, void *out,
+                          float *lse, int B, int T_new, int Hq, int Hkv, int D, int T_k, int64_t kv_batch_stride,
+                          int64_t kv_token_stride, int window_left, int32_t *status, void *stream) {
     using namespace nckv;
     if (!q || !k || !v || !out || !status) {
         set_error("prefill_attn: null pointer argument");
@@ -570,6 +573,7 @@ extern "C" int nckv_prefill_attn(const void *q, const void *k, const void *v, co
     PrefillParams p;
     p.seqlens = cache_seqlens;
     p.out = static_cast<__nv_bfloat16 *>(out);
+    p.lse = lse;
     p.status = status;
     p.B = B; p.T_new = T_new; p.Hq = Hq; p.Hkv = Hkv; p.T_k = T_k;
     p.window_left = window_left;
@@ -624,4 +628,24 @@ extern "C" int nckv_prefill_attn(const void *q, const void *k, const void *v, co
     cfg.numAttrs = 1;
     NCKV_CUDA_CHECK(cudaLaunchKernelEx(&cfg, prefill_attn_kernel, mq, mk, mv, p));
     return NCKV_OK;
+}
+
+extern "C" int nckv_prefill_attn(const void *q, const void *k, const void *v, const int32_t *cache_seqlens,
+                                 void *out, int B, int T_new, int Hq, int Hkv, int D, int T_k,
+                                 int64_t kv_batch_stride, int64_t kv_token_stride, int window_left,
+                                 int32_t *status, void *stream) {
+    return prefill_launch(q, k, v, cache_seqlens, out, nullptr, B, T_new, Hq, Hkv, D, T_k, kv_batch_stride,
+                          kv_token_stride, window_left, status, stream);
+}
+
+// Forward of flash_attn_func for training: the same kernel over plain (B, T, H, D) tensors, which also
+// writes the log-sum-exp of every row for the backward pass.
+extern "C" int nckv_flash_attn_fwd(const void *q, const void *k, const void *v, void *out, float *lse, int B, int T,
+                                   int Hq, int Hkv, int D, int window_left, int32_t *status, void *stream) {
+    if (!lse) {
+        nckv::set_error("flash_attn_fwd: null lse pointer");
+        return NCKV_E_ARG;
+    }
+    return prefill_launch(q, k, v, nullptr, out, lse, B, T, Hq, Hkv, D, T, (int64_t)T * Hkv * D, (int64_t)Hkv * D,
+                          window_left, status, stream);
 }

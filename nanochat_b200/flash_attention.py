@@ -47,11 +47,11 @@ def flash_attn_func(q, k, v, causal=False, window_size=(-1, -1)):
 
     As in the fallback it replaces (flash_attention.py:122-128), masking is always causal with the
     left window ``window_size[0]``; ``causal`` and ``window_size[1]`` are accepted and not consulted.
-    Inference only: inputs that require grad are rejected (the training backward stays with the
-    reference's own path).
+    When an input requires grad (training, gpt.py:108) the call goes through an autograd function whose
+    backward runs the library's own dq/dk/dv kernels; the forward is the same kernel either way.
     """
-    if q.requires_grad or k.requires_grad or v.requires_grad:
-        raise NotImplementedError("flash_attn_func here is inference-only; autograd inputs are not supported")
+    if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
+        return ops.FlashAttnTrainFunction.apply(q, k, v, _window_left(window_size))
     return ops.prefill_attention(q, k, v, None, _window_left(window_size))
 
 

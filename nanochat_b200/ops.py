@@ -318,6 +318,73 @@ _NS.impl("prefill_attn", _prefill_attn, "CUDA")
 _NS.impl("prefill_attn", _prefill_attn, "CPU")
 
 # ------------------------------------------------------------------------------------------------
+# flash_attn_func for training: forward that keeps the log-sum-exp, and backward
+# ------------------------------------------------------------------------------------------------
+def _check_train_qkv(name, q, k, v):
+    _require_cuda(name, q, k, v)
+    _require_bf16(name, q, k, v)
+    if q.dim() != 4 or q.size(3) != HEAD_DIM:
+        raise RuntimeError(f"nckv::{name}: q must be (B, T, Hq, {HEAD_DIM}), got {tuple(q.shape)}")
+    B, T, Hq, _ = q.shape
+    if k.shape != v.shape or k.dim() != 4 or k.size(0) != B or k.size(1) != T or k.size(3) != HEAD_DIM or Hq % k.size(2):
+        raise RuntimeError(f"nckv::{name}: k/v {tuple(k.shape)} / {tuple(v.shape)} do not match q {tuple(q.shape)}")
+    return B, T, Hq, k.size(2)
+
+
+def flash_attn_fwd(q, k, v, window_left=-1):
+    """Causal attention (left window) over plain (B, T, H, D) tensors; returns (out, lse (B, Hq, T) fp32)."""
+    name = "flash_attn_fwd"
+    B, T, Hq, Hkv = _check_train_qkv(name, q, k, v)
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    out = torch.empty_like(q)
+    lse = torch.empty(B, Hq, T, dtype=torch.float32, device=q.device)
+    idx, stream, ws = _launch_ctx(q, B, Hq, Hkv)
+    with _device_guard(idx):
+        rc = _lib.call("nckv_flash_attn_fwd", _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse), B, T, Hq, Hkv, HEAD_DIM,
+                       int(window_left), _ptr(ws), stream)
+    if rc < 0:
+        _lib.check("nckv_flash_attn_fwd", rc)
+    return out, lse
+
+
+def flash_attn_bwd(q, k, v, out, dout, lse, window_left=-1):
+    """Gradients (dq, dk, dv) of flash_attn_fwd's output with respect to q, k, v."""
+    name = "flash_attn_bwd"
+    B, T, Hq, Hkv = _check_train_qkv(name, q, k, v)
+    _require_cuda(name, out, dout, lse)
+    _require_bf16(name, out, dout)
+    if out.shape != q.shape or dout.shape != q.shape or tuple(lse.shape) != (B, Hq, T) or lse.dtype != torch.float32:
+        raise RuntimeError(f"nckv::{name}: out/dout must have q's shape and lse must be fp32 (B, Hq, T)")
+    q, k, v, out, dout, lse = (t.contiguous() for t in (q, k, v, out, dout, lse))
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    scratch = torch.empty(_lib.call("nckv_flash_attn_bwd_workspace_bytes", B, T, Hq), dtype=torch.uint8, device=q.device)
+    idx = q.device.index if q.device.index is not None else torch.cuda.current_device()
+    with _device_guard(idx):
+        rc = _lib.call("nckv_flash_attn_bwd", _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(dout), _ptr(lse), _ptr(dq), _ptr(dk),
+                       _ptr(dv), _ptr(scratch), B, T, Hq, Hkv, HEAD_DIM, int(window_left), _stream(idx))
+    if rc < 0:
+        _lib.check("nckv_flash_attn_bwd", rc)
+    return dq, dk, dv
+
+
+class FlashAttnTrainFunction(torch.autograd.Function):
+    """flash_attn_func with a backward pass: both directions run libnckv kernels."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, window_left):
+        out, lse = flash_attn_fwd(q, k, v, window_left)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.window_left = window_left
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse = ctx.saved_tensors
+        dq, dk, dv = flash_attn_bwd(q, k, v, out, dout.to(torch.bfloat16), lse, ctx.window_left)
+        return dq, dk, dv, None
+
+
+# ------------------------------------------------------------------------------------------------
 # prefill broadcast and LSE combine
 # ------------------------------------------------------------------------------------------------
 _NS.define("prefill_broadcast(Tensor src_k, Tensor src_v, Tensor(a!) dst_k, Tensor(b!) dst_v, "
