@@ -908,6 +908,29 @@ def run_case(args):
                    us_per_call=sec * 1e6, frac=flops / sec / 1e12 / tpeak, peak=tpeak,
                    torch_sdpa={"us_per_call": sdpa_sec * 1e6, "tflops": flops / sdpa_sec / 1e12},
                    config={"B": Bc, "T": T, "Hq": Hq, "Hkv": Hkv})
+    elif args.case == "train_attn":         # flash_attn_func forward + backward, d24 training shape
+        Bc, T, Hq, Hkv = 8, 2048, 12, 12
+        q, k, v = (rnd(Bc, T, Hq, D).requires_grad_(True), rnd(Bc, T, Hkv, D).requires_grad_(True),
+                   rnd(Bc, T, Hkv, D).requires_grad_(True))
+        dout = rnd(Bc, T, Hq, D)
+        from nanochat_b200.flash_attention import flash_attn
+
+        def ours(i):
+            flash_attn.flash_attn_func(q, k, v, causal=True, window_size=(-1, 0)).backward(dout)
+        o_, lse_ = ops.flash_attn_fwd(q.detach(), k.detach(), v.detach(), -1)
+        sec = _time_cuda(ours, iters)
+        bwd_sec = _time_cuda(lambda i: ops.flash_attn_bwd(q.detach(), k.detach(), v.detach(), o_, dout, lse_, -1), iters)
+        qs, ks, vs = (t.detach().transpose(1, 2).requires_grad_(True) for t in (q, k, v))
+        dts = dout.transpose(1, 2)
+
+        def sdpa(i):  # what the reference runs on this GPU when training (flash_attention.py:122-128)
+            torch.nn.functional.scaled_dot_product_attention(qs, ks, vs, is_causal=True).backward(dts)
+        sdpa_sec = _time_cuda(sdpa, iters)
+        flops = 3.5 * 4.0 * D * Bc * Hq * (T * (T + 1) / 2)  # forward 2 products, backward 5, causal half
+        out.update(metric="attention forward + backward, us per call (causal, training shape)", value=sec * 1e6, unit="us",
+                   backward_us=bwd_sec * 1e6, useful_tflops=flops / sec / 1e12,
+                   torch_sdpa={"us_per_call": sdpa_sec * 1e6, "useful_tflops": flops / sdpa_sec / 1e12},
+                   config={"B": Bc, "T": T, "Hq": Hq, "Hkv": Hkv})
     elif args.case == "broadcast":          # configs[4]: 8192-token block -> 64 sample rows, one layer
         L, Bc, p, Hkv = 1, 64, 8192, 4
         src_k, src_v = rnd(L, 1, p, Hkv, D), rnd(L, 1, p, Hkv, D)
@@ -987,7 +1010,7 @@ def main():
                     help="headline workload only: skip the long_context, d24_sharded and gpu_reference legs")
     ap.add_argument("--case", default=None,
                     help="secondary op-level measurement instead of the headline workload: decode_long, decode_gqa, "
-                         "decode_gqa_window, decode_d24, decode_paged, prefill, prefill_paged, broadcast, append, engine_d24, engine_d24_small, engine_d32, "
+                         "decode_gqa_window, decode_d24, decode_paged, prefill, prefill_paged, train_attn, broadcast, append, engine_d24, engine_d24_small, engine_d32, "
                          "engine_d32_small, engine_api_d24, engine_api_small")
     args = ap.parse_args()
     global REGIONS_OVERRIDE

@@ -26,7 +26,7 @@ namespace nckv {
 namespace wm = nvcuda::wmma;
 
 constexpr int BW_T = 64;             // queries and keys per tile
-constexpr int BW_THREADS = 256;      // 8 warps
+constexpr int BW_THREADS = 512;      // 16 warps: one per 16 x 16 score fragment
 constexpr int BW_LD = NCKV_D + 8;    // bf16 row stride of the 64 x 128 operand tiles (272 B: no bank conflicts)
 constexpr int BW_LDS = BW_T + 8;     // row stride of the 64 x 64 score tiles (fp32 and bf16)
 
@@ -39,87 +39,93 @@ struct BwdParams {
     float scale, scale_log2;
 };
 
+// The tiles a CTA keeps for its whole life (`own`) and the tiles it walks (`walk`, two stages filled with
+// cp.async one iteration ahead).  dK/dV kernel: own = K, V; walk = Q, dO and their row statistics.
+// dQ kernel: own = Q, dO and the statistics (stage 0 of the walk arrays for those); walk = K, V.
 struct BwdSmem {
-    __nv_bfloat16 q[BW_T * BW_LD];
-    __nv_bfloat16 dout[BW_T * BW_LD];
-    __nv_bfloat16 k[BW_T * BW_LD];
-    __nv_bfloat16 v[BW_T * BW_LD];
+    __nv_bfloat16 own[2][BW_T * BW_LD];
+    __nv_bfloat16 walk[2][2][BW_T * BW_LD];  // [stage][tile]
     float s[BW_T * BW_LDS];   // scores, then (with dp, contiguous) staging of a 64 x 128 fp32 result
     float dp[BW_T * BW_LDS];
     __nv_bfloat16 p[BW_T * BW_LDS];
     __nv_bfloat16 ds[BW_T * BW_LDS];
-    float lse2[BW_T];   // log-sum-exp in powers of two
-    float delta[BW_T];
+    float lse[2][BW_T];    // [stage]: natural-log log-sum-exp of the rows
+    float delta[2][BW_T];
 };
 static_assert(2 * BW_T * BW_LDS >= BW_T * NCKV_D, "the result staging area spans s and dp");
 
-// 64 rows x 256 bytes of a (B, T, H, D) tensor into a padded shared-memory tile; rows at or beyond T are zero.
+// Asynchronous copies (cp.async): `bytes` of the source are copied, the rest of the 16 or 4 bytes is zero-filled.
+__device__ __forceinline__ void cp_async_16(void *dst, const void *src, int bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_4(void *dst, const void *src, int bytes) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// 64 rows x 256 bytes of a (B, T, H, D) tensor into a padded shared-memory tile, asynchronously; rows at or
+// beyond T are zero-filled (the source address is clamped to a valid row, no byte of it is read).
 __device__ __forceinline__ void load_tile(__nv_bfloat16 *dst, const __nv_bfloat16 *src, int b, int t0, int h, int T,
                                           int H) {
     for (int i = threadIdx.x; i < BW_T * (NCKV_D / 8); i += BW_THREADS) {
         const int r = i / (NCKV_D / 8), c = i % (NCKV_D / 8);
         const int t = t0 + r;
-        uint4 val = make_uint4(0, 0, 0, 0);
-        if (t < T) val = *reinterpret_cast<const uint4 *>(src + (((long long)b * T + t) * H + h) * NCKV_D + c * 8);
-        *reinterpret_cast<uint4 *>(dst + r * BW_LD + c * 8) = val;
+        const int tc = t < T ? t : T - 1;
+        cp_async_16(dst + r * BW_LD + c * 8, src + (((long long)b * T + tc) * H + h) * NCKV_D + c * 8, t < T ? 16 : 0);
     }
 }
 
-// S = Q K^T and dP = dO V^T for the staged tiles: 4 x 4 output fragments each, two per warp and product.
-__device__ __forceinline__ void scores_and_dp(BwdSmem &sm, int warp) {
-    const int r = warp >> 1, c0 = (warp & 1) * 2;
-    wm::fragment<wm::accumulator, 16, 16, 16, float> acc_s[2], acc_p[2];
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-        wm::fill_fragment(acc_s[j], 0.f);
-        wm::fill_fragment(acc_p[j], 0.f);
-    }
+// S = Q K^T and dP = dO V^T for the staged tiles: 4 x 4 output fragments each, one per warp and product.
+__device__ __forceinline__ void scores_and_dp(BwdSmem &sm, const __nv_bfloat16 *tq, const __nv_bfloat16 *tdo,
+                                              const __nv_bfloat16 *tk, const __nv_bfloat16 *tv, int warp) {
+    const int r = warp >> 2, c = warp & 3;
+    wm::fragment<wm::accumulator, 16, 16, 16, float> acc_s, acc_p;
+    wm::fill_fragment(acc_s, 0.f);
+    wm::fill_fragment(acc_p, 0.f);
 #pragma unroll
     for (int kk = 0; kk < NCKV_D / 16; ++kk) {
         wm::fragment<wm::matrix_a, 16, 16, 16, __nv_bfloat16, wm::row_major> a_q, a_do;
-        wm::load_matrix_sync(a_q, sm.q + r * 16 * BW_LD + kk * 16, BW_LD);
-        wm::load_matrix_sync(a_do, sm.dout + r * 16 * BW_LD + kk * 16, BW_LD);
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            // B(k = channel, n = key) sits at tile[key][channel]: column-major with the tile's row stride
-            wm::fragment<wm::matrix_b, 16, 16, 16, __nv_bfloat16, wm::col_major> b_k, b_v;
-            wm::load_matrix_sync(b_k, sm.k + (c0 + j) * 16 * BW_LD + kk * 16, BW_LD);
-            wm::load_matrix_sync(b_v, sm.v + (c0 + j) * 16 * BW_LD + kk * 16, BW_LD);
-            wm::mma_sync(acc_s[j], a_q, b_k, acc_s[j]);
-            wm::mma_sync(acc_p[j], a_do, b_v, acc_p[j]);
-        }
+        wm::load_matrix_sync(a_q, tq + r * 16 * BW_LD + kk * 16, BW_LD);
+        wm::load_matrix_sync(a_do, tdo + r * 16 * BW_LD + kk * 16, BW_LD);
+        // B(k = channel, n = key) sits at tile[key][channel]: column-major with the tile's row stride
+        wm::fragment<wm::matrix_b, 16, 16, 16, __nv_bfloat16, wm::col_major> b_k, b_v;
+        wm::load_matrix_sync(b_k, tk + c * 16 * BW_LD + kk * 16, BW_LD);
+        wm::load_matrix_sync(b_v, tv + c * 16 * BW_LD + kk * 16, BW_LD);
+        wm::mma_sync(acc_s, a_q, b_k, acc_s);
+        wm::mma_sync(acc_p, a_do, b_v, acc_p);
     }
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-        wm::store_matrix_sync(sm.s + r * 16 * BW_LDS + (c0 + j) * 16, acc_s[j], BW_LDS, wm::mem_row_major);
-        wm::store_matrix_sync(sm.dp + r * 16 * BW_LDS + (c0 + j) * 16, acc_p[j], BW_LDS, wm::mem_row_major);
-    }
+    wm::store_matrix_sync(sm.s + r * 16 * BW_LDS + c * 16, acc_s, BW_LDS, wm::mem_row_major);
+    wm::store_matrix_sync(sm.dp + r * 16 * BW_LDS + c * 16, acc_p, BW_LDS, wm::mem_row_major);
 }
 
 // P and dS of the staged score tile (queries q0.., keys k0..), rounded to bf16 for the products that follow.
-__device__ __forceinline__ void probabilities(BwdSmem &sm, const BwdParams &p, int q0, int k0) {
+__device__ __forceinline__ void probabilities(BwdSmem &sm, const BwdParams &p, const float *lse, const float *delta,
+                                              int q0, int k0) {
     for (int i = threadIdx.x; i < BW_T * BW_T; i += BW_THREADS) {
         const int r = i / BW_T, c = i % BW_T;
         const int tq = q0 + r, tk = k0 + c;
         const bool visible = tq < p.T && tk <= tq && (p.window_left < 0 || tq - tk <= p.window_left);
         float pr = 0.f, ds = 0.f;
         if (visible) {
-            pr = exp2f(sm.s[r * BW_LDS + c] * p.scale_log2 - sm.lse2[r]);
-            ds = pr * (sm.dp[r * BW_LDS + c] - sm.delta[r]) * p.scale;
+            // a visible score implies a finite log-sum-exp (the row has at least this key)
+            pr = exp2f(sm.s[r * BW_LDS + c] * p.scale_log2 - lse[r] * 1.4426950408889634f);
+            ds = pr * (sm.dp[r * BW_LDS + c] - delta[r]) * p.scale;
         }
         sm.p[r * BW_LDS + c] = __float2bfloat16(pr);
         sm.ds[r * BW_LDS + c] = __float2bfloat16(ds);
     }
 }
 
-__device__ __forceinline__ void load_row_stats(BwdSmem &sm, const BwdParams &p, int b, int hq, int q0) {
+__device__ __forceinline__ void load_row_stats(float *lse, float *delta, const BwdParams &p, int b, int hq, int q0) {
     for (int r = threadIdx.x; r < BW_T; r += BW_THREADS) {
         const int t = q0 + r;
-        const long long o = ((long long)b * p.Hq + hq) * p.T + t;
-        // a row without keys (lse = -inf) cannot occur under a causal mask; keep exp2 finite anyway
-        const float l = t < p.T ? p.lse[o] : 0.f;
-        sm.lse2[r] = l == -INFINITY ? 0.f : l * 1.4426950408889634f;
-        sm.delta[r] = t < p.T ? p.delta[o] : 0.f;
+        const long long o = ((long long)b * p.Hq + hq) * p.T + (t < p.T ? t : p.T - 1);
+        cp_async_4(lse + r, p.lse + o, t < p.T ? 4 : 0);
+        cp_async_4(delta + r, p.delta + o, t < p.T ? 4 : 0);
     }
 }
 
@@ -174,57 +180,69 @@ __global__ void __launch_bounds__(BW_THREADS) attn_bwd_dkdv_kernel(const BwdPara
     const int k0 = blockIdx.x * BW_T, hkv = blockIdx.y, b = blockIdx.z;
     const int rep = p.Hq / p.Hkv;
 
-    load_tile(sm.k, p.k, b, k0, hkv, p.T, p.Hkv);
-    load_tile(sm.v, p.v, b, k0, hkv, p.T, p.Hkv);
+    __nv_bfloat16 *sk = sm.own[0], *sv = sm.own[1];
+    load_tile(sk, p.k, b, k0, hkv, p.T, p.Hkv);
+    load_tile(sv, p.v, b, k0, hkv, p.T, p.Hkv);
 
-    // output fragments: 4 (key blocks) x 8 (channel blocks); warp w owns channel block w
-    wm::fragment<wm::accumulator, 16, 16, 16, float> acc_dk[4], acc_dv[4];
+    // output fragments: 4 (key blocks) x 8 (channel blocks); a warp owns channel block cb and key blocks rb, rb + 1
+    const int cb = warp & 7, rb = (warp >> 3) * 2;
+    wm::fragment<wm::accumulator, 16, 16, 16, float> acc_dk[2], acc_dv[2];
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
+    for (int r = 0; r < 2; ++r) {
         wm::fill_fragment(acc_dk[r], 0.f);
         wm::fill_fragment(acc_dv[r], 0.f);
     }
-    // query tiles that see any of these keys: positions k0 .. (last key + window)
+    // query tiles that see any of these keys: positions k0 .. (last key + window), for every q head of the group
     const int last_key = min(k0 + BW_T, p.T) - 1;
     const int q_hi = p.window_left >= 0 ? min(p.T - 1, last_key + p.window_left) : p.T - 1;
-    for (int g = 0; g < rep; ++g) {
-        const int hq = hkv * rep + g;
-        for (int q0 = k0; q0 <= q_hi; q0 += BW_T) {  // causal: queries at or after the tile's first key
-            __syncthreads();  // the previous iteration's products have read q, dout, p, ds
-            load_tile(sm.q, p.q, b, q0, hq, p.T, p.Hq);
-            load_tile(sm.dout, p.dout, b, q0, hq, p.T, p.Hq);
-            load_row_stats(sm, p, b, hq, q0);
-            __syncthreads();
-            scores_and_dp(sm, warp);
-            __syncthreads();
-            probabilities(sm, p, q0, k0);
-            __syncthreads();
+    const int per_head = (q_hi - k0) / BW_T + 1;  // causal: queries at or after the tile's first key
+    const int n_iter = rep * per_head;
+    auto fetch = [&](int it) {  // iteration `it` -> stage it & 1
+        const int hq = hkv * rep + it / per_head, q0 = k0 + (it % per_head) * BW_T, st = it & 1;
+        load_tile(sm.walk[st][0], p.q, b, q0, hq, p.T, p.Hq);
+        load_tile(sm.walk[st][1], p.dout, b, q0, hq, p.T, p.Hq);
+        load_row_stats(sm.lse[st], sm.delta[st], p, b, hq, q0);
+    };
+    fetch(0);
+    cp_async_commit();
+    for (int it = 0; it < n_iter; ++it) {
+        const int st = it & 1, q0 = k0 + (it % per_head) * BW_T;
+        const __nv_bfloat16 *sq = sm.walk[st][0], *sdo = sm.walk[st][1];
+        __syncthreads();  // the previous iteration's products have read the other stage, p and ds
+        if (it + 1 < n_iter) fetch(it + 1);
+        cp_async_commit();
+        cp_async_wait<1>();  // everything but the group just committed has landed (this thread's part)
+        __syncthreads();
+        scores_and_dp(sm, sq, sdo, sk, sv, warp);
+        __syncthreads();
+        probabilities(sm, p, sm.lse[st], sm.delta[st], q0, k0);
+        __syncthreads();
 #pragma unroll
-            for (int qq = 0; qq < BW_T / 16; ++qq) {
-                wm::fragment<wm::matrix_b, 16, 16, 16, __nv_bfloat16, wm::row_major> b_do, b_q;
-                wm::load_matrix_sync(b_do, sm.dout + qq * 16 * BW_LD + warp * 16, BW_LD);
-                wm::load_matrix_sync(b_q, sm.q + qq * 16 * BW_LD + warp * 16, BW_LD);
+        for (int qq = 0; qq < BW_T / 16; ++qq) {
+            wm::fragment<wm::matrix_b, 16, 16, 16, __nv_bfloat16, wm::row_major> b_do, b_q;
+            wm::load_matrix_sync(b_do, sdo + qq * 16 * BW_LD + cb * 16, BW_LD);
+            wm::load_matrix_sync(b_q, sq + qq * 16 * BW_LD + cb * 16, BW_LD);
 #pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                    // A(m = key, k = query) sits at tile[query][key]: column-major
-                    wm::fragment<wm::matrix_a, 16, 16, 16, __nv_bfloat16, wm::col_major> a_p, a_ds;
-                    wm::load_matrix_sync(a_p, sm.p + qq * 16 * BW_LDS + r * 16, BW_LDS);
-                    wm::load_matrix_sync(a_ds, sm.ds + qq * 16 * BW_LDS + r * 16, BW_LDS);
-                    wm::mma_sync(acc_dv[r], a_p, b_do, acc_dv[r]);
-                    wm::mma_sync(acc_dk[r], a_ds, b_q, acc_dk[r]);
-                }
+            for (int r = 0; r < 2; ++r) {
+                // A(m = key, k = query) sits at tile[query][key]: column-major
+                wm::fragment<wm::matrix_a, 16, 16, 16, __nv_bfloat16, wm::col_major> a_p, a_ds;
+                wm::load_matrix_sync(a_p, sm.p + qq * 16 * BW_LDS + (rb + r) * 16, BW_LDS);
+                wm::load_matrix_sync(a_ds, sm.ds + qq * 16 * BW_LDS + (rb + r) * 16, BW_LDS);
+                wm::mma_sync(acc_dv[r], a_p, b_do, acc_dv[r]);
+                wm::mma_sync(acc_dk[r], a_ds, b_q, acc_dk[r]);
             }
         }
     }
+    cp_async_wait<0>();
     __syncthreads();
     float *stage = sm.s;
 #pragma unroll
-    for (int r = 0; r < 4; ++r) wm::store_matrix_sync(stage + r * 16 * NCKV_D + warp * 16, acc_dk[r], NCKV_D, wm::mem_row_major);
+    for (int r = 0; r < 2; ++r) wm::store_matrix_sync(stage + (rb + r) * 16 * NCKV_D + cb * 16, acc_dk[r], NCKV_D, wm::mem_row_major);
     __syncthreads();
     store_result(stage, p.dk, b, k0, hkv, p.T, p.Hkv);
     __syncthreads();
 #pragma unroll
-    for (int r = 0; r < 4; ++r) wm::store_matrix_sync(stage + r * 16 * NCKV_D + warp * 16, acc_dv[r], NCKV_D, wm::mem_row_major);
+    for (int r = 0; r < 2; ++r) wm::store_matrix_sync(stage + (rb + r) * 16 * NCKV_D + cb * 16, acc_dv[r], NCKV_D, wm::mem_row_major);
     __syncthreads();
     store_result(stage, p.dv, b, k0, hkv, p.T, p.Hkv);
 }
@@ -238,42 +256,55 @@ __global__ void __launch_bounds__(BW_THREADS) attn_bwd_dq_kernel(const BwdParams
     const int q0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * BW_T, hq = blockIdx.y, b = blockIdx.z;
     const int hkv = hq / (p.Hq / p.Hkv);
 
-    load_tile(sm.q, p.q, b, q0, hq, p.T, p.Hq);
-    load_tile(sm.dout, p.dout, b, q0, hq, p.T, p.Hq);
-    load_row_stats(sm, p, b, hq, q0);
+    __nv_bfloat16 *sq = sm.own[0], *sdo = sm.own[1];
+    load_tile(sq, p.q, b, q0, hq, p.T, p.Hq);
+    load_tile(sdo, p.dout, b, q0, hq, p.T, p.Hq);
+    load_row_stats(sm.lse[0], sm.delta[0], p, b, hq, q0);
 
-    wm::fragment<wm::accumulator, 16, 16, 16, float> acc_dq[4];  // 4 (query blocks) x channel block `warp`
+    const int cb = warp & 7, rb = (warp >> 3) * 2;  // channel block and the first of this warp's two query blocks
+    wm::fragment<wm::accumulator, 16, 16, 16, float> acc_dq[2];
 #pragma unroll
-    for (int r = 0; r < 4; ++r) wm::fill_fragment(acc_dq[r], 0.f);
+    for (int r = 0; r < 2; ++r) wm::fill_fragment(acc_dq[r], 0.f);
 
     const int last_q = min(q0 + BW_T, p.T) - 1;
     int k_lo = p.window_left >= 0 ? max(0, q0 - p.window_left) : 0;
     k_lo -= k_lo % BW_T;
-    for (int k0 = k_lo; k0 <= last_q; k0 += BW_T) {
-        __syncthreads();  // the previous iteration's product has read k and ds
-        load_tile(sm.k, p.k, b, k0, hkv, p.T, p.Hkv);
-        load_tile(sm.v, p.v, b, k0, hkv, p.T, p.Hkv);
+    const int n_iter = (last_q - k_lo) / BW_T + 1;
+    auto fetch = [&](int it) {
+        load_tile(sm.walk[it & 1][0], p.k, b, k_lo + it * BW_T, hkv, p.T, p.Hkv);
+        load_tile(sm.walk[it & 1][1], p.v, b, k_lo + it * BW_T, hkv, p.T, p.Hkv);
+    };
+    fetch(0);
+    cp_async_commit();
+    for (int it = 0; it < n_iter; ++it) {
+        const int k0 = k_lo + it * BW_T;
+        const __nv_bfloat16 *sk = sm.walk[it & 1][0], *sv = sm.walk[it & 1][1];
+        __syncthreads();  // the previous iteration's product has read the other stage and ds
+        if (it + 1 < n_iter) fetch(it + 1);
+        cp_async_commit();
+        cp_async_wait<1>();
         __syncthreads();
-        scores_and_dp(sm, warp);
+        scores_and_dp(sm, sq, sdo, sk, sv, warp);
         __syncthreads();
-        probabilities(sm, p, q0, k0);
+        probabilities(sm, p, sm.lse[0], sm.delta[0], q0, k0);
         __syncthreads();
 #pragma unroll
         for (int kk = 0; kk < BW_T / 16; ++kk) {
             wm::fragment<wm::matrix_b, 16, 16, 16, __nv_bfloat16, wm::row_major> b_k;  // B(k = key, n = channel)
-            wm::load_matrix_sync(b_k, sm.k + kk * 16 * BW_LD + warp * 16, BW_LD);
+            wm::load_matrix_sync(b_k, sk + kk * 16 * BW_LD + cb * 16, BW_LD);
 #pragma unroll
-            for (int r = 0; r < 4; ++r) {
+            for (int r = 0; r < 2; ++r) {
                 wm::fragment<wm::matrix_a, 16, 16, 16, __nv_bfloat16, wm::row_major> a_ds;
-                wm::load_matrix_sync(a_ds, sm.ds + r * 16 * BW_LDS + kk * 16, BW_LDS);
+                wm::load_matrix_sync(a_ds, sm.ds + (rb + r) * 16 * BW_LDS + kk * 16, BW_LDS);
                 wm::mma_sync(acc_dq[r], a_ds, b_k, acc_dq[r]);
             }
         }
     }
+    cp_async_wait<0>();
     __syncthreads();
     float *stage = sm.s;
 #pragma unroll
-    for (int r = 0; r < 4; ++r) wm::store_matrix_sync(stage + r * 16 * NCKV_D + warp * 16, acc_dq[r], NCKV_D, wm::mem_row_major);
+    for (int r = 0; r < 2; ++r) wm::store_matrix_sync(stage + (rb + r) * 16 * NCKV_D + cb * 16, acc_dq[r], NCKV_D, wm::mem_row_major);
     __syncthreads();
     store_result(stage, p.dq, b, q0, hq, p.T, p.Hq);
 }
