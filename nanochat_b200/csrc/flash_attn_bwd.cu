@@ -11,24 +11,22 @@
 // them; the dQ kernel gives a CTA one tile of 64 queries of one (row, q head) and walks its key
 // tiles.  Scores are recomputed in both (7 matrix products per tile pair instead of 5) so that no
 // gradient needs atomics: results do not depend on scheduling.  The products run on the warp-level
-// tensor-core path (16x16x16 bf16 fragments, fp32 accumulation), operands staged in shared memory;
-// this path is a first, correct version and makes no claim on the tensor-core roofline.
+// tensor-core path (ldmatrix + mma.sync.m16n8k16 bf16, fp32 accumulation) with operands staged in shared
+// memory by cp.async; P and dS are formed in registers from the score accumulators.  This is a first,
+// correct version: it makes no claim on the tcgen05 roofline.
 //
 // Replaces: autograd through F.scaled_dot_product_attention as reached from flash_attn_func
 // (flash_attention.py:107-128, caller gpt.py:108) when training.
 #include <math.h>
-#include <mma.h>
 
 #include "nckv_common.cuh"
 
 namespace nckv {
 
-namespace wm = nvcuda::wmma;
-
 constexpr int BW_T = 64;             // queries and keys per tile
-constexpr int BW_THREADS = 512;      // 16 warps: one per 16 x 16 score fragment
-constexpr int BW_LD = NCKV_D + 8;    // bf16 row stride of the 64 x 128 operand tiles (272 B: no bank conflicts)
-constexpr int BW_LDS = BW_T + 8;     // row stride of the 64 x 64 score tiles (fp32 and bf16)
+constexpr int BW_THREADS = 512;      // 16 warps: one per 16 x 16 block of a score tile
+constexpr int BW_LD = NCKV_D + 8;    // bf16 row stride of the 64 x 128 operand tiles (272 B: ldmatrix without bank conflicts)
+constexpr int BW_LDS = BW_T + 8;     // bf16 row stride of the 64 x 64 P and dS tiles (144 B)
 
 struct BwdParams {
     const __nv_bfloat16 *q, *k, *v, *dout;
@@ -41,18 +39,58 @@ struct BwdParams {
 
 // The tiles a CTA keeps for its whole life (`own`) and the tiles it walks (`walk`, two stages filled with
 // cp.async one iteration ahead).  dK/dV kernel: own = K, V; walk = Q, dO and their row statistics.
-// dQ kernel: own = Q, dO and the statistics (stage 0 of the walk arrays for those); walk = K, V.
+// dQ kernel: own = Q, dO and the statistics (stage 0 of those arrays); walk = K, V.
 struct BwdSmem {
     __nv_bfloat16 own[2][BW_T * BW_LD];
-    __nv_bfloat16 walk[2][2][BW_T * BW_LD];  // [stage][tile]
-    float s[BW_T * BW_LDS];   // scores, then (with dp, contiguous) staging of a 64 x 128 fp32 result
-    float dp[BW_T * BW_LDS];
+    __nv_bfloat16 walk[2][2][BW_T * BW_LD];  // [stage][tile]; after the loop: staging of a 64 x 128 fp32 result
     __nv_bfloat16 p[BW_T * BW_LDS];
     __nv_bfloat16 ds[BW_T * BW_LDS];
     float lse[2][BW_T];    // [stage]: natural-log log-sum-exp of the rows
     float delta[2][BW_T];
 };
-static_assert(2 * BW_T * BW_LDS >= BW_T * NCKV_D, "the result staging area spans s and dp");
+static_assert(sizeof(__nv_bfloat16) * 4 * BW_T * BW_LD >= sizeof(float) * BW_T * NCKV_D, "the result staging area");
+
+// ---- 16 x 16 x 16 products on the warp-level tensor-core path: ldmatrix + mma.sync.m16n8k16 ----------------
+struct FragA { uint32_t r[4]; };   // A, 16 (m) x 16 (k)
+struct FragB { uint32_t r[4]; };   // B, 16 (k) x 16 (n): r[0], r[1] for n 0..7, r[2], r[3] for n 8..15
+struct Acc { float c[8]; };        // 16 x 16 fp32: c[0..3] columns 0..7, c[4..7] columns 8..15
+// element e of Acc sits at row (lane / 4) + 8 * ((e >> 1) & 1), column 8 * (e >> 2) + 2 * (lane % 4) + (e & 1)
+
+__device__ __forceinline__ void load_a_mk(FragA &f, const __nv_bfloat16 *base, int ld, int lane) {  // A(m,k) at base[m ld + k]
+    const __nv_bfloat16 *ptr = base + ((lane & 7) + ((lane >> 3) & 1) * 8) * ld + (lane >> 4) * 8;
+    ldmatrix_x4(f.r[0], f.r[1], f.r[2], f.r[3], smem_u32(ptr));
+}
+__device__ __forceinline__ void load_a_km(FragA &f, const __nv_bfloat16 *base, int ld, int lane) {  // A(m,k) at base[k ld + m]
+    const int i = lane >> 3, j = lane & 7;
+    const __nv_bfloat16 *ptr = base + ((i >> 1) * 8 + j) * ld + (i & 1) * 8;
+    ldmatrix_x4_trans(f.r[0], f.r[1], f.r[2], f.r[3], smem_u32(ptr));
+}
+__device__ __forceinline__ void load_b_nk(FragB &f, const __nv_bfloat16 *base, int ld, int lane) {  // B(k,n) at base[n ld + k]
+    const int i = lane >> 3, j = lane & 7;
+    const __nv_bfloat16 *ptr = base + ((i >> 1) * 8 + j) * ld + (i & 1) * 8;
+    ldmatrix_x4(f.r[0], f.r[1], f.r[2], f.r[3], smem_u32(ptr));
+}
+__device__ __forceinline__ void load_b_kn(FragB &f, const __nv_bfloat16 *base, int ld, int lane) {  // B(k,n) at base[k ld + n]
+    const int i = lane >> 3, j = lane & 7;
+    const __nv_bfloat16 *ptr = base + ((i & 1) * 8 + j) * ld + (i >> 1) * 8;
+    ldmatrix_x4_trans(f.r[0], f.r[1], f.r[2], f.r[3], smem_u32(ptr));
+}
+__device__ __forceinline__ void mma16(Acc &d, const FragA &a, const FragB &b) {
+    mma_bf16_16816(d.c[0], d.c[1], d.c[2], d.c[3], a.r[0], a.r[1], a.r[2], a.r[3], b.r[0], b.r[1]);
+    mma_bf16_16816(d.c[4], d.c[5], d.c[6], d.c[7], a.r[0], a.r[1], a.r[2], a.r[3], b.r[2], b.r[3]);
+}
+__device__ __forceinline__ void zero(Acc &d) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) d.c[e] = 0.f;
+}
+// fp32 accumulator block (rows r0.., columns c0..) into a row-major fp32 array
+__device__ __forceinline__ void store_acc(float *dst, int ld, int r0, int c0, const Acc &d, int lane) {
+#pragma unroll
+    for (int e = 0; e < 8; e += 2) {
+        const int row = r0 + (lane >> 2) + 8 * ((e >> 1) & 1), col = c0 + 8 * (e >> 2) + 2 * (lane & 3);
+        *reinterpret_cast<float2 *>(dst + row * ld + col) = make_float2(d.c[e], d.c[e + 1]);
+    }
+}
 
 // Asynchronous copies (cp.async): `bytes` of the source are copied, the rest of the 16 or 4 bytes is zero-filled.
 __device__ __forceinline__ void cp_async_16(void *dst, const void *src, int bytes) {
@@ -79,44 +117,47 @@ __device__ __forceinline__ void load_tile(__nv_bfloat16 *dst, const __nv_bfloat1
     }
 }
 
-// S = Q K^T and dP = dO V^T for the staged tiles: 4 x 4 output fragments each, one per warp and product.
-__device__ __forceinline__ void scores_and_dp(BwdSmem &sm, const __nv_bfloat16 *tq, const __nv_bfloat16 *tdo,
-                                              const __nv_bfloat16 *tk, const __nv_bfloat16 *tv, int warp) {
+// One warp's 16 x 16 block of S = Q K^T and of dP = dO V^T, turned in registers into P and dS (bf16, written
+// to shared memory for the products that follow).  Queries q0 + 16 r .., keys k0 + 16 c ..
+__device__ __forceinline__ void scores_to_p_ds(BwdSmem &sm, const BwdParams &p, const __nv_bfloat16 *tq,
+                                               const __nv_bfloat16 *tdo, const __nv_bfloat16 *tk, const __nv_bfloat16 *tv,
+                                               const float *lse, const float *delta, int q0, int k0, int warp, int lane) {
     const int r = warp >> 2, c = warp & 3;
-    wm::fragment<wm::accumulator, 16, 16, 16, float> acc_s, acc_p;
-    wm::fill_fragment(acc_s, 0.f);
-    wm::fill_fragment(acc_p, 0.f);
+    Acc acc_s, acc_p;
+    zero(acc_s);
+    zero(acc_p);
 #pragma unroll
     for (int kk = 0; kk < NCKV_D / 16; ++kk) {
-        wm::fragment<wm::matrix_a, 16, 16, 16, __nv_bfloat16, wm::row_major> a_q, a_do;
-        wm::load_matrix_sync(a_q, tq + r * 16 * BW_LD + kk * 16, BW_LD);
-        wm::load_matrix_sync(a_do, tdo + r * 16 * BW_LD + kk * 16, BW_LD);
-        // B(k = channel, n = key) sits at tile[key][channel]: column-major with the tile's row stride
-        wm::fragment<wm::matrix_b, 16, 16, 16, __nv_bfloat16, wm::col_major> b_k, b_v;
-        wm::load_matrix_sync(b_k, tk + c * 16 * BW_LD + kk * 16, BW_LD);
-        wm::load_matrix_sync(b_v, tv + c * 16 * BW_LD + kk * 16, BW_LD);
-        wm::mma_sync(acc_s, a_q, b_k, acc_s);
-        wm::mma_sync(acc_p, a_do, b_v, acc_p);
+        FragA a_q, a_do;
+        FragB b_k, b_v;
+        load_a_mk(a_q, tq + r * 16 * BW_LD + kk * 16, BW_LD, lane);
+        load_a_mk(a_do, tdo + r * 16 * BW_LD + kk * 16, BW_LD, lane);
+        load_b_nk(b_k, tk + c * 16 * BW_LD + kk * 16, BW_LD, lane);  // B(k = channel, n = key) at tile[key][channel]
+        load_b_nk(b_v, tv + c * 16 * BW_LD + kk * 16, BW_LD, lane);
+        mma16(acc_s, a_q, b_k);
+        mma16(acc_p, a_do, b_v);
     }
-    wm::store_matrix_sync(sm.s + r * 16 * BW_LDS + c * 16, acc_s, BW_LDS, wm::mem_row_major);
-    wm::store_matrix_sync(sm.dp + r * 16 * BW_LDS + c * 16, acc_p, BW_LDS, wm::mem_row_major);
-}
-
-// P and dS of the staged score tile (queries q0.., keys k0..), rounded to bf16 for the products that follow.
-__device__ __forceinline__ void probabilities(BwdSmem &sm, const BwdParams &p, const float *lse, const float *delta,
-                                              int q0, int k0) {
-    for (int i = threadIdx.x; i < BW_T * BW_T; i += BW_THREADS) {
-        const int r = i / BW_T, c = i % BW_T;
-        const int tq = q0 + r, tk = k0 + c;
-        const bool visible = tq < p.T && tk <= tq && (p.window_left < 0 || tq - tk <= p.window_left);
-        float pr = 0.f, ds = 0.f;
-        if (visible) {
-            // a visible score implies a finite log-sum-exp (the row has at least this key)
-            pr = exp2f(sm.s[r * BW_LDS + c] * p.scale_log2 - lse[r] * 1.4426950408889634f);
-            ds = pr * (sm.dp[r * BW_LDS + c] - delta[r]) * p.scale;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {  // the thread's two rows
+        const int row = r * 16 + (lane >> 2) + 8 * h;
+        const int tq_ = q0 + row;
+        const float lse2 = lse[row] * 1.4426950408889634f, dl = delta[row];
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb) {
+            const int col = c * 16 + 8 * nb + 2 * (lane & 3);
+            float pr[2], ds[2];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int e = nb * 4 + h * 2 + j;
+                const int tk_ = k0 + col + j;
+                const bool visible = tq_ < p.T && tk_ <= tq_ && (p.window_left < 0 || tq_ - tk_ <= p.window_left);
+                // a visible score implies a finite log-sum-exp (the row has at least this key)
+                pr[j] = visible ? exp2f(acc_s.c[e] * p.scale_log2 - lse2) : 0.f;
+                ds[j] = visible ? pr[j] * (acc_p.c[e] - dl) * p.scale : 0.f;
+            }
+            *reinterpret_cast<uint32_t *>(sm.p + row * BW_LDS + col) = pack_bf16x2(pr[0], pr[1]);
+            *reinterpret_cast<uint32_t *>(sm.ds + row * BW_LDS + col) = pack_bf16x2(ds[0], ds[1]);
         }
-        sm.p[r * BW_LDS + c] = __float2bfloat16(pr);
-        sm.ds[r * BW_LDS + c] = __float2bfloat16(ds);
     }
 }
 
@@ -176,7 +217,7 @@ __global__ void __launch_bounds__(256) attn_bwd_delta_kernel(const __nv_bfloat16
 __global__ void __launch_bounds__(BW_THREADS) attn_bwd_dkdv_kernel(const BwdParams p) {
     extern __shared__ __align__(128) uint8_t bw_smem[];
     BwdSmem &sm = *reinterpret_cast<BwdSmem *>(bw_smem);
-    const int warp = threadIdx.x >> 5;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k0 = blockIdx.x * BW_T, hkv = blockIdx.y, b = blockIdx.z;
     const int rep = p.Hq / p.Hkv;
 
@@ -186,11 +227,11 @@ __global__ void __launch_bounds__(BW_THREADS) attn_bwd_dkdv_kernel(const BwdPara
 
     // output fragments: 4 (key blocks) x 8 (channel blocks); a warp owns channel block cb and key blocks rb, rb + 1
     const int cb = warp & 7, rb = (warp >> 3) * 2;
-    wm::fragment<wm::accumulator, 16, 16, 16, float> acc_dk[2], acc_dv[2];
+    Acc acc_dk[2], acc_dv[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
-        wm::fill_fragment(acc_dk[r], 0.f);
-        wm::fill_fragment(acc_dv[r], 0.f);
+        zero(acc_dk[r]);
+        zero(acc_dv[r]);
     }
     // query tiles that see any of these keys: positions k0 .. (last key + window), for every q head of the group
     const int last_key = min(k0 + BW_T, p.T) - 1;
@@ -213,36 +254,33 @@ __global__ void __launch_bounds__(BW_THREADS) attn_bwd_dkdv_kernel(const BwdPara
         cp_async_commit();
         cp_async_wait<1>();  // everything but the group just committed has landed (this thread's part)
         __syncthreads();
-        scores_and_dp(sm, sq, sdo, sk, sv, warp);
-        __syncthreads();
-        probabilities(sm, p, sm.lse[st], sm.delta[st], q0, k0);
+        scores_to_p_ds(sm, p, sq, sdo, sk, sv, sm.lse[st], sm.delta[st], q0, k0, warp, lane);
         __syncthreads();
 #pragma unroll
         for (int qq = 0; qq < BW_T / 16; ++qq) {
-            wm::fragment<wm::matrix_b, 16, 16, 16, __nv_bfloat16, wm::row_major> b_do, b_q;
-            wm::load_matrix_sync(b_do, sdo + qq * 16 * BW_LD + cb * 16, BW_LD);
-            wm::load_matrix_sync(b_q, sq + qq * 16 * BW_LD + cb * 16, BW_LD);
+            FragB b_do, b_q;  // B(k = query, n = channel) at tile[query][channel]
+            load_b_kn(b_do, sdo + qq * 16 * BW_LD + cb * 16, BW_LD, lane);
+            load_b_kn(b_q, sq + qq * 16 * BW_LD + cb * 16, BW_LD, lane);
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
-                // A(m = key, k = query) sits at tile[query][key]: column-major
-                wm::fragment<wm::matrix_a, 16, 16, 16, __nv_bfloat16, wm::col_major> a_p, a_ds;
-                wm::load_matrix_sync(a_p, sm.p + qq * 16 * BW_LDS + (rb + r) * 16, BW_LDS);
-                wm::load_matrix_sync(a_ds, sm.ds + qq * 16 * BW_LDS + (rb + r) * 16, BW_LDS);
-                wm::mma_sync(acc_dv[r], a_p, b_do, acc_dv[r]);
-                wm::mma_sync(acc_dk[r], a_ds, b_q, acc_dk[r]);
+                FragA a_p, a_ds;  // A(m = key, k = query) at tile[query][key]
+                load_a_km(a_p, sm.p + qq * 16 * BW_LDS + (rb + r) * 16, BW_LDS, lane);
+                load_a_km(a_ds, sm.ds + qq * 16 * BW_LDS + (rb + r) * 16, BW_LDS, lane);
+                mma16(acc_dv[r], a_p, b_do);
+                mma16(acc_dk[r], a_ds, b_q);
             }
         }
     }
     cp_async_wait<0>();
     __syncthreads();
-    float *stage = sm.s;
+    float *stage = reinterpret_cast<float *>(&sm.walk[0][0][0]);
 #pragma unroll
-    for (int r = 0; r < 2; ++r) wm::store_matrix_sync(stage + (rb + r) * 16 * NCKV_D + cb * 16, acc_dk[r], NCKV_D, wm::mem_row_major);
+    for (int r = 0; r < 2; ++r) store_acc(stage, NCKV_D, (rb + r) * 16, cb * 16, acc_dk[r], lane);
     __syncthreads();
     store_result(stage, p.dk, b, k0, hkv, p.T, p.Hkv);
     __syncthreads();
 #pragma unroll
-    for (int r = 0; r < 2; ++r) wm::store_matrix_sync(stage + (rb + r) * 16 * NCKV_D + cb * 16, acc_dv[r], NCKV_D, wm::mem_row_major);
+    for (int r = 0; r < 2; ++r) store_acc(stage, NCKV_D, (rb + r) * 16, cb * 16, acc_dv[r], lane);
     __syncthreads();
     store_result(stage, p.dv, b, k0, hkv, p.T, p.Hkv);
 }
@@ -251,7 +289,7 @@ __global__ void __launch_bounds__(BW_THREADS) attn_bwd_dkdv_kernel(const BwdPara
 __global__ void __launch_bounds__(BW_THREADS) attn_bwd_dq_kernel(const BwdParams p) {
     extern __shared__ __align__(128) uint8_t bw_smem[];
     BwdSmem &sm = *reinterpret_cast<BwdSmem *>(bw_smem);
-    const int warp = threadIdx.x >> 5;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // longest tiles first: the last query tile sees the most keys
     const int q0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * BW_T, hq = blockIdx.y, b = blockIdx.z;
     const int hkv = hq / (p.Hq / p.Hkv);
@@ -262,9 +300,9 @@ __global__ void __launch_bounds__(BW_THREADS) attn_bwd_dq_kernel(const BwdParams
     load_row_stats(sm.lse[0], sm.delta[0], p, b, hq, q0);
 
     const int cb = warp & 7, rb = (warp >> 3) * 2;  // channel block and the first of this warp's two query blocks
-    wm::fragment<wm::accumulator, 16, 16, 16, float> acc_dq[2];
+    Acc acc_dq[2];
 #pragma unroll
-    for (int r = 0; r < 2; ++r) wm::fill_fragment(acc_dq[r], 0.f);
+    for (int r = 0; r < 2; ++r) zero(acc_dq[r]);
 
     const int last_q = min(q0 + BW_T, p.T) - 1;
     int k_lo = p.window_left >= 0 ? max(0, q0 - p.window_left) : 0;
@@ -284,27 +322,25 @@ __global__ void __launch_bounds__(BW_THREADS) attn_bwd_dq_kernel(const BwdParams
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
-        scores_and_dp(sm, sq, sdo, sk, sv, warp);
-        __syncthreads();
-        probabilities(sm, p, sm.lse[0], sm.delta[0], q0, k0);
+        scores_to_p_ds(sm, p, sq, sdo, sk, sv, sm.lse[0], sm.delta[0], q0, k0, warp, lane);
         __syncthreads();
 #pragma unroll
         for (int kk = 0; kk < BW_T / 16; ++kk) {
-            wm::fragment<wm::matrix_b, 16, 16, 16, __nv_bfloat16, wm::row_major> b_k;  // B(k = key, n = channel)
-            wm::load_matrix_sync(b_k, sk + kk * 16 * BW_LD + cb * 16, BW_LD);
+            FragB b_k;  // B(k = key, n = channel) at tile[key][channel]
+            load_b_kn(b_k, sk + kk * 16 * BW_LD + cb * 16, BW_LD, lane);
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
-                wm::fragment<wm::matrix_a, 16, 16, 16, __nv_bfloat16, wm::row_major> a_ds;
-                wm::load_matrix_sync(a_ds, sm.ds + (rb + r) * 16 * BW_LDS + kk * 16, BW_LDS);
-                wm::mma_sync(acc_dq[r], a_ds, b_k, acc_dq[r]);
+                FragA a_ds;  // A(m = query, k = key) at tile[query][key]
+                load_a_mk(a_ds, sm.ds + (rb + r) * 16 * BW_LDS + kk * 16, BW_LDS, lane);
+                mma16(acc_dq[r], a_ds, b_k);
             }
         }
     }
     cp_async_wait<0>();
     __syncthreads();
-    float *stage = sm.s;
+    float *stage = reinterpret_cast<float *>(&sm.walk[0][0][0]);
 #pragma unroll
-    for (int r = 0; r < 2; ++r) wm::store_matrix_sync(stage + (rb + r) * 16 * NCKV_D + cb * 16, acc_dq[r], NCKV_D, wm::mem_row_major);
+    for (int r = 0; r < 2; ++r) store_acc(stage, NCKV_D, (rb + r) * 16, cb * 16, acc_dq[r], lane);
     __syncthreads();
     store_result(stage, p.dq, b, q0, hq, p.T, p.Hq);
 }
