@@ -155,8 +155,12 @@ NCKV_API int nckv_append(const void *k_in, const void *v_in, void *k_cache, void
  * callers do around it (engine.py:279: ids to the device; the result read back on the host).
  * qkv_host: pinned host block [q (B,Hq,D) | k (B,Hkv,D) | v (B,Hkv,D)] bf16; qkv_dev: device block of
  * the same size; q_rot_dev, out_dev: device (B,Hq,D) bf16 scratch/result; out_host: pinned host
- * (B,Hq,D) bf16.  Performs H2D, nckv_append_rope_norm, nckv_decode_attn, D2H and a stream
- * synchronise; on return out_host holds the attention output.  cache_seqlens is not advanced.
+ * (B,Hq,D) bf16.  Performs H2D, nckv_append_rope_norm, nckv_decode_attn, D2H and waits for them; on
+ * return out_host holds the attention output.  cache_seqlens is not advanced.  The operations are
+ * ordered after everything already enqueued on `stream`.  They are captured once per distinct argument
+ * list (a small table, least recently used entry replaced) into a CUDA graph on a stream of the
+ * library's own and replayed by later calls; the wait is a bounded spin on a pinned word the graph's last
+ * node writes, with a stream synchronise as its fallback.  Calls are serialised by a mutex.
  * Mapped mode: with qkv_dev == NULL the append kernel reads the pinned host block itself (over
  * PCIe, through the device alias of the host pointer) and no H2D copy is enqueued; with
  * out_dev == NULL the attention kernels store the result straight into out_host and no D2H copy

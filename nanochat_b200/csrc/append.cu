@@ -389,56 +389,4 @@ int nckv_append(const void *k_in, const void *v_in, void *k_cache, void *v_cache
     return launch_append(p, static_cast<cudaStream_t>(stream));
 }
 
-// One decode step for a caller whose new-token activations live in host memory: copies q|k|v (one
-// contiguous pinned block) to the device staging block, runs the fused append and the decode
-// attention, copies the (B, Hq, D) output back and waits for the stream.  Everything a step needs
-// crosses the C ABI once.
-int nckv_decode_step_host(const void *qkv_host, void *qkv_dev, void *q_rot_dev, void *out_dev, void *out_host,
-                          void *k_cache, void *v_cache, const int32_t *cache_seqlens, const void *cos,
-                          const void *sin, int B, int Hq, int Hkv, int D, int T_max, int64_t cache_batch_stride,
-                          int64_t cache_token_stride, int rope_len, float qk_scale, float eps, int window_left,
-                          void *workspace, size_t workspace_bytes, void *stream) {
-    using namespace nckv;
-    if (!qkv_host || !q_rot_dev || !out_host || !workspace) {
-        set_error("decode_step_host: null pointer argument");
-        return NCKV_E_ARG;
-    }
-    if (B <= 0 || Hq <= 0 || Hkv <= 0 || D != NCKV_D) {
-        set_error("decode_step_host: bad shape (B=%d Hq=%d Hkv=%d D=%d)", B, Hq, Hkv, D);
-        return D != NCKV_D ? NCKV_E_UNSUPPORTED : NCKV_E_ARG;
-    }
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const size_t nq = (size_t)B * Hq * D, nk = (size_t)B * Hkv * D;
-    const __nv_bfloat16 *base = static_cast<const __nv_bfloat16 *>(qkv_dev);
-    if (qkv_dev) {
-        NCKV_CUDA_CHECK(cudaMemcpyAsync(qkv_dev, qkv_host, (nq + 2 * nk) * 2, cudaMemcpyHostToDevice, s));
-    } else {  // mapped mode: the append kernel reads the host block through its device alias
-        void *alias = nullptr;
-        if (cudaHostGetDevicePointer(&alias, const_cast<void *>(qkv_host), 0) != cudaSuccess || !alias) {
-            (void)cudaGetLastError();
-            set_error("decode_step_host: qkv_host is not page-locked memory the device can address");
-            return NCKV_E_ARG;
-        }
-        base = static_cast<const __nv_bfloat16 *>(alias);
-    }
-    void *out_target = out_dev;
-    if (!out_dev) {  // mapped mode: the attention kernels store into the host block
-        if (cudaHostGetDevicePointer(&out_target, out_host, 0) != cudaSuccess || !out_target) {
-            (void)cudaGetLastError();
-            set_error("decode_step_host: out_host is not page-locked memory the device can address");
-            return NCKV_E_ARG;
-        }
-    }
-    int rc = nckv_append_rope_norm(base, base + nq, base + nq + nk, q_rot_dev, k_cache, v_cache, cache_seqlens, cos, sin,
-                                   B, 1, Hq, Hkv, D, T_max, cache_batch_stride, cache_token_stride, rope_len, qk_scale,
-                                   eps, static_cast<int32_t *>(workspace), stream);
-    if (rc != NCKV_OK) return rc;
-    rc = nckv_decode_attn(q_rot_dev, k_cache, v_cache, cache_seqlens, out_target, nullptr, nullptr, B, Hq, Hkv, D, T_max,
-                          cache_batch_stride, cache_token_stride, 1, window_left, 0, 0, workspace, workspace_bytes, stream);
-    if (rc != NCKV_OK) return rc;
-    if (out_dev) NCKV_CUDA_CHECK(cudaMemcpyAsync(out_host, out_dev, nq * 2, cudaMemcpyDeviceToHost, s));
-    NCKV_CUDA_CHECK(cudaStreamSynchronize(s));
-    return NCKV_OK;
-}
-
 }  // extern "C"

@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(HERE)
 OUT = os.path.join(PKG, "libnckv.so")
 SOURCES = ["host.cu", "append.cu", "decode_attn.cu", "prefill_broadcast.cu", "lse_combine.cu",
-           "prefill_attn.cu", "p2p_exchange.cu", "glue.cu", "flash_attn_bwd.cu"]
+           "prefill_attn.cu", "p2p_exchange.cu", "glue.cu", "flash_attn_bwd.cu", "host_step.cu"]
 HEADERS = ["nckv_common.cuh", "tc05.cuh", os.path.join("..", "..", "include", "nckv.h")]
 
 

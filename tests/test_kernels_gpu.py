@@ -563,6 +563,33 @@ def test_host_decode_step_matches_device_path(transfer):
     assert ops().read_status(DEV) == 0
 
 
+@pytest.mark.parametrize("transfer", ["copy", "mapped"])
+def test_host_decode_step_replays_follow_the_callers_stream(transfer):
+    """Six steps through the same HostDecodeStep (the first captures the step, the others replay it): new
+    host inputs and cache_seqlens advanced on the caller's stream between steps; every step equals the device
+    ops run on a copy of the cache."""
+    gen = torch.Generator(device=DEV).manual_seed(78)
+    B, Hq, Hkv, T_max = 4, 4, 4, 128
+    cos, sin = E.rotary_tables(T_max, 128, DEV, BF)
+    st = torch.tensor([3, 40, 0, 100], device=DEV, dtype=torch.int32)
+    k_cache, v_cache = make_cache(B, T_max, Hkv, None, gen)
+    kc2, vc2, st2 = k_cache.clone(), v_cache.clone(), st.clone()
+    step = ops().HostDecodeStep(B, Hq, Hkv, cos, sin, DEV, transfer=transfer)
+    for i in range(6):
+        q = torch.randn(B, 1, Hq, 128, generator=gen, device=DEV).to(BF)
+        k = torch.randn(B, 1, Hkv, 128, generator=gen, device=DEV).to(BF)
+        v = torch.randn(B, 1, Hkv, 128, generator=gen, device=DEV).to(BF)
+        q2 = ops().append_rope_norm(q, k, v, k_cache, v_cache, st, cos, sin)
+        ref = ops().decode_attention(q2[:, 0], k_cache, v_cache, st)
+        step.q.copy_(q[:, 0].cpu()); step.k.copy_(k[:, 0].cpu()); step.v.copy_(v[:, 0].cpu())
+        out = step.run(kc2, vc2, st2)
+        assert torch.equal(bits(out), bits(ref.cpu())), f"step {i}"
+        st += 1
+        st2 += 1  # enqueued on the caller's stream, not synchronised: the next step must come after it
+    assert torch.equal(bits(kc2), bits(k_cache)) and torch.equal(bits(vc2), bits(v_cache))
+    assert ops().read_status(DEV) == 0
+
+
 def test_p2p_wait_runs_out_and_reports_instead_of_hanging():
     """A peer that never delivers: the wait/combine kernel gives up after its limit, sets the timeout
     bit, leaves the output untouched and the context usable.  (The failure is a flag nothing sets.)"""
