@@ -17,7 +17,25 @@
 
 namespace nckv {
 
+// The three small kernels of a step are launched with programmatic dependent launch like the library's other
+// kernels: each lets its successor be scheduled at once and waits for its predecessors before touching data.
+template <typename Kernel, typename... Args>
+static cudaError_t launch_dependent(Kernel kernel, int grid, int block, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((unsigned)block);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 __global__ void host_flag_kernel(unsigned long long *counter, volatile unsigned long long *flag) {
+    pdl_launch_dependents();
+    pdl_wait_prior_grids();
     const unsigned long long v = *counter + 1;
     *counter = v;
     __threadfence_system();  // the result stores of the kernels before this one are ordered before the flag
@@ -27,6 +45,8 @@ __global__ void host_flag_kernel(unsigned long long *counter, volatile unsigned 
 // 16-byte copy between a pinned host block (through its device alias) and device memory.  Inside a graph a
 // copy of a few hundred KB issued by the SMs starts sooner than a copy-engine node.
 __global__ void __launch_bounds__(256) host_block_copy_kernel(uint4 *dst, const uint4 *src, long long n16) {
+    pdl_launch_dependents();
+    pdl_wait_prior_grids();
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (long long)gridDim.x * blockDim.x)
         dst[i] = src[i];
 }
@@ -43,8 +63,8 @@ static void *device_alias(const void *host) {
 static cudaError_t copy_block(void *dst, const void *src, size_t bytes, cudaStream_t s) {
     const long long n16 = (long long)(bytes / 16);
     const int grid = (int)((n16 + 255) / 256 < 4 * sm_count() ? (n16 + 255) / 256 : 4 * sm_count());
-    host_block_copy_kernel<<<grid, 256, 0, s>>>(static_cast<uint4 *>(dst), static_cast<const uint4 *>(src), n16);
-    return cudaGetLastError();
+    return launch_dependent(host_block_copy_kernel, grid, 256, s, static_cast<uint4 *>(dst), static_cast<const uint4 *>(src),
+                            n16);
 }
 
 struct StepArgs {
@@ -158,7 +178,8 @@ static bool build_plan(StepPlan &pl, const StepArgs &a) {
     if (ok) {
         const int rc = enqueue_step(a, pl.stream);
         if (rc == NCKV_OK)
-            host_flag_kernel<<<1, 1, 0, pl.stream>>>(pl.counter_dev, static_cast<unsigned long long *>(flag_alias));
+            (void)launch_dependent(host_flag_kernel, 1, 1, pl.stream, pl.counter_dev,
+                                   static_cast<volatile unsigned long long *>(flag_alias));
         const bool ended = cudaStreamEndCapture(pl.stream, &graph) == cudaSuccess && graph;
         ok = rc == NCKV_OK && ended && cudaGraphInstantiate(&pl.exec, graph, 0) == cudaSuccess;
     }
