@@ -186,3 +186,41 @@ def test_fused_append_bytes_equal_the_references_own_functions(B, T_new, Hq, Hkv
         bad += (kc[b:b + 1, L:L + T_new].view(torch.int16) != k_ref.view(torch.int16)).sum().item()
         bad += (vc[b:b + 1, L:L + T_new].view(torch.int16) != v[b:b + 1].view(torch.int16)).sum().item()
     assert bad == 0, f"{bad} elements differ from the reference's bf16 GPU path"
+
+
+def test_reference_training_step_with_flash_attn_func_swapped_in():
+    """The reference GPT's own training forward (gpt.py:416-472 with targets, attention through
+    flash_attn_func at gpt.py:108) and loss.backward(), once on its SDPA path and once with flash_attn pointed
+    at the mirror: the loss and every parameter gradient agree to bf16 accuracy.  Short windows on three of the
+    four layers so that the sliding-window backward is exercised."""
+    ref_gpt, ref_engine = _ref()
+    model = _config0(ref_gpt, binding=True, seed=5)
+    model.window_sizes = [(64, 0), (96, 0), (64, 0), (2048, 0)]
+    gen = torch.Generator().manual_seed(9)
+    idx = torch.randint(0, 32768, (2, 320), generator=gen).to(DEV)
+    targets = torch.randint(0, 32768, (2, 320), generator=gen).to(DEV)
+
+    def step():
+        model.zero_grad(set_to_none=True)
+        loss = model(idx, targets)
+        loss.backward()
+        return loss.detach().float().item(), {n: p.grad.detach().float().clone() for n, p in model.named_parameters()
+                                             if p.grad is not None}
+
+    loss_ref, g_ref = step()
+    with _mirrors_swapped_in(ref_gpt, ref_engine):
+        loss_our, g_our = step()
+    from nanochat_b200 import ops
+    assert ops.read_status(DEV) == 0
+    assert abs(loss_our - loss_ref) <= 2e-3 * abs(loss_ref), (loss_our, loss_ref)
+    assert g_our.keys() == g_ref.keys() and len(g_ref) > 10
+    worst = 0.0
+    for n in g_ref:
+        denom = g_ref[n].norm().item()
+        if denom == 0.0:
+            assert g_our[n].norm().item() == 0.0, n
+            continue
+        rel = (g_our[n] - g_ref[n]).norm().item() / denom
+        worst = max(worst, rel)
+        assert rel <= 3e-2, f"{n}: gradient differs by {rel:.4f} of its norm"
+    print(f"training step: loss {loss_our:.5f} vs {loss_ref:.5f}, worst relative gradient difference {worst:.4f}")
