@@ -87,6 +87,19 @@ NCKV_API int nckv_append_rope_norm(const void *q_in, const void *k_in, const voi
                           int32_t *status, void *stream);
 
 /*
+ * nckv_append_rope_norm with q_in, k_in and v_in given as strided rows: token t of row b starts
+ * (b T_new + t) * stride elements into the tensor, its heads packed behind each other.  Lets q, k and v be
+ * column slices of the output of one [c_q; c_k; c_v] projection.  Strides are multiples of 8 elements;
+ * 0 means packed.  q_out is always packed (B, T_new, Hq, D).
+ */
+NCKV_API int nckv_append_rope_norm_strided(const void *q_in, const void *k_in, const void *v_in, int64_t q_token_stride,
+                                  int64_t k_token_stride, int64_t v_token_stride, void *q_out, void *k_cache,
+                                  void *v_cache, const int32_t *cache_seqlens, const void *cos, const void *sin, int B,
+                                  int T_new, int Hq, int Hkv, int D, int T_max, int64_t cache_batch_stride,
+                                  int64_t cache_token_stride, int rope_len, float qk_scale, float eps, int32_t *status,
+                                  void *stream);
+
+/*
  * Same as nckv_append_rope_norm for a sequence-split cache (no counterpart in the reference):
  * `positions[b]` is the sequence position of row b's first new token (drives RoPE, as
  * cache_seqlens does above) while `write_slots[b]` is the index in THIS shard's cache where its
@@ -366,13 +379,14 @@ NCKV_API int nckv_flash_attn_bwd(const void *q, const void *k, const void *v, co
  * normalised row; the fp32 sum of squares is accumulated in the order of torch's row kernel.
  * nckv_glue_relu_sq: out = bf16(max(h, 0)^2) over n elements (n % 8 == 0), MLP.forward gpt.py:136.
  * nckv_glue_ve_gate: v_out = bf16(v + bf16(bf16(3 * bf16(sigmoid(gate_lin))) * ve)) with v, ve (rows, Hkv, D)
- * and gate_lin (rows, Hkv) the output of the gate's linear layer: the value residual of gpt.py:92-95.
+ * and gate_lin (rows, Hkv) the output of the gate's linear layer: the value residual of gpt.py:92-95.  v may have
+ * its own row stride in elements (v_row_stride, 0 = packed): a column slice of a projection output.
  */
 NCKV_API int nckv_glue_mix_norm(const void *x, const void *add, const void *x0, const void *x_backout, void *out_sum,
                        void *out_x, void *out_norm, int rows, int C, int mode, float resid_lambda, float x0_lambda,
                        float backout_lambda, float eps, void *stream);
 NCKV_API int nckv_glue_relu_sq(const void *h, void *out, int64_t n, void *stream);
-NCKV_API int nckv_glue_ve_gate(const void *v, const void *gate_lin, const void *ve, void *v_out, int rows, int Hkv, int D,
+NCKV_API int nckv_glue_ve_gate(const void *v, int64_t v_row_stride, const void *gate_lin, const void *ve, void *v_out, int rows, int Hkv, int D,
                       void *stream);
 
 #ifdef __cplusplus

@@ -46,7 +46,9 @@ SIGNATURES = {
                                       ctypes.c_uint64, c_void_p]),
     "nckv_glue_mix_norm": (c_int, [c_void_p] * 7 + [c_int] * 3 + [c_float] * 4 + [c_void_p]),
     "nckv_glue_relu_sq": (c_int, [c_void_p, c_void_p, c_i64, c_void_p]),
-    "nckv_glue_ve_gate": (c_int, [c_void_p] * 4 + [c_int] * 3 + [c_void_p]),
+    "nckv_glue_ve_gate": (c_int, [c_void_p, c_i64] + [c_void_p] * 3 + [c_int] * 3 + [c_void_p]),
+    "nckv_append_rope_norm_strided": (c_int, [c_void_p] * 3 + [c_i64] * 3 + [c_void_p] * 6 + [c_int] * 6 + [c_i64, c_i64, c_int, c_float, c_float,
+                                              c_void_p, c_void_p]),
     "nckv_paged_tile_tokens": (c_int, []),
     "nckv_append_rope_norm_paged": (c_int, [c_void_p] * 10 + [c_int] * 8 + [c_i64, c_i64, c_int, c_float, c_float,
                                                              c_void_p, c_void_p]),

@@ -35,6 +35,9 @@ struct AppendParams {
     // T_max is then max_pages * page_tokens and cache_batch_stride the distance between pages
     const int32_t *block_table;
     int page_tokens, max_pages, n_pages;
+    // distance between the tokens of q_in / k_in / v_in in 16-byte units (heads of a token are packed); lets the
+    // three be column slices of one projection output
+    long long q_stride, k_stride, v_stride;
 };
 
 __device__ __forceinline__ void unpack8(const uint4 &v, float (&f)[8]) {
@@ -143,11 +146,12 @@ __global__ void __launch_bounds__(256) append_rope_norm_kernel(const AppendParam
         const int h = kind == 0 ? slot : (kind == 1 ? slot - q_heads : slot - q_heads - p.Hkv);
         const bool transform = kind == 0 || (kind == 1 && p.transform_k);
         const uint4 *src = kind == 0 ? p.q_in : (kind == 1 ? p.k_in : p.v_in);
-        const long long src_idx = (bt * (kind == 0 ? p.Hq : p.Hkv) + h) * 16 + j;
+        const long long src_idx = (bt * (kind == 0 ? p.Hq : p.Hkv) + h) * 16 + j;  // packed: where q_out goes
+        const long long in_idx = bt * (kind == 0 ? p.q_stride : (kind == 1 ? p.k_stride : p.v_stride)) + h * 16 + j;
         // the input row does not depend on the row's length: its load goes out together with the
         // length's, one round trip ahead of the table rows that do
         uint4 x = make_uint4(0, 0, 0, 0);
-        if (live) x = src[src_idx];
+        if (live) x = src[in_idx];
         const int len = p.cache_seqlens[b];          // sequence position of token 0 (drives RoPE)
         int wslot = p.write_slots ? p.write_slots[b] : len;  // cache index of token 0
         if (p.split.block > 0 && len >= 0)
@@ -259,8 +263,15 @@ static int append_rope_norm_impl(const void *q_in, const void *k_in, const void 
                                  int Hq, int Hkv, int D, int T_max, int64_t cache_batch_stride,
                                  int64_t cache_token_stride, int rope_len, float qk_scale, float eps,
                                  int32_t *status, void *stream, const int32_t *block_table = nullptr,
-                                 int page_tokens = 0, int max_pages = 0, int n_pages = 0) {
+                                 int page_tokens = 0, int max_pages = 0, int n_pages = 0, int64_t q_token_stride = 0,
+                                 int64_t k_token_stride = 0, int64_t v_token_stride = 0) {
     using namespace nckv;
+    if ((q_token_stride && (q_token_stride % 8 || q_token_stride < (int64_t)Hq * D)) ||
+        (k_token_stride && (k_token_stride % 8 || k_token_stride < (int64_t)Hkv * D)) ||
+        (v_token_stride && (v_token_stride % 8 || v_token_stride < (int64_t)Hkv * D))) {
+        set_error("append_rope_norm: token strides must be multiples of 8 elements and span a token's heads");
+        return NCKV_E_ARG;
+    }
     int rc = check_common(k_in, v_in, k_cache, v_cache, cache_seqlens, B, T_new, Hkv, D, T_max,
                           cache_batch_stride, cache_token_stride, status);
     if (rc != NCKV_OK) return rc;
@@ -297,7 +308,26 @@ static int append_rope_norm_impl(const void *q_in, const void *k_in, const void 
     p.split = split;
     p.block_table = block_table;
     p.page_tokens = page_tokens; p.max_pages = max_pages; p.n_pages = n_pages;
+    p.q_stride = q_token_stride ? q_token_stride / 8 : (long long)Hq * 16;
+    p.k_stride = k_token_stride ? k_token_stride / 8 : (long long)Hkv * 16;
+    p.v_stride = v_token_stride ? v_token_stride / 8 : (long long)Hkv * 16;
     return launch_append(p, static_cast<cudaStream_t>(stream));
+}
+
+int nckv_append_rope_norm_strided(const void *q_in, const void *k_in, const void *v_in, int64_t q_token_stride,
+                                  int64_t k_token_stride, int64_t v_token_stride, void *q_out, void *k_cache,
+                                  void *v_cache, const int32_t *cache_seqlens, const void *cos, const void *sin, int B,
+                                  int T_new, int Hq, int Hkv, int D, int T_max, int64_t cache_batch_stride,
+                                  int64_t cache_token_stride, int rope_len, float qk_scale, float eps, int32_t *status,
+                                  void *stream) {
+    if (((uintptr_t)k_in | (uintptr_t)v_in) & 15) {
+        nckv::set_error("append_rope_norm_strided: tensors must be 16-byte aligned");
+        return NCKV_E_ARG;
+    }
+    return append_rope_norm_impl(q_in, k_in, v_in, q_out, k_cache, v_cache, cache_seqlens, nullptr, nckv::KvSplit{0, 0, 0}, cos,
+                                 sin, B, T_new, Hq, Hkv, D, T_max, cache_batch_stride, cache_token_stride, rope_len,
+                                 qk_scale, eps, status, stream, nullptr, 0, 0, 0, q_token_stride, k_token_stride,
+                                 v_token_stride);
 }
 
 int nckv_append_rope_norm(const void *q_in, const void *k_in, const void *v_in, void *q_out,
@@ -386,6 +416,8 @@ int nckv_append(const void *k_in, const void *v_in, void *k_cache, void *v_cache
     p.split = KvSplit{0, 0, 0};
     p.block_table = nullptr;
     p.page_tokens = p.max_pages = p.n_pages = 0;
+    p.q_stride = 0;
+    p.k_stride = p.v_stride = (long long)Hkv * 16;
     return launch_append(p, static_cast<cudaStream_t>(stream));
 }
 

@@ -119,15 +119,17 @@ __global__ void __launch_bounds__(256) relu_sq_kernel(const uint4 *__restrict__ 
     }
 }
 
-// v, ve, v_out: (rows, Hkv, 128) bf16; g: (rows, Hkv) bf16 (output of the gate's linear layer)
+// v, ve, v_out: (rows, Hkv, 128) bf16, v with its own row stride (it may be a column slice of a projection
+// output); g: (rows, Hkv) bf16 (output of the gate's linear layer)
 __global__ void __launch_bounds__(256) ve_gate_kernel(const uint4 *__restrict__ v, const __nv_bfloat16 *__restrict__ g,
                                                       const uint4 *__restrict__ ve, uint4 *__restrict__ v_out,
-                                                      long long n_vec) {
+                                                      long long n_vec, int row_vecs, long long v_row_stride) {
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (long long)gridDim.x * blockDim.x) {
         const float lin = __bfloat162float(g[i >> 4]);  // 16 vectors of 8 channels per head
         const float sig = round_bf16(__fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-lin))));
         const float gate = round_bf16(__fmul_rn(3.0f, sig));
-        const uint4 a = v[i], b = ve[i];
+        const long long row = i / row_vecs;
+        const uint4 a = v[row * v_row_stride + (i - row * row_vecs)], b = ve[i];
         const uint32_t av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
         uint32_t res[4];
 #pragma unroll
@@ -199,8 +201,8 @@ int nckv_glue_relu_sq(const void *h, void *out, int64_t n, void *stream) {
     return NCKV_OK;
 }
 
-int nckv_glue_ve_gate(const void *v, const void *gate_lin, const void *ve, void *v_out, int rows, int Hkv, int D,
-                      void *stream) {
+int nckv_glue_ve_gate(const void *v, int64_t v_row_stride, const void *gate_lin, const void *ve, void *v_out, int rows,
+                      int Hkv, int D, void *stream) {
     using namespace nckv;
     if (!v || !gate_lin || !ve || !v_out || rows <= 0 || Hkv <= 0) {
         set_error("glue_ve_gate: null pointer or non-positive size");
@@ -209,6 +211,11 @@ int nckv_glue_ve_gate(const void *v, const void *gate_lin, const void *ve, void 
     if (D != NCKV_D) {
         set_error("glue_ve_gate: head_dim %d unsupported (kernels are built for 128)", D);
         return NCKV_E_UNSUPPORTED;
+    }
+    if (v_row_stride == 0) v_row_stride = (int64_t)Hkv * D;
+    if (v_row_stride % 8 || v_row_stride < (int64_t)Hkv * D) {
+        set_error("glue_ve_gate: v_row_stride must be a multiple of 8 elements and span a row's heads");
+        return NCKV_E_ARG;
     }
     if (((uintptr_t)v | (uintptr_t)ve | (uintptr_t)v_out) & 15) {
         set_error("glue_ve_gate: tensors must be 16-byte aligned");
@@ -220,7 +227,7 @@ int nckv_glue_ve_gate(const void *v, const void *gate_lin, const void *ve, void 
     if (blocks > cap) blocks = cap;
     ve_gate_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint4 *>(v), static_cast<const __nv_bfloat16 *>(gate_lin), static_cast<const uint4 *>(ve),
-        static_cast<uint4 *>(v_out), n_vec);
+        static_cast<uint4 *>(v_out), n_vec, Hkv * (NCKV_D / 8), (long long)(v_row_stride / 8));
     NCKV_CUDA_CHECK(cudaGetLastError());
     return NCKV_OK;
 }

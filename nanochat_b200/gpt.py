@@ -133,6 +133,33 @@ class Attention(nn.Module):
         self.ve_gate_channels = 12
         self.ve_gate = (CastLinear(self.ve_gate_channels, self.n_kv_head, bias=False)
                         if layer_has_value_embedding(layer_idx, config.n_layer) else None)
+        self._qkv_cache = None
+
+    def fused_qkv_weight(self, x):
+        """[c_q; c_k; c_v] as one weight for activations like ``x`` (rows, n_embd), or None.
+
+        One product over the stacked weight replaces three launches.  It is only used when it reproduces the
+        three separate products bit for bit (the K/V bytes that reach the cache must be those of the
+        reference's projections, gpt.py:88-90): that is checked once per (weights, dtype, row count) on
+        random activations, outside stream capture; a step captured before the check has run keeps the three
+        products.  Costs a second copy of the three weights.  (Stacking the value gate's rows as well, zero
+        over the channels it does not read, was bit-identical only for some shapes and saved nothing measurable.)"""
+        ws = (self.c_q.weight, self.c_k.weight, self.c_v.weight)
+        rows = x.numel() // x.size(-1)
+        key = tuple((w.data_ptr(), w._version) for w in ws) + (x.dtype, rows)
+        if self._qkv_cache is None or self._qkv_cache[0] != key:
+            if torch.cuda.is_current_stream_capturing():
+                return None
+            wq, wk, wv = (w.detach().to(x.dtype) for w in ws)
+            stacked = torch.cat([wq, wk, wv], 0).contiguous()
+            gen = torch.Generator(device=x.device).manual_seed(1234)
+            same = True
+            for _ in range(2):
+                probe = torch.randn(rows, x.size(-1), generator=gen, device=x.device).to(x.dtype)
+                apart = torch.cat([F.linear(probe, wq), F.linear(probe, wk), F.linear(probe, wv)], 1)
+                same = same and torch.equal(F.linear(probe, stacked), apart)
+            self._qkv_cache = (key, stacked if same else None)
+        return self._qkv_cache[1]
 
     def forward(self, x, ve, rope_tables, window_size, kv_cache):
         B, T, _ = x.shape
@@ -208,6 +235,7 @@ class GPT(nn.Module):
         # products through the fused kernels of libnckv (bit-identical to the eager ops); set False to
         # run the eager op sequence everywhere.
         self.fused_glue = True
+        self.fused_qkv = True   # one [c_q; c_k; c_v] product per layer in the decode trunk where it is bit-identical
         self._lambda_cache = None
         self.rotary_seq_len = config.sequence_len * 10  # same over-allocation as gpt.py:195
         self.register_buffer("cos", torch.empty(0), persistent=False)
@@ -339,9 +367,17 @@ class GPT(nn.Module):
             if i == backout_at + 1:
                 x_backout = x_sum
             attn = block.attn
-            q = attn.c_q(xn).view(B, 1, attn.n_head, attn.head_dim)
-            k = attn.c_k(xn).view(B, 1, attn.n_kv_head, attn.head_dim)
-            v = attn.c_v(xn).view(B, 1, attn.n_kv_head, attn.head_dim)
+            w_qkv = attn.fused_qkv_weight(xn) if self.fused_qkv else None
+            if w_qkv is not None:  # one product; q, k, v are column slices of its output (the kernels take the stride)
+                nq, nkv = attn.n_head * attn.head_dim, attn.n_kv_head * attn.head_dim
+                qkv = F.linear(xn, w_qkv)
+                q = qkv[..., :nq].view(B, 1, attn.n_head, attn.head_dim)
+                k = qkv[..., nq:nq + nkv].view(B, 1, attn.n_kv_head, attn.head_dim)
+                v = qkv[..., nq + nkv:].view(B, 1, attn.n_kv_head, attn.head_dim)
+            else:
+                q = attn.c_q(xn).view(B, 1, attn.n_head, attn.head_dim)
+                k = attn.c_k(xn).view(B, 1, attn.n_kv_head, attn.head_dim)
+                v = attn.c_v(xn).view(B, 1, attn.n_kv_head, attn.head_dim)
             if str(i) in self.value_embeds:
                 ve = self.value_embeds[str(i)](idx).to(x.dtype)
                 v = ops.glue_ve_gate(v, attn.ve_gate(xn[..., :attn.ve_gate_channels]), ve)

@@ -166,11 +166,28 @@ def _append_rope_norm(q, k, v, k_cache, v_cache, cache_seqlens, cos, sin, qk_sca
     sin2 = sin.reshape(-1, D // 2)
     if not (cos2.is_contiguous() and sin2.is_contiguous()):
         cos2, sin2 = cos2.contiguous(), sin2.contiguous()
-    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
-    q_out = torch.empty_like(q)
+    # q, k, v may be column slices of one projection output: packed heads, a common token stride per tensor
+    strided = None
+    if split is None and write_slots is None and not (q.is_contiguous() and k.is_contiguous() and v.is_contiguous()):
+        def token_stride(t, H):
+            ok = t.stride(3) == 1 and t.stride(2) == D and (T_new == 1 or t.stride(0) == T_new * t.stride(1)) and \
+                t.stride(1 if T_new > 1 else 0) % 8 == 0 and t.data_ptr() % 16 == 0
+            return t.stride(1 if T_new > 1 else 0) if ok else None
+        strided = (token_stride(q, Hq), token_stride(k, Hkv), token_stride(v, Hkv))
+        if None in strided:
+            strided = None
+    if strided is None:
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    q_out = torch.empty((B, T_new, Hq, D), dtype=q.dtype, device=q.device)
     idx, stream, ws = _launch_ctx(q, B, Hq, Hkv)
     with _device_guard(idx):
-        if split is not None:
+        if strided is not None:
+            rc = _lib.lib.nckv_append_rope_norm_strided(q.data_ptr(), k.data_ptr(), v.data_ptr(), strided[0], strided[1],
+                                                        strided[2], q_out.data_ptr(), k_cache.data_ptr(),
+                                                        v_cache.data_ptr(), cache_seqlens.data_ptr(), cos2.data_ptr(),
+                                                        sin2.data_ptr(), B, T_new, Hq, Hkv, D, k_cache.size(1), sb, st,
+                                                        cos2.size(0), qk_scale, eps, ws.data_ptr(), stream)
+        elif split is not None:
             world, rank, block = split
             rc = _lib.lib.nckv_append_rope_norm_split(q.data_ptr(), k.data_ptr(), v.data_ptr(), q_out.data_ptr(),
                                                       k_cache.data_ptr(), v_cache.data_ptr(), cache_seqlens.data_ptr(),
@@ -696,17 +713,28 @@ def glue_ve_gate(v, gate_lin, ve):
     """v + 3 * sigmoid(gate_lin)[..., None] * ve in one launch (gpt.py:92-95); v, ve: (..., Hkv, 128),
     gate_lin: (..., Hkv) — the output of the gate's linear layer."""
     for t in (v, gate_lin, ve):
-        if not t.is_cuda or t.dtype != torch.bfloat16 or not t.is_contiguous():
-            raise RuntimeError("nckv::glue_ve_gate needs contiguous CUDA bfloat16 tensors")
+        if not t.is_cuda or t.dtype != torch.bfloat16:
+            raise RuntimeError("nckv::glue_ve_gate needs CUDA bfloat16 tensors")
     Hkv, Dh = v.size(-2), v.size(-1)
     rows = v.numel() // (Hkv * Dh)
     if gate_lin.numel() != rows * Hkv or ve.numel() != v.numel():
         raise RuntimeError(f"nckv::glue_ve_gate: shapes {tuple(v.shape)} / {tuple(gate_lin.shape)} / {tuple(ve.shape)} do not match")
-    out = torch.empty_like(v)
+    # v may be a column slice of a projection output: (rows..., Hkv, D) with packed heads and one row stride
+    row_stride = 0
+    if not v.is_contiguous():
+        lead = [(n, s) for n, s in zip(v.shape[:-2], v.stride()[:-2]) if n > 1]
+        regular = v.stride(-1) == 1 and v.stride(-2) == Dh and all(
+            lead[i][1] == lead[i + 1][0] * lead[i + 1][1] for i in range(len(lead) - 1))
+        if regular and lead and lead[-1][1] % 8 == 0 and v.data_ptr() % 16 == 0:
+            row_stride = lead[-1][1]
+        else:
+            v = v.contiguous()
+    gate_lin, ve = gate_lin.contiguous(), ve.contiguous()
+    out = torch.empty(v.shape, dtype=v.dtype, device=v.device)
     idx = v.device.index
     with _device_guard(idx):
-        _lib.call("nckv_glue_ve_gate", v.data_ptr(), gate_lin.data_ptr(), ve.data_ptr(), out.data_ptr(), rows, Hkv, Dh,
-                  torch.cuda.current_stream(idx).cuda_stream)
+        _lib.call("nckv_glue_ve_gate", v.data_ptr(), row_stride, gate_lin.data_ptr(), ve.data_ptr(), out.data_ptr(), rows,
+                  Hkv, Dh, torch.cuda.current_stream(idx).cuda_stream)
     return out
 
 

@@ -116,6 +116,41 @@ def test_fused_trunk_gives_the_logits_and_cache_bytes_of_the_eager_trunk(shape):
             logits.append(model.forward(logits[-1].argmax(-1, keepdim=True), kv_cache=cache)[:, -1, :])
         runs.append((torch.stack(logits), cache))
     (l_eager, c_eager), (l_fused, c_fused) = runs
+    stacked = model.transformer.h[0].attn._qkv_cache
+    print("stacked q/k/v projection in use:", stacked is not None and stacked[1] is not None)
     assert torch.equal(l_eager, l_fused), f"logits differ by {(l_eager - l_fused).abs().max().item()}"
     assert torch.equal(_bits(c_eager.k_cache), _bits(c_fused.k_cache)) and torch.equal(_bits(c_eager.v_cache), _bits(c_fused.v_cache))
     assert torch.equal(c_eager.cache_seqlens, c_fused.cache_seqlens)
+
+
+def test_strided_qkv_slices_equal_packed_inputs():
+    """q, k, v as column slices of one (B, 1, Nq + 2 Nkv) projection output: the append kernel and the value gate
+    take the token stride and give the bytes they give for packed copies of the slices."""
+    from nanochat_b200 import ops
+    from oracle import torch_ref as E
+    gen = torch.Generator(device=DEV).manual_seed(21)
+    B, Hq, Hkv, T_max = 6, 8, 2, 96
+    nq, nkv = Hq * 128, Hkv * 128
+    qkv = torch.randn(B, 1, nq + 2 * nkv, generator=gen, device=DEV).to(BF)
+    q = qkv[..., :nq].view(B, 1, Hq, 128)
+    k = qkv[..., nq:nq + nkv].view(B, 1, Hkv, 128)
+    v = qkv[..., nq + nkv:].view(B, 1, Hkv, 128)
+    assert not q.is_contiguous() and not v.is_contiguous()
+    gate = torch.randn(B, 1, Hkv, generator=gen, device=DEV).to(BF)
+    ve = torch.randn(B, 1, Hkv, 128, generator=gen, device=DEV).to(BF)
+    v_a = ops.glue_ve_gate(v, gate, ve)
+    v_b = ops.glue_ve_gate(v.contiguous(), gate, ve)
+    assert torch.equal(_bits(v_a), _bits(v_b))
+    cos, sin = E.rotary_tables(T_max, 128, DEV, BF)
+    lens = torch.tensor([0, 5, 17, 94, 33, 60], device=DEV, dtype=torch.int32)
+    caches = []
+    for strided in (True, False):
+        kc = torch.zeros(B, T_max, Hkv, 128, device=DEV, dtype=BF)
+        vc = torch.zeros_like(kc)
+        args = (q, k, v) if strided else (q.contiguous(), k.contiguous(), v.contiguous())
+        q_out = ops.append_rope_norm(*args, kc, vc, lens, cos, sin)
+        caches.append((q_out, kc, vc))
+    torch.cuda.synchronize()
+    assert ops.read_status(DEV) == 0
+    for a, b in zip(*caches):
+        assert a.is_contiguous() and torch.equal(_bits(a), _bits(b))
