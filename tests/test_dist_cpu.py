@@ -1,4 +1,4 @@
-"""N > 1 host logic on CPU: world_size-2 (and 3) gloo groups exercise the row sharding and the
+"""N > 1 host logic on CPU: world_size-2, 3 and 8 gloo groups exercise the row sharding and the
 key-split exchange (all-gather + log-sum-exp combine) with the oracle standing in for the kernels."""
 import os
 import socket
@@ -126,7 +126,7 @@ def _cyclic_worker(rank, world, port, block, seqlens, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,block", [(2, 16), (3, 32)])
+@pytest.mark.parametrize("world,block", [(2, 16), (3, 32), (8, 16)])
 def test_block_cyclic_split_matches_unsplit_attention(world, block):
     ctx = mp.get_context("spawn")
     ret = ctx.Queue()
