@@ -488,23 +488,21 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                     (n_tiles > 0 && l_run > 0.f) ? (m_used + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
             uint4 *dst = reinterpret_cast<uint4 *>(p.out + (((long long)it.b * p.T_new + tq) * p.Hq + it.hq) * NCKV_D);
 #pragma unroll
-            for (int ch = 0; ch < NCKV_D / 32; ++ch) {
-                float c[32];
+            for (int ch = 0; ch < NCKV_D / 64; ++ch) {
+                float c[64];
                 if (n_tiles > 0) {
-                    tmem_ld32(tmem_o + lane_sel + ch * 32, c);
+                    tmem_ld64(tmem_o + lane_sel + ch * 64, c);
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) c[i] = 0.f;
+                    for (int i = 0; i < 64; ++i) c[i] = 0.f;
                 }
                 if (tq < p.T_new) {  // rows past the end of the sequence are padding
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        uint4 v;
-                        v.x = pack_bf16x2(c[8 * i + 0] * inv, c[8 * i + 1] * inv);
-                        v.y = pack_bf16x2(c[8 * i + 2] * inv, c[8 * i + 3] * inv);
-                        v.z = pack_bf16x2(c[8 * i + 4] * inv, c[8 * i + 5] * inv);
-                        v.w = pack_bf16x2(c[8 * i + 6] * inv, c[8 * i + 7] * inv);
-                        dst[ch * 4 + i] = v;
+                    for (int i = 0; i < 4; ++i) {  // 32 bytes per store: whole sectors
+                        uint32_t w[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) w[e] = pack_bf16x2(c[16 * i + 2 * e] * inv, c[16 * i + 2 * e + 1] * inv);
+                        st_global_v8(dst + (ch * 4 + i) * 2, w);
                     }
                 }
             }

@@ -123,6 +123,12 @@ __device__ __forceinline__ void umma_bf16_a_tmem(uint32_t d_tmem, uint32_t a_tme
         : "memory");
 }
 
+// One 32-byte store (the address must be 32-byte aligned): a whole sector per thread.
+__device__ __forceinline__ void st_global_v8(void *ptr, const uint32_t (&w)[8]) {
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(ptr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]),
+                 "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+                 : "memory");
+}
 // Two-wide fp32 arithmetic (one instruction for a register pair, same rounding per element as the
 // scalar forms) and the three-input max.
 __device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
