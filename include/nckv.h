@@ -171,7 +171,7 @@ NCKV_API int nckv_append(const void *k_in, const void *v_in, void *k_cache, void
  * (B,Hq,D) bf16.  Performs H2D, nckv_append_rope_norm, nckv_decode_attn, D2H and waits for them; on
  * return out_host holds the attention output.  cache_seqlens is not advanced.  The operations are
  * ordered after everything already enqueued on `stream`.  They are captured once per distinct argument
- * list (a small table, least recently used entry replaced) into a CUDA graph on a stream of the
+ * list (a table of 64, least recently used entry replaced; a caller that never repeats an argument list gets the operations directly on its stream) into a CUDA graph on a stream of the
  * library's own and replayed by later calls; the wait is a bounded spin on a pinned word the graph's last
  * node writes, with a stream synchronise as its fallback.  Calls are serialised by a mutex.
  * Mapped mode: with qkv_dev == NULL the append kernel reads the pinned host block itself (over

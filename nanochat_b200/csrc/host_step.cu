@@ -143,10 +143,12 @@ struct StepPlan {
     unsigned long long last_use = 0;
 };
 
-constexpr int STEP_PLANS = 8;
+constexpr int STEP_PLANS = 64;  // one per (layer, cache) a caller cycles through; least recently used entry replaced
 static std::mutex g_step_mutex;  // guards the table and serialises the steps that go through it
 static StepPlan g_step_plans[STEP_PLANS];
 static unsigned long long g_step_tick = 0;
+static int g_step_misses = 0;  // plans built since the last replay: a caller that never repeats an argument list
+                               // would pay a capture per call, so beyond a table's worth it gets the direct path
 
 static void release_plan(StepPlan &pl) {
     if (pl.exec) cudaGraphExecDestroy(pl.exec);
@@ -227,7 +229,10 @@ extern "C" int nckv_decode_step_host(const void *qkv_host, void *qkv_dev, void *
             if (c.live && memcmp(&c.args, &a, sizeof(a)) == 0) pl = &c;
             if (!c.live || (victim->live && c.last_use < victim->last_use)) victim = &c;
         }
-        if (!pl) {
+        if (pl) {
+            g_step_misses = 0;
+        } else if (g_step_misses < STEP_PLANS) {
+            ++g_step_misses;
             if (victim->live) release_plan(*victim);
             if (build_plan(*victim, a)) pl = victim;
         }
