@@ -12,7 +12,9 @@
 // tiles.  Scores are recomputed in both (7 matrix products per tile pair instead of 5) so that no
 // gradient needs atomics: results do not depend on scheduling.  The products run on the warp-level
 // tensor-core path (ldmatrix + mma.sync.m16n8k16 bf16, fp32 accumulation) with operands staged in shared
-// memory by cp.async; P and dS are formed in registers from the score accumulators.  This is a first,
+// memory by cp.async; P and dS are formed in registers from the score accumulators.  The kernels are bound by
+// shared-memory operand fetches, so a warp owns 2 x 2 blocks of 16 x 16 of each gradient (every fragment it loads
+// feeds two products) and two CTAs of 8 warps share an SM.  This is a first,
 // correct version: it makes no claim on the tcgen05 roofline.
 //
 // Replaces: autograd through F.scaled_dot_product_attention as reached from flash_attn_func
@@ -24,7 +26,7 @@
 namespace nckv {
 
 constexpr int BW_T = 64;             // queries and keys per tile
-constexpr int BW_THREADS = 512;      // 16 warps: one per 16 x 16 block of a score tile
+constexpr int BW_THREADS = 256;      // 8 warps; two CTAs per SM overlap each other's barrier-separated phases
 constexpr int BW_LD = NCKV_D + 8;    // bf16 row stride of the 64 x 128 operand tiles (272 B: ldmatrix without bank conflicts)
 constexpr int BW_LDS = BW_T + 8;     // bf16 row stride of the 64 x 64 P and dS tiles (144 B)
 
@@ -37,18 +39,18 @@ struct BwdParams {
     float scale, scale_log2;
 };
 
-// The tiles a CTA keeps for its whole life (`own`) and the tiles it walks (`walk`, two stages filled with
-// cp.async one iteration ahead).  dK/dV kernel: own = K, V; walk = Q, dO and their row statistics.
-// dQ kernel: own = Q, dO and the statistics (stage 0 of those arrays); walk = K, V.
+// The tiles a CTA keeps for its whole life (`own`) and the tiles it walks (`walk`, refilled with cp.async every
+// iteration; 89 KB in all, so that two CTAs share an SM and one computes while the other waits for its copies).
+// dK/dV kernel: own = K, V; walk = Q, dO and their row statistics.  dQ kernel: own = Q, dO and the statistics; walk = K, V.
 struct BwdSmem {
     __nv_bfloat16 own[2][BW_T * BW_LD];
-    __nv_bfloat16 walk[2][2][BW_T * BW_LD];  // [stage][tile]; after the loop: staging of a 64 x 128 fp32 result
+    __nv_bfloat16 walk[2][BW_T * BW_LD];  // [tile]; after the loop: staging of a 64 x 128 fp32 result
     __nv_bfloat16 p[BW_T * BW_LDS];
     __nv_bfloat16 ds[BW_T * BW_LDS];
-    float lse[2][BW_T];    // [stage]: natural-log log-sum-exp of the rows
-    float delta[2][BW_T];
+    float lse[BW_T];    // natural-log log-sum-exp of the rows
+    float delta[BW_T];
 };
-static_assert(sizeof(__nv_bfloat16) * 4 * BW_T * BW_LD >= sizeof(float) * BW_T * NCKV_D, "the result staging area");
+static_assert(sizeof(__nv_bfloat16) * 2 * BW_T * BW_LD >= sizeof(float) * BW_T * NCKV_D, "the result staging area");
 
 // ---- 16 x 16 x 16 products on the warp-level tensor-core path: ldmatrix + mma.sync.m16n8k16 ----------------
 struct FragA { uint32_t r[4]; };   // A, 16 (m) x 16 (k)
@@ -117,25 +119,32 @@ __device__ __forceinline__ void load_tile(__nv_bfloat16 *dst, const __nv_bfloat1
     }
 }
 
-// One warp's 16 x 16 block of S = Q K^T and of dP = dO V^T, turned in registers into P and dS (bf16, written
-// to shared memory for the products that follow).  Queries q0 + 16 r .., keys k0 + 16 c ..
+// One warp's 16 x 32 block of S = Q K^T and of dP = dO V^T (the Q / dO fragments feed two key blocks each), turned
+// in registers into P and dS (bf16, written to shared memory for the products that follow).
+// Queries q0 + 16 r .., keys k0 + 32 c2 ..
 __device__ __forceinline__ void scores_to_p_ds(BwdSmem &sm, const BwdParams &p, const __nv_bfloat16 *tq,
                                                const __nv_bfloat16 *tdo, const __nv_bfloat16 *tk, const __nv_bfloat16 *tv,
                                                const float *lse, const float *delta, int q0, int k0, int warp, int lane) {
-    const int r = warp >> 2, c = warp & 3;
-    Acc acc_s, acc_p;
-    zero(acc_s);
-    zero(acc_p);
+    const int r = warp >> 1, c2 = warp & 1;
+    Acc acc_s[2], acc_p[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        zero(acc_s[j]);
+        zero(acc_p[j]);
+    }
 #pragma unroll
     for (int kk = 0; kk < NCKV_D / 16; ++kk) {
         FragA a_q, a_do;
-        FragB b_k, b_v;
         load_a_mk(a_q, tq + r * 16 * BW_LD + kk * 16, BW_LD, lane);
         load_a_mk(a_do, tdo + r * 16 * BW_LD + kk * 16, BW_LD, lane);
-        load_b_nk(b_k, tk + c * 16 * BW_LD + kk * 16, BW_LD, lane);  // B(k = channel, n = key) at tile[key][channel]
-        load_b_nk(b_v, tv + c * 16 * BW_LD + kk * 16, BW_LD, lane);
-        mma16(acc_s, a_q, b_k);
-        mma16(acc_p, a_do, b_v);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            FragB b_k, b_v;  // B(k = channel, n = key) at tile[key][channel]
+            load_b_nk(b_k, tk + (c2 * 2 + j) * 16 * BW_LD + kk * 16, BW_LD, lane);
+            load_b_nk(b_v, tv + (c2 * 2 + j) * 16 * BW_LD + kk * 16, BW_LD, lane);
+            mma16(acc_s[j], a_q, b_k);
+            mma16(acc_p[j], a_do, b_v);
+        }
     }
 #pragma unroll
     for (int h = 0; h < 2; ++h) {  // the thread's two rows
@@ -143,20 +152,23 @@ __device__ __forceinline__ void scores_to_p_ds(BwdSmem &sm, const BwdParams &p, 
         const int tq_ = q0 + row;
         const float lse2 = lse[row] * 1.4426950408889634f, dl = delta[row];
 #pragma unroll
-        for (int nb = 0; nb < 2; ++nb) {
-            const int col = c * 16 + 8 * nb + 2 * (lane & 3);
-            float pr[2], ds[2];
+        for (int j = 0; j < 2; ++j) {
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                const int e = nb * 4 + h * 2 + j;
-                const int tk_ = k0 + col + j;
-                const bool visible = tq_ < p.T && tk_ <= tq_ && (p.window_left < 0 || tq_ - tk_ <= p.window_left);
-                // a visible score implies a finite log-sum-exp (the row has at least this key)
-                pr[j] = visible ? exp2f(acc_s.c[e] * p.scale_log2 - lse2) : 0.f;
-                ds[j] = visible ? pr[j] * (acc_p.c[e] - dl) * p.scale : 0.f;
+            for (int nb = 0; nb < 2; ++nb) {
+                const int col = (c2 * 2 + j) * 16 + 8 * nb + 2 * (lane & 3);
+                float pr[2], ds[2];
+#pragma unroll
+                for (int x = 0; x < 2; ++x) {
+                    const int e = nb * 4 + h * 2 + x;
+                    const int tk_ = k0 + col + x;
+                    const bool visible = tq_ < p.T && tk_ <= tq_ && (p.window_left < 0 || tq_ - tk_ <= p.window_left);
+                    // a visible score implies a finite log-sum-exp (the row has at least this key)
+                    pr[x] = visible ? exp2f(acc_s[j].c[e] * p.scale_log2 - lse2) : 0.f;
+                    ds[x] = visible ? pr[x] * (acc_p[j].c[e] - dl) * p.scale : 0.f;
+                }
+                *reinterpret_cast<uint32_t *>(sm.p + row * BW_LDS + col) = pack_bf16x2(pr[0], pr[1]);
+                *reinterpret_cast<uint32_t *>(sm.ds + row * BW_LDS + col) = pack_bf16x2(ds[0], ds[1]);
             }
-            *reinterpret_cast<uint32_t *>(sm.p + row * BW_LDS + col) = pack_bf16x2(pr[0], pr[1]);
-            *reinterpret_cast<uint32_t *>(sm.ds + row * BW_LDS + col) = pack_bf16x2(ds[0], ds[1]);
         }
     }
 }
@@ -214,7 +226,7 @@ __global__ void __launch_bounds__(256) attn_bwd_delta_kernel(const __nv_bfloat16
 }
 
 // One CTA: 64 keys of one (row, kv head).  grid = (key tiles, Hkv, B)
-__global__ void __launch_bounds__(BW_THREADS) attn_bwd_dkdv_kernel(const BwdParams p) {
+__global__ void __launch_bounds__(BW_THREADS, 2) attn_bwd_dkdv_kernel(const BwdParams p) {
     extern __shared__ __align__(128) uint8_t bw_smem[];
     BwdSmem &sm = *reinterpret_cast<BwdSmem *>(bw_smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -222,71 +234,79 @@ __global__ void __launch_bounds__(BW_THREADS) attn_bwd_dkdv_kernel(const BwdPara
     const int rep = p.Hq / p.Hkv;
 
     __nv_bfloat16 *sk = sm.own[0], *sv = sm.own[1];
+    __nv_bfloat16 *sq = sm.walk[0], *sdo = sm.walk[1];
     load_tile(sk, p.k, b, k0, hkv, p.T, p.Hkv);
     load_tile(sv, p.v, b, k0, hkv, p.T, p.Hkv);
 
-    // output fragments: 4 (key blocks) x 8 (channel blocks); a warp owns channel block cb and key blocks rb, rb + 1
-    const int cb = warp & 7, rb = (warp >> 3) * 2;
-    Acc acc_dk[2], acc_dv[2];
+    // output: 4 (key blocks) x 8 (channel blocks) of 16 x 16; a warp owns key blocks rb, rb + 1 x channel blocks cb, cb + 1
+    const int cb = (warp & 3) * 2, rb = (warp >> 2) * 2;
+    Acc acc_dk[2][2], acc_dv[2][2];
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        zero(acc_dk[r]);
-        zero(acc_dv[r]);
-    }
+    for (int r = 0; r < 2; ++r)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            zero(acc_dk[r][c]);
+            zero(acc_dv[r][c]);
+        }
     // query tiles that see any of these keys: positions k0 .. (last key + window), for every q head of the group
     const int last_key = min(k0 + BW_T, p.T) - 1;
     const int q_hi = p.window_left >= 0 ? min(p.T - 1, last_key + p.window_left) : p.T - 1;
     const int per_head = (q_hi - k0) / BW_T + 1;  // causal: queries at or after the tile's first key
     const int n_iter = rep * per_head;
-    auto fetch = [&](int it) {  // iteration `it` -> stage it & 1
-        const int hq = hkv * rep + it / per_head, q0 = k0 + (it % per_head) * BW_T, st = it & 1;
-        load_tile(sm.walk[st][0], p.q, b, q0, hq, p.T, p.Hq);
-        load_tile(sm.walk[st][1], p.dout, b, q0, hq, p.T, p.Hq);
-        load_row_stats(sm.lse[st], sm.delta[st], p, b, hq, q0);
-    };
-    fetch(0);
-    cp_async_commit();
     for (int it = 0; it < n_iter; ++it) {
-        const int st = it & 1, q0 = k0 + (it % per_head) * BW_T;
-        const __nv_bfloat16 *sq = sm.walk[st][0], *sdo = sm.walk[st][1];
-        __syncthreads();  // the previous iteration's products have read the other stage, p and ds
-        if (it + 1 < n_iter) fetch(it + 1);
+        const int hq = hkv * rep + it / per_head, q0 = k0 + (it % per_head) * BW_T;
+        __syncthreads();  // the previous iteration's products have read q, dout, p and ds
+        load_tile(sq, p.q, b, q0, hq, p.T, p.Hq);
+        load_tile(sdo, p.dout, b, q0, hq, p.T, p.Hq);
+        load_row_stats(sm.lse, sm.delta, p, b, hq, q0);
         cp_async_commit();
-        cp_async_wait<1>();  // everything but the group just committed has landed (this thread's part)
+        cp_async_wait<0>();
         __syncthreads();
-        scores_to_p_ds(sm, p, sq, sdo, sk, sv, sm.lse[st], sm.delta[st], q0, k0, warp, lane);
+        scores_to_p_ds(sm, p, sq, sdo, sk, sv, sm.lse, sm.delta, q0, k0, warp, lane);
         __syncthreads();
 #pragma unroll
         for (int qq = 0; qq < BW_T / 16; ++qq) {
-            FragB b_do, b_q;  // B(k = query, n = channel) at tile[query][channel]
-            load_b_kn(b_do, sdo + qq * 16 * BW_LD + cb * 16, BW_LD, lane);
-            load_b_kn(b_q, sq + qq * 16 * BW_LD + cb * 16, BW_LD, lane);
+            FragB b_do[2], b_q[2];  // B(k = query, n = channel) at tile[query][channel]
+            FragA a_p[2], a_ds[2];  // A(m = key, k = query) at tile[query][key]
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                load_b_kn(b_do[c], sdo + qq * 16 * BW_LD + (cb + c) * 16, BW_LD, lane);
+                load_b_kn(b_q[c], sq + qq * 16 * BW_LD + (cb + c) * 16, BW_LD, lane);
+            }
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
-                FragA a_p, a_ds;  // A(m = key, k = query) at tile[query][key]
-                load_a_km(a_p, sm.p + qq * 16 * BW_LDS + (rb + r) * 16, BW_LDS, lane);
-                load_a_km(a_ds, sm.ds + qq * 16 * BW_LDS + (rb + r) * 16, BW_LDS, lane);
-                mma16(acc_dv[r], a_p, b_do);
-                mma16(acc_dk[r], a_ds, b_q);
+                load_a_km(a_p[r], sm.p + qq * 16 * BW_LDS + (rb + r) * 16, BW_LDS, lane);
+                load_a_km(a_ds[r], sm.ds + qq * 16 * BW_LDS + (rb + r) * 16, BW_LDS, lane);
             }
+#pragma unroll
+            for (int r = 0; r < 2; ++r)
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    mma16(acc_dv[r][c], a_p[r], b_do[c]);
+                    mma16(acc_dk[r][c], a_ds[r], b_q[c]);
+                }
         }
     }
     cp_async_wait<0>();
     __syncthreads();
-    float *stage = reinterpret_cast<float *>(&sm.walk[0][0][0]);
+    float *stage = reinterpret_cast<float *>(&sm.walk[0][0]);
 #pragma unroll
-    for (int r = 0; r < 2; ++r) store_acc(stage, NCKV_D, (rb + r) * 16, cb * 16, acc_dk[r], lane);
+    for (int r = 0; r < 2; ++r)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) store_acc(stage, NCKV_D, (rb + r) * 16, (cb + c) * 16, acc_dk[r][c], lane);
     __syncthreads();
     store_result(stage, p.dk, b, k0, hkv, p.T, p.Hkv);
     __syncthreads();
 #pragma unroll
-    for (int r = 0; r < 2; ++r) store_acc(stage, NCKV_D, (rb + r) * 16, cb * 16, acc_dv[r], lane);
+    for (int r = 0; r < 2; ++r)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) store_acc(stage, NCKV_D, (rb + r) * 16, (cb + c) * 16, acc_dv[r][c], lane);
     __syncthreads();
     store_result(stage, p.dv, b, k0, hkv, p.T, p.Hkv);
 }
 
 // One CTA: 64 queries of one (row, q head).  grid = (query tiles, Hq, B)
-__global__ void __launch_bounds__(BW_THREADS) attn_bwd_dq_kernel(const BwdParams p) {
+__global__ void __launch_bounds__(BW_THREADS, 2) attn_bwd_dq_kernel(const BwdParams p) {
     extern __shared__ __align__(128) uint8_t bw_smem[];
     BwdSmem &sm = *reinterpret_cast<BwdSmem *>(bw_smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -295,52 +315,52 @@ __global__ void __launch_bounds__(BW_THREADS) attn_bwd_dq_kernel(const BwdParams
     const int hkv = hq / (p.Hq / p.Hkv);
 
     __nv_bfloat16 *sq = sm.own[0], *sdo = sm.own[1];
+    __nv_bfloat16 *sk = sm.walk[0], *sv = sm.walk[1];
     load_tile(sq, p.q, b, q0, hq, p.T, p.Hq);
     load_tile(sdo, p.dout, b, q0, hq, p.T, p.Hq);
-    load_row_stats(sm.lse[0], sm.delta[0], p, b, hq, q0);
+    load_row_stats(sm.lse, sm.delta, p, b, hq, q0);
 
-    const int cb = warp & 7, rb = (warp >> 3) * 2;  // channel block and the first of this warp's two query blocks
-    Acc acc_dq[2];
+    // output: 4 (query blocks) x 8 (channel blocks); a warp owns query blocks rb, rb + 1 x channel blocks cb, cb + 1
+    const int cb = (warp & 3) * 2, rb = (warp >> 2) * 2;
+    Acc acc_dq[2][2];
 #pragma unroll
-    for (int r = 0; r < 2; ++r) zero(acc_dq[r]);
+    for (int r = 0; r < 2; ++r)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) zero(acc_dq[r][c]);
 
     const int last_q = min(q0 + BW_T, p.T) - 1;
     int k_lo = p.window_left >= 0 ? max(0, q0 - p.window_left) : 0;
     k_lo -= k_lo % BW_T;
-    const int n_iter = (last_q - k_lo) / BW_T + 1;
-    auto fetch = [&](int it) {
-        load_tile(sm.walk[it & 1][0], p.k, b, k_lo + it * BW_T, hkv, p.T, p.Hkv);
-        load_tile(sm.walk[it & 1][1], p.v, b, k_lo + it * BW_T, hkv, p.T, p.Hkv);
-    };
-    fetch(0);
-    cp_async_commit();
-    for (int it = 0; it < n_iter; ++it) {
-        const int k0 = k_lo + it * BW_T;
-        const __nv_bfloat16 *sk = sm.walk[it & 1][0], *sv = sm.walk[it & 1][1];
-        __syncthreads();  // the previous iteration's product has read the other stage and ds
-        if (it + 1 < n_iter) fetch(it + 1);
+    for (int k0 = k_lo; k0 <= last_q; k0 += BW_T) {
+        __syncthreads();  // the previous iteration's product has read k and ds
+        load_tile(sk, p.k, b, k0, hkv, p.T, p.Hkv);
+        load_tile(sv, p.v, b, k0, hkv, p.T, p.Hkv);
         cp_async_commit();
-        cp_async_wait<1>();
+        cp_async_wait<0>();
         __syncthreads();
-        scores_to_p_ds(sm, p, sq, sdo, sk, sv, sm.lse[0], sm.delta[0], q0, k0, warp, lane);
+        scores_to_p_ds(sm, p, sq, sdo, sk, sv, sm.lse, sm.delta, q0, k0, warp, lane);
         __syncthreads();
 #pragma unroll
         for (int kk = 0; kk < BW_T / 16; ++kk) {
-            FragB b_k;  // B(k = key, n = channel) at tile[key][channel]
-            load_b_kn(b_k, sk + kk * 16 * BW_LD + cb * 16, BW_LD, lane);
+            FragB b_k[2];   // B(k = key, n = channel) at tile[key][channel]
+            FragA a_ds[2];  // A(m = query, k = key) at tile[query][key]
 #pragma unroll
-            for (int r = 0; r < 2; ++r) {
-                FragA a_ds;  // A(m = query, k = key) at tile[query][key]
-                load_a_mk(a_ds, sm.ds + (rb + r) * 16 * BW_LDS + kk * 16, BW_LDS, lane);
-                mma16(acc_dq[r], a_ds, b_k);
-            }
+            for (int c = 0; c < 2; ++c) load_b_kn(b_k[c], sk + kk * 16 * BW_LD + (cb + c) * 16, BW_LD, lane);
+#pragma unroll
+            for (int r = 0; r < 2; ++r) load_a_mk(a_ds[r], sm.ds + (rb + r) * 16 * BW_LDS + kk * 16, BW_LDS, lane);
+#pragma unroll
+            for (int r = 0; r < 2; ++r)
+#pragma unroll
+                for (int c = 0; c < 2; ++c) mma16(acc_dq[r][c], a_ds[r], b_k[c]);
         }
     }
     cp_async_wait<0>();
     __syncthreads();
-    float *stage = reinterpret_cast<float *>(&sm.walk[0][0][0]);
+    float *stage = reinterpret_cast<float *>(&sm.walk[0][0]);
 #pragma unroll
-    for (int r = 0; r < 2; ++r) store_acc(stage, NCKV_D, (rb + r) * 16, cb * 16, acc_dq[r], lane);
+    for (int r = 0; r < 2; ++r)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) store_acc(stage, NCKV_D, (rb + r) * 16, (cb + c) * 16, acc_dq[r][c], lane);
     __syncthreads();
     store_result(stage, p.dq, b, q0, hq, p.T, p.Hq);
 }
