@@ -626,3 +626,40 @@ def test_p2p_wait_runs_out_and_reports_instead_of_hanging():
     torch.cuda.synchronize()
     assert status.item() == 0
     assert torch.allclose(out.float(), send[:rows * 128].view(rows, 128).to(BF).float(), atol=1e-2, rtol=1e-2)
+
+
+def test_prefill_attention_random_shapes_match_fp32_and_repeat_bit_for_bit():
+    """Sixty random (rows, tokens, heads, window, cached prefix, capacity) combinations of the dense kernel against
+    an fp32 masked softmax of the same bf16 inputs (1e-2 of the largest output), each run twice: a persistent kernel
+    with several asynchronous roles must return the same bytes every time."""
+    import math
+    import random
+    rng = random.Random(0)
+    for case in range(60):
+        B = rng.choice([1, 2, 3, 5])
+        T = rng.choice([1, 2, 7, 64, 100, 128, 129, 255, 256, 300, 511, 700, 1000, 1537])
+        Hkv = rng.choice([1, 2, 4])
+        Hq = Hkv * rng.choice([1, 2, 4])
+        window = rng.choice([-1, -1, 0, 5, 63, 64, 200, 1024])
+        prefix = rng.choice([0, 0, 1, 17, 128, 333])
+        lens = torch.tensor([rng.randint(0, prefix) for _ in range(B)], dtype=torch.int32, device=DEV)
+        Tk = int(lens.max()) + T + rng.choice([0, 3, 64])
+        gen = torch.Generator(device=DEV).manual_seed(case)
+        q = torch.randn(B, T, Hq, 128, generator=gen, device=DEV).to(BF)
+        k = torch.randn(B, Tk, Hkv, 128, generator=gen, device=DEV).to(BF)
+        v = torch.randn(B, Tk, Hkv, 128, generator=gen, device=DEV).to(BF)
+        first = ops().prefill_attention(q, k, v, lens, window)
+        second = ops().prefill_attention(q, k, v, lens, window)
+        kf = k.float().repeat_interleave(Hq // Hkv, 2)
+        vf = v.float().repeat_interleave(Hq // Hkv, 2)
+        s = torch.einsum("bthd,bshd->bhts", q.float(), kf) / math.sqrt(128)
+        pos = lens.view(B, 1) + torch.arange(T, device=DEV).view(1, T)
+        key = torch.arange(Tk, device=DEV).view(1, 1, Tk)
+        mask = key <= pos.unsqueeze(-1)
+        if window >= 0:
+            mask &= (pos.unsqueeze(-1) - key) <= window
+        ref = torch.einsum("bhts,bshd->bthd", torch.softmax(s.masked_fill(~mask.unsqueeze(1), float("-inf")), -1), vf)
+        what = dict(case=case, B=B, T=T, Hq=Hq, Hkv=Hkv, window=window, prefix=prefix, Tk=Tk)
+        assert torch.equal(bits(first), bits(second)), what
+        assert (first.float() - ref).abs().max() <= 1e-2 * ref.abs().max(), what
+    assert ops().read_status(DEV) == 0
