@@ -1,203 +1,53 @@
-// Backward of flash_attn_func (training): dq, dk, dv of causal / sliding-window attention over plain
-// (B, T, H, D) tensors, from q, k, v, the forward output, its gradient and the forward's log-sum-exp.
+// Backward of flash_attn_func (causal, optional sliding window, GQA) on the 5th-generation tensor cores.
 //
-//   P  = exp(scale * Q K^T - lse)            (recomputed per tile, never stored)
-//   dV = P^T dO
-//   dP = dO V^T,   delta = rowsum(dO * O),   dS = P * (dP - delta)
-//   dQ = scale * dS K,    dK = scale * dS^T Q
+//   delta[b, h, t] = sum_c dO * O                                       (attn_bwd_delta_kernel)
+//   P = exp(S / sqrt(D) - lse),  dP = dO V^T,  dS = P o (dP - delta) / sqrt(D)
+//   dV = P^T dO,  dK = dS^T Q                                          (attn_bwd_dkdv_kernel: one CTA per 128 keys)
+//   dQ = dS K                                                           (attn_bwd_dq_kernel:   one CTA per 128 queries)
 //
-// Three kernels.  `delta` is one warp per (row, token, head).  The dK/dV kernel gives a CTA one tile
-// of 64 keys of one (row, kv head) and walks the query tiles (of every q head of the group) that see
-// them; the dQ kernel gives a CTA one tile of 64 queries of one (row, q head) and walks its key
-// tiles.  Scores are recomputed in both (7 matrix products per tile pair instead of 5) so that no
-// gradient needs atomics: results do not depend on scheduling.  The products run on the warp-level
-// tensor-core path (ldmatrix + mma.sync.m16n8k16 bf16, fp32 accumulation) with operands staged in shared
-// memory by cp.async; P and dS are formed in registers from the score accumulators.  The kernels are bound by
-// shared-memory operand fetches, so a warp owns 2 x 2 blocks of 16 x 16 of each gradient (every fragment it loads
-// feeds two products) and two CTAs of 8 warps share an SM.  This is a first,
-// correct version: it makes no claim on the tcgen05 roofline.
+// Scores and probabilities are recomputed from q, k and the forward's log-sum-exp; nothing is accumulated
+// with atomics, so the gradients are the same bits on every run.  Both kernels follow the forward kernel's
+// forms: operands arrive by TMA into 128-byte-swizzled shared memory, tcgen05.mma accumulates in tensor memory,
+// one thread issues copies and products, four warps (one thread per accumulator row) do the elementwise work
+// between the two groups of products and write P / dS back to tensor memory as bf16 over the scores they came
+// from, where the second group of products reads them as its A operand.
 //
-// Replaces: autograd through F.scaled_dot_product_attention as reached from flash_attn_func
-// (flash_attention.py:107-128, caller gpt.py:108) when training.
+//   dK/dV kernel   the CTA owns K_j, V_j (128 keys) and walks the query blocks i that see them, for every q head
+//                  of the kv head.  Per step:  S^T = K_j Q_i^T and dP^T = V_j dO_i^T (accumulator rows = keys),
+//                  elementwise over a key's row (lse and delta of the 128 queries come from shared memory),
+//                  dV += P^T dO_i and dK += dS^T Q_i.  Tensor memory: S^T, dP^T, dV, dK = 4 x 128 columns.
+//   dQ kernel      the CTA owns Q_i, dO_i (128 queries of one q head) and walks the key blocks j it sees.  Per step:
+//                  S = Q_i K_j^T and dP = dO_i V_j^T (accumulator rows = queries, lse and delta are per thread),
+//                  dQ += dS K_j.  Tensor memory: S, dP, dQ.
+// The walked operands are double-buffered; the copies of step it + 1 are issued as soon as the products of
+// step it - 1 have completed.  Every barrier wait is bounded; a wait that runs out sets NCKV_ST_TIMEOUT in the
+// status word, the CTA stops issuing work, frees its tensor memory and returns.
+//
+// Replaces: the backward of F.scaled_dot_product_attention / flash_attn_func as reached from
+// flash_attention.py:107-128 during training (gpt.py:108).
 #include <math.h>
 
 #include "nckv_common.cuh"
+#include "tc05.cuh"
 
 namespace nckv {
 
-constexpr int BW_T = 64;             // queries and keys per tile
-constexpr int BW_THREADS = 256;      // 8 warps; two CTAs per SM overlap each other's barrier-separated phases
-constexpr int BW_LD = NCKV_D + 8;    // bf16 row stride of the 64 x 128 operand tiles (272 B: ldmatrix without bank conflicts)
-constexpr int BW_LDS = BW_T + 8;     // bf16 row stride of the 64 x 64 P and dS tiles (144 B)
+constexpr int BT = 128;                        // keys per dK/dV CTA, queries per dQ CTA, and the walked block
+constexpr int BT_TILE_BYTES = BT * NCKV_D * 2;  // 32 KB: two 64-channel halves of [128][128 B]
+constexpr int BT_HALF = BT_TILE_BYTES / 2;
+constexpr int BT_THREADS = 160;                // 4 elementwise warps + the warp whose lane 0 issues copies and products
+constexpr int BT_TMEM_COLS = 512;
+constexpr unsigned long long BT_WAIT_LIMIT = NCKV_WAIT_LIMIT_NS;
 
 struct BwdParams {
-    const __nv_bfloat16 *q, *k, *v, *dout;
-    const float *lse, *delta;
+    const float *lse;    // (B, Hq, T) natural log-sum-exp of the forward
+    const float *delta;  // (B, Hq, T)
     __nv_bfloat16 *dq, *dk, *dv;
-    int B, T, Hq, Hkv;
+    int32_t *status;
+    int B, T, Hq, Hkv, n_blocks;
     int window_left;
     float scale, scale_log2;
 };
-
-// The tiles a CTA keeps for its whole life (`own`) and the tiles it walks (`walk`, refilled with cp.async every
-// iteration; 89 KB in all, so that two CTAs share an SM and one computes while the other waits for its copies).
-// dK/dV kernel: own = K, V; walk = Q, dO and their row statistics.  dQ kernel: own = Q, dO and the statistics; walk = K, V.
-struct BwdSmem {
-    __nv_bfloat16 own[2][BW_T * BW_LD];
-    __nv_bfloat16 walk[2][BW_T * BW_LD];  // [tile]; after the loop: staging of a 64 x 128 fp32 result
-    __nv_bfloat16 p[BW_T * BW_LDS];
-    __nv_bfloat16 ds[BW_T * BW_LDS];
-    float lse[BW_T];    // natural-log log-sum-exp of the rows
-    float delta[BW_T];
-};
-static_assert(sizeof(__nv_bfloat16) * 2 * BW_T * BW_LD >= sizeof(float) * BW_T * NCKV_D, "the result staging area");
-
-// ---- 16 x 16 x 16 products on the warp-level tensor-core path: ldmatrix + mma.sync.m16n8k16 ----------------
-struct FragA { uint32_t r[4]; };   // A, 16 (m) x 16 (k)
-struct FragB { uint32_t r[4]; };   // B, 16 (k) x 16 (n): r[0], r[1] for n 0..7, r[2], r[3] for n 8..15
-struct Acc { float c[8]; };        // 16 x 16 fp32: c[0..3] columns 0..7, c[4..7] columns 8..15
-// element e of Acc sits at row (lane / 4) + 8 * ((e >> 1) & 1), column 8 * (e >> 2) + 2 * (lane % 4) + (e & 1)
-
-__device__ __forceinline__ void load_a_mk(FragA &f, const __nv_bfloat16 *base, int ld, int lane) {  // A(m,k) at base[m ld + k]
-    const __nv_bfloat16 *ptr = base + ((lane & 7) + ((lane >> 3) & 1) * 8) * ld + (lane >> 4) * 8;
-    ldmatrix_x4(f.r[0], f.r[1], f.r[2], f.r[3], smem_u32(ptr));
-}
-__device__ __forceinline__ void load_a_km(FragA &f, const __nv_bfloat16 *base, int ld, int lane) {  // A(m,k) at base[k ld + m]
-    const int i = lane >> 3, j = lane & 7;
-    const __nv_bfloat16 *ptr = base + ((i >> 1) * 8 + j) * ld + (i & 1) * 8;
-    ldmatrix_x4_trans(f.r[0], f.r[1], f.r[2], f.r[3], smem_u32(ptr));
-}
-__device__ __forceinline__ void load_b_nk(FragB &f, const __nv_bfloat16 *base, int ld, int lane) {  // B(k,n) at base[n ld + k]
-    const int i = lane >> 3, j = lane & 7;
-    const __nv_bfloat16 *ptr = base + ((i >> 1) * 8 + j) * ld + (i & 1) * 8;
-    ldmatrix_x4(f.r[0], f.r[1], f.r[2], f.r[3], smem_u32(ptr));
-}
-__device__ __forceinline__ void load_b_kn(FragB &f, const __nv_bfloat16 *base, int ld, int lane) {  // B(k,n) at base[k ld + n]
-    const int i = lane >> 3, j = lane & 7;
-    const __nv_bfloat16 *ptr = base + ((i & 1) * 8 + j) * ld + (i >> 1) * 8;
-    ldmatrix_x4_trans(f.r[0], f.r[1], f.r[2], f.r[3], smem_u32(ptr));
-}
-__device__ __forceinline__ void mma16(Acc &d, const FragA &a, const FragB &b) {
-    mma_bf16_16816(d.c[0], d.c[1], d.c[2], d.c[3], a.r[0], a.r[1], a.r[2], a.r[3], b.r[0], b.r[1]);
-    mma_bf16_16816(d.c[4], d.c[5], d.c[6], d.c[7], a.r[0], a.r[1], a.r[2], a.r[3], b.r[2], b.r[3]);
-}
-__device__ __forceinline__ void zero(Acc &d) {
-#pragma unroll
-    for (int e = 0; e < 8; ++e) d.c[e] = 0.f;
-}
-// fp32 accumulator block (rows r0.., columns c0..) into a row-major fp32 array
-__device__ __forceinline__ void store_acc(float *dst, int ld, int r0, int c0, const Acc &d, int lane) {
-#pragma unroll
-    for (int e = 0; e < 8; e += 2) {
-        const int row = r0 + (lane >> 2) + 8 * ((e >> 1) & 1), col = c0 + 8 * (e >> 2) + 2 * (lane & 3);
-        *reinterpret_cast<float2 *>(dst + row * ld + col) = make_float2(d.c[e], d.c[e + 1]);
-    }
-}
-
-// Asynchronous copies (cp.async): `bytes` of the source are copied, the rest of the 16 or 4 bytes is zero-filled.
-__device__ __forceinline__ void cp_async_16(void *dst, const void *src, int bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_4(void *dst, const void *src, int bytes) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-
-// 64 rows x 256 bytes of a (B, T, H, D) tensor into a padded shared-memory tile, asynchronously; rows at or
-// beyond T are zero-filled (the source address is clamped to a valid row, no byte of it is read).
-__device__ __forceinline__ void load_tile(__nv_bfloat16 *dst, const __nv_bfloat16 *src, int b, int t0, int h, int T,
-                                          int H) {
-    for (int i = threadIdx.x; i < BW_T * (NCKV_D / 8); i += BW_THREADS) {
-        const int r = i / (NCKV_D / 8), c = i % (NCKV_D / 8);
-        const int t = t0 + r;
-        const int tc = t < T ? t : T - 1;
-        cp_async_16(dst + r * BW_LD + c * 8, src + (((long long)b * T + tc) * H + h) * NCKV_D + c * 8, t < T ? 16 : 0);
-    }
-}
-
-// One warp's 16 x 32 block of S = Q K^T and of dP = dO V^T (the Q / dO fragments feed two key blocks each), turned
-// in registers into P and dS (bf16, written to shared memory for the products that follow).
-// Queries q0 + 16 r .., keys k0 + 32 c2 ..
-__device__ __forceinline__ void scores_to_p_ds(BwdSmem &sm, const BwdParams &p, const __nv_bfloat16 *tq,
-                                               const __nv_bfloat16 *tdo, const __nv_bfloat16 *tk, const __nv_bfloat16 *tv,
-                                               const float *lse, const float *delta, int q0, int k0, int warp, int lane) {
-    const int r = warp >> 1, c2 = warp & 1;
-    Acc acc_s[2], acc_p[2];
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-        zero(acc_s[j]);
-        zero(acc_p[j]);
-    }
-#pragma unroll
-    for (int kk = 0; kk < NCKV_D / 16; ++kk) {
-        FragA a_q, a_do;
-        load_a_mk(a_q, tq + r * 16 * BW_LD + kk * 16, BW_LD, lane);
-        load_a_mk(a_do, tdo + r * 16 * BW_LD + kk * 16, BW_LD, lane);
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            FragB b_k, b_v;  // B(k = channel, n = key) at tile[key][channel]
-            load_b_nk(b_k, tk + (c2 * 2 + j) * 16 * BW_LD + kk * 16, BW_LD, lane);
-            load_b_nk(b_v, tv + (c2 * 2 + j) * 16 * BW_LD + kk * 16, BW_LD, lane);
-            mma16(acc_s[j], a_q, b_k);
-            mma16(acc_p[j], a_do, b_v);
-        }
-    }
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {  // the thread's two rows
-        const int row = r * 16 + (lane >> 2) + 8 * h;
-        const int tq_ = q0 + row;
-        const float lse2 = lse[row] * 1.4426950408889634f, dl = delta[row];
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-#pragma unroll
-            for (int nb = 0; nb < 2; ++nb) {
-                const int col = (c2 * 2 + j) * 16 + 8 * nb + 2 * (lane & 3);
-                float pr[2], ds[2];
-#pragma unroll
-                for (int x = 0; x < 2; ++x) {
-                    const int e = nb * 4 + h * 2 + x;
-                    const int tk_ = k0 + col + x;
-                    const bool visible = tq_ < p.T && tk_ <= tq_ && (p.window_left < 0 || tq_ - tk_ <= p.window_left);
-                    // a visible score implies a finite log-sum-exp (the row has at least this key)
-                    pr[x] = visible ? exp2f(acc_s[j].c[e] * p.scale_log2 - lse2) : 0.f;
-                    ds[x] = visible ? pr[x] * (acc_p[j].c[e] - dl) * p.scale : 0.f;
-                }
-                *reinterpret_cast<uint32_t *>(sm.p + row * BW_LDS + col) = pack_bf16x2(pr[0], pr[1]);
-                *reinterpret_cast<uint32_t *>(sm.ds + row * BW_LDS + col) = pack_bf16x2(ds[0], ds[1]);
-            }
-        }
-    }
-}
-
-__device__ __forceinline__ void load_row_stats(float *lse, float *delta, const BwdParams &p, int b, int hq, int q0) {
-    for (int r = threadIdx.x; r < BW_T; r += BW_THREADS) {
-        const int t = q0 + r;
-        const long long o = ((long long)b * p.Hq + hq) * p.T + (t < p.T ? t : p.T - 1);
-        cp_async_4(lse + r, p.lse + o, t < p.T ? 4 : 0);
-        cp_async_4(delta + r, p.delta + o, t < p.T ? 4 : 0);
-    }
-}
-
-// fp32 64 x 128 result in the staging area -> bf16 rows of a (B, T, H, D) tensor
-__device__ __forceinline__ void store_result(const float *stage, __nv_bfloat16 *dst, int b, int t0, int h, int T,
-                                             int H) {
-    for (int i = threadIdx.x; i < BW_T * (NCKV_D / 8); i += BW_THREADS) {
-        const int r = i / (NCKV_D / 8), c = i % (NCKV_D / 8);
-        const int t = t0 + r;
-        if (t >= T) continue;
-        const float *src = stage + r * NCKV_D + c * 8;
-        uint4 val;
-        val.x = pack_bf16x2(src[0], src[1]);
-        val.y = pack_bf16x2(src[2], src[3]);
-        val.z = pack_bf16x2(src[4], src[5]);
-        val.w = pack_bf16x2(src[6], src[7]);
-        *reinterpret_cast<uint4 *>(dst + (((long long)b * T + t) * H + h) * NCKV_D + c * 8) = val;
-    }
-}
 
 // delta[b, h, t] = sum_c dO[b, t, h, c] * O[b, t, h, c]
 __global__ void __launch_bounds__(256) attn_bwd_delta_kernel(const __nv_bfloat16 *out, const __nv_bfloat16 *dout,
@@ -225,150 +75,402 @@ __global__ void __launch_bounds__(256) attn_bwd_delta_kernel(const __nv_bfloat16
     }
 }
 
-// One CTA: 64 keys of one (row, kv head).  grid = (key tiles, Hkv, B)
-__global__ void __launch_bounds__(BW_THREADS, 2) attn_bwd_dkdv_kernel(const BwdParams p) {
-    extern __shared__ __align__(128) uint8_t bw_smem[];
-    BwdSmem &sm = *reinterpret_cast<BwdSmem *>(bw_smem);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int k0 = blockIdx.x * BW_T, hkv = blockIdx.y, b = blockIdx.z;
-    const int rep = p.Hq / p.Hkv;
-
-    __nv_bfloat16 *sk = sm.own[0], *sv = sm.own[1];
-    __nv_bfloat16 *sq = sm.walk[0], *sdo = sm.walk[1];
-    load_tile(sk, p.k, b, k0, hkv, p.T, p.Hkv);
-    load_tile(sv, p.v, b, k0, hkv, p.T, p.Hkv);
-
-    // output: 4 (key blocks) x 8 (channel blocks) of 16 x 16; a warp owns key blocks rb, rb + 1 x channel blocks cb, cb + 1
-    const int cb = (warp & 3) * 2, rb = (warp >> 2) * 2;
-    Acc acc_dk[2][2], acc_dv[2][2];
+// ---- pieces shared by the two kernels -------------------------------------------------------------------
+// 128 x 128 x 128 product with both operands K-major in shared memory (rows x channels tiles): D = A B^T.
+__device__ __forceinline__ void bt_mma_ss(uint32_t d_tmem, uint64_t desc_a, uint64_t desc_b) {
+    constexpr uint32_t IDESC = umma_idesc(BT, BT, 0, 0);
 #pragma unroll
-    for (int r = 0; r < 2; ++r)
+    for (int kk = 0; kk < NCKV_D / 16; ++kk) {
+        const uint64_t off = (uint64_t)(((kk >> 2) * BT_HALF + (kk & 3) * 32) >> 4);
+        umma_bf16(d_tmem, desc_a + off, desc_b + off, IDESC, kk > 0 ? 1u : 0u);
+    }
+}
+// D (+)= A B with A (128 rows x 128 bf16 = 64 columns) in tensor memory and B a rows x channels tile used in
+// place as an MN-major operand: the contraction runs over the tile's 128 rows, 16 per instruction.
+__device__ __forceinline__ void bt_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t desc_b_mn, bool accumulate) {
+    constexpr uint32_t IDESC = umma_idesc(BT, NCKV_D, 0, 1);
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-            zero(acc_dk[r][c]);
-            zero(acc_dv[r][c]);
-        }
-    // query tiles that see any of these keys: positions k0 .. (last key + window), for every q head of the group
-    const int last_key = min(k0 + BW_T, p.T) - 1;
-    const int q_hi = p.window_left >= 0 ? min(p.T - 1, last_key + p.window_left) : p.T - 1;
-    const int per_head = (q_hi - k0) / BW_T + 1;  // causal: queries at or after the tile's first key
-    const int n_iter = rep * per_head;
-    for (int it = 0; it < n_iter; ++it) {
-        const int hq = hkv * rep + it / per_head, q0 = k0 + (it % per_head) * BW_T;
-        __syncthreads();  // the previous iteration's products have read q, dout, p and ds
-        load_tile(sq, p.q, b, q0, hq, p.T, p.Hq);
-        load_tile(sdo, p.dout, b, q0, hq, p.T, p.Hq);
-        load_row_stats(sm.lse, sm.delta, p, b, hq, q0);
-        cp_async_commit();
-        cp_async_wait<0>();
-        __syncthreads();
-        scores_to_p_ds(sm, p, sq, sdo, sk, sv, sm.lse, sm.delta, q0, k0, warp, lane);
-        __syncthreads();
+    for (int ks = 0; ks < BT / 16; ++ks)
+        umma_bf16_a_tmem(d_tmem, a_tmem + (uint32_t)ks * 8, desc_b_mn + (uint64_t)((ks * 16 * 128) >> 4), IDESC,
+                         (accumulate || ks > 0) ? 1u : 0u);
+}
+__device__ __forceinline__ void bt_load_tile(uint8_t *dst, const CUtensorMap *map, uint64_t *bar, int head, int tok0, int b) {
+    tma_load_4d(dst, map, bar, 0, head, tok0, b);
+    tma_load_4d(dst + BT_HALF, map, bar, 64, head, tok0, b);
+}
+// One accumulator row (128 fp32 columns starting at `taddr`) -> 128 bf16 at `dst` (32-byte aligned).
+__device__ __forceinline__ void bt_store_row(uint32_t taddr, __nv_bfloat16 *dst, bool live) {
 #pragma unroll
-        for (int qq = 0; qq < BW_T / 16; ++qq) {
-            FragB b_do[2], b_q[2];  // B(k = query, n = channel) at tile[query][channel]
-            FragA a_p[2], a_ds[2];  // A(m = key, k = query) at tile[query][key]
+    for (int ch = 0; ch < 2; ++ch) {
+        float c[64];
+        tmem_ld64(taddr + ch * 64, c);
+        if (live) {
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                load_b_kn(b_do[c], sdo + qq * 16 * BW_LD + (cb + c) * 16, BW_LD, lane);
-                load_b_kn(b_q[c], sq + qq * 16 * BW_LD + (cb + c) * 16, BW_LD, lane);
+            for (int i = 0; i < 4; ++i) {
+                uint32_t w[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) w[e] = pack_bf16x2(c[16 * i + 2 * e], c[16 * i + 2 * e + 1]);
+                st_global_v8(reinterpret_cast<uint4 *>(dst) + (ch * 4 + i) * 2, w);
             }
-#pragma unroll
-            for (int r = 0; r < 2; ++r) {
-                load_a_km(a_p[r], sm.p + qq * 16 * BW_LDS + (rb + r) * 16, BW_LDS, lane);
-                load_a_km(a_ds[r], sm.ds + qq * 16 * BW_LDS + (rb + r) * 16, BW_LDS, lane);
-            }
-#pragma unroll
-            for (int r = 0; r < 2; ++r)
-#pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    mma16(acc_dv[r][c], a_p[r], b_do[c]);
-                    mma16(acc_dk[r][c], a_ds[r], b_q[c]);
-                }
         }
     }
-    cp_async_wait<0>();
-    __syncthreads();
-    float *stage = reinterpret_cast<float *>(&sm.walk[0][0]);
-#pragma unroll
-    for (int r = 0; r < 2; ++r)
-#pragma unroll
-        for (int c = 0; c < 2; ++c) store_acc(stage, NCKV_D, (rb + r) * 16, (cb + c) * 16, acc_dk[r][c], lane);
-    __syncthreads();
-    store_result(stage, p.dk, b, k0, hkv, p.T, p.Hkv);
-    __syncthreads();
-#pragma unroll
-    for (int r = 0; r < 2; ++r)
-#pragma unroll
-        for (int c = 0; c < 2; ++c) store_acc(stage, NCKV_D, (rb + r) * 16, (cb + c) * 16, acc_dv[r][c], lane);
-    __syncthreads();
-    store_result(stage, p.dv, b, k0, hkv, p.T, p.Hkv);
 }
 
-// One CTA: 64 queries of one (row, q head).  grid = (query tiles, Hq, B)
-__global__ void __launch_bounds__(BW_THREADS, 2) attn_bwd_dq_kernel(const BwdParams p) {
-    extern __shared__ __align__(128) uint8_t bw_smem[];
-    BwdSmem &sm = *reinterpret_cast<BwdSmem *>(bw_smem);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // longest tiles first: the last query tile sees the most keys
-    const int q0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * BW_T, hq = blockIdx.y, b = blockIdx.z;
-    const int hkv = hq / (p.Hq / p.Hkv);
+struct BtShared {  // behind the operand tiles
+    uint64_t bar_own, bar_walk[2], bar_s, bar_p, bar_d;
+    uint32_t tmem_slot;
+    int abort_flag;
+    float lse2[2][BT], delta[2][BT];  // dK/dV kernel: the walked queries' values, one per accumulator column
+};
+constexpr int BT_SMEM_BYTES = 6 * BT_TILE_BYTES + (int)sizeof(BtShared);
 
-    __nv_bfloat16 *sq = sm.own[0], *sdo = sm.own[1];
-    __nv_bfloat16 *sk = sm.walk[0], *sv = sm.walk[1];
-    load_tile(sq, p.q, b, q0, hq, p.T, p.Hq);
-    load_tile(sdo, p.dout, b, q0, hq, p.T, p.Hq);
-    load_row_stats(sm.lse, sm.delta, p, b, hq, q0);
+// grid: (key blocks x Hkv x B), heaviest key blocks (most query blocks to walk) first
+__global__ void __launch_bounds__(BT_THREADS, 1)
+attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                     const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
+                     const BwdParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    if ((smem_u32(smem) & 1023u) != 0) {  // uniform; checked rather than assumed
+        if (threadIdx.x == 0) atomicOr(p.status, (int)NCKV_ST_TIMEOUT);
+        return;
+    }
+    uint8_t *sK = smem, *sV = smem + BT_TILE_BYTES;
+    uint8_t *sWalk = smem + 2 * BT_TILE_BYTES;  // [2][Q tile, dO tile]
+    BtShared &sh = *reinterpret_cast<BtShared *>(smem + 6 * BT_TILE_BYTES);
 
-    // output: 4 (query blocks) x 8 (channel blocks); a warp owns query blocks rb, rb + 1 x channel blocks cb, cb + 1
-    const int cb = (warp & 3) * 2, rb = (warp >> 2) * 2;
-    Acc acc_dq[2][2];
-#pragma unroll
-    for (int r = 0; r < 2; ++r)
-#pragma unroll
-        for (int c = 0; c < 2; ++c) zero(acc_dq[r][c]);
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int pairs = p.B * p.Hkv;
+    const int jb = blockIdx.x / pairs;  // key blocks in ascending order: the first ones walk the most query blocks
+    const int hkv = (blockIdx.x % pairs) % p.Hkv, b = (blockIdx.x % pairs) / p.Hkv;
+    const int k0 = jb * BT;
+    const int rep = p.Hq / p.Hkv;
+    // query blocks that see a key of this block: causal from the diagonal on, up to the window's reach
+    const int i_lo = jb;
+    const int i_hi = p.window_left >= 0 ? min(p.n_blocks - 1, (k0 + BT - 1 + p.window_left) / BT) : p.n_blocks - 1;
+    const int per_head = i_hi - i_lo + 1;
+    const int n_it = per_head * rep;  // >= 1
 
-    const int last_q = min(q0 + BW_T, p.T) - 1;
-    int k_lo = p.window_left >= 0 ? max(0, q0 - p.window_left) : 0;
-    k_lo -= k_lo % BW_T;
-    for (int k0 = k_lo; k0 <= last_q; k0 += BW_T) {
-        __syncthreads();  // the previous iteration's product has read k and ds
-        load_tile(sk, p.k, b, k0, hkv, p.T, p.Hkv);
-        load_tile(sv, p.v, b, k0, hkv, p.T, p.Hkv);
-        cp_async_commit();
-        cp_async_wait<0>();
-        __syncthreads();
-        scores_to_p_ds(sm, p, sq, sdo, sk, sv, sm.lse, sm.delta, q0, k0, warp, lane);
-        __syncthreads();
+    if (tid == 0) {
+        prefetch_tensormap(&tmap_q);
+        prefetch_tensormap(&tmap_k);
+        prefetch_tensormap(&tmap_v);
+        prefetch_tensormap(&tmap_do);
+        mbar_init(&sh.bar_own, 1);
+        mbar_init(&sh.bar_walk[0], 1);
+        mbar_init(&sh.bar_walk[1], 1);
+        mbar_init(&sh.bar_s, 1);
+        mbar_init(&sh.bar_p, 4);
+        mbar_init(&sh.bar_d, 1);
+        sh.abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 0) {
+        tmem_alloc(&sh.tmem_slot, BT_TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = sh.tmem_slot;
+    const uint32_t tmem_s = tmem_base, tmem_dp = tmem_base + 128, tmem_dv = tmem_base + 256, tmem_dk = tmem_base + 384;
+    volatile int *abort_flag = &sh.abort_flag;
+    auto timed_out = [&]() {
+        *abort_flag = 1;
+        atomicOr(p.status, (int)NCKV_ST_TIMEOUT);
+    };
+
+    if (warp == 4) {
+        // =============== one thread issues the copies and the products ===============================
+        if ((tid & 31) == 0) {
+            const uint64_t desc_k = smem_desc_sw128(smem_u32(sK), 16, 1024);
+            const uint64_t desc_v = smem_desc_sw128(smem_u32(sV), 16, 1024);
+            auto load_walk = [&](int it) {
+                const int hq = hkv * rep + it / per_head, i = i_lo + it % per_head;
+                uint8_t *dst = sWalk + (it & 1) * 2 * BT_TILE_BYTES;
+                mbar_arrive_expect_tx(&sh.bar_walk[it & 1], 2 * BT_TILE_BYTES);
+                bt_load_tile(dst, &tmap_q, &sh.bar_walk[it & 1], hq, i * BT, b);
+                bt_load_tile(dst + BT_TILE_BYTES, &tmap_do, &sh.bar_walk[it & 1], hq, i * BT, b);
+            };
+            mbar_arrive_expect_tx(&sh.bar_own, 2 * BT_TILE_BYTES);
+            bt_load_tile(sK, &tmap_k, &sh.bar_own, hkv, k0, b);
+            bt_load_tile(sV, &tmap_v, &sh.bar_own, hkv, k0, b);
+            load_walk(0);
+            bool ok = mbar_wait_bounded(&sh.bar_own, 0, BT_WAIT_LIMIT);
+            for (int it = 0; it < n_it && ok; ++it) {
+                const uint32_t qa = smem_u32(sWalk + (it & 1) * 2 * BT_TILE_BYTES), da = qa + BT_TILE_BYTES;
+                ok = mbar_wait_bounded(&sh.bar_walk[it & 1], (uint32_t)(it >> 1) & 1u, BT_WAIT_LIMIT);
+                if (!ok) break;
+                tc_fence_after();
+                // S^T = K Q^T, dP^T = V dO^T: rows = keys.  Issued behind the products of the step before, which
+                // read P^T / dS^T from the columns these overwrite (products of one thread execute in order).
+                bt_mma_ss(tmem_s, desc_k, smem_desc_sw128(qa, 16, 1024));
+                bt_mma_ss(tmem_dp, desc_v, smem_desc_sw128(da, 16, 1024));
+                umma_commit(&sh.bar_s);
+                // the other walk buffer is free once the second group of products of step it - 1 has completed
+                if (it >= 1) ok = mbar_wait_bounded(&sh.bar_d, (uint32_t)(it - 1) & 1u, BT_WAIT_LIMIT);
+                if (!ok) break;
+                if (it + 1 < n_it) load_walk(it + 1);
+                ok = mbar_wait_bounded(&sh.bar_p, (uint32_t)it & 1u, BT_WAIT_LIMIT);
+                if (!ok) break;
+                tc_fence_after();
+                // dV += P^T dO, dK += dS^T Q: the walked tiles in place as MN-major operands (contraction over queries)
+                bt_mma_ts(tmem_dv, tmem_s, smem_desc_sw128(da, BT_HALF, 1024), it > 0);
+                bt_mma_ts(tmem_dk, tmem_dp, smem_desc_sw128(qa, BT_HALF, 1024), it > 0);
+                umma_commit(&sh.bar_d);
+            }
+            if (!ok) timed_out();
+        }
+        __syncwarp();
+    } else {
+        // =============== elementwise threads: one per key of the block ===============================
+        const int kr = tid;       // accumulator row == TMEM lane
+        const int kp = k0 + kr;   // the key's position
+        const uint32_t lane_sel = (uint32_t)(warp * 32) << 16;
+        bool aborted = false;
+        auto warp_wait = [&](uint64_t *bar, uint32_t parity) -> bool {
+            int ok = 1;
+            if ((tid & 31) == 0) ok = mbar_wait_bounded(bar, parity, BT_WAIT_LIMIT) ? 1 : 0;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            __syncwarp();
+            return ok != 0;
+        };
+        for (int it = 0; it < n_it; ++it) {
+            const int hq = hkv * rep + it / per_head, i = i_lo + it % per_head;
+            const int q0 = i * BT, buf = it & 1;
+            // this thread fetches the values of query q0 + kr for everybody; in flight during the wait for the scores
+            const int tq = q0 + kr;
+            float my_lse2 = INFINITY, my_delta = 0.f;  // a query past the end: P = 2^-inf = 0
+            if (tq < p.T) {
+                const long long o = ((long long)b * p.Hq + hq) * p.T + tq;
+                const float l = p.lse[o];
+                my_lse2 = l == -INFINITY ? INFINITY : l * 1.4426950408889634f;
+                my_delta = p.delta[o];
+            }
+            // (all four warps take the same decision here: they meet at a named barrier right below)
+            if (!warp_wait(&sh.bar_s, (uint32_t)it & 1u)) {
+                timed_out();
+                aborted = true;
+                break;
+            }
+            tc_fence_after();
+            sh.lse2[buf][kr] = my_lse2;
+            sh.delta[buf][kr] = my_delta;
+            asm volatile("bar.sync 1, 128;" ::: "memory");  // the four elementwise warps
+            // only blocks on the diagonal or at the window's edge need masking: this key is seen by the
+            // block's queries [c_lo, c_hi)
+            const bool edge = (i == jb) || (p.window_left >= 0 && q0 + BT - 1 - k0 > p.window_left);
+            const int c_lo = kp - q0;
+            const int c_hi = p.window_left >= 0 ? kp + p.window_left - q0 + 1 : BT;
+#pragma unroll 1
+            for (int c4 = 0; c4 < 4; ++c4) {
+                float s[32], d[32];
+                tmem_ld32(tmem_s + lane_sel + c4 * 32, s);
+                tmem_ld32(tmem_dp + lane_sel + c4 * 32, d);
+                uint32_t pw[16], dw[16];
 #pragma unroll
-        for (int kk = 0; kk < BW_T / 16; ++kk) {
-            FragB b_k[2];   // B(k = key, n = channel) at tile[key][channel]
-            FragA a_ds[2];  // A(m = query, k = key) at tile[query][key]
+                for (int c = 0; c < 32; c += 2) {
+                    float pr[2], ds[2];
 #pragma unroll
-            for (int c = 0; c < 2; ++c) load_b_kn(b_k[c], sk + kk * 16 * BW_LD + (cb + c) * 16, BW_LD, lane);
-#pragma unroll
-            for (int r = 0; r < 2; ++r) load_a_mk(a_ds[r], sm.ds + (rb + r) * 16 * BW_LDS + kk * 16, BW_LDS, lane);
-#pragma unroll
-            for (int r = 0; r < 2; ++r)
-#pragma unroll
-                for (int c = 0; c < 2; ++c) mma16(acc_dq[r][c], a_ds[r], b_k[c]);
+                    for (int e = 0; e < 2; ++e) {
+                        const int col = c4 * 32 + c + e;
+                        float pe = ex2_approx(fmaf(s[c + e], p.scale_log2, -sh.lse2[buf][col]));
+                        if (edge && !(col >= c_lo && col < c_hi)) pe = 0.f;
+                        pr[e] = pe;
+                        ds[e] = pe * (d[c + e] - sh.delta[buf][col]) * p.scale;
+                    }
+                    pw[c / 2] = pack_bf16x2(pr[0], pr[1]);
+                    dw[c / 2] = pack_bf16x2(ds[0], ds[1]);
+                }
+                // bf16 over the front of the fp32 scores: chunk c4 lands on columns [16 c4, 16 c4 + 16), all read by now
+                tmem_st_words(tmem_s + lane_sel + c4 * 16, pw);
+                tmem_st_words(tmem_dp + lane_sel + c4 * 16, dw);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if ((tid & 31) == 0) mbar_arrive(&sh.bar_p);
+        }
+        if (!aborted) {
+            if (warp_wait(&sh.bar_d, (uint32_t)(n_it - 1) & 1u)) {
+                tc_fence_after();
+                const bool live = kp < p.T;
+                const long long o = (((long long)b * p.T + (live ? kp : 0)) * p.Hkv + hkv) * NCKV_D;
+                bt_store_row(tmem_dv + lane_sel, p.dv + o, live);
+                bt_store_row(tmem_dk + lane_sel, p.dk + o, live);
+            } else {
+                timed_out();
+            }
         }
     }
-    cp_async_wait<0>();
+    tc_fence_before();
     __syncthreads();
-    float *stage = reinterpret_cast<float *>(&sm.walk[0][0]);
-#pragma unroll
-    for (int r = 0; r < 2; ++r)
-#pragma unroll
-        for (int c = 0; c < 2; ++c) store_acc(stage, NCKV_D, (rb + r) * 16, (cb + c) * 16, acc_dq[r][c], lane);
+    if (warp == 0) tmem_dealloc(tmem_base, BT_TMEM_COLS);
+}
+
+// grid: (query blocks x Hq x B), heaviest query blocks (most key blocks to walk) first
+__global__ void __launch_bounds__(BT_THREADS, 1)
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                   const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
+                   const BwdParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    if ((smem_u32(smem) & 1023u) != 0) {  // uniform; checked rather than assumed
+        if (threadIdx.x == 0) atomicOr(p.status, (int)NCKV_ST_TIMEOUT);
+        return;
+    }
+    uint8_t *sQ = smem, *sdO = smem + BT_TILE_BYTES;
+    uint8_t *sWalk = smem + 2 * BT_TILE_BYTES;  // [2][K tile, V tile]
+    BtShared &sh = *reinterpret_cast<BtShared *>(smem + 6 * BT_TILE_BYTES);
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int pairs = p.B * p.Hq;
+    const int ib = p.n_blocks - 1 - blockIdx.x / pairs;  // the last query blocks walk the most key blocks: first
+    const int hq = (blockIdx.x % pairs) % p.Hq, b = (blockIdx.x % pairs) / p.Hq;
+    const int hkv = hq / (p.Hq / p.Hkv);
+    const int q0 = ib * BT;
+    const int j_lo = p.window_left >= 0 ? max(0, (q0 - p.window_left) / BT) : 0;
+    const int n_it = ib - j_lo + 1;  // >= 1
+
+    if (tid == 0) {
+        prefetch_tensormap(&tmap_q);
+        prefetch_tensormap(&tmap_k);
+        prefetch_tensormap(&tmap_v);
+        prefetch_tensormap(&tmap_do);
+        mbar_init(&sh.bar_own, 1);
+        mbar_init(&sh.bar_walk[0], 1);
+        mbar_init(&sh.bar_walk[1], 1);
+        mbar_init(&sh.bar_s, 1);
+        mbar_init(&sh.bar_p, 4);
+        mbar_init(&sh.bar_d, 1);
+        sh.abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 0) {
+        tmem_alloc(&sh.tmem_slot, BT_TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
     __syncthreads();
-    store_result(stage, p.dq, b, q0, hq, p.T, p.Hq);
+    tc_fence_after();
+    const uint32_t tmem_base = sh.tmem_slot;
+    const uint32_t tmem_s = tmem_base, tmem_dp = tmem_base + 128, tmem_dq = tmem_base + 256;
+    volatile int *abort_flag = &sh.abort_flag;
+    auto timed_out = [&]() {
+        *abort_flag = 1;
+        atomicOr(p.status, (int)NCKV_ST_TIMEOUT);
+    };
+
+    if (warp == 4) {
+        // =============== one thread issues the copies and the products ===============================
+        if ((tid & 31) == 0) {
+            const uint64_t desc_q = smem_desc_sw128(smem_u32(sQ), 16, 1024);
+            const uint64_t desc_do = smem_desc_sw128(smem_u32(sdO), 16, 1024);
+            auto load_walk = [&](int it) {
+                uint8_t *dst = sWalk + (it & 1) * 2 * BT_TILE_BYTES;
+                mbar_arrive_expect_tx(&sh.bar_walk[it & 1], 2 * BT_TILE_BYTES);
+                bt_load_tile(dst, &tmap_k, &sh.bar_walk[it & 1], hkv, (j_lo + it) * BT, b);
+                bt_load_tile(dst + BT_TILE_BYTES, &tmap_v, &sh.bar_walk[it & 1], hkv, (j_lo + it) * BT, b);
+            };
+            mbar_arrive_expect_tx(&sh.bar_own, 2 * BT_TILE_BYTES);
+            bt_load_tile(sQ, &tmap_q, &sh.bar_own, hq, q0, b);
+            bt_load_tile(sdO, &tmap_do, &sh.bar_own, hq, q0, b);
+            load_walk(0);
+            bool ok = mbar_wait_bounded(&sh.bar_own, 0, BT_WAIT_LIMIT);
+            for (int it = 0; it < n_it && ok; ++it) {
+                const uint32_t ka = smem_u32(sWalk + (it & 1) * 2 * BT_TILE_BYTES), va = ka + BT_TILE_BYTES;
+                ok = mbar_wait_bounded(&sh.bar_walk[it & 1], (uint32_t)(it >> 1) & 1u, BT_WAIT_LIMIT);
+                if (!ok) break;
+                tc_fence_after();
+                // S = Q K^T, dP = dO V^T: rows = queries
+                bt_mma_ss(tmem_s, desc_q, smem_desc_sw128(ka, 16, 1024));
+                bt_mma_ss(tmem_dp, desc_do, smem_desc_sw128(va, 16, 1024));
+                umma_commit(&sh.bar_s);
+                if (it >= 1) ok = mbar_wait_bounded(&sh.bar_d, (uint32_t)(it - 1) & 1u, BT_WAIT_LIMIT);
+                if (!ok) break;
+                if (it + 1 < n_it) load_walk(it + 1);
+                ok = mbar_wait_bounded(&sh.bar_p, (uint32_t)it & 1u, BT_WAIT_LIMIT);
+                if (!ok) break;
+                tc_fence_after();
+                // dQ += dS K: the K tile in place as an MN-major operand (contraction over keys)
+                bt_mma_ts(tmem_dq, tmem_s, smem_desc_sw128(ka, BT_HALF, 1024), it > 0);
+                umma_commit(&sh.bar_d);
+            }
+            if (!ok) timed_out();
+        }
+        __syncwarp();
+    } else {
+        // =============== elementwise threads: one per query of the block =============================
+        const int qp = q0 + tid;  // the query's position; accumulator row == TMEM lane == tid
+        const uint32_t lane_sel = (uint32_t)(warp * 32) << 16;
+        bool aborted = false;
+        auto warp_wait = [&](uint64_t *bar, uint32_t parity) -> bool {
+            int ok = 1;
+            if ((tid & 31) == 0) ok = mbar_wait_bounded(bar, parity, BT_WAIT_LIMIT) ? 1 : 0;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            __syncwarp();
+            return ok != 0;
+        };
+        float lse2 = INFINITY, delta = 0.f;  // a query past the end: P = 2^-inf = 0
+        if (qp < p.T) {
+            const long long o = ((long long)b * p.Hq + hq) * p.T + qp;
+            const float l = p.lse[o];
+            lse2 = l == -INFINITY ? INFINITY : l * 1.4426950408889634f;
+            delta = p.delta[o];
+        }
+        for (int it = 0; it < n_it; ++it) {
+            const int jblk = j_lo + it, k0 = jblk * BT;
+            if (!warp_wait(&sh.bar_s, (uint32_t)it & 1u)) {
+                timed_out();
+                aborted = true;
+                break;
+            }
+            tc_fence_after();
+            // this query sees the block's keys [c_lo, c_hi)
+            const bool edge = (jblk == ib) || (p.window_left >= 0 && q0 + BT - 1 - k0 > p.window_left);
+            const int c_hi = qp - k0 + 1;
+            const int c_lo = p.window_left >= 0 ? qp - p.window_left - k0 : 0;
+#pragma unroll 1
+            for (int c4 = 0; c4 < 4; ++c4) {
+                float s[32], d[32];
+                tmem_ld32(tmem_s + lane_sel + c4 * 32, s);
+                tmem_ld32(tmem_dp + lane_sel + c4 * 32, d);
+                uint32_t dw[16];
+#pragma unroll
+                for (int c = 0; c < 32; c += 2) {
+                    float ds[2];
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int col = c4 * 32 + c + e;
+                        float pe = ex2_approx(fmaf(s[c + e], p.scale_log2, -lse2));
+                        if (edge && !(col >= c_lo && col < c_hi)) pe = 0.f;
+                        ds[e] = pe * (d[c + e] - delta) * p.scale;
+                    }
+                    dw[c / 2] = pack_bf16x2(ds[0], ds[1]);
+                }
+                tmem_st_words(tmem_s + lane_sel + c4 * 16, dw);  // over the front of the scores, all read by now
+            }
+            tc_fence_before();
+            __syncwarp();
+            if ((tid & 31) == 0) mbar_arrive(&sh.bar_p);
+        }
+        if (!aborted) {
+            if (warp_wait(&sh.bar_d, (uint32_t)(n_it - 1) & 1u)) {
+                tc_fence_after();
+                const bool live = qp < p.T;
+                bt_store_row(tmem_dq + lane_sel, p.dq + (((long long)b * p.T + (live ? qp : 0)) * p.Hq + hq) * NCKV_D, live);
+            } else {
+                timed_out();
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_base, BT_TMEM_COLS);
 }
 
 }  // namespace nckv
 
 extern "C" size_t nckv_flash_attn_bwd_workspace_bytes(int B, int T, int Hq) {
-    return (size_t)B * (size_t)T * (size_t)Hq * sizeof(float);
+    const size_t delta_bytes = (size_t)B * (size_t)T * (size_t)Hq * sizeof(float);
+    return (delta_bytes + 255) / 256 * 256 + 256;  // delta, then the device status word (NCKV_ST_* bits, 0 = clean)
 }
 
 extern "C" int nckv_flash_attn_bwd(const void *q, const void *k, const void *v, const void *out, const void *dout,
@@ -391,49 +493,55 @@ extern "C" int nckv_flash_attn_bwd(const void *q, const void *k, const void *v, 
         set_error("flash_attn_bwd: Hq=%d must be a multiple of Hkv=%d", Hq, Hkv);
         return NCKV_E_UNSUPPORTED;
     }
-    const int n_tiles = (T + BW_T - 1) / BW_T;
-    if (Hq > 65535 || B > 65535) {
-        set_error("flash_attn_bwd: B=%d or Hq=%d exceeds the grid limit 65535", B, Hq);
+    const int n_blocks = (T + BT - 1) / BT;
+    if ((long long)n_blocks * Hq * B > 0x7fffffffLL) {
+        set_error("flash_attn_bwd: B=%d x Hq=%d x %d blocks exceed the grid limit", B, Hq, n_blocks);
         return NCKV_E_UNSUPPORTED;
     }
     if ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out | (uintptr_t)dout | (uintptr_t)dq | (uintptr_t)dk |
-          (uintptr_t)dv) & 15) != 0) {
-        set_error("flash_attn_bwd: tensors must be 16-byte aligned");
+          (uintptr_t)dv | (uintptr_t)workspace) & 31) != 0) {
+        set_error("flash_attn_bwd: tensors must be 32-byte aligned");
         return NCKV_E_ARG;
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t delta_bytes = (size_t)B * T * Hq * sizeof(float);
     BwdParams p;
-    p.q = static_cast<const __nv_bfloat16 *>(q);
-    p.k = static_cast<const __nv_bfloat16 *>(k);
-    p.v = static_cast<const __nv_bfloat16 *>(v);
-    p.dout = static_cast<const __nv_bfloat16 *>(dout);
     p.lse = lse;
     p.delta = static_cast<const float *>(workspace);
+    p.status = reinterpret_cast<int32_t *>(static_cast<uint8_t *>(workspace) + (delta_bytes + 255) / 256 * 256);
+    NCKV_CUDA_CHECK(cudaMemsetAsync(p.status, 0, sizeof(int32_t), st));
     p.dq = static_cast<__nv_bfloat16 *>(dq);
     p.dk = static_cast<__nv_bfloat16 *>(dk);
     p.dv = static_cast<__nv_bfloat16 *>(dv);
-    p.B = B; p.T = T; p.Hq = Hq; p.Hkv = Hkv;
+    p.B = B; p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.n_blocks = n_blocks;
     p.window_left = window_left;
     p.scale = (float)(1.0 / sqrt((double)D));
     p.scale_log2 = (float)(1.4426950408889634 / sqrt((double)D));
 
+    CUtensorMap mq, mk, mv, mdo;
+    int rc = make_kv_tensor_map(&mq, q, B, T, Hq, (int64_t)T * Hq * D, (int64_t)Hq * D, BT);
+    if (rc == NCKV_OK) rc = make_kv_tensor_map(&mdo, dout, B, T, Hq, (int64_t)T * Hq * D, (int64_t)Hq * D, BT);
+    if (rc == NCKV_OK) rc = make_kv_tensor_map(&mk, k, B, T, Hkv, (int64_t)T * Hkv * D, (int64_t)Hkv * D, BT);
+    if (rc == NCKV_OK) rc = make_kv_tensor_map(&mv, v, B, T, Hkv, (int64_t)T * Hkv * D, (int64_t)Hkv * D, BT);
+    if (rc != NCKV_OK) return rc;
+
     const long long rows = (long long)B * T * Hq;
-    attn_bwd_delta_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(out), p.dout,
+    attn_bwd_delta_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(out),
+                                                                       static_cast<const __nv_bfloat16 *>(dout),
                                                                        static_cast<float *>(workspace), B, T, Hq);
     NCKV_CUDA_CHECK(cudaGetLastError());
 
-    const size_t smem = sizeof(BwdSmem);
-    static bool attr_set[64] = {false};
+    static bool attr_set[64] = {false};  // per device; setting the attribute twice from racing threads is harmless
     int dev = 0;
     NCKV_CUDA_CHECK(cudaGetDevice(&dev));
     if (dev < 64 && !attr_set[dev]) {
-        NCKV_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        NCKV_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        NCKV_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BT_SMEM_BYTES));
+        NCKV_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BT_SMEM_BYTES));
         attr_set[dev] = true;
     }
-    attn_bwd_dkdv_kernel<<<dim3((unsigned)n_tiles, (unsigned)Hkv, (unsigned)B), BW_THREADS, smem, st>>>(p);
+    attn_bwd_dkdv_kernel<<<(unsigned)(n_blocks * Hkv * B), BT_THREADS, BT_SMEM_BYTES, st>>>(mq, mk, mv, mdo, p);
     NCKV_CUDA_CHECK(cudaGetLastError());
-    attn_bwd_dq_kernel<<<dim3((unsigned)n_tiles, (unsigned)Hq, (unsigned)B), BW_THREADS, smem, st>>>(p);
+    attn_bwd_dq_kernel<<<(unsigned)(n_blocks * Hq * B), BT_THREADS, BT_SMEM_BYTES, st>>>(mq, mk, mv, mdo, p);
     NCKV_CUDA_CHECK(cudaGetLastError());
     return NCKV_OK;
 }
