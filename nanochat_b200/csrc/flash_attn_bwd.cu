@@ -8,9 +8,9 @@
 // Scores and probabilities are recomputed from q, k and the forward's log-sum-exp; nothing is accumulated
 // with atomics, so the gradients are the same bits on every run.  Both kernels follow the forward kernel's
 // forms: operands arrive by TMA into 128-byte-swizzled shared memory, tcgen05.mma accumulates in tensor memory,
-// one thread issues copies and products, four warps (one thread per accumulator row) do the elementwise work
-// between the two groups of products and write P / dS back to tensor memory as bf16 over the scores they came
-// from, where the second group of products reads them as its A operand.
+// one thread issues copies and products, eight warps (two threads per accumulator row, 64 columns each) do the
+// elementwise work between the two groups of products and write P / dS back to tensor memory as bf16 over the
+// scores they came from, where the second group of products reads them as its A operand.
 //
 //   dK/dV kernel   the CTA owns K_j, V_j (128 keys) and walks the query blocks i that see them, for every q head
 //                  of the kv head.  Per step:  S^T = K_j Q_i^T and dP^T = V_j dO_i^T (accumulator rows = keys),
@@ -27,6 +27,8 @@
 // flash_attention.py:107-128 during training (gpt.py:108).
 #include <math.h>
 
+#include <type_traits>
+
 #include "nckv_common.cuh"
 #include "tc05.cuh"
 
@@ -35,7 +37,8 @@ namespace nckv {
 constexpr int BT = 128;                        // keys per dK/dV CTA, queries per dQ CTA, and the walked block
 constexpr int BT_TILE_BYTES = BT * NCKV_D * 2;  // 32 KB: two 64-channel halves of [128][128 B]
 constexpr int BT_HALF = BT_TILE_BYTES / 2;
-constexpr int BT_THREADS = 160;                // 4 elementwise warps + the warp whose lane 0 issues copies and products
+constexpr int BT_EW_THREADS = 256;             // elementwise threads: two per accumulator row, 64 columns each
+constexpr int BT_THREADS = BT_EW_THREADS + 32;  // + the warp whose lane 0 issues copies and products
 constexpr int BT_TMEM_COLS = 512;
 constexpr unsigned long long BT_WAIT_LIMIT = NCKV_WAIT_LIMIT_NS;
 
@@ -85,33 +88,32 @@ __device__ __forceinline__ void bt_mma_ss(uint32_t d_tmem, uint64_t desc_a, uint
         umma_bf16(d_tmem, desc_a + off, desc_b + off, IDESC, kk > 0 ? 1u : 0u);
     }
 }
-// D (+)= A B with A (128 rows x 128 bf16 = 64 columns) in tensor memory and B a rows x channels tile used in
-// place as an MN-major operand: the contraction runs over the tile's 128 rows, 16 per instruction.
+// D (+)= A B with A (128 rows x 128 bf16) in tensor memory and B a rows x channels tile used in place as an
+// MN-major operand: the contraction runs over the tile's 128 rows, 16 per instruction.  A sits where the
+// elementwise threads left it: the bf16 of score columns [0, 64) over columns [0, 32) of the fp32 scores, those of
+// score columns [64, 128) over columns [64, 96) (each thread overwrites only scores it has read itself).
 __device__ __forceinline__ void bt_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t desc_b_mn, bool accumulate) {
     constexpr uint32_t IDESC = umma_idesc(BT, NCKV_D, 0, 1);
 #pragma unroll
     for (int ks = 0; ks < BT / 16; ++ks)
-        umma_bf16_a_tmem(d_tmem, a_tmem + (uint32_t)ks * 8, desc_b_mn + (uint64_t)((ks * 16 * 128) >> 4), IDESC,
-                         (accumulate || ks > 0) ? 1u : 0u);
+        umma_bf16_a_tmem(d_tmem, a_tmem + (uint32_t)(ks * 8 + (ks >= 4 ? 32 : 0)), desc_b_mn + (uint64_t)((ks * 16 * 128) >> 4),
+                         IDESC, (accumulate || ks > 0) ? 1u : 0u);
 }
 __device__ __forceinline__ void bt_load_tile(uint8_t *dst, const CUtensorMap *map, uint64_t *bar, int head, int tok0, int b) {
     tma_load_4d(dst, map, bar, 0, head, tok0, b);
     tma_load_4d(dst + BT_HALF, map, bar, 64, head, tok0, b);
 }
-// One accumulator row (128 fp32 columns starting at `taddr`) -> 128 bf16 at `dst` (32-byte aligned).
-__device__ __forceinline__ void bt_store_row(uint32_t taddr, __nv_bfloat16 *dst, bool live) {
+// 64 fp32 accumulator columns starting at `taddr` -> 64 bf16 at `dst` (32-byte aligned).
+__device__ __forceinline__ void bt_store_half_row(uint32_t taddr, __nv_bfloat16 *dst, bool live) {
+    float c[64];
+    tmem_ld64(taddr, c);
+    if (live) {
 #pragma unroll
-    for (int ch = 0; ch < 2; ++ch) {
-        float c[64];
-        tmem_ld64(taddr + ch * 64, c);
-        if (live) {
+        for (int i = 0; i < 4; ++i) {
+            uint32_t w[8];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                uint32_t w[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) w[e] = pack_bf16x2(c[16 * i + 2 * e], c[16 * i + 2 * e + 1]);
-                st_global_v8(reinterpret_cast<uint4 *>(dst) + (ch * 4 + i) * 2, w);
-            }
+            for (int e = 0; e < 8; ++e) w[e] = pack_bf16x2(c[16 * i + 2 * e], c[16 * i + 2 * e + 1]);
+            st_global_v8(reinterpret_cast<uint4 *>(dst) + i * 2, w);
         }
     }
 }
@@ -120,7 +122,9 @@ struct BtShared {  // behind the operand tiles
     uint64_t bar_own, bar_walk[2], bar_s, bar_p, bar_d;
     uint32_t tmem_slot;
     int abort_flag;
-    float lse2[2][BT], delta[2][BT];  // dK/dV kernel: the walked queries' values, one per accumulator column
+    // dK/dV kernel: the walked queries' values, one per accumulator column: -lse * log2(e) and delta / sqrt(D)
+    alignas(16) float neg_lse2[2][BT];
+    alignas(16) float delta_s[2][BT];
 };
 constexpr int BT_SMEM_BYTES = 6 * BT_TILE_BYTES + (int)sizeof(BtShared);
 
@@ -159,7 +163,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         mbar_init(&sh.bar_walk[0], 1);
         mbar_init(&sh.bar_walk[1], 1);
         mbar_init(&sh.bar_s, 1);
-        mbar_init(&sh.bar_p, 4);
+        mbar_init(&sh.bar_p, BT_EW_THREADS / 32);
         mbar_init(&sh.bar_d, 1);
         sh.abort_flag = 0;
         fence_mbar_init();
@@ -179,7 +183,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         atomicOr(p.status, (int)NCKV_ST_TIMEOUT);
     };
 
-    if (warp == 4) {
+    if (warp == BT_EW_THREADS / 32) {
         // =============== one thread issues the copies and the products ===============================
         if ((tid & 31) == 0) {
             const uint64_t desc_k = smem_desc_sw128(smem_u32(sK), 16, 1024);
@@ -222,10 +226,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         }
         __syncwarp();
     } else {
-        // =============== elementwise threads: one per key of the block ===============================
-        const int kr = tid;       // accumulator row == TMEM lane
-        const int kp = k0 + kr;   // the key's position
-        const uint32_t lane_sel = (uint32_t)(warp * 32) << 16;
+        // =============== elementwise threads: two per key of the block ===============================
+        const int kr = tid & (BT - 1);  // accumulator row == TMEM lane
+        const int half = tid >> 7;      // which 64 of the 128 query columns
+        const int kp = k0 + kr;         // the key's position
+        const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
         bool aborted = false;
         auto warp_wait = [&](uint64_t *bar, uint32_t parity) -> bool {
             int ok = 1;
@@ -237,53 +242,77 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         for (int it = 0; it < n_it; ++it) {
             const int hq = hkv * rep + it / per_head, i = i_lo + it % per_head;
             const int q0 = i * BT, buf = it & 1;
-            // this thread fetches the values of query q0 + kr for everybody; in flight during the wait for the scores
+            // the first 128 threads fetch -lse * log2(e), the others delta / sqrt(D), of query q0 + kr for everybody;
+            // in flight during the wait for the scores
             const int tq = q0 + kr;
-            float my_lse2 = INFINITY, my_delta = 0.f;  // a query past the end: P = 2^-inf = 0
+            float mine = half == 0 ? -INFINITY : 0.f;  // a query past the end: P = 2^-inf = 0
             if (tq < p.T) {
                 const long long o = ((long long)b * p.Hq + hq) * p.T + tq;
-                const float l = p.lse[o];
-                my_lse2 = l == -INFINITY ? INFINITY : l * 1.4426950408889634f;
-                my_delta = p.delta[o];
+                if (half == 0) {
+                    const float l = p.lse[o];
+                    mine = l == -INFINITY ? -INFINITY : -l * 1.4426950408889634f;
+                } else {
+                    mine = p.delta[o] * p.scale;
+                }
             }
-            // (all four warps take the same decision here: they meet at a named barrier right below)
+            // (all eight warps take the same decision here: they meet at a named barrier right below)
             if (!warp_wait(&sh.bar_s, (uint32_t)it & 1u)) {
                 timed_out();
                 aborted = true;
                 break;
             }
             tc_fence_after();
-            sh.lse2[buf][kr] = my_lse2;
-            sh.delta[buf][kr] = my_delta;
-            asm volatile("bar.sync 1, 128;" ::: "memory");  // the four elementwise warps
+            (half == 0 ? sh.neg_lse2 : sh.delta_s)[buf][kr] = mine;
+            asm volatile("bar.sync 1, 256;" ::: "memory");  // the eight elementwise warps
             // only blocks on the diagonal or at the window's edge need masking: this key is seen by the
             // block's queries [c_lo, c_hi)
             const bool edge = (i == jb) || (p.window_left >= 0 && q0 + BT - 1 - k0 > p.window_left);
             const int c_lo = kp - q0;
             const int c_hi = p.window_left >= 0 ? kp + p.window_left - q0 + 1 : BT;
-#pragma unroll 1
-            for (int c4 = 0; c4 < 4; ++c4) {
+            const float2 scale_log2_2 = make_float2(p.scale_log2, p.scale_log2), scale_2 = make_float2(p.scale, p.scale);
+            const float2 zero_2 = make_float2(0.f, 0.f);
+            // two copies of the loop: the masked one only runs for the few blocks that need it
+            auto chunk = [&](auto masked, int cc) {
+                constexpr bool MASKED = decltype(masked)::value;
+                const int col0 = half * 64 + cc * 32;
                 float s[32], d[32];
-                tmem_ld32(tmem_s + lane_sel + c4 * 32, s);
-                tmem_ld32(tmem_dp + lane_sel + c4 * 32, d);
+                tmem_ld32(tmem_s + lane_sel + col0, s);
+                tmem_ld32(tmem_dp + lane_sel + col0, d);
                 uint32_t pw[16], dw[16];
 #pragma unroll
-                for (int c = 0; c < 32; c += 2) {
-                    float pr[2], ds[2];
-#pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        const int col = c4 * 32 + c + e;
-                        float pe = ex2_approx(fmaf(s[c + e], p.scale_log2, -sh.lse2[buf][col]));
-                        if (edge && !(col >= c_lo && col < c_hi)) pe = 0.f;
-                        pr[e] = pe;
-                        ds[e] = pe * (d[c + e] - sh.delta[buf][col]) * p.scale;
+                for (int c = 0; c < 32; c += 4) {
+                    const float4 nl = *reinterpret_cast<const float4 *>(&sh.neg_lse2[buf][col0 + c]);
+                    const float4 dl = *reinterpret_cast<const float4 *>(&sh.delta_s[buf][col0 + c]);
+                    // P = 2^(s * scale * log2(e) - lse * log2(e));  dS = P * (dP * scale - delta * scale)
+                    const float2 x01 = ffma2(make_float2(s[c], s[c + 1]), scale_log2_2, make_float2(nl.x, nl.y));
+                    const float2 x23 = ffma2(make_float2(s[c + 2], s[c + 3]), scale_log2_2, make_float2(nl.z, nl.w));
+                    const float2 t01 = ffma2(make_float2(d[c], d[c + 1]), scale_2, make_float2(-dl.x, -dl.y));
+                    const float2 t23 = ffma2(make_float2(d[c + 2], d[c + 3]), scale_2, make_float2(-dl.z, -dl.w));
+                    float2 p01 = make_float2(ex2_approx(x01.x), ex2_approx(x01.y));
+                    float2 p23 = make_float2(ex2_approx(x23.x), ex2_approx(x23.y));
+                    if (MASKED) {
+                        const int col = col0 + c;
+                        if (!(col >= c_lo && col < c_hi)) p01.x = 0.f;
+                        if (!(col + 1 >= c_lo && col + 1 < c_hi)) p01.y = 0.f;
+                        if (!(col + 2 >= c_lo && col + 2 < c_hi)) p23.x = 0.f;
+                        if (!(col + 3 >= c_lo && col + 3 < c_hi)) p23.y = 0.f;
                     }
-                    pw[c / 2] = pack_bf16x2(pr[0], pr[1]);
-                    dw[c / 2] = pack_bf16x2(ds[0], ds[1]);
+                    const float2 ds01 = ffma2(p01, t01, zero_2), ds23 = ffma2(p23, t23, zero_2);
+                    pw[c / 2] = pack_bf16x2(p01.x, p01.y);
+                    pw[c / 2 + 1] = pack_bf16x2(p23.x, p23.y);
+                    dw[c / 2] = pack_bf16x2(ds01.x, ds01.y);
+                    dw[c / 2 + 1] = pack_bf16x2(ds23.x, ds23.y);
                 }
-                // bf16 over the front of the fp32 scores: chunk c4 lands on columns [16 c4, 16 c4 + 16), all read by now
-                tmem_st_words(tmem_s + lane_sel + c4 * 16, pw);
-                tmem_st_words(tmem_dp + lane_sel + c4 * 16, dw);
+                // bf16 over the front of this thread's own fp32 scores, all of which it has read by now
+                tmem_st_words(tmem_s + lane_sel + half * 64 + cc * 16, pw);
+                tmem_st_words(tmem_dp + lane_sel + half * 64 + cc * 16, dw);
+            };
+            if (edge) {
+                chunk(std::true_type{}, 0);
+                chunk(std::true_type{}, 1);
+            } else {
+                chunk(std::false_type{}, 0);
+                chunk(std::false_type{}, 1);
             }
             tc_fence_before();
             __syncwarp();
@@ -294,8 +323,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
                 tc_fence_after();
                 const bool live = kp < p.T;
                 const long long o = (((long long)b * p.T + (live ? kp : 0)) * p.Hkv + hkv) * NCKV_D;
-                bt_store_row(tmem_dv + lane_sel, p.dv + o, live);
-                bt_store_row(tmem_dk + lane_sel, p.dk + o, live);
+                // the first 128 threads store dV, the others dK
+                const uint32_t acc = (half == 0 ? tmem_dv : tmem_dk) + lane_sel;
+                __nv_bfloat16 *dst = (half == 0 ? p.dv : p.dk) + o;
+                bt_store_half_row(acc, dst, live);
+                bt_store_half_row(acc + 64, dst + 64, live);
             } else {
                 timed_out();
             }
@@ -338,7 +370,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         mbar_init(&sh.bar_walk[0], 1);
         mbar_init(&sh.bar_walk[1], 1);
         mbar_init(&sh.bar_s, 1);
-        mbar_init(&sh.bar_p, 4);
+        mbar_init(&sh.bar_p, BT_EW_THREADS / 32);
         mbar_init(&sh.bar_d, 1);
         sh.abort_flag = 0;
         fence_mbar_init();
@@ -358,7 +390,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         atomicOr(p.status, (int)NCKV_ST_TIMEOUT);
     };
 
-    if (warp == 4) {
+    if (warp == BT_EW_THREADS / 32) {
         // =============== one thread issues the copies and the products ===============================
         if ((tid & 31) == 0) {
             const uint64_t desc_q = smem_desc_sw128(smem_u32(sQ), 16, 1024);
@@ -397,9 +429,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         }
         __syncwarp();
     } else {
-        // =============== elementwise threads: one per query of the block =============================
-        const int qp = q0 + tid;  // the query's position; accumulator row == TMEM lane == tid
-        const uint32_t lane_sel = (uint32_t)(warp * 32) << 16;
+        // =============== elementwise threads: two per query of the block =============================
+        const int qr = tid & (BT - 1);  // accumulator row == TMEM lane
+        const int half = tid >> 7;      // which 64 of the 128 key columns (and, at the end, of the channels)
+        const int qp = q0 + qr;         // the query's position
+        const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
         bool aborted = false;
         auto warp_wait = [&](uint64_t *bar, uint32_t parity) -> bool {
             int ok = 1;
@@ -408,12 +442,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             __syncwarp();
             return ok != 0;
         };
-        float lse2 = INFINITY, delta = 0.f;  // a query past the end: P = 2^-inf = 0
+        float neg_lse2 = -INFINITY, delta_s = 0.f;  // a query past the end: P = 2^-inf = 0
         if (qp < p.T) {
             const long long o = ((long long)b * p.Hq + hq) * p.T + qp;
             const float l = p.lse[o];
-            lse2 = l == -INFINITY ? INFINITY : l * 1.4426950408889634f;
-            delta = p.delta[o];
+            neg_lse2 = l == -INFINITY ? -INFINITY : -l * 1.4426950408889634f;
+            delta_s = p.delta[o] * p.scale;
         }
         for (int it = 0; it < n_it; ++it) {
             const int jblk = j_lo + it, k0 = jblk * BT;
@@ -427,25 +461,40 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             const bool edge = (jblk == ib) || (p.window_left >= 0 && q0 + BT - 1 - k0 > p.window_left);
             const int c_hi = qp - k0 + 1;
             const int c_lo = p.window_left >= 0 ? qp - p.window_left - k0 : 0;
-#pragma unroll 1
-            for (int c4 = 0; c4 < 4; ++c4) {
+            const float2 scale_log2_2 = make_float2(p.scale_log2, p.scale_log2), scale_2 = make_float2(p.scale, p.scale);
+            const float2 neg_lse2_2 = make_float2(neg_lse2, neg_lse2), neg_delta_2 = make_float2(-delta_s, -delta_s);
+            const float2 zero_2 = make_float2(0.f, 0.f);
+            // two copies of the loop: the masked one only runs for the few blocks that need it
+            auto chunk = [&](auto masked, int cc) {
+                constexpr bool MASKED = decltype(masked)::value;
+                const int col0 = half * 64 + cc * 32;
                 float s[32], d[32];
-                tmem_ld32(tmem_s + lane_sel + c4 * 32, s);
-                tmem_ld32(tmem_dp + lane_sel + c4 * 32, d);
+                tmem_ld32(tmem_s + lane_sel + col0, s);
+                tmem_ld32(tmem_dp + lane_sel + col0, d);
                 uint32_t dw[16];
 #pragma unroll
                 for (int c = 0; c < 32; c += 2) {
-                    float ds[2];
-#pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        const int col = c4 * 32 + c + e;
-                        float pe = ex2_approx(fmaf(s[c + e], p.scale_log2, -lse2));
-                        if (edge && !(col >= c_lo && col < c_hi)) pe = 0.f;
-                        ds[e] = pe * (d[c + e] - delta) * p.scale;
+                    // P = 2^(s * scale * log2(e) - lse * log2(e));  dS = P * (dP * scale - delta * scale)
+                    const float2 x = ffma2(make_float2(s[c], s[c + 1]), scale_log2_2, neg_lse2_2);
+                    const float2 t = ffma2(make_float2(d[c], d[c + 1]), scale_2, neg_delta_2);
+                    float2 pe = make_float2(ex2_approx(x.x), ex2_approx(x.y));
+                    if (MASKED) {
+                        const int col = col0 + c;
+                        if (!(col >= c_lo && col < c_hi)) pe.x = 0.f;
+                        if (!(col + 1 >= c_lo && col + 1 < c_hi)) pe.y = 0.f;
                     }
-                    dw[c / 2] = pack_bf16x2(ds[0], ds[1]);
+                    const float2 ds = ffma2(pe, t, zero_2);
+                    dw[c / 2] = pack_bf16x2(ds.x, ds.y);
                 }
-                tmem_st_words(tmem_s + lane_sel + c4 * 16, dw);  // over the front of the scores, all read by now
+                // over the front of this thread's own fp32 scores, all of which it has read by now
+                tmem_st_words(tmem_s + lane_sel + half * 64 + cc * 16, dw);
+            };
+            if (edge) {
+                chunk(std::true_type{}, 0);
+                chunk(std::true_type{}, 1);
+            } else {
+                chunk(std::false_type{}, 0);
+                chunk(std::false_type{}, 1);
             }
             tc_fence_before();
             __syncwarp();
@@ -455,7 +504,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             if (warp_wait(&sh.bar_d, (uint32_t)(n_it - 1) & 1u)) {
                 tc_fence_after();
                 const bool live = qp < p.T;
-                bt_store_row(tmem_dq + lane_sel, p.dq + (((long long)b * p.T + (live ? qp : 0)) * p.Hq + hq) * NCKV_D, live);
+                bt_store_half_row(tmem_dq + lane_sel + half * 64,
+                                  p.dq + (((long long)b * p.T + (live ? qp : 0)) * p.Hq + hq) * NCKV_D + half * 64, live);
             } else {
                 timed_out();
             }
