@@ -52,25 +52,27 @@ struct BwdParams {
     float scale, scale_log2;
 };
 
-// delta[b, h, t] = sum_c dO[b, t, h, c] * O[b, t, h, c]
+// delta[b, h, t] = sum_c dO[b, t, h, c] * O[b, t, h, c]: half a warp per row, 16 bytes of each tensor per lane
 __global__ void __launch_bounds__(256) attn_bwd_delta_kernel(const __nv_bfloat16 *out, const __nv_bfloat16 *dout,
                                                              float *delta, int B, int T, int Hq) {
-    const long long row = (long long)blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5);  // (b, t, h) flattened
-    if (row >= (long long)B * T * Hq) return;
-    const int lane = threadIdx.x & 31;
-    const uint2 o = *reinterpret_cast<const uint2 *>(out + row * NCKV_D + lane * 4);
-    const uint2 g = *reinterpret_cast<const uint2 *>(dout + row * NCKV_D + lane * 4);
-    const __nv_bfloat162 *o2 = reinterpret_cast<const __nv_bfloat162 *>(&o);
-    const __nv_bfloat162 *g2 = reinterpret_cast<const __nv_bfloat162 *>(&g);
+    const long long row = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 4;  // (b, t, h) flattened
+    const int j = threadIdx.x & 15;
+    const bool live = row < (long long)B * T * Hq;
     float acc = 0.f;
+    if (live) {
+        const uint4 o = __ldg(reinterpret_cast<const uint4 *>(out + row * NCKV_D) + j);
+        const uint4 g = __ldg(reinterpret_cast<const uint4 *>(dout + row * NCKV_D) + j);
+        const __nv_bfloat162 *o2 = reinterpret_cast<const __nv_bfloat162 *>(&o);
+        const __nv_bfloat162 *g2 = reinterpret_cast<const __nv_bfloat162 *>(&g);
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        const float2 a = __bfloat1622float2(o2[i]), c = __bfloat1622float2(g2[i]);
-        acc += a.x * c.x + a.y * c.y;
+        for (int i = 0; i < 4; ++i) {
+            const float2 a = __bfloat1622float2(o2[i]), c = __bfloat1622float2(g2[i]);
+            acc += a.x * c.x + a.y * c.y;
+        }
     }
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-    if (lane == 0) {
+    for (int off = 8; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (live && j == 0) {
         const int h = (int)(row % Hq);
         const long long bt = row / Hq;
         const int t = (int)(bt % T), b = (int)(bt / T);
@@ -576,7 +578,7 @@ extern "C" int nckv_flash_attn_bwd(const void *q, const void *k, const void *v, 
     if (rc != NCKV_OK) return rc;
 
     const long long rows = (long long)B * T * Hq;
-    attn_bwd_delta_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(out),
+    attn_bwd_delta_kernel<<<(unsigned)((rows + 15) / 16), 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(out),
                                                                        static_cast<const __nv_bfloat16 *>(dout),
                                                                        static_cast<float *>(workspace), B, T, Hq);
     NCKV_CUDA_CHECK(cudaGetLastError());
