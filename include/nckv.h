@@ -354,8 +354,10 @@ NCKV_API int nckv_prefill_attn(const void *q, const void *k, const void *v, cons
  *                         exponentials of the scaled scores.  Same kernel as nckv_prefill_attn; `status` is
  *                         the first word of a zero-initialised workspace as there.
  *   nckv_flash_attn_bwd   dq (B, T, Hq, D), dk and dv (B, T, Hkv, D) from q, k, v, out, dout and lse.
- *                         `workspace` holds nckv_flash_attn_bwd_workspace_bytes(B, T, Hq) bytes of scratch
- *                         (rowsum(dout * out)); no atomics are used, results do not depend on scheduling.
+ *                         `workspace` holds nckv_flash_attn_bwd_workspace_bytes(B, T, Hq) bytes of scratch:
+ *                         rowsum(dout * out), and in its last 256 bytes the call's device status word (an int32
+ *                         of NCKV_ST_* bits, cleared by the call, 0 = no guard fired).  All pointers 32-byte
+ *                         aligned.  No atomics are used: the gradients are the same bits on every run.
  */
 NCKV_API int nckv_flash_attn_fwd(const void *q, const void *k, const void *v, void *out, float *lse, int B, int T,
                         int Hq, int Hkv, int D, int window_left, int32_t *status, void *stream);

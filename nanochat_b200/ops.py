@@ -26,6 +26,7 @@ _workspaces = {}  # (device index, stream id) -> uint8 tensor
 # graph captured while one of them was current still launches kernels that point at it.  A (device,
 # stream) pair only ever grows its workspace a handful of times (the size depends on Hq / Hkv alone).
 _retired_workspaces = []
+_bwd_status = {}  # device index -> int32 view of the status word of the latest flash_attn_bwd call's scratch
 
 
 def _ptr(t):
@@ -117,18 +118,21 @@ def workspace(device, B, Hq, Hkv):
 
 def read_status(device, clear=True):
     """Synchronously read (and by default clear) the device status word of the current stream's
-    workspace; 0 means no guard fired.  Bits: 1 overflow, 2 timeout, 4 bad cache_seqlens, 8 bad page."""
+    workspace (and of the device's latest attention backward); 0 means no guard fired.  Bits: 1 overflow, 2 timeout, 4 bad cache_seqlens, 8 bad page."""
     device = torch.device(device)
     idx = device.index if device.index is not None else torch.cuda.current_device()
     key = (idx, torch.cuda.current_stream(idx).cuda_stream)
     ws = _workspaces.get(key)
-    if ws is None:
-        return 0
     with torch.cuda.device(idx):
-        st = _lib.call("nckv_read_status", _ptr(ws), int(bool(clear)), _stream(idx))
+        st = _lib.call("nckv_read_status", _ptr(ws), int(bool(clear)), _stream(idx)) if ws is not None else 0
         for old in _retired_workspaces:  # graphs captured earlier report into the workspace they were captured with
             if old.device.index == idx:
                 st |= _lib.call("nckv_read_status", _ptr(old), int(bool(clear)), _stream(idx))
+        last_bwd = _bwd_status.get(idx)  # the latest attention backward on this device reports into its own scratch
+        if last_bwd is not None:
+            st |= int(last_bwd.item())
+            if clear:
+                del _bwd_status[idx]
     return st
 
 
@@ -381,6 +385,7 @@ def flash_attn_bwd(q, k, v, out, dout, lse, window_left=-1):
                        _ptr(dv), _ptr(scratch), B, T, Hq, Hkv, HEAD_DIM, int(window_left), _stream(idx))
     if rc < 0:
         _lib.check("nckv_flash_attn_bwd", rc)
+    _bwd_status[idx] = scratch[-256:-252].view(torch.int32)  # the call's device status word; read_status() looks at it
     return dq, dk, dv
 
 
