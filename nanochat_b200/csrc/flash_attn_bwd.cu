@@ -278,8 +278,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
                 constexpr bool MASKED = decltype(masked)::value;
                 const int col0 = half * 64 + cc * 32;
                 float s[32], d[32];
-                tmem_ld32(tmem_s + lane_sel + col0, s);
-                tmem_ld32(tmem_dp + lane_sel + col0, d);
+                tmem_ld32x2(tmem_s + lane_sel + col0, s, tmem_dp + lane_sel + col0, d);
                 uint32_t pw[16], dw[16];
 #pragma unroll
                 for (int c = 0; c < 32; c += 4) {
@@ -471,8 +470,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                 constexpr bool MASKED = decltype(masked)::value;
                 const int col0 = half * 64 + cc * 32;
                 float s[32], d[32];
-                tmem_ld32(tmem_s + lane_sel + col0, s);
-                tmem_ld32(tmem_dp + lane_sel + col0, d);
+                tmem_ld32x2(tmem_s + lane_sel + col0, s, tmem_dp + lane_sel + col0, d);
                 uint32_t dw[16];
 #pragma unroll
                 for (int c = 0; c < 32; c += 2) {
