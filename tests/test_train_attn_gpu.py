@@ -41,6 +41,9 @@ def _reference(q, k, v, window_left):
     (1, 1000, 2, 2, 256),
     (1, 64, 2, 1, -1),
     (3, 33, 2, 2, 7),
+    (1, 1500, 8, 2, -1),     # a dozen 128-row blocks, four q heads per kv head
+    (1, 2048, 4, 4, 1024),   # window wider than a block
+    (2, 130, 4, 1, 128),     # a block and two rows, window of exactly one block
 ])
 def test_flash_attn_func_forward_and_backward(B, T, Hq, Hkv, window):
     from nanochat_b200 import ops
