@@ -88,7 +88,7 @@ def test_window_sizes_match_reference(golden_dir):
         seq_len, n_layer, pattern = key.split("_")
         got = np.array(O.window_sizes(int(seq_len), int(n_layer), pattern), dtype=np.int64)
         assert np.array_equal(got, g[key]), key
-    # the case the survey notes: 2048 -> short window 512, long 2048
+    # sequence_len 2048: short layers get a window of 512 (a quarter, rounded up to the tile), long layers 2048
     assert O.window_sizes(2048, 4)[0] == (512, 0) and O.window_sizes(2048, 4)[-1] == (2048, 0)
     with pytest.raises(ValueError):
         O.window_sizes(2048, 4, "SXL")
