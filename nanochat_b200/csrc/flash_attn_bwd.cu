@@ -16,12 +16,15 @@
 //                  of the kv head.  Per step:  S^T = K_j Q_i^T and dP^T = V_j dO_i^T (accumulator rows = keys),
 //                  elementwise over a key's row (lse and delta of the 128 queries come from shared memory),
 //                  dV += P^T dO_i and dK += dS^T Q_i.  Tensor memory: S^T, dP^T, dV, dK = 4 x 128 columns.
-//   dQ kernel      the CTA owns Q_i, dO_i (128 queries of one q head) and walks the key blocks j it sees.  Per step:
-//                  S = Q_i K_j^T and dP = dO_i V_j^T (accumulator rows = queries, lse and delta are per thread),
-//                  dQ += dS K_j.  Tensor memory: S, dP, dQ.
-// The walked operands are double-buffered; the copies of step it + 1 are issued as soon as the products of
-// step it - 1 have completed.  Every barrier wait is bounded; a wait that runs out sets NCKV_ST_TIMEOUT in the
-// status word, the CTA stops issuing work, frees its tensor memory and returns.
+//   dQ kernel      the CTA owns Q_i, dO_i (128 queries of one q head) and walks the keys it sees 64 at a step ("unit").
+//                  Per unit: S = Q_i K_u^T and dP = dO_i V_u^T (accumulator rows = queries, lse and delta are per
+//                  thread), dQ += dS K_u.  Tensor memory holds S and dP of three units (3 x 128 columns) and dQ, so
+//                  the score products run two units ahead of the elementwise threads: a group of products is only
+//                  known to be complete some 900 cycles after its last instruction was issued, and this way
+//                  that latency is not on the threads' path.  (The dK/dV kernel has no columns left for that.)
+// The dK/dV kernel double-buffers its walked tiles (the copies of step it + 1 are issued as soon as the products of
+// step it - 1 have completed); the dQ kernel keeps a ring of five units.  Every barrier wait is bounded; a wait that
+// runs out sets NCKV_ST_TIMEOUT in the status word, the CTA stops issuing work, frees its tensor memory and returns.
 //
 // Replaces: the backward of F.scaled_dot_product_attention / flash_attn_func as reached from
 // flash_attention.py:107-128 during training (gpt.py:108).
@@ -339,7 +342,45 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     if (warp == 0) tmem_dealloc(tmem_base, BT_TMEM_COLS);
 }
 
-// grid: (query blocks x Hq x B), heaviest query blocks (most key blocks to walk) first
+// ---- dQ kernel: the walked keys come 64 at a step ("unit"), three units' scores in tensor memory ----------
+constexpr int BU = 64;                          // keys per unit
+constexpr int BU_TILE_BYTES = BU * NCKV_D * 2;  // 16 KB: two 64-channel halves of [64][128 B]
+constexpr int BU_HALF = BU_TILE_BYTES / 2;
+constexpr int BU_RING = 5;                      // units (one K and one V tile each) in shared memory
+constexpr int BU_BUFS = 3;                      // units whose S and dP are in tensor memory: the score products run two units ahead
+
+struct BuShared {  // behind the operand tiles of the dQ kernel
+    // bar_walk[u % 5] (phase u / 5) "the unit's K and V tiles have landed"; bar_s[u % 3] (phase u / 3) "its score products
+    // are complete"; bar_p[u % 3] "its dS is in tensor memory"; bar_d[u & 1] (phase u / 2) "its gradient product is complete"
+    uint64_t bar_own, bar_walk[BU_RING], bar_s[BU_BUFS], bar_p[BU_BUFS], bar_d[2];
+    uint32_t tmem_slot;
+    int abort_flag;
+};
+constexpr int BU_SMEM_BYTES = 2 * BT_TILE_BYTES + BU_RING * 2 * BU_TILE_BYTES + (int)sizeof(BuShared);
+
+// D = A B^T, 128 x 64 x 128: A an own tile (128 rows), B a unit tile (64 rows), both K-major in shared memory.
+__device__ __forceinline__ void bu_mma_ss(uint32_t d_tmem, uint64_t desc_a, uint64_t desc_b) {
+    constexpr uint32_t IDESC = umma_idesc(BT, BU, 0, 0);
+#pragma unroll
+    for (int kk = 0; kk < NCKV_D / 16; ++kk) {
+        const uint64_t off_a = (uint64_t)(((kk >> 2) * BT_HALF + (kk & 3) * 32) >> 4);
+        const uint64_t off_b = (uint64_t)(((kk >> 2) * BU_HALF + (kk & 3) * 32) >> 4);
+        umma_bf16(d_tmem, desc_a + off_a, desc_b + off_b, IDESC, kk > 0 ? 1u : 0u);
+    }
+}
+// D (+)= A B, 128 x 128 x 64, with A (128 rows x 64 bf16) in tensor memory and B a unit tile used in place as an
+// MN-major operand (contraction over the unit's 64 rows, 16 per instruction).  A sits where the elementwise threads
+// left it: the bf16 of score columns [0, 32) over columns [0, 16) of the unit's fp32 scores, those of score columns
+// [32, 64) over columns [32, 48) (each thread overwrites only scores it has read itself).
+__device__ __forceinline__ void bu_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t desc_b_mn, bool accumulate) {
+    constexpr uint32_t IDESC = umma_idesc(BT, NCKV_D, 0, 1);
+#pragma unroll
+    for (int ks = 0; ks < BU / 16; ++ks)
+        umma_bf16_a_tmem(d_tmem, a_tmem + (uint32_t)((ks >> 1) * 32 + (ks & 1) * 8), desc_b_mn + (uint64_t)((ks * 16 * 128) >> 4),
+                         IDESC, (accumulate || ks > 0) ? 1u : 0u);
+}
+
+// grid: (query blocks x Hq x B), heaviest query blocks (most keys to walk) first
 __global__ void __launch_bounds__(BT_THREADS, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                    const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
@@ -350,17 +391,19 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         return;
     }
     uint8_t *sQ = smem, *sdO = smem + BT_TILE_BYTES;
-    uint8_t *sWalk = smem + 2 * BT_TILE_BYTES;  // [2][K tile, V tile]
-    BtShared &sh = *reinterpret_cast<BtShared *>(smem + 6 * BT_TILE_BYTES);
+    uint8_t *ring = smem + 2 * BT_TILE_BYTES;  // [5][K unit, V unit]
+    BuShared &sh = *reinterpret_cast<BuShared *>(ring + BU_RING * 2 * BU_TILE_BYTES);
 
     const int tid = threadIdx.x, warp = tid >> 5;
     const int pairs = p.B * p.Hq;
-    const int ib = p.n_blocks - 1 - blockIdx.x / pairs;  // the last query blocks walk the most key blocks: first
+    const int ib = p.n_blocks - 1 - blockIdx.x / pairs;  // the last query blocks walk the most keys: first
     const int hq = (blockIdx.x % pairs) % p.Hq, b = (blockIdx.x % pairs) / p.Hq;
     const int hkv = hq / (p.Hq / p.Hkv);
     const int q0 = ib * BT;
-    const int j_lo = p.window_left >= 0 ? max(0, (q0 - p.window_left) / BT) : 0;
-    const int n_it = ib - j_lo + 1;  // >= 1
+    // key units a query of this block sees: from the window's reach up to the end of the diagonal block
+    const int u_lo = p.window_left >= 0 ? max(0, (q0 - p.window_left) / BU) : 0;
+    const int u_hi = min((p.T + BU - 1) / BU - 1, 2 * ib + 1);
+    const int n_units = u_hi - u_lo + 1;  // >= 1
 
     if (tid == 0) {
         prefetch_tensormap(&tmap_q);
@@ -368,11 +411,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         prefetch_tensormap(&tmap_v);
         prefetch_tensormap(&tmap_do);
         mbar_init(&sh.bar_own, 1);
-        mbar_init(&sh.bar_walk[0], 1);
-        mbar_init(&sh.bar_walk[1], 1);
-        mbar_init(&sh.bar_s, 1);
-        mbar_init(&sh.bar_p, BT_EW_THREADS / 32);
-        mbar_init(&sh.bar_d, 1);
+        for (int i = 0; i < BU_RING; ++i) mbar_init(&sh.bar_walk[i], 1);
+        for (int i = 0; i < BU_BUFS; ++i) {
+            mbar_init(&sh.bar_s[i], 1);
+            mbar_init(&sh.bar_p[i], BT_EW_THREADS / 32);
+        }
+        mbar_init(&sh.bar_d[0], 1);
+        mbar_init(&sh.bar_d[1], 1);
         sh.abort_flag = 0;
         fence_mbar_init();
     }
@@ -384,10 +429,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = sh.tmem_slot;
-    const uint32_t tmem_s = tmem_base, tmem_dp = tmem_base + 128, tmem_dq = tmem_base + 256;
-    volatile int *abort_flag = &sh.abort_flag;
+    // unit u: S at columns 128 (u % 3) + [0, 64), dP at + [64, 128); dQ at [384, 512)
+    const uint32_t tmem_dq = tmem_base + 384;
     auto timed_out = [&]() {
-        *abort_flag = 1;
+        sh.abort_flag = 1;
         atomicOr(p.status, (int)NCKV_ST_TIMEOUT);
     };
 
@@ -396,35 +441,52 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         if ((tid & 31) == 0) {
             const uint64_t desc_q = smem_desc_sw128(smem_u32(sQ), 16, 1024);
             const uint64_t desc_do = smem_desc_sw128(smem_u32(sdO), 16, 1024);
-            auto load_walk = [&](int it) {
-                uint8_t *dst = sWalk + (it & 1) * 2 * BT_TILE_BYTES;
-                mbar_arrive_expect_tx(&sh.bar_walk[it & 1], 2 * BT_TILE_BYTES);
-                bt_load_tile(dst, &tmap_k, &sh.bar_walk[it & 1], hkv, (j_lo + it) * BT, b);
-                bt_load_tile(dst + BT_TILE_BYTES, &tmap_v, &sh.bar_walk[it & 1], hkv, (j_lo + it) * BT, b);
-            };
             mbar_arrive_expect_tx(&sh.bar_own, 2 * BT_TILE_BYTES);
             bt_load_tile(sQ, &tmap_q, &sh.bar_own, hq, q0, b);
             bt_load_tile(sdO, &tmap_do, &sh.bar_own, hq, q0, b);
-            load_walk(0);
+            auto load_unit = [&](int u) {
+                uint8_t *dst = ring + (u % BU_RING) * 2 * BU_TILE_BYTES;
+                uint64_t *bar = &sh.bar_walk[u % BU_RING];
+                mbar_arrive_expect_tx(bar, 2 * BU_TILE_BYTES);
+                tma_load_4d(dst, &tmap_k, bar, 0, hkv, (u_lo + u) * BU, b);
+                tma_load_4d(dst + BU_HALF, &tmap_k, bar, 64, hkv, (u_lo + u) * BU, b);
+                tma_load_4d(dst + BU_TILE_BYTES, &tmap_v, bar, 0, hkv, (u_lo + u) * BU, b);
+                tma_load_4d(dst + BU_TILE_BYTES + BU_HALF, &tmap_v, bar, 64, hkv, (u_lo + u) * BU, b);
+            };
+            // S = Q K^T, dP = dO V^T (rows = queries) into the unit's score columns
+            auto scores = [&](int u) -> bool {
+                if (!mbar_wait_bounded(&sh.bar_walk[u % BU_RING], (uint32_t)(u / BU_RING) & 1u, BT_WAIT_LIMIT)) return false;
+                tc_fence_after();
+                const uint32_t ka = smem_u32(ring + (u % BU_RING) * 2 * BU_TILE_BYTES), va = ka + BU_TILE_BYTES;
+                const uint32_t ts = tmem_base + (uint32_t)(u % BU_BUFS) * 128;
+                bu_mma_ss(ts, desc_q, smem_desc_sw128(ka, 16, 1024));
+                bu_mma_ss(ts + 64, desc_do, smem_desc_sw128(va, 16, 1024));
+                umma_commit(&sh.bar_s[u % BU_BUFS]);
+                return true;
+            };
+            for (int u = 0; u < BU_RING - 1 && u < n_units; ++u) load_unit(u);
             bool ok = mbar_wait_bounded(&sh.bar_own, 0, BT_WAIT_LIMIT);
-            for (int it = 0; it < n_it && ok; ++it) {
-                const uint32_t ka = smem_u32(sWalk + (it & 1) * 2 * BT_TILE_BYTES), va = ka + BT_TILE_BYTES;
-                ok = mbar_wait_bounded(&sh.bar_walk[it & 1], (uint32_t)(it >> 1) & 1u, BT_WAIT_LIMIT);
+            // the score products run two units ahead of the elementwise threads: their completion is known to the
+            // threads some 900 cycles after the last one has been issued
+            for (int u = 0; u < BU_BUFS - 1 && u < n_units && ok; ++u) ok = scores(u);
+            for (int u = 0; u < n_units && ok; ++u) {
+                // buffer (u + 2) % 3 held unit u - 1, whose dS the gradient product issued in the last round has read
+                // (products of one thread execute in order)
+                if (u + BU_BUFS - 1 < n_units) ok = scores(u + BU_BUFS - 1);
+                if (!ok) break;
+                ok = mbar_wait_bounded(&sh.bar_p[u % BU_BUFS], (uint32_t)(u / BU_BUFS) & 1u, BT_WAIT_LIMIT);
                 if (!ok) break;
                 tc_fence_after();
-                // S = Q K^T, dP = dO V^T: rows = queries
-                bt_mma_ss(tmem_s, desc_q, smem_desc_sw128(ka, 16, 1024));
-                bt_mma_ss(tmem_dp, desc_do, smem_desc_sw128(va, 16, 1024));
-                umma_commit(&sh.bar_s);
-                if (it >= 1) ok = mbar_wait_bounded(&sh.bar_d, (uint32_t)(it - 1) & 1u, BT_WAIT_LIMIT);
-                if (!ok) break;
-                if (it + 1 < n_it) load_walk(it + 1);
-                ok = mbar_wait_bounded(&sh.bar_p, (uint32_t)it & 1u, BT_WAIT_LIMIT);
-                if (!ok) break;
-                tc_fence_after();
-                // dQ += dS K: the K tile in place as an MN-major operand (contraction over keys)
-                bt_mma_ts(tmem_dq, tmem_s, smem_desc_sw128(ka, BT_HALF, 1024), it > 0);
-                umma_commit(&sh.bar_d);
+                // dQ += dS K with the unit's K tile in place as an MN-major operand (contraction over its keys)
+                const uint32_t ka = smem_u32(ring + (u % BU_RING) * 2 * BU_TILE_BYTES);
+                bu_mma_ts(tmem_dq, tmem_base + (uint32_t)(u % BU_BUFS) * 128, smem_desc_sw128(ka, BU_HALF, 1024), u > 0);
+                umma_commit(&sh.bar_d[u & 1]);
+                // the ring slot of unit u + 4 held unit u - 1: free once that unit's gradient product has completed
+                if (u + BU_RING - 1 < n_units) {
+                    if (u >= 1) ok = mbar_wait_bounded(&sh.bar_d[(u - 1) & 1], (uint32_t)((u - 1) >> 1) & 1u, BT_WAIT_LIMIT);
+                    if (!ok) break;
+                    load_unit(u + BU_RING - 1);
+                }
             }
             if (!ok) timed_out();
         }
@@ -432,7 +494,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     } else {
         // =============== elementwise threads: two per query of the block =============================
         const int qr = tid & (BT - 1);  // accumulator row == TMEM lane
-        const int half = tid >> 7;      // which 64 of the 128 key columns (and, at the end, of the channels)
+        const int half = tid >> 7;      // which 32 of a unit's 64 key columns (and, at the end, which 64 channels)
         const int qp = q0 + qr;         // the query's position
         const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
         bool aborted = false;
@@ -450,27 +512,28 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             neg_lse2 = l == -INFINITY ? -INFINITY : -l * 1.4426950408889634f;
             delta_s = p.delta[o] * p.scale;
         }
-        for (int it = 0; it < n_it; ++it) {
-            const int jblk = j_lo + it, k0 = jblk * BT;
-            if (!warp_wait(&sh.bar_s, (uint32_t)it & 1u)) {
+        const float2 scale_log2_2 = make_float2(p.scale_log2, p.scale_log2), scale_2 = make_float2(p.scale, p.scale);
+        const float2 neg_lse2_2 = make_float2(neg_lse2, neg_lse2), neg_delta_2 = make_float2(-delta_s, -delta_s);
+        const float2 zero_2 = make_float2(0.f, 0.f);
+        for (int u = 0; u < n_units; ++u) {
+            const int k0 = (u_lo + u) * BU, buf = u % BU_BUFS;
+            if (!warp_wait(&sh.bar_s[buf], (uint32_t)(u / BU_BUFS) & 1u)) {
                 timed_out();
                 aborted = true;
                 break;
             }
             tc_fence_after();
-            // this query sees the block's keys [c_lo, c_hi)
-            const bool edge = (jblk == ib) || (p.window_left >= 0 && q0 + BT - 1 - k0 > p.window_left);
+            // only units on the diagonal or at the window's edge need masking: this query sees the unit's keys [c_lo, c_hi)
+            const bool edge = (k0 + BU - 1 > q0) || (p.window_left >= 0 && q0 + BT - 1 - k0 > p.window_left);
             const int c_hi = qp - k0 + 1;
             const int c_lo = p.window_left >= 0 ? qp - p.window_left - k0 : 0;
-            const float2 scale_log2_2 = make_float2(p.scale_log2, p.scale_log2), scale_2 = make_float2(p.scale, p.scale);
-            const float2 neg_lse2_2 = make_float2(neg_lse2, neg_lse2), neg_delta_2 = make_float2(-delta_s, -delta_s);
-            const float2 zero_2 = make_float2(0.f, 0.f);
-            // two copies of the loop: the masked one only runs for the few blocks that need it
-            auto chunk = [&](auto masked, int cc) {
+            const int col0 = half * 32;
+            const uint32_t t_s = tmem_base + (uint32_t)buf * 128 + lane_sel + col0;
+            // two copies of the loop: the masked one only runs for the few units that need it
+            auto chunk = [&](auto masked) {
                 constexpr bool MASKED = decltype(masked)::value;
-                const int col0 = half * 64 + cc * 32;
                 float s[32], d[32];
-                tmem_ld32x2(tmem_s + lane_sel + col0, s, tmem_dp + lane_sel + col0, d);
+                tmem_ld32x2(t_s, s, t_s + 64, d);
                 uint32_t dw[16];
 #pragma unroll
                 for (int c = 0; c < 32; c += 2) {
@@ -486,22 +549,16 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                     const float2 ds = ffma2(pe, t, zero_2);
                     dw[c / 2] = pack_bf16x2(ds.x, ds.y);
                 }
-                // over the front of this thread's own fp32 scores, all of which it has read by now
-                tmem_st_words(tmem_s + lane_sel + half * 64 + cc * 16, dw);
+                tmem_st_words(t_s, dw);  // over the front of this thread's own fp32 scores, all of which it has read by now
             };
-            if (edge) {
-                chunk(std::true_type{}, 0);
-                chunk(std::true_type{}, 1);
-            } else {
-                chunk(std::false_type{}, 0);
-                chunk(std::false_type{}, 1);
-            }
+            if (edge) chunk(std::true_type{});
+            else chunk(std::false_type{});
             tc_fence_before();
             __syncwarp();
-            if ((tid & 31) == 0) mbar_arrive(&sh.bar_p);
+            if ((tid & 31) == 0) mbar_arrive(&sh.bar_p[buf]);
         }
         if (!aborted) {
-            if (warp_wait(&sh.bar_d, (uint32_t)(n_it - 1) & 1u)) {
+            if (warp_wait(&sh.bar_d[(n_units - 1) & 1], (uint32_t)((n_units - 1) >> 1) & 1u)) {
                 tc_fence_after();
                 const bool live = qp < p.T;
                 bt_store_half_row(tmem_dq + lane_sel + half * 64,
@@ -573,6 +630,10 @@ extern "C" int nckv_flash_attn_bwd(const void *q, const void *k, const void *v, 
     if (rc == NCKV_OK) rc = make_kv_tensor_map(&mdo, dout, B, T, Hq, (int64_t)T * Hq * D, (int64_t)Hq * D, BT);
     if (rc == NCKV_OK) rc = make_kv_tensor_map(&mk, k, B, T, Hkv, (int64_t)T * Hkv * D, (int64_t)Hkv * D, BT);
     if (rc == NCKV_OK) rc = make_kv_tensor_map(&mv, v, B, T, Hkv, (int64_t)T * Hkv * D, (int64_t)Hkv * D, BT);
+    // the dQ kernel walks K and V in units of 64 rows
+    CUtensorMap mk_unit, mv_unit;
+    if (rc == NCKV_OK) rc = make_kv_tensor_map(&mk_unit, k, B, T, Hkv, (int64_t)T * Hkv * D, (int64_t)Hkv * D, BU);
+    if (rc == NCKV_OK) rc = make_kv_tensor_map(&mv_unit, v, B, T, Hkv, (int64_t)T * Hkv * D, (int64_t)Hkv * D, BU);
     if (rc != NCKV_OK) return rc;
 
     const long long rows = (long long)B * T * Hq;
@@ -586,12 +647,12 @@ extern "C" int nckv_flash_attn_bwd(const void *q, const void *k, const void *v, 
     NCKV_CUDA_CHECK(cudaGetDevice(&dev));
     if (dev < 64 && !attr_set[dev]) {
         NCKV_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BT_SMEM_BYTES));
-        NCKV_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BT_SMEM_BYTES));
+        NCKV_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BU_SMEM_BYTES));
         attr_set[dev] = true;
     }
     attn_bwd_dkdv_kernel<<<(unsigned)(n_blocks * Hkv * B), BT_THREADS, BT_SMEM_BYTES, st>>>(mq, mk, mv, mdo, p);
     NCKV_CUDA_CHECK(cudaGetLastError());
-    attn_bwd_dq_kernel<<<(unsigned)(n_blocks * Hq * B), BT_THREADS, BT_SMEM_BYTES, st>>>(mq, mk, mv, mdo, p);
+    attn_bwd_dq_kernel<<<(unsigned)(n_blocks * Hq * B), BT_THREADS, BU_SMEM_BYTES, st>>>(mq, mk_unit, mv_unit, mdo, p);
     NCKV_CUDA_CHECK(cudaGetLastError());
     return NCKV_OK;
 }
