@@ -21,7 +21,9 @@
 //                  thread), dQ += dS K_u.  Tensor memory holds S and dP of three units (3 x 128 columns) and dQ, so
 //                  the score products run two units ahead of the elementwise threads: a group of products is only
 //                  known to be complete some 900 cycles after its last instruction was issued, and this way
-//                  that latency is not on the threads' path.  (The dK/dV kernel has no columns left for that.)
+//                  that latency is not on the threads' path; a second thread issues the copies, because what
+//                  bounds this kernel is the time of the thread that issues the products.  (The dK/dV kernel has no
+//                  columns left for that.)
 // The dK/dV kernel double-buffers its walked tiles (the copies of step it + 1 are issued as soon as the products of
 // step it - 1 have completed); the dQ kernel keeps a ring of five units.  Every barrier wait is bounded; a wait that
 // runs out sets NCKV_ST_TIMEOUT in the status word, the CTA stops issuing work, frees its tensor memory and returns.
@@ -380,8 +382,10 @@ __device__ __forceinline__ void bu_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint
                          IDESC, (accumulate || ks > 0) ? 1u : 0u);
 }
 
+constexpr int BU_THREADS = BT_EW_THREADS + 64;  // + a warp whose lane 0 issues the products + a warp whose lane 0 issues the copies
+
 // grid: (query blocks x Hq x B), heaviest query blocks (most keys to walk) first
-__global__ void __launch_bounds__(BT_THREADS, 1)
+__global__ void __launch_bounds__(BU_THREADS, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                    const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
                    const BwdParams p) {
@@ -436,15 +440,20 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         atomicOr(p.status, (int)NCKV_ST_TIMEOUT);
     };
 
-    if (warp == BT_EW_THREADS / 32) {
-        // =============== one thread issues the copies and the products ===============================
+    if (warp == BT_EW_THREADS / 32 + 1) {
+        // =============== one thread issues the copies ================================================
         if ((tid & 31) == 0) {
-            const uint64_t desc_q = smem_desc_sw128(smem_u32(sQ), 16, 1024);
-            const uint64_t desc_do = smem_desc_sw128(smem_u32(sdO), 16, 1024);
             mbar_arrive_expect_tx(&sh.bar_own, 2 * BT_TILE_BYTES);
             bt_load_tile(sQ, &tmap_q, &sh.bar_own, hq, q0, b);
             bt_load_tile(sdO, &tmap_do, &sh.bar_own, hq, q0, b);
-            auto load_unit = [&](int u) {
+            bool ok = true;
+            for (int u = 0; u < n_units && ok; ++u) {
+                // the ring slot of unit u held unit u - 5: free once that unit's gradient product has completed
+                if (u >= BU_RING) {
+                    const int w = u - BU_RING;
+                    ok = mbar_wait_bounded(&sh.bar_d[w & 1], (uint32_t)(w >> 1) & 1u, BT_WAIT_LIMIT);
+                    if (!ok) break;
+                }
                 uint8_t *dst = ring + (u % BU_RING) * 2 * BU_TILE_BYTES;
                 uint64_t *bar = &sh.bar_walk[u % BU_RING];
                 mbar_arrive_expect_tx(bar, 2 * BU_TILE_BYTES);
@@ -452,41 +461,58 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                 tma_load_4d(dst + BU_HALF, &tmap_k, bar, 64, hkv, (u_lo + u) * BU, b);
                 tma_load_4d(dst + BU_TILE_BYTES, &tmap_v, bar, 0, hkv, (u_lo + u) * BU, b);
                 tma_load_4d(dst + BU_TILE_BYTES + BU_HALF, &tmap_v, bar, 64, hkv, (u_lo + u) * BU, b);
-            };
-            // S = Q K^T, dP = dO V^T (rows = queries) into the unit's score columns
-            auto scores = [&](int u) -> bool {
-                if (!mbar_wait_bounded(&sh.bar_walk[u % BU_RING], (uint32_t)(u / BU_RING) & 1u, BT_WAIT_LIMIT)) return false;
+            }
+            if (!ok) timed_out();
+        }
+        __syncwarp();
+    } else if (warp == BT_EW_THREADS / 32) {
+        // =============== one thread issues the products ==============================================
+        if ((tid & 31) == 0) {
+            const uint64_t desc_q = smem_desc_sw128(smem_u32(sQ), 16, 1024);
+            const uint64_t desc_do = smem_desc_sw128(smem_u32(sdO), 16, 1024);
+            const uint32_t ring_addr = smem_u32(ring);
+            // S = Q K^T, dP = dO V^T (rows = queries) into score buffer `buf` from ring slot `slot` (phase parities given)
+            auto scores = [&](int slot, uint32_t slot_parity, int buf) -> bool {
+                if (!mbar_wait_bounded(&sh.bar_walk[slot], slot_parity, BT_WAIT_LIMIT)) return false;
                 tc_fence_after();
-                const uint32_t ka = smem_u32(ring + (u % BU_RING) * 2 * BU_TILE_BYTES), va = ka + BU_TILE_BYTES;
-                const uint32_t ts = tmem_base + (uint32_t)(u % BU_BUFS) * 128;
+                const uint32_t ka = ring_addr + (uint32_t)slot * 2 * BU_TILE_BYTES, va = ka + BU_TILE_BYTES;
+                const uint32_t ts = tmem_base + (uint32_t)buf * 128;
                 bu_mma_ss(ts, desc_q, smem_desc_sw128(ka, 16, 1024));
                 bu_mma_ss(ts + 64, desc_do, smem_desc_sw128(va, 16, 1024));
-                umma_commit(&sh.bar_s[u % BU_BUFS]);
+                umma_commit(&sh.bar_s[buf]);
                 return true;
             };
-            for (int u = 0; u < BU_RING - 1 && u < n_units; ++u) load_unit(u);
             bool ok = mbar_wait_bounded(&sh.bar_own, 0, BT_WAIT_LIMIT);
             // the score products run two units ahead of the elementwise threads: their completion is known to the
-            // threads some 900 cycles after the last one has been issued
-            for (int u = 0; u < BU_BUFS - 1 && u < n_units && ok; ++u) ok = scores(u);
+            // threads some 900 cycles after the last one has been issued.  (Counters instead of divisions: this
+            // thread's time per unit is what bounds the kernel.)
+            int s_slot = 0, s_buf = 0;          // ring slot and score buffer of the next unit to get its score products
+            uint32_t s_slot_par = 0;
+            for (int u = 0; u < BU_BUFS - 1 && u < n_units && ok; ++u) {
+                ok = scores(s_slot, s_slot_par, s_buf);
+                if (++s_slot == BU_RING) { s_slot = 0; s_slot_par ^= 1u; }
+                if (++s_buf == BU_BUFS) s_buf = 0;
+            }
+            int g_slot = 0, g_buf = 0;          // the same for the next unit to get its gradient product
+            uint32_t g_buf_par = 0;
             for (int u = 0; u < n_units && ok; ++u) {
                 // buffer (u + 2) % 3 held unit u - 1, whose dS the gradient product issued in the last round has read
                 // (products of one thread execute in order)
-                if (u + BU_BUFS - 1 < n_units) ok = scores(u + BU_BUFS - 1);
+                if (u + BU_BUFS - 1 < n_units) {
+                    ok = scores(s_slot, s_slot_par, s_buf);
+                    if (++s_slot == BU_RING) { s_slot = 0; s_slot_par ^= 1u; }
+                    if (++s_buf == BU_BUFS) s_buf = 0;
+                }
                 if (!ok) break;
-                ok = mbar_wait_bounded(&sh.bar_p[u % BU_BUFS], (uint32_t)(u / BU_BUFS) & 1u, BT_WAIT_LIMIT);
+                ok = mbar_wait_bounded(&sh.bar_p[g_buf], g_buf_par, BT_WAIT_LIMIT);
                 if (!ok) break;
                 tc_fence_after();
                 // dQ += dS K with the unit's K tile in place as an MN-major operand (contraction over its keys)
-                const uint32_t ka = smem_u32(ring + (u % BU_RING) * 2 * BU_TILE_BYTES);
-                bu_mma_ts(tmem_dq, tmem_base + (uint32_t)(u % BU_BUFS) * 128, smem_desc_sw128(ka, BU_HALF, 1024), u > 0);
+                bu_mma_ts(tmem_dq, tmem_base + (uint32_t)g_buf * 128,
+                          smem_desc_sw128(ring_addr + (uint32_t)g_slot * 2 * BU_TILE_BYTES, BU_HALF, 1024), u > 0);
                 umma_commit(&sh.bar_d[u & 1]);
-                // the ring slot of unit u + 4 held unit u - 1: free once that unit's gradient product has completed
-                if (u + BU_RING - 1 < n_units) {
-                    if (u >= 1) ok = mbar_wait_bounded(&sh.bar_d[(u - 1) & 1], (uint32_t)((u - 1) >> 1) & 1u, BT_WAIT_LIMIT);
-                    if (!ok) break;
-                    load_unit(u + BU_RING - 1);
-                }
+                if (++g_slot == BU_RING) g_slot = 0;
+                if (++g_buf == BU_BUFS) { g_buf = 0; g_buf_par ^= 1u; }
             }
             if (!ok) timed_out();
         }
@@ -652,7 +678,7 @@ extern "C" int nckv_flash_attn_bwd(const void *q, const void *k, const void *v, 
     }
     attn_bwd_dkdv_kernel<<<(unsigned)(n_blocks * Hkv * B), BT_THREADS, BT_SMEM_BYTES, st>>>(mq, mk, mv, mdo, p);
     NCKV_CUDA_CHECK(cudaGetLastError());
-    attn_bwd_dq_kernel<<<(unsigned)(n_blocks * Hq * B), BT_THREADS, BU_SMEM_BYTES, st>>>(mq, mk_unit, mv_unit, mdo, p);
+    attn_bwd_dq_kernel<<<(unsigned)(n_blocks * Hq * B), BU_THREADS, BU_SMEM_BYTES, st>>>(mq, mk_unit, mv_unit, mdo, p);
     NCKV_CUDA_CHECK(cudaGetLastError());
     return NCKV_OK;
 }
