@@ -43,7 +43,6 @@ constexpr int BT = 128;                        // keys per dK/dV CTA, queries pe
 constexpr int BT_TILE_BYTES = BT * NCKV_D * 2;  // 32 KB: two 64-channel halves of [128][128 B]
 constexpr int BT_HALF = BT_TILE_BYTES / 2;
 constexpr int BT_EW_THREADS = 256;             // elementwise threads: two per accumulator row, 64 columns each
-constexpr int BT_THREADS = BT_EW_THREADS + 32;  // + the warp whose lane 0 issues copies and products
 constexpr int BT_TMEM_COLS = 512;
 constexpr unsigned long long BT_WAIT_LIMIT = NCKV_WAIT_LIMIT_NS;
 
@@ -86,26 +85,6 @@ __global__ void __launch_bounds__(256) attn_bwd_delta_kernel(const __nv_bfloat16
 }
 
 // ---- pieces shared by the two kernels -------------------------------------------------------------------
-// 128 x 128 x 128 product with both operands K-major in shared memory (rows x channels tiles): D = A B^T.
-__device__ __forceinline__ void bt_mma_ss(uint32_t d_tmem, uint64_t desc_a, uint64_t desc_b) {
-    constexpr uint32_t IDESC = umma_idesc(BT, BT, 0, 0);
-#pragma unroll
-    for (int kk = 0; kk < NCKV_D / 16; ++kk) {
-        const uint64_t off = (uint64_t)(((kk >> 2) * BT_HALF + (kk & 3) * 32) >> 4);
-        umma_bf16(d_tmem, desc_a + off, desc_b + off, IDESC, kk > 0 ? 1u : 0u);
-    }
-}
-// D (+)= A B with A (128 rows x 128 bf16) in tensor memory and B a rows x channels tile used in place as an
-// MN-major operand: the contraction runs over the tile's 128 rows, 16 per instruction.  A sits where the
-// elementwise threads left it: the bf16 of score columns [0, 64) over columns [0, 32) of the fp32 scores, those of
-// score columns [64, 128) over columns [64, 96) (each thread overwrites only scores it has read itself).
-__device__ __forceinline__ void bt_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t desc_b_mn, bool accumulate) {
-    constexpr uint32_t IDESC = umma_idesc(BT, NCKV_D, 0, 1);
-#pragma unroll
-    for (int ks = 0; ks < BT / 16; ++ks)
-        umma_bf16_a_tmem(d_tmem, a_tmem + (uint32_t)(ks * 8 + (ks >= 4 ? 32 : 0)), desc_b_mn + (uint64_t)((ks * 16 * 128) >> 4),
-                         IDESC, (accumulate || ks > 0) ? 1u : 0u);
-}
 __device__ __forceinline__ void bt_load_tile(uint8_t *dst, const CUtensorMap *map, uint64_t *bar, int head, int tok0, int b) {
     tma_load_4d(dst, map, bar, 0, head, tok0, b);
     tma_load_4d(dst + BT_HALF, map, bar, 64, head, tok0, b);
@@ -125,231 +104,12 @@ __device__ __forceinline__ void bt_store_half_row(uint32_t taddr, __nv_bfloat16 
     }
 }
 
-struct BtShared {  // behind the operand tiles
-    uint64_t bar_own, bar_walk[2], bar_s, bar_p, bar_d;
-    uint32_t tmem_slot;
-    int abort_flag;
-    // dK/dV kernel: the walked queries' values, one per accumulator column: -lse * log2(e) and delta / sqrt(D)
-    alignas(16) float neg_lse2[2][BT];
-    alignas(16) float delta_s[2][BT];
-};
-constexpr int BT_SMEM_BYTES = 6 * BT_TILE_BYTES + (int)sizeof(BtShared);
-
-// grid: (key blocks x Hkv x B), heaviest key blocks (most query blocks to walk) first
-__global__ void __launch_bounds__(BT_THREADS, 1)
-attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                     const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
-                     const BwdParams p) {
-    extern __shared__ __align__(1024) uint8_t smem[];
-    if ((smem_u32(smem) & 1023u) != 0) {  // uniform; checked rather than assumed
-        if (threadIdx.x == 0) atomicOr(p.status, (int)NCKV_ST_TIMEOUT);
-        return;
-    }
-    uint8_t *sK = smem, *sV = smem + BT_TILE_BYTES;
-    uint8_t *sWalk = smem + 2 * BT_TILE_BYTES;  // [2][Q tile, dO tile]
-    BtShared &sh = *reinterpret_cast<BtShared *>(smem + 6 * BT_TILE_BYTES);
-
-    const int tid = threadIdx.x, warp = tid >> 5;
-    const int pairs = p.B * p.Hkv;
-    const int jb = blockIdx.x / pairs;  // key blocks in ascending order: the first ones walk the most query blocks
-    const int hkv = (blockIdx.x % pairs) % p.Hkv, b = (blockIdx.x % pairs) / p.Hkv;
-    const int k0 = jb * BT;
-    const int rep = p.Hq / p.Hkv;
-    // query blocks that see a key of this block: causal from the diagonal on, up to the window's reach
-    const int i_lo = jb;
-    const int i_hi = p.window_left >= 0 ? min(p.n_blocks - 1, (k0 + BT - 1 + p.window_left) / BT) : p.n_blocks - 1;
-    const int per_head = i_hi - i_lo + 1;
-    const int n_it = per_head * rep;  // >= 1
-
-    if (tid == 0) {
-        prefetch_tensormap(&tmap_q);
-        prefetch_tensormap(&tmap_k);
-        prefetch_tensormap(&tmap_v);
-        prefetch_tensormap(&tmap_do);
-        mbar_init(&sh.bar_own, 1);
-        mbar_init(&sh.bar_walk[0], 1);
-        mbar_init(&sh.bar_walk[1], 1);
-        mbar_init(&sh.bar_s, 1);
-        mbar_init(&sh.bar_p, BT_EW_THREADS / 32);
-        mbar_init(&sh.bar_d, 1);
-        sh.abort_flag = 0;
-        fence_mbar_init();
-    }
-    if (warp == 0) {
-        tmem_alloc(&sh.tmem_slot, BT_TMEM_COLS);
-        tmem_relinquish();
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = sh.tmem_slot;
-    const uint32_t tmem_s = tmem_base, tmem_dp = tmem_base + 128, tmem_dv = tmem_base + 256, tmem_dk = tmem_base + 384;
-    volatile int *abort_flag = &sh.abort_flag;
-    auto timed_out = [&]() {
-        *abort_flag = 1;
-        atomicOr(p.status, (int)NCKV_ST_TIMEOUT);
-    };
-
-    if (warp == BT_EW_THREADS / 32) {
-        // =============== one thread issues the copies and the products ===============================
-        if ((tid & 31) == 0) {
-            const uint64_t desc_k = smem_desc_sw128(smem_u32(sK), 16, 1024);
-            const uint64_t desc_v = smem_desc_sw128(smem_u32(sV), 16, 1024);
-            auto load_walk = [&](int it) {
-                const int hq = hkv * rep + it / per_head, i = i_lo + it % per_head;
-                uint8_t *dst = sWalk + (it & 1) * 2 * BT_TILE_BYTES;
-                mbar_arrive_expect_tx(&sh.bar_walk[it & 1], 2 * BT_TILE_BYTES);
-                bt_load_tile(dst, &tmap_q, &sh.bar_walk[it & 1], hq, i * BT, b);
-                bt_load_tile(dst + BT_TILE_BYTES, &tmap_do, &sh.bar_walk[it & 1], hq, i * BT, b);
-            };
-            mbar_arrive_expect_tx(&sh.bar_own, 2 * BT_TILE_BYTES);
-            bt_load_tile(sK, &tmap_k, &sh.bar_own, hkv, k0, b);
-            bt_load_tile(sV, &tmap_v, &sh.bar_own, hkv, k0, b);
-            load_walk(0);
-            bool ok = mbar_wait_bounded(&sh.bar_own, 0, BT_WAIT_LIMIT);
-            for (int it = 0; it < n_it && ok; ++it) {
-                const uint32_t qa = smem_u32(sWalk + (it & 1) * 2 * BT_TILE_BYTES), da = qa + BT_TILE_BYTES;
-                ok = mbar_wait_bounded(&sh.bar_walk[it & 1], (uint32_t)(it >> 1) & 1u, BT_WAIT_LIMIT);
-                if (!ok) break;
-                tc_fence_after();
-                // S^T = K Q^T, dP^T = V dO^T: rows = keys.  Issued behind the products of the step before, which
-                // read P^T / dS^T from the columns these overwrite (products of one thread execute in order).
-                bt_mma_ss(tmem_s, desc_k, smem_desc_sw128(qa, 16, 1024));
-                bt_mma_ss(tmem_dp, desc_v, smem_desc_sw128(da, 16, 1024));
-                umma_commit(&sh.bar_s);
-                // the other walk buffer is free once the second group of products of step it - 1 has completed
-                if (it >= 1) ok = mbar_wait_bounded(&sh.bar_d, (uint32_t)(it - 1) & 1u, BT_WAIT_LIMIT);
-                if (!ok) break;
-                if (it + 1 < n_it) load_walk(it + 1);
-                ok = mbar_wait_bounded(&sh.bar_p, (uint32_t)it & 1u, BT_WAIT_LIMIT);
-                if (!ok) break;
-                tc_fence_after();
-                // dV += P^T dO, dK += dS^T Q: the walked tiles in place as MN-major operands (contraction over queries)
-                bt_mma_ts(tmem_dv, tmem_s, smem_desc_sw128(da, BT_HALF, 1024), it > 0);
-                bt_mma_ts(tmem_dk, tmem_dp, smem_desc_sw128(qa, BT_HALF, 1024), it > 0);
-                umma_commit(&sh.bar_d);
-            }
-            if (!ok) timed_out();
-        }
-        __syncwarp();
-    } else {
-        // =============== elementwise threads: two per key of the block ===============================
-        const int kr = tid & (BT - 1);  // accumulator row == TMEM lane
-        const int half = tid >> 7;      // which 64 of the 128 query columns
-        const int kp = k0 + kr;         // the key's position
-        const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
-        bool aborted = false;
-        auto warp_wait = [&](uint64_t *bar, uint32_t parity) -> bool {
-            int ok = 1;
-            if ((tid & 31) == 0) ok = mbar_wait_bounded(bar, parity, BT_WAIT_LIMIT) ? 1 : 0;
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            __syncwarp();
-            return ok != 0;
-        };
-        for (int it = 0; it < n_it; ++it) {
-            const int hq = hkv * rep + it / per_head, i = i_lo + it % per_head;
-            const int q0 = i * BT, buf = it & 1;
-            // the first 128 threads fetch -lse * log2(e), the others delta / sqrt(D), of query q0 + kr for everybody;
-            // in flight during the wait for the scores
-            const int tq = q0 + kr;
-            float mine = half == 0 ? -INFINITY : 0.f;  // a query past the end: P = 2^-inf = 0
-            if (tq < p.T) {
-                const long long o = ((long long)b * p.Hq + hq) * p.T + tq;
-                if (half == 0) {
-                    const float l = p.lse[o];
-                    mine = l == -INFINITY ? -INFINITY : -l * 1.4426950408889634f;
-                } else {
-                    mine = p.delta[o] * p.scale;
-                }
-            }
-            // (all eight warps take the same decision here: they meet at a named barrier right below)
-            if (!warp_wait(&sh.bar_s, (uint32_t)it & 1u)) {
-                timed_out();
-                aborted = true;
-                break;
-            }
-            tc_fence_after();
-            (half == 0 ? sh.neg_lse2 : sh.delta_s)[buf][kr] = mine;
-            asm volatile("bar.sync 1, 256;" ::: "memory");  // the eight elementwise warps
-            // only blocks on the diagonal or at the window's edge need masking: this key is seen by the
-            // block's queries [c_lo, c_hi)
-            const bool edge = (i == jb) || (p.window_left >= 0 && q0 + BT - 1 - k0 > p.window_left);
-            const int c_lo = kp - q0;
-            const int c_hi = p.window_left >= 0 ? kp + p.window_left - q0 + 1 : BT;
-            const float2 scale_log2_2 = make_float2(p.scale_log2, p.scale_log2), scale_2 = make_float2(p.scale, p.scale);
-            const float2 zero_2 = make_float2(0.f, 0.f);
-            // two copies of the loop: the masked one only runs for the few blocks that need it
-            auto chunk = [&](auto masked, int cc) {
-                constexpr bool MASKED = decltype(masked)::value;
-                const int col0 = half * 64 + cc * 32;
-                float s[32], d[32];
-                tmem_ld32x2(tmem_s + lane_sel + col0, s, tmem_dp + lane_sel + col0, d);
-                uint32_t pw[16], dw[16];
-#pragma unroll
-                for (int c = 0; c < 32; c += 4) {
-                    const float4 nl = *reinterpret_cast<const float4 *>(&sh.neg_lse2[buf][col0 + c]);
-                    const float4 dl = *reinterpret_cast<const float4 *>(&sh.delta_s[buf][col0 + c]);
-                    // P = 2^(s * scale * log2(e) - lse * log2(e));  dS = P * (dP * scale - delta * scale)
-                    const float2 x01 = ffma2(make_float2(s[c], s[c + 1]), scale_log2_2, make_float2(nl.x, nl.y));
-                    const float2 x23 = ffma2(make_float2(s[c + 2], s[c + 3]), scale_log2_2, make_float2(nl.z, nl.w));
-                    const float2 t01 = ffma2(make_float2(d[c], d[c + 1]), scale_2, make_float2(-dl.x, -dl.y));
-                    const float2 t23 = ffma2(make_float2(d[c + 2], d[c + 3]), scale_2, make_float2(-dl.z, -dl.w));
-                    float2 p01 = make_float2(ex2_approx(x01.x), ex2_approx(x01.y));
-                    float2 p23 = make_float2(ex2_approx(x23.x), ex2_approx(x23.y));
-                    if (MASKED) {
-                        const int col = col0 + c;
-                        if (!(col >= c_lo && col < c_hi)) p01.x = 0.f;
-                        if (!(col + 1 >= c_lo && col + 1 < c_hi)) p01.y = 0.f;
-                        if (!(col + 2 >= c_lo && col + 2 < c_hi)) p23.x = 0.f;
-                        if (!(col + 3 >= c_lo && col + 3 < c_hi)) p23.y = 0.f;
-                    }
-                    const float2 ds01 = ffma2(p01, t01, zero_2), ds23 = ffma2(p23, t23, zero_2);
-                    pw[c / 2] = pack_bf16x2(p01.x, p01.y);
-                    pw[c / 2 + 1] = pack_bf16x2(p23.x, p23.y);
-                    dw[c / 2] = pack_bf16x2(ds01.x, ds01.y);
-                    dw[c / 2 + 1] = pack_bf16x2(ds23.x, ds23.y);
-                }
-                // bf16 over the front of this thread's own fp32 scores, all of which it has read by now
-                tmem_st_words(tmem_s + lane_sel + half * 64 + cc * 16, pw);
-                tmem_st_words(tmem_dp + lane_sel + half * 64 + cc * 16, dw);
-            };
-            if (edge) {
-                chunk(std::true_type{}, 0);
-                chunk(std::true_type{}, 1);
-            } else {
-                chunk(std::false_type{}, 0);
-                chunk(std::false_type{}, 1);
-            }
-            tc_fence_before();
-            __syncwarp();
-            if ((tid & 31) == 0) mbar_arrive(&sh.bar_p);
-        }
-        if (!aborted) {
-            if (warp_wait(&sh.bar_d, (uint32_t)(n_it - 1) & 1u)) {
-                tc_fence_after();
-                const bool live = kp < p.T;
-                const long long o = (((long long)b * p.T + (live ? kp : 0)) * p.Hkv + hkv) * NCKV_D;
-                // the first 128 threads store dV, the others dK
-                const uint32_t acc = (half == 0 ? tmem_dv : tmem_dk) + lane_sel;
-                __nv_bfloat16 *dst = (half == 0 ? p.dv : p.dk) + o;
-                bt_store_half_row(acc, dst, live);
-                bt_store_half_row(acc + 64, dst + 64, live);
-            } else {
-                timed_out();
-            }
-        }
-    }
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 0) tmem_dealloc(tmem_base, BT_TMEM_COLS);
-}
-
-// ---- dQ kernel: the walked keys come 64 at a step ("unit"), three units' scores in tensor memory ----------
-constexpr int BU = 64;                          // keys per unit
+// ---- walked rows come 64 at a step ("unit"): queries in the dK/dV kernel, keys in the dQ kernel ---------------
+constexpr int BU = 64;                          // walked rows per unit
 constexpr int BU_TILE_BYTES = BU * NCKV_D * 2;  // 16 KB: two 64-channel halves of [64][128 B]
 constexpr int BU_HALF = BU_TILE_BYTES / 2;
-constexpr int BU_RING = 5;                      // units (one K and one V tile each) in shared memory
-constexpr int BU_BUFS = 3;                      // units whose S and dP are in tensor memory: the score products run two units ahead
+constexpr int BU_RING = 5;                      // units (two tiles each) in shared memory
+constexpr int BU_BUFS = 3;                      // dQ kernel: units whose S and dP are in tensor memory (score products two units ahead)
 
 struct BuShared {  // behind the operand tiles of the dQ kernel
     // bar_walk[u % 5] (phase u / 5) "the unit's K and V tiles have landed"; bar_s[u % 3] (phase u / 3) "its score products
@@ -383,6 +143,266 @@ __device__ __forceinline__ void bu_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint
 }
 
 constexpr int BU_THREADS = BT_EW_THREADS + 64;  // + a warp whose lane 0 issues the products + a warp whose lane 0 issues the copies
+
+struct BvShared {  // behind the operand tiles of the dK/dV kernel
+    // bar_walk[u % 5] (phase u / 5) "the unit's Q and dO tiles have landed"; bar_s[u & 1] (phase u / 2) "its score
+    // products are complete"; bar_p[u & 1] "its P^T and dS^T are in tensor memory"; bar_d[u & 1] "its gradient products
+    // are complete"
+    uint64_t bar_own, bar_walk[BU_RING], bar_s[2], bar_p[2], bar_d[2];
+    uint32_t tmem_slot;
+    int abort_flag;
+    // the walked queries' values, one per accumulator column: -lse * log2(e) and delta / sqrt(D)
+    alignas(16) float neg_lse2[2][BU];
+    alignas(16) float delta_s[2][BU];
+};
+constexpr int BV_SMEM_BYTES = 2 * BT_TILE_BYTES + BU_RING * 2 * BU_TILE_BYTES + (int)sizeof(BvShared);
+
+// grid: (key blocks x Hkv x B), heaviest key blocks (most queries to walk) first
+__global__ void __launch_bounds__(BU_THREADS, 1)
+attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                     const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
+                     const BwdParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    if ((smem_u32(smem) & 1023u) != 0) {  // uniform; checked rather than assumed
+        if (threadIdx.x == 0) atomicOr(p.status, (int)NCKV_ST_TIMEOUT);
+        return;
+    }
+    uint8_t *sK = smem, *sV = smem + BT_TILE_BYTES;
+    uint8_t *ring = smem + 2 * BT_TILE_BYTES;  // [5][Q unit, dO unit]
+    BvShared &sh = *reinterpret_cast<BvShared *>(ring + BU_RING * 2 * BU_TILE_BYTES);
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int pairs = p.B * p.Hkv;
+    const int jb = blockIdx.x / pairs;  // key blocks in ascending order: the first ones walk the most queries
+    const int hkv = (blockIdx.x % pairs) % p.Hkv, b = (blockIdx.x % pairs) / p.Hkv;
+    const int k0 = jb * BT;
+    const int rep = p.Hq / p.Hkv;
+    // query units (64 rows) that see a key of this block: causal from the diagonal on, up to the window's reach
+    const int u_lo = 2 * jb;
+    const int u_last = (p.T + BU - 1) / BU - 1;
+    const int u_hi = p.window_left >= 0 ? min(u_last, (k0 + BT - 1 + p.window_left) / BU) : u_last;
+    const int per_head = u_hi - u_lo + 1;
+    const int n_units = per_head * rep;  // >= 1
+
+    if (tid == 0) {
+        prefetch_tensormap(&tmap_q);
+        prefetch_tensormap(&tmap_k);
+        prefetch_tensormap(&tmap_v);
+        prefetch_tensormap(&tmap_do);
+        mbar_init(&sh.bar_own, 1);
+        for (int i = 0; i < BU_RING; ++i) mbar_init(&sh.bar_walk[i], 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&sh.bar_s[i], 1);
+            mbar_init(&sh.bar_p[i], BT_EW_THREADS / 32);
+            mbar_init(&sh.bar_d[i], 1);
+        }
+        sh.abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 0) {
+        tmem_alloc(&sh.tmem_slot, BT_TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = sh.tmem_slot;
+    // unit u: S^T at columns 128 (u & 1) + [0, 64), dP^T at + [64, 128); dV at [256, 384), dK at [384, 512)
+    const uint32_t tmem_dv = tmem_base + 256, tmem_dk = tmem_base + 384;
+    auto timed_out = [&]() {
+        sh.abort_flag = 1;
+        atomicOr(p.status, (int)NCKV_ST_TIMEOUT);
+    };
+
+    if (warp == BT_EW_THREADS / 32 + 1) {
+        // =============== one thread issues the copies ================================================
+        if ((tid & 31) == 0) {
+            mbar_arrive_expect_tx(&sh.bar_own, 2 * BT_TILE_BYTES);
+            bt_load_tile(sK, &tmap_k, &sh.bar_own, hkv, k0, b);
+            bt_load_tile(sV, &tmap_v, &sh.bar_own, hkv, k0, b);
+            bool ok = true;
+            for (int u = 0; u < n_units && ok; ++u) {
+                // the ring slot of unit u held unit u - 5: free once that unit's gradient products have completed
+                if (u >= BU_RING) {
+                    const int w = u - BU_RING;
+                    ok = mbar_wait_bounded(&sh.bar_d[w & 1], (uint32_t)(w >> 1) & 1u, BT_WAIT_LIMIT);
+                    if (!ok) break;
+                }
+                const int hq = hkv * rep + u / per_head, q0 = (u_lo + u % per_head) * BU;
+                uint8_t *dst = ring + (u % BU_RING) * 2 * BU_TILE_BYTES;
+                uint64_t *bar = &sh.bar_walk[u % BU_RING];
+                mbar_arrive_expect_tx(bar, 2 * BU_TILE_BYTES);
+                tma_load_4d(dst, &tmap_q, bar, 0, hq, q0, b);
+                tma_load_4d(dst + BU_HALF, &tmap_q, bar, 64, hq, q0, b);
+                tma_load_4d(dst + BU_TILE_BYTES, &tmap_do, bar, 0, hq, q0, b);
+                tma_load_4d(dst + BU_TILE_BYTES + BU_HALF, &tmap_do, bar, 64, hq, q0, b);
+            }
+            if (!ok) timed_out();
+        }
+        __syncwarp();
+    } else if (warp == BT_EW_THREADS / 32) {
+        // =============== one thread issues the products ==============================================
+        if ((tid & 31) == 0) {
+            const uint64_t desc_k = smem_desc_sw128(smem_u32(sK), 16, 1024);
+            const uint64_t desc_v = smem_desc_sw128(smem_u32(sV), 16, 1024);
+            const uint32_t ring_addr = smem_u32(ring);
+            // S^T = K Q^T, dP^T = V dO^T (rows = keys) into score buffer `buf` from ring slot `slot`
+            auto scores = [&](int slot, uint32_t slot_parity, int buf) -> bool {
+                if (!mbar_wait_bounded(&sh.bar_walk[slot], slot_parity, BT_WAIT_LIMIT)) return false;
+                tc_fence_after();
+                const uint32_t qa = ring_addr + (uint32_t)slot * 2 * BU_TILE_BYTES, da = qa + BU_TILE_BYTES;
+                const uint32_t ts = tmem_base + (uint32_t)buf * 128;
+                bu_mma_ss(ts, desc_k, smem_desc_sw128(qa, 16, 1024));
+                bu_mma_ss(ts + 64, desc_v, smem_desc_sw128(da, 16, 1024));
+                umma_commit(&sh.bar_s[buf]);
+                return true;
+            };
+            bool ok = mbar_wait_bounded(&sh.bar_own, 0, BT_WAIT_LIMIT);
+            // The score products run one unit ahead of the elementwise threads (tensor memory has room for two units'
+            // scores beside dV and dK).  Counters instead of divisions: this thread's time per unit bounds the kernel.
+            int s_slot = 0;
+            uint32_t s_slot_par = 0;
+            if (ok) {
+                ok = scores(0, 0, 0);
+                s_slot = 1;
+            }
+            int g_slot = 0;
+            for (int u = 0; u < n_units && ok; ++u) {
+                // buffer (u + 1) & 1 held unit u - 1, whose P^T / dS^T the gradient products issued in the last round
+                // have read (products of one thread execute in order)
+                if (u + 1 < n_units) {
+                    ok = scores(s_slot, s_slot_par, (u + 1) & 1);
+                    if (++s_slot == BU_RING) { s_slot = 0; s_slot_par ^= 1u; }
+                }
+                if (!ok) break;
+                ok = mbar_wait_bounded(&sh.bar_p[u & 1], (uint32_t)(u >> 1) & 1u, BT_WAIT_LIMIT);
+                if (!ok) break;
+                tc_fence_after();
+                // dV += P^T dO, dK += dS^T Q with the unit's tiles in place as MN-major operands (contraction over its queries)
+                const uint32_t qa = ring_addr + (uint32_t)g_slot * 2 * BU_TILE_BYTES, da = qa + BU_TILE_BYTES;
+                const uint32_t ts = tmem_base + (uint32_t)(u & 1) * 128;
+                bu_mma_ts(tmem_dv, ts, smem_desc_sw128(da, BU_HALF, 1024), u > 0);
+                bu_mma_ts(tmem_dk, ts + 64, smem_desc_sw128(qa, BU_HALF, 1024), u > 0);
+                umma_commit(&sh.bar_d[u & 1]);
+                if (++g_slot == BU_RING) g_slot = 0;
+            }
+            if (!ok) timed_out();
+        }
+        __syncwarp();
+    } else {
+        // =============== elementwise threads: two per key of the block ===============================
+        const int kr = tid & (BT - 1);  // accumulator row == TMEM lane
+        const int half = tid >> 7;      // which 32 of a unit's 64 query columns (and, at the end, dV or dK)
+        const int kp = k0 + kr;         // the key's position
+        const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
+        bool aborted = false;
+        auto warp_wait = [&](uint64_t *bar, uint32_t parity) -> bool {
+            int ok = 1;
+            if ((tid & 31) == 0) ok = mbar_wait_bounded(bar, parity, BT_WAIT_LIMIT) ? 1 : 0;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            __syncwarp();
+            return ok != 0;
+        };
+        const float2 scale_log2_2 = make_float2(p.scale_log2, p.scale_log2), scale_2 = make_float2(p.scale, p.scale);
+        const float2 zero_2 = make_float2(0.f, 0.f);
+        int head = 0, in_head = 0;  // u / per_head, u % per_head
+        for (int u = 0; u < n_units; ++u) {
+            const int hq = hkv * rep + head, q0 = (u_lo + in_head) * BU;
+            if (++in_head == per_head) { in_head = 0; ++head; }
+            const int buf = u & 1;
+            // threads 0-63 fetch -lse * log2(e), threads 64-127 delta / sqrt(D), of one of the unit's queries for
+            // everybody; in flight during the wait for the scores
+            float mine = 0.f;
+            if (tid < 2 * BU) {
+                const int tq = q0 + (tid & (BU - 1));
+                mine = tid < BU ? -INFINITY : 0.f;  // a query past the end: P = 2^-inf = 0
+                if (tq < p.T) {
+                    const long long o = ((long long)b * p.Hq + hq) * p.T + tq;
+                    if (tid < BU) {
+                        const float l = p.lse[o];
+                        mine = l == -INFINITY ? -INFINITY : -l * 1.4426950408889634f;
+                    } else {
+                        mine = p.delta[o] * p.scale;
+                    }
+                }
+            }
+            // (all eight warps take the same decision here: they meet at a named barrier right below)
+            if (!warp_wait(&sh.bar_s[buf], (uint32_t)(u >> 1) & 1u)) {
+                timed_out();
+                aborted = true;
+                break;
+            }
+            tc_fence_after();
+            if (tid < BU) sh.neg_lse2[buf][tid] = mine;
+            else if (tid < 2 * BU) sh.delta_s[buf][tid - BU] = mine;
+            asm volatile("bar.sync 1, 256;" ::: "memory");  // the eight elementwise warps
+            // only units on the diagonal or at the window's edge need masking: this key is seen by the unit's
+            // queries [c_lo, c_hi)
+            const bool edge = (q0 < k0 + BT - 1) || (p.window_left >= 0 && q0 + BU - 1 - k0 > p.window_left);
+            const int c_lo = kp - q0;
+            const int c_hi = p.window_left >= 0 ? kp + p.window_left - q0 + 1 : BU;
+            const int col0 = half * 32;
+            const uint32_t t_s = tmem_base + (uint32_t)buf * 128 + lane_sel + col0;
+            const float *nls = &sh.neg_lse2[buf][col0], *dls = &sh.delta_s[buf][col0];
+            // two copies of the loop: the masked one only runs for the few units that need it
+            auto chunk = [&](auto masked) {
+                constexpr bool MASKED = decltype(masked)::value;
+                float s[32], d[32];
+                tmem_ld32x2(t_s, s, t_s + 64, d);
+                uint32_t pw[16], dw[16];
+#pragma unroll
+                for (int c = 0; c < 32; c += 4) {
+                    const float4 nl = *reinterpret_cast<const float4 *>(nls + c);
+                    const float4 dl = *reinterpret_cast<const float4 *>(dls + c);
+                    // P = 2^(s * scale * log2(e) - lse * log2(e));  dS = P * (dP * scale - delta * scale)
+                    const float2 x01 = ffma2(make_float2(s[c], s[c + 1]), scale_log2_2, make_float2(nl.x, nl.y));
+                    const float2 x23 = ffma2(make_float2(s[c + 2], s[c + 3]), scale_log2_2, make_float2(nl.z, nl.w));
+                    const float2 t01 = ffma2(make_float2(d[c], d[c + 1]), scale_2, make_float2(-dl.x, -dl.y));
+                    const float2 t23 = ffma2(make_float2(d[c + 2], d[c + 3]), scale_2, make_float2(-dl.z, -dl.w));
+                    float2 p01 = make_float2(ex2_approx(x01.x), ex2_approx(x01.y));
+                    float2 p23 = make_float2(ex2_approx(x23.x), ex2_approx(x23.y));
+                    if (MASKED) {
+                        const int col = col0 + c;
+                        if (!(col >= c_lo && col < c_hi)) p01.x = 0.f;
+                        if (!(col + 1 >= c_lo && col + 1 < c_hi)) p01.y = 0.f;
+                        if (!(col + 2 >= c_lo && col + 2 < c_hi)) p23.x = 0.f;
+                        if (!(col + 3 >= c_lo && col + 3 < c_hi)) p23.y = 0.f;
+                    }
+                    const float2 ds01 = ffma2(p01, t01, zero_2), ds23 = ffma2(p23, t23, zero_2);
+                    pw[c / 2] = pack_bf16x2(p01.x, p01.y);
+                    pw[c / 2 + 1] = pack_bf16x2(p23.x, p23.y);
+                    dw[c / 2] = pack_bf16x2(ds01.x, ds01.y);
+                    dw[c / 2 + 1] = pack_bf16x2(ds23.x, ds23.y);
+                }
+                // bf16 over the front of this thread's own fp32 scores, all of which it has read by now
+                tmem_st_words(t_s, pw);
+                tmem_st_words(t_s + 64, dw);
+            };
+            if (edge) chunk(std::true_type{});
+            else chunk(std::false_type{});
+            tc_fence_before();
+            __syncwarp();
+            if ((tid & 31) == 0) mbar_arrive(&sh.bar_p[buf]);
+        }
+        if (!aborted) {
+            if (warp_wait(&sh.bar_d[(n_units - 1) & 1], (uint32_t)((n_units - 1) >> 1) & 1u)) {
+                tc_fence_after();
+                const bool live = kp < p.T;
+                const long long o = (((long long)b * p.T + (live ? kp : 0)) * p.Hkv + hkv) * NCKV_D;
+                // the first 128 threads store dV, the others dK
+                const uint32_t acc = (half == 0 ? tmem_dv : tmem_dk) + lane_sel;
+                __nv_bfloat16 *dst = (half == 0 ? p.dv : p.dk) + o;
+                bt_store_half_row(acc, dst, live);
+                bt_store_half_row(acc + 64, dst + 64, live);
+            } else {
+                timed_out();
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_base, BT_TMEM_COLS);
+}
 
 // grid: (query blocks x Hq x B), heaviest query blocks (most keys to walk) first
 __global__ void __launch_bounds__(BU_THREADS, 1)
@@ -651,15 +671,16 @@ extern "C" int nckv_flash_attn_bwd(const void *q, const void *k, const void *v, 
     p.scale = (float)(1.0 / sqrt((double)D));
     p.scale_log2 = (float)(1.4426950408889634 / sqrt((double)D));
 
-    CUtensorMap mq, mk, mv, mdo;
-    int rc = make_kv_tensor_map(&mq, q, B, T, Hq, (int64_t)T * Hq * D, (int64_t)Hq * D, BT);
-    if (rc == NCKV_OK) rc = make_kv_tensor_map(&mdo, dout, B, T, Hq, (int64_t)T * Hq * D, (int64_t)Hq * D, BT);
-    if (rc == NCKV_OK) rc = make_kv_tensor_map(&mk, k, B, T, Hkv, (int64_t)T * Hkv * D, (int64_t)Hkv * D, BT);
-    if (rc == NCKV_OK) rc = make_kv_tensor_map(&mv, v, B, T, Hkv, (int64_t)T * Hkv * D, (int64_t)Hkv * D, BT);
-    // the dQ kernel walks K and V in units of 64 rows
-    CUtensorMap mk_unit, mv_unit;
-    if (rc == NCKV_OK) rc = make_kv_tensor_map(&mk_unit, k, B, T, Hkv, (int64_t)T * Hkv * D, (int64_t)Hkv * D, BU);
-    if (rc == NCKV_OK) rc = make_kv_tensor_map(&mv_unit, v, B, T, Hkv, (int64_t)T * Hkv * D, (int64_t)Hkv * D, BU);
+    // every tensor is an own operand (boxes of 128 rows) in one kernel and a walked one (boxes of 64 rows) in the other
+    CUtensorMap mq[2], mk[2], mv[2], mdo[2];
+    int rc = NCKV_OK;
+    for (int i = 0; i < 2 && rc == NCKV_OK; ++i) {
+        const int box = i == 0 ? BT : BU;
+        rc = make_kv_tensor_map(&mq[i], q, B, T, Hq, (int64_t)T * Hq * D, (int64_t)Hq * D, box);
+        if (rc == NCKV_OK) rc = make_kv_tensor_map(&mdo[i], dout, B, T, Hq, (int64_t)T * Hq * D, (int64_t)Hq * D, box);
+        if (rc == NCKV_OK) rc = make_kv_tensor_map(&mk[i], k, B, T, Hkv, (int64_t)T * Hkv * D, (int64_t)Hkv * D, box);
+        if (rc == NCKV_OK) rc = make_kv_tensor_map(&mv[i], v, B, T, Hkv, (int64_t)T * Hkv * D, (int64_t)Hkv * D, box);
+    }
     if (rc != NCKV_OK) return rc;
 
     const long long rows = (long long)B * T * Hq;
@@ -672,13 +693,13 @@ extern "C" int nckv_flash_attn_bwd(const void *q, const void *k, const void *v, 
     int dev = 0;
     NCKV_CUDA_CHECK(cudaGetDevice(&dev));
     if (dev < 64 && !attr_set[dev]) {
-        NCKV_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BT_SMEM_BYTES));
+        NCKV_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BV_SMEM_BYTES));
         NCKV_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BU_SMEM_BYTES));
         attr_set[dev] = true;
     }
-    attn_bwd_dkdv_kernel<<<(unsigned)(n_blocks * Hkv * B), BT_THREADS, BT_SMEM_BYTES, st>>>(mq, mk, mv, mdo, p);
+    attn_bwd_dkdv_kernel<<<(unsigned)(n_blocks * Hkv * B), BU_THREADS, BV_SMEM_BYTES, st>>>(mq[1], mk[0], mv[0], mdo[1], p);
     NCKV_CUDA_CHECK(cudaGetLastError());
-    attn_bwd_dq_kernel<<<(unsigned)(n_blocks * Hq * B), BU_THREADS, BU_SMEM_BYTES, st>>>(mq, mk_unit, mv_unit, mdo, p);
+    attn_bwd_dq_kernel<<<(unsigned)(n_blocks * Hq * B), BU_THREADS, BU_SMEM_BYTES, st>>>(mq[0], mk[1], mv[1], mdo[0], p);
     NCKV_CUDA_CHECK(cudaGetLastError());
     return NCKV_OK;
 }
