@@ -8,25 +8,26 @@
 // Scores and probabilities are recomputed from q, k and the forward's log-sum-exp; nothing is accumulated
 // with atomics, so the gradients are the same bits on every run.  Both kernels follow the forward kernel's
 // forms: operands arrive by TMA into 128-byte-swizzled shared memory, tcgen05.mma accumulates in tensor memory,
-// one thread issues copies and products, eight warps (two threads per accumulator row, 64 columns each) do the
+// one thread issues the products and another the copies, eight warps (two threads per accumulator row) do the
 // elementwise work between the two groups of products and write P / dS back to tensor memory as bf16 over the
-// scores they came from, where the second group of products reads them as its A operand.
+// scores they came from, where the second group of products reads them as its A operand.  A CTA owns 128 rows
+// (two tiles, loaded once) and walks the rows of the other side 64 at a step ("unit") through a ring of five units.
 //
-//   dK/dV kernel   the CTA owns K_j, V_j (128 keys) and walks the query blocks i that see them, for every q head
-//                  of the kv head.  Per step:  S^T = K_j Q_i^T and dP^T = V_j dO_i^T (accumulator rows = keys),
-//                  elementwise over a key's row (lse and delta of the 128 queries come from shared memory),
-//                  dV += P^T dO_i and dK += dS^T Q_i.  Tensor memory: S^T, dP^T, dV, dK = 4 x 128 columns.
-//   dQ kernel      the CTA owns Q_i, dO_i (128 queries of one q head) and walks the keys it sees 64 at a step ("unit").
-//                  Per unit: S = Q_i K_u^T and dP = dO_i V_u^T (accumulator rows = queries, lse and delta are per
-//                  thread), dQ += dS K_u.  Tensor memory holds S and dP of three units (3 x 128 columns) and dQ, so
-//                  the score products run two units ahead of the elementwise threads: a group of products is only
-//                  known to be complete some 900 cycles after its last instruction was issued, and this way
-//                  that latency is not on the threads' path; a second thread issues the copies, because what
-//                  bounds this kernel is the time of the thread that issues the products.  (The dK/dV kernel has no
-//                  columns left for that.)
-// The dK/dV kernel double-buffers its walked tiles (the copies of step it + 1 are issued as soon as the products of
-// step it - 1 have completed); the dQ kernel keeps a ring of five units.  Every barrier wait is bounded; a wait that
-// runs out sets NCKV_ST_TIMEOUT in the status word, the CTA stops issuing work, frees its tensor memory and returns.
+//   dK/dV kernel   the CTA owns K_j, V_j (128 keys) and walks the queries that see them, for every q head of the kv
+//                  head.  Per unit: S^T = K_j Q_u^T and dP^T = V_j dO_u^T (accumulator rows = keys, 64 columns each),
+//                  elementwise over a key's row (lse and delta of the unit's queries come from shared memory),
+//                  dV += P^T dO_u and dK += dS^T Q_u.  Tensor memory: S^T and dP^T of two units (2 x 128 columns), dV,
+//                  dK (128 columns each); the score products run one unit ahead of the elementwise threads.
+//   dQ kernel      the CTA owns Q_i, dO_i (128 queries of one q head) and walks the keys it sees.  Per unit:
+//                  S = Q_i K_u^T and dP = dO_i V_u^T (accumulator rows = queries, lse and delta are per thread),
+//                  dQ += dS K_u.  Tensor memory: S and dP of three units (3 x 128 columns) and dQ; the score
+//                  products run two units ahead.
+// Running ahead matters because a group of products is only known to be complete some 900 cycles after its last
+// instruction was issued; with the scores of the next unit(s) already under way that latency is not on the
+// elementwise threads' path.  What then bounds both kernels is the time of the thread that issues the products
+// (issue runs at the tensor pipe's pace), which is why the copies have a thread of their own and the loops keep
+// counters instead of dividing.  Every barrier wait is bounded; a wait that runs out sets NCKV_ST_TIMEOUT in the
+// status word, the CTA stops issuing work, frees its tensor memory and returns.
 //
 // Replaces: the backward of F.scaled_dot_product_attention / flash_attn_func as reached from
 // flash_attention.py:107-128 during training (gpt.py:108).
@@ -305,16 +306,13 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         };
         const float2 scale_log2_2 = make_float2(p.scale_log2, p.scale_log2), scale_2 = make_float2(p.scale, p.scale);
         const float2 zero_2 = make_float2(0.f, 0.f);
-        int head = 0, in_head = 0;  // u / per_head, u % per_head
-        for (int u = 0; u < n_units; ++u) {
-            const int hq = hkv * rep + head, q0 = (u_lo + in_head) * BU;
-            if (++in_head == per_head) { in_head = 0; ++head; }
-            const int buf = u & 1;
-            // threads 0-63 fetch -lse * log2(e), threads 64-127 delta / sqrt(D), of one of the unit's queries for
-            // everybody; in flight during the wait for the scores
+        // threads 0-63 fetch -lse * log2(e), threads 64-127 delta / sqrt(D), of one of a unit's queries for everybody,
+        // one unit ahead so that the load is not on the path
+        int head = 0, in_head = 0;  // of the unit whose values are fetched next: u / per_head, u % per_head
+        auto fetch = [&]() -> float {
             float mine = 0.f;
-            if (tid < 2 * BU) {
-                const int tq = q0 + (tid & (BU - 1));
+            if (tid < 2 * BU && head < rep) {
+                const int hq = hkv * rep + head, tq = (u_lo + in_head) * BU + (tid & (BU - 1));
                 mine = tid < BU ? -INFINITY : 0.f;  // a query past the end: P = 2^-inf = 0
                 if (tq < p.T) {
                     const long long o = ((long long)b * p.Hq + hq) * p.T + tq;
@@ -326,6 +324,16 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
                     }
                 }
             }
+            if (++in_head == per_head) { in_head = 0; ++head; }
+            return mine;
+        };
+        float mine = fetch();
+        int cur_in_head = 0;  // u % per_head of the current unit
+        for (int u = 0; u < n_units; ++u) {
+            const int q0 = (u_lo + cur_in_head) * BU;
+            if (++cur_in_head == per_head) cur_in_head = 0;
+            const int buf = u & 1;
+            const float mine_next = fetch();  // unit u + 1 (nothing past the last unit)
             // (all eight warps take the same decision here: they meet at a named barrier right below)
             if (!warp_wait(&sh.bar_s[buf], (uint32_t)(u >> 1) & 1u)) {
                 timed_out();
@@ -383,6 +391,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             tc_fence_before();
             __syncwarp();
             if ((tid & 31) == 0) mbar_arrive(&sh.bar_p[buf]);
+            mine = mine_next;
         }
         if (!aborted) {
             if (warp_wait(&sh.bar_d[(n_units - 1) & 1], (uint32_t)((n_units - 1) >> 1) & 1u)) {
